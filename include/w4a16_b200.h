@@ -1,0 +1,172 @@
+/*
+ * w4a16_b200 -- C ABI of the B200 (sm_100a) W4A16 group-128 contraction kernels.
+ *
+ * One entry point per launch function of the reference engine's include/kernels.cuh
+ * that lies on the W4 projection path, with the same parameter order and meaning.
+ * Differences from the reference functions, all forced by the C boundary:
+ *   - `half*` is `void*` (fp16 storage), `cudaStream_t` is `w4a16_stream_t`;
+ *   - QKVProjectionView is passed by pointer to an identical 9-pointer struct;
+ *   - instead of throwing std::runtime_error (reference include/tensor.cuh:11-23) every
+ *     function returns a status: 0 = ok, >0 = the cudaError_t of the failed CUDA call,
+ *     <0 = one of the W4A16_ERR_* argument errors below.  Nothing is launched when an
+ *     argument error is returned.
+ *
+ * Contract shared by all launchers (as the reference's): the caller owns every buffer,
+ * all pointers are device pointers valid on the current device, launchers allocate
+ * nothing, keep no per-call state, do not synchronise, and may be stream-captured into
+ * a CUDA graph after one eager call on the device (that first call sets kernel
+ * attributes).  `residual` may alias `output_y` (the engine calls it in place).
+ *
+ * Data layout (reference include/quant_primitives.cuh:20-26, tools/export_qwen25.py:42-78):
+ *   qweight  uint32 [N][K/8], row-major, linear in K; word w of a row holds elements
+ *            8w..8w+7 as nibbles q0 | q4<<4 | q1<<8 | q5<<12 | q2<<16 | q6<<20 | q3<<24 | q7<<28,
+ *            weight = (q - 8) * scale;
+ *   scales   fp16 [N][K/128];
+ *   Q8_1 x   int8 q8[K], fp32 scale[K/128], int32 sum8[K/8] (= -8 * sum of each octet).
+ * K must be a multiple of 256 (the exporter asserts it).
+ */
+#ifndef W4A16_B200_H
+#define W4A16_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define W4A16_API __attribute__((visibility("default")))
+#else
+#define W4A16_API
+#endif
+
+typedef struct CUstream_st* w4a16_stream_t; /* == cudaStream_t */
+
+enum {
+    W4A16_OK = 0,
+    W4A16_ERR_INVALID_ARG = -1, /* null pointer, non-positive size */
+    W4A16_ERR_SHAPE = -2,       /* K not a multiple of 256, dims the kernels cannot tile */
+    W4A16_ERR_ALIGNMENT = -3,   /* a pointer below the minimum alignment of its type */
+    W4A16_ERR_NO_DEVICE = -4,   /* no sm_100 device current */
+    W4A16_ERR_TOO_LARGE = -5    /* a size beyond a stated maximum */
+};
+
+/* Mirror of reference include/kernels.cuh:23-27 (QKVProjectionView). */
+typedef struct w4a16_qkv_view {
+    const void* q_weight; const void* q_scale; void* d_q;
+    const void* k_weight; const void* k_scale; void* d_k;
+    const void* v_weight; const void* v_scale; void* d_v;
+} w4a16_qkv_view;
+
+/* Library version (major*10000 + minor*100 + patch). */
+W4A16_API int w4a16_version(void);
+
+/* Text for a status returned by any function here. Never NULL. */
+W4A16_API const char* w4a16_status_string(int status);
+
+/*
+ * Optional one-time set-up for the current device: queries the SM count and raises the
+ * dynamic shared-memory limit of every kernel.  The launchers do the same lazily on
+ * their first call per device; call this (or make one eager call) before stream capture.
+ */
+W4A16_API int w4a16_init(void);
+
+/* Run-time switches. */
+enum {
+    W4A16_OPT_PDL = 1 /* 1 (default): launch with programmatic dependent launch so the next
+                         kernel's weight prefetch overlaps this kernel's tail; 0: plain launches */
+};
+W4A16_API int w4a16_set_option(int option, int value);
+W4A16_API int w4a16_get_option(int option);
+
+/* ---- Q8_1 activation quantisers ------------------------------------------------ */
+
+/* reference include/kernels.cuh:50-57 launch_quantize_fp16_to_q8_1
+ * (src/kernels/rmsnorm_rope.cu:273-314).  num_elements: multiple of 128. */
+W4A16_API int w4a16_quantize_fp16_to_q8_1(const void* input_x, int8_t* out_q8, float* out_scale,
+                                          int32_t* out_sum8, int num_elements, w4a16_stream_t stream);
+
+/* reference include/kernels.cuh:39-48 launch_rmsnorm_q8_1
+ * (src/kernels/rmsnorm_rope.cu:156-267).  output_fp16_opt may be NULL. */
+W4A16_API int w4a16_rmsnorm_q8_1(const void* input, const void* gamma, void* output_fp16_opt,
+                                 int8_t* out_q8, float* out_scale, int32_t* out_sum8,
+                                 w4a16_stream_t stream, int hidden_size);
+
+/* ---- batch-1 decode GEMV ------------------------------------------------------- */
+
+/* reference include/kernels.cuh:60-69 launch_gemv_w4a16 (src/kernels/gemv_w4a16.cu:636-746,
+ * 960-979): fp16 activations, quantised to Q8_1 inside the kernel.  residual may be NULL. */
+W4A16_API int w4a16_gemv_w4a16(const uint32_t* qweight, const void* scales, const void* input_x,
+                               const void* residual, void* output_y, int out_features,
+                               int in_features, w4a16_stream_t stream);
+
+/* reference include/kernels.cuh:71-82 launch_gemv_w4a8 (src/kernels/gemv_w4a16.cu:74-121,
+ * 264-381, 864-891): pre-quantised Q8_1 activations.  residual may be NULL. */
+W4A16_API int w4a16_gemv_w4a8(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                              const float* input_scale, const int32_t* input_sum8,
+                              const void* residual, void* output_y, int out_features,
+                              int in_features, w4a16_stream_t stream);
+
+/* reference include/kernels.cuh:84-94 launch_gemv_qkv_w4a8 (src/kernels/gemv_w4a16.cu:123-194,
+ * 387-513, 893-926): q, k and v projections in one launch. */
+W4A16_API int w4a16_gemv_qkv_w4a8(const w4a16_qkv_view* view, const int8_t* input_q8,
+                                  const float* input_scale, const int32_t* input_sum8,
+                                  w4a16_stream_t stream, int in_features, int num_q_heads,
+                                  int num_kv_heads, int head_dim);
+
+/* reference include/kernels.cuh:96-104 launch_gemv_dual_gate_up_swiglu_w4a16
+ * (src/kernels/gemv_w4a16.cu:752-858, 981-999): rows 2i / 2i+1 = gate_i / up_i,
+ * output_mlp[i] = silu(gate_i . x) * (up_i . x). */
+W4A16_API int w4a16_gemv_dual_gate_up_swiglu_w4a16(const uint32_t* gate_up_qweight,
+                                                   const void* gate_up_scales, const void* input_x,
+                                                   void* output_mlp, int hidden_size,
+                                                   int intermediate_size, w4a16_stream_t stream);
+
+/* reference include/kernels.cuh:106-116 launch_gemv_dual_gate_up_swiglu_w4a8
+ * (src/kernels/gemv_w4a16.cu:196-258, 519-630, 928-958). */
+W4A16_API int w4a16_gemv_dual_gate_up_swiglu_w4a8(const uint32_t* gate_up_qweight,
+                                                  const void* gate_up_scales, const int8_t* input_q8,
+                                                  const float* input_scale, const int32_t* input_sum8,
+                                                  void* output_mlp, int hidden_size,
+                                                  int intermediate_size, w4a16_stream_t stream);
+
+/* ---- M-token contraction (small-M decode batches and prefill) ------------------- */
+
+/* reference include/kernels.cuh:119-130 launch_gemm_prefill_w4a16
+ * (src/kernels/gemm_prefill.cu:319-386, 616-640): Y[M][N] = X[M][K] . dequant(W)^T (+ residual),
+ * fp16 in, fp32 accumulate, fp16 out.  sm_count is accepted for signature parity and ignored. */
+W4A16_API int w4a16_gemm_prefill_w4a16(const uint32_t* qweight, const void* scales, const void* input_x,
+                                       const void* residual, void* output_y, int M, int N, int K,
+                                       w4a16_stream_t stream, int sm_count);
+
+/* reference include/kernels.cuh:132-142 launch_gemm_prefill_qkv_w4a16
+ * (src/kernels/gemm_prefill.cu:392-489, 642-666). */
+W4A16_API int w4a16_gemm_prefill_qkv_w4a16(const w4a16_qkv_view* view, const void* input_x, int M,
+                                           w4a16_stream_t stream, int in_features, int num_q_heads,
+                                           int num_kv_heads, int head_dim, int sm_count);
+
+/* reference include/kernels.cuh:144-153 launch_gemm_prefill_dual_gate_up_swiglu_w4a16
+ * (src/kernels/gemm_prefill.cu:495-610, 668-684). */
+W4A16_API int w4a16_gemm_prefill_dual_gate_up_swiglu_w4a16(const uint32_t* gate_up_qweight,
+                                                           const void* gate_up_scales,
+                                                           const void* input_x, void* output_mlp, int M,
+                                                           w4a16_stream_t stream, int hidden_size,
+                                                           int intermediate_size);
+
+/* ---- diagnostics ----------------------------------------------------------------- */
+
+/*
+ * Per-group integer partial sums of the decode GEMV, D[n][g] = sum over the 128 elements
+ * of group g of (q[n][k] - 8) * q8[k], computed with the same dp4a routine the GEMV
+ * kernels use (the quantity reference include/quant_primitives.cuh:28-32 accumulates).
+ * No counterpart launcher in the reference; it exists so the integer intermediates can
+ * be compared bit for bit.  out_dots: int32 [N][K/128].
+ */
+W4A16_API int w4a16_gemv_group_dots(const uint32_t* qweight, const int8_t* input_q8,
+                                    const int32_t* input_sum8, int32_t* out_dots, int out_features,
+                                    int in_features, w4a16_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* W4A16_B200_H */

@@ -1,0 +1,195 @@
+"""ctypes front end of the CPU oracle (oracle/w4a16_oracle.c).  TEST INFRASTRUCTURE ONLY.
+
+Only the tests, the smoke check and the benchmark's cpu_baseline / reference arm import
+this module; the product package never does.  fp16 arrays are numpy float16 and cross
+into C as their raw bits.
+
+The shared object is built per host ISA (the file name carries it), so a library built
+on one machine is never loaded on a CPU that lacks its instructions; a missing one is
+compiled on first use with gcc.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_HERE = Path(__file__).resolve().parent
+GROUP = 128
+
+ROUND_HALF_EVEN = 0  # device __float2int_rn; canonical
+ROUND_HALF_AWAY = 1  # std::round, the reference test's CPU flavour
+
+
+def _host_isa() -> str:
+    try:
+        flags = set()
+        with open("/proc/cpuinfo") as f:
+            for line in f:
+                if line.startswith("flags"):
+                    flags = set(line.split(":", 1)[1].split())
+                    break
+        if {"avx2", "fma", "f16c"} <= flags:
+            return "x86-64-v3"
+    except OSError:
+        pass
+    return "generic"
+
+
+def lib_path() -> Path:
+    return _HERE / "_build" / f"libw4a16_oracle.{_host_isa()}.so"
+
+
+def build(force: bool = False) -> Path:
+    """Compile the C oracle for this host (gcc), unless an up-to-date build exists."""
+    out = lib_path()
+    src = _HERE / "w4a16_oracle.c"
+    if force or not out.exists() or out.stat().st_mtime < src.stat().st_mtime:
+        subprocess.run(["make", "-C", str(_HERE), f"ISA={_host_isa()}"], check=True,
+                       stdout=subprocess.DEVNULL)
+    return out
+
+
+_lib = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        _lib = ctypes.CDLL(str(build()))
+        _lib.orc_rmsnorm.restype = ctypes.c_float
+    return _lib
+
+
+def default_threads() -> int:
+    return max(1, len(os.sched_getaffinity(0)))
+
+
+def _p(a: np.ndarray | None):
+    if a is None:
+        return ctypes.c_void_p(0)
+    assert a.flags["C_CONTIGUOUS"], "oracle arrays must be contiguous"
+    return ctypes.c_void_p(a.ctypes.data)
+
+
+def _i64(v):
+    return ctypes.c_int64(int(v))
+
+
+def pack_nibbles(q: np.ndarray) -> np.ndarray:
+    """q uint8 [N][K] in 0..15 -> packed uint32 [N][K/8] (reference nibble order)."""
+    q = np.ascontiguousarray(q, dtype=np.uint8)
+    N, K = q.shape
+    out = np.empty((N, K // 8), dtype=np.uint32)
+    lib().orc_pack_nibbles(_p(q), _p(out), _i64(N), ctypes.c_int(K))
+    return out
+
+
+def unpack_nibbles(packed: np.ndarray) -> np.ndarray:
+    packed = np.ascontiguousarray(packed, dtype=np.uint32)
+    N, W = packed.shape
+    out = np.empty((N, W * 8), dtype=np.uint8)
+    lib().orc_unpack_nibbles(_p(packed), _p(out), _i64(N), ctypes.c_int(W * 8))
+    return out
+
+
+def quantize_weights(w: np.ndarray):
+    """fp32 [N][K] -> (packed uint32 [N][K/8], scales float16 [N][K/128])."""
+    w = np.ascontiguousarray(w, dtype=np.float32)
+    N, K = w.shape
+    packed = np.empty((N, K // 8), dtype=np.uint32)
+    scales = np.empty((N, K // GROUP), dtype=np.float16)
+    lib().orc_quantize_weights(_p(w), _i64(N), ctypes.c_int(K), _p(packed), _p(scales))
+    return packed, scales
+
+
+def quantize_q8_1(x: np.ndarray, round_mode: int = ROUND_HALF_EVEN):
+    """float16 [n] -> (q8 int8 [n], scale float32 [n/128], sum8 int32 [n/8])."""
+    x = np.ascontiguousarray(x, dtype=np.float16).reshape(-1)
+    n = x.size
+    assert n % GROUP == 0
+    q8 = np.empty(n, dtype=np.int8)
+    scale = np.empty(n // GROUP, dtype=np.float32)
+    sum8 = np.empty(n // 8, dtype=np.int32)
+    lib().orc_quantize_q8_1(_p(x), _i64(n), _p(q8), _p(scale), _p(sum8), ctypes.c_int(round_mode))
+    return q8, scale, sum8
+
+
+def group_dots(packed: np.ndarray, q8: np.ndarray, threads: int | None = None) -> np.ndarray:
+    """int32 [N][K/128]: the per-group integer dots of (q-8) with the Q8_1 bytes."""
+    packed = np.ascontiguousarray(packed, dtype=np.uint32)
+    q8 = np.ascontiguousarray(q8, dtype=np.int8)
+    N, W = packed.shape
+    K = W * 8
+    assert q8.size == K
+    D = np.empty((N, K // GROUP), dtype=np.int32)
+    lib().orc_group_dots(_p(packed), _p(q8), _i64(N), ctypes.c_int(K), _p(D),
+                         ctypes.c_int(threads or default_threads()))
+    return D
+
+
+def _gemv_common(fn, packed, scales, xarg, xscale, residual, swiglu, threads, want64=True):
+    packed = np.ascontiguousarray(packed, dtype=np.uint32)
+    scales = np.ascontiguousarray(scales, dtype=np.float16)
+    N, W = packed.shape
+    K = W * 8
+    n_out = N // 2 if swiglu else N
+    y64 = np.empty(n_out, dtype=np.float64) if want64 else None
+    y16 = np.empty(n_out, dtype=np.float16)
+    if residual is not None:
+        residual = np.ascontiguousarray(residual, dtype=np.float16)
+    args = [_p(packed), _p(scales)] + xarg + [_p(residual), _i64(N), ctypes.c_int(K),
+                                              ctypes.c_int(1 if swiglu else 0), _p(y64), _p(y16),
+                                              ctypes.c_int(threads or default_threads())]
+    fn(*args)
+    return y64, y16
+
+
+def gemv_q8(packed, scales, q8, xscale, residual=None, swiglu=False, threads=None, want64=True):
+    """W4A8 golden on Q8_1 activations: (double [n_out], float16 [n_out])."""
+    q8 = np.ascontiguousarray(q8, dtype=np.int8)
+    xscale = np.ascontiguousarray(xscale, dtype=np.float32)
+    return _gemv_common(lib().orc_gemv_q8, packed, scales, [_p(q8), _p(xscale)], None, residual,
+                        swiglu, threads, want64)
+
+
+def gemv_dequant(packed, scales, x_f32, residual=None, swiglu=False, threads=None):
+    """fp32 dequantise-then-matmul golden on fp32 activations."""
+    x_f32 = np.ascontiguousarray(x_f32, dtype=np.float32)
+    return _gemv_common(lib().orc_gemv_dequant, packed, scales, [_p(x_f32)], None, residual,
+                        swiglu, threads)
+
+
+def gemm_prefill(packed, scales, x, m_idx, n_idx, residual=None, swiglu=False, threads=None):
+    """Prefill golden on the listed token rows / output columns: (double, float16) [nm][nn]."""
+    packed = np.ascontiguousarray(packed, dtype=np.uint32)
+    scales = np.ascontiguousarray(scales, dtype=np.float16)
+    x = np.ascontiguousarray(x, dtype=np.float16)
+    m_idx = np.ascontiguousarray(m_idx, dtype=np.int32)
+    n_idx = np.ascontiguousarray(n_idx, dtype=np.int32)
+    K = packed.shape[1] * 8
+    assert x.shape[1] == K
+    ldr = 0
+    if residual is not None:
+        residual = np.ascontiguousarray(residual, dtype=np.float16)
+        ldr = residual.shape[1]
+    out64 = np.empty((m_idx.size, n_idx.size), dtype=np.float64)
+    out16 = np.empty((m_idx.size, n_idx.size), dtype=np.float16)
+    lib().orc_gemm_prefill(_p(packed), _p(scales), _p(x), _p(residual), _i64(ldr), ctypes.c_int(K),
+                           ctypes.c_int(1 if swiglu else 0), _p(m_idx), ctypes.c_int(m_idx.size),
+                           _p(n_idx), ctypes.c_int(n_idx.size), _p(out64), _p(out16),
+                           ctypes.c_int(threads or default_threads()))
+    return out64, out16
+
+
+def rmsnorm(x, gamma, eps=1e-6, inv_rms_override=0.0):
+    """RMSNorm with the reference's fp16 roundings: (float16 [n], inv_rms float)."""
+    x = np.ascontiguousarray(x, dtype=np.float16).reshape(-1)
+    gamma = np.ascontiguousarray(gamma, dtype=np.float16).reshape(-1)
+    y = np.empty_like(x)
+    inv = lib().orc_rmsnorm(_p(x), _p(gamma), ctypes.c_int(x.size), ctypes.c_float(eps),
+                            ctypes.c_float(inv_rms_override), _p(y))
+    return y, float(inv)

@@ -1,0 +1,79 @@
+"""Loads libw4a16_b200.so and declares its C ABI (include/w4a16_b200.h) for ctypes.
+
+There is no fallback: if the shared library is missing or cannot be loaded, importing the
+operators raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, c_char_p, c_int, c_void_p
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libw4a16_b200.so"
+
+
+class QKVView(ctypes.Structure):
+    """Mirror of w4a16_qkv_view / the reference's QKVProjectionView (include/kernels.cuh:23-27)."""
+    _fields_ = [(n, c_void_p) for n in ("q_weight", "q_scale", "d_q", "k_weight", "k_scale", "d_k",
+                                        "v_weight", "v_scale", "d_v")]
+
+
+# name -> argtypes; every function returns int except the two noted below
+SIGNATURES = {
+    "w4a16_version": [],
+    "w4a16_init": [],
+    "w4a16_set_option": [c_int, c_int],
+    "w4a16_get_option": [c_int],
+    "w4a16_quantize_fp16_to_q8_1": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
+    "w4a16_rmsnorm_q8_1": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int],
+    "w4a16_gemv_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "w4a16_gemv_w4a8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                        c_void_p],
+    "w4a16_gemv_qkv_w4a8": [POINTER(QKVView), c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int],
+    "w4a16_gemv_dual_gate_up_swiglu_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "w4a16_gemv_dual_gate_up_swiglu_w4a8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                            c_int, c_void_p],
+    "w4a16_gemm_prefill_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                 c_int],
+    "w4a16_gemm_prefill_qkv_w4a16": [POINTER(QKVView), c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                     c_int],
+    "w4a16_gemm_prefill_dual_gate_up_swiglu_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                                     c_int, c_int],
+    "w4a16_gemv_group_dots": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Returns the loaded library; raises if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m qwen_engine_b200.build` "
+            "(there is no non-CUDA fallback)")
+    lib = ctypes.CDLL(str(LIB_PATH))
+    for name, argtypes in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.argtypes = argtypes
+        fn.restype = c_int
+    lib.w4a16_status_string.argtypes = [c_int]
+    lib.w4a16_status_string.restype = c_char_p
+    _lib = lib
+    return lib
+
+
+class W4A16Error(RuntimeError):
+    """A launcher returned a nonzero status (the reference throws std::runtime_error there)."""
+
+    def __init__(self, fn: str, status: int):
+        msg = load().w4a16_status_string(status).decode()
+        super().__init__(f"{fn}: status {status}: {msg}")
+        self.status = status
+
+
+def check(fn: str, status: int) -> None:
+    if status != 0:
+        raise W4A16Error(fn, status)

@@ -1,0 +1,280 @@
+// extern "C" boundary of the library: argument checks, then the kernel launchers.
+// Declarations and the reference functions they replace: include/w4a16_b200.h.
+#include <atomic>
+#include <cstdlib>
+#include <mutex>
+
+#include "w4a16_internal.hpp"
+
+namespace w4 {
+namespace {
+
+constexpr int kMaxDevices = 64;
+DeviceInfo g_dev[kMaxDevices];
+std::mutex g_dev_mutex;
+std::atomic<bool> g_dev_ready[kMaxDevices];
+std::atomic<int> g_pdl{-1};
+
+}  // namespace
+
+int env_int(const char* name, int fallback) {
+    const char* v = std::getenv(name);
+    return (v && *v) ? std::atoi(v) : fallback;
+}
+
+bool pdl_enabled() {
+    int v = g_pdl.load(std::memory_order_relaxed);
+    if (v < 0) {
+        v = env_int("W4A16_PDL", 1) ? 1 : 0;
+        g_pdl.store(v, std::memory_order_relaxed);
+    }
+    return v != 0;
+}
+void set_pdl_enabled(bool on) { g_pdl.store(on ? 1 : 0, std::memory_order_relaxed); }
+
+int ensure_device_ready(const DeviceInfo** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev < 0 || dev >= kMaxDevices) return W4A16_ERR_NO_DEVICE;
+    if (!g_dev_ready[dev].load(std::memory_order_acquire)) {
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        if (!g_dev_ready[dev].load(std::memory_order_relaxed)) {
+            DeviceInfo info;
+            if ((e = cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess)
+                return static_cast<int>(e);
+            if ((e = cudaDeviceGetAttribute(&info.cc_major, cudaDevAttrComputeCapabilityMajor, dev)) != cudaSuccess)
+                return static_cast<int>(e);
+            if (info.cc_major != 10) return W4A16_ERR_NO_DEVICE;  // the kernels are sm_100a only
+            if (int st = quantize_set_attributes()) return st;
+            if (int st = gemv_set_attributes()) return st;
+            if (int st = gemm_set_attributes()) return st;
+            info.ready = true;
+            g_dev[dev] = info;
+            g_dev_ready[dev].store(true, std::memory_order_release);
+        }
+    }
+    if (out) *out = &g_dev[dev];
+    return 0;
+}
+
+}  // namespace w4
+
+namespace {
+
+using namespace w4;
+
+inline const __half* H(const void* p) { return static_cast<const __half*>(p); }
+inline __half* H(void* p) { return static_cast<__half*>(p); }
+inline cudaStream_t S(w4a16_stream_t s) { return reinterpret_cast<cudaStream_t>(s); }
+inline bool misaligned(const void* p, size_t a) { return reinterpret_cast<uintptr_t>(p) % a != 0; }
+
+int check_k(int K) { return (K > 0 && K % 256 == 0) ? 0 : W4A16_ERR_SHAPE; }
+
+}  // namespace
+
+extern "C" {
+
+int w4a16_version(void) { return 100; }
+
+const char* w4a16_status_string(int status) {
+    switch (status) {
+        case W4A16_OK: return "ok";
+        case W4A16_ERR_INVALID_ARG: return "invalid argument (null pointer or non-positive size)";
+        case W4A16_ERR_SHAPE: return "unsupported shape (in_features must be a positive multiple of 256)";
+        case W4A16_ERR_ALIGNMENT: return "pointer below the minimum alignment of its element type";
+        case W4A16_ERR_NO_DEVICE: return "current device is not an sm_100 GPU";
+        case W4A16_ERR_TOO_LARGE: return "size beyond the supported maximum";
+        default: break;
+    }
+    if (status > 0) return cudaGetErrorString(static_cast<cudaError_t>(status));
+    return "unknown status";
+}
+
+int w4a16_init(void) { return ensure_device_ready(nullptr); }
+
+int w4a16_set_option(int option, int value) {
+    if (option == W4A16_OPT_PDL) {
+        set_pdl_enabled(value != 0);
+        return 0;
+    }
+    return W4A16_ERR_INVALID_ARG;
+}
+int w4a16_get_option(int option) {
+    if (option == W4A16_OPT_PDL) return pdl_enabled() ? 1 : 0;
+    return W4A16_ERR_INVALID_ARG;
+}
+
+int w4a16_quantize_fp16_to_q8_1(const void* input_x, int8_t* out_q8, float* out_scale, int32_t* out_sum8,
+                                int num_elements, w4a16_stream_t stream) {
+    if (!input_x || !out_q8 || !out_scale || !out_sum8 || num_elements <= 0) return W4A16_ERR_INVALID_ARG;
+    if (num_elements % 128 != 0) return W4A16_ERR_SHAPE;
+    if (misaligned(input_x, 8) || misaligned(out_q8, 4) || misaligned(out_scale, 4) || misaligned(out_sum8, 4))
+        return W4A16_ERR_ALIGNMENT;
+    if (int st = ensure_device_ready(nullptr)) return st;
+    return quantize_fp16_to_q8_1(H(input_x), out_q8, out_scale, out_sum8, num_elements, S(stream));
+}
+
+int w4a16_rmsnorm_q8_1(const void* input, const void* gamma, void* output_fp16_opt, int8_t* out_q8, float* out_scale,
+                       int32_t* out_sum8, w4a16_stream_t stream, int hidden_size) {
+    if (!input || !gamma || !out_q8 || !out_scale || !out_sum8 || hidden_size <= 0) return W4A16_ERR_INVALID_ARG;
+    if (hidden_size % 128 != 0) return W4A16_ERR_SHAPE;
+    if (hidden_size > 100 * 1024) return W4A16_ERR_TOO_LARGE;
+    if (misaligned(input, 8) || misaligned(gamma, 4) || misaligned(output_fp16_opt, 4) || misaligned(out_q8, 4) ||
+        misaligned(out_scale, 4) || misaligned(out_sum8, 4))
+        return W4A16_ERR_ALIGNMENT;
+    if (int st = ensure_device_ready(nullptr)) return st;
+    return rmsnorm_q8_1(H(input), H(gamma), H(output_fp16_opt), out_q8, out_scale, out_sum8, hidden_size, S(stream));
+}
+
+static int gemv_plain(const uint32_t* qweight, const void* scales, const void* x_fp16, const int8_t* q8,
+                      const float* xscale, const int32_t* sum8, const void* residual, void* y, int N, int K,
+                      w4a16_stream_t stream) {
+    if (!qweight || !scales || !y || N <= 0) return W4A16_ERR_INVALID_ARG;
+    if (int st = check_k(K)) return st;
+    if (misaligned(qweight, 4) || misaligned(scales, 2) || misaligned(y, 2) || misaligned(residual, 2) ||
+        misaligned(x_fp16, 8) || misaligned(xscale, 4) || misaligned(sum8, 4))
+        return W4A16_ERR_ALIGNMENT;
+    GemvArgs a = {};
+    a.qweight[0] = qweight; a.scales[0] = H(scales); a.out[0] = H(y); a.rows[0] = N;
+    a.q8 = q8; a.xscale = xscale; a.sum8 = sum8; a.x_fp16 = H(x_fp16);
+    a.residual = H(residual);
+    a.K = K; a.units = N;
+    return gemv_launch(kPlain, a, S(stream));
+}
+
+int w4a16_gemv_w4a16(const uint32_t* qweight, const void* scales, const void* input_x, const void* residual,
+                     void* output_y, int out_features, int in_features, w4a16_stream_t stream) {
+    if (!input_x) return W4A16_ERR_INVALID_ARG;
+    return gemv_plain(qweight, scales, input_x, nullptr, nullptr, nullptr, residual, output_y, out_features,
+                      in_features, stream);
+}
+
+int w4a16_gemv_w4a8(const uint32_t* qweight, const void* scales, const int8_t* input_q8, const float* input_scale,
+                    const int32_t* input_sum8, const void* residual, void* output_y, int out_features,
+                    int in_features, w4a16_stream_t stream) {
+    if (!input_q8 || !input_scale || !input_sum8) return W4A16_ERR_INVALID_ARG;
+    return gemv_plain(qweight, scales, nullptr, input_q8, input_scale, input_sum8, residual, output_y, out_features,
+                      in_features, stream);
+}
+
+static int fill_qkv(const w4a16_qkv_view* v, int nq, int nkv, int hd, const uint32_t* qw[3], const __half* sc[3],
+                    __half* out[3], int rows[3]) {
+    if (!v || !v->q_weight || !v->q_scale || !v->d_q || !v->k_weight || !v->k_scale || !v->d_k || !v->v_weight ||
+        !v->v_scale || !v->d_v || nq <= 0 || nkv <= 0 || hd <= 0)
+        return W4A16_ERR_INVALID_ARG;
+    const void* ws[3] = {v->q_weight, v->k_weight, v->v_weight};
+    const void* ss[3] = {v->q_scale, v->k_scale, v->v_scale};
+    void* os[3] = {v->d_q, v->d_k, v->d_v};
+    for (int t = 0; t < 3; ++t) {
+        if (misaligned(ws[t], 4) || misaligned(ss[t], 2) || misaligned(os[t], 2)) return W4A16_ERR_ALIGNMENT;
+        qw[t] = static_cast<const uint32_t*>(ws[t]);
+        sc[t] = H(ss[t]);
+        out[t] = H(os[t]);
+    }
+    rows[0] = nq * hd;
+    rows[1] = nkv * hd;
+    rows[2] = nkv * hd;
+    return 0;
+}
+
+int w4a16_gemv_qkv_w4a8(const w4a16_qkv_view* view, const int8_t* input_q8, const float* input_scale,
+                        const int32_t* input_sum8, w4a16_stream_t stream, int in_features, int num_q_heads,
+                        int num_kv_heads, int head_dim) {
+    if (!input_q8 || !input_scale || !input_sum8) return W4A16_ERR_INVALID_ARG;
+    if (int st = check_k(in_features)) return st;
+    if (misaligned(input_scale, 4) || misaligned(input_sum8, 4)) return W4A16_ERR_ALIGNMENT;
+    GemvArgs a = {};
+    if (int st = fill_qkv(view, num_q_heads, num_kv_heads, head_dim, a.qweight, a.scales, a.out, a.rows)) return st;
+    a.q8 = input_q8; a.xscale = input_scale; a.sum8 = input_sum8;
+    a.K = in_features;
+    a.units = a.rows[0] + a.rows[1] + a.rows[2];
+    return gemv_launch(kQkv, a, S(stream));
+}
+
+static int gemv_swiglu(const uint32_t* qweight, const void* scales, const void* x_fp16, const int8_t* q8,
+                       const float* xscale, const int32_t* sum8, void* out, int hidden, int inter,
+                       w4a16_stream_t stream) {
+    if (!qweight || !scales || !out || inter <= 0) return W4A16_ERR_INVALID_ARG;
+    if (int st = check_k(hidden)) return st;
+    if (misaligned(qweight, 4) || misaligned(scales, 2) || misaligned(out, 2) || misaligned(x_fp16, 8) ||
+        misaligned(xscale, 4) || misaligned(sum8, 4))
+        return W4A16_ERR_ALIGNMENT;
+    GemvArgs a = {};
+    a.qweight[0] = qweight; a.scales[0] = H(scales); a.out[0] = H(out); a.rows[0] = 2 * inter;
+    a.q8 = q8; a.xscale = xscale; a.sum8 = sum8; a.x_fp16 = H(x_fp16);
+    a.K = hidden; a.units = inter;
+    return gemv_launch(kSwiglu, a, S(stream));
+}
+
+int w4a16_gemv_dual_gate_up_swiglu_w4a16(const uint32_t* gate_up_qweight, const void* gate_up_scales,
+                                         const void* input_x, void* output_mlp, int hidden_size,
+                                         int intermediate_size, w4a16_stream_t stream) {
+    if (!input_x) return W4A16_ERR_INVALID_ARG;
+    return gemv_swiglu(gate_up_qweight, gate_up_scales, input_x, nullptr, nullptr, nullptr, output_mlp, hidden_size,
+                       intermediate_size, stream);
+}
+
+int w4a16_gemv_dual_gate_up_swiglu_w4a8(const uint32_t* gate_up_qweight, const void* gate_up_scales,
+                                        const int8_t* input_q8, const float* input_scale, const int32_t* input_sum8,
+                                        void* output_mlp, int hidden_size, int intermediate_size,
+                                        w4a16_stream_t stream) {
+    if (!input_q8 || !input_scale || !input_sum8) return W4A16_ERR_INVALID_ARG;
+    return gemv_swiglu(gate_up_qweight, gate_up_scales, nullptr, input_q8, input_scale, input_sum8, output_mlp,
+                       hidden_size, intermediate_size, stream);
+}
+
+int w4a16_gemm_prefill_w4a16(const uint32_t* qweight, const void* scales, const void* input_x, const void* residual,
+                             void* output_y, int M, int N, int K, w4a16_stream_t stream, int sm_count) {
+    (void)sm_count;
+    if (!qweight || !scales || !input_x || !output_y || M <= 0 || N <= 0) return W4A16_ERR_INVALID_ARG;
+    if (int st = check_k(K)) return st;
+    if (misaligned(qweight, 4) || misaligned(scales, 2) || misaligned(input_x, 16) || misaligned(output_y, 2) ||
+        misaligned(residual, 2))
+        return W4A16_ERR_ALIGNMENT;
+    GemmArgs g = {};
+    g.qweight[0] = qweight; g.scales[0] = H(scales); g.out[0] = H(output_y); g.rows[0] = N;
+    g.x = H(input_x); g.residual = H(residual);
+    g.M = M; g.K = K; g.mode = kPlain;
+    return gemm_launch(g, S(stream));
+}
+
+int w4a16_gemm_prefill_qkv_w4a16(const w4a16_qkv_view* view, const void* input_x, int M, w4a16_stream_t stream,
+                                 int in_features, int num_q_heads, int num_kv_heads, int head_dim, int sm_count) {
+    (void)sm_count;
+    if (!input_x || M <= 0) return W4A16_ERR_INVALID_ARG;
+    if (int st = check_k(in_features)) return st;
+    if (misaligned(input_x, 16)) return W4A16_ERR_ALIGNMENT;
+    GemmArgs g = {};
+    if (int st = fill_qkv(view, num_q_heads, num_kv_heads, head_dim, g.qweight, g.scales, g.out, g.rows)) return st;
+    g.x = H(input_x);
+    g.M = M; g.K = in_features; g.mode = kQkv;
+    return gemm_launch(g, S(stream));
+}
+
+int w4a16_gemm_prefill_dual_gate_up_swiglu_w4a16(const uint32_t* gate_up_qweight, const void* gate_up_scales,
+                                                 const void* input_x, void* output_mlp, int M,
+                                                 w4a16_stream_t stream, int hidden_size, int intermediate_size) {
+    if (!gate_up_qweight || !gate_up_scales || !input_x || !output_mlp || M <= 0 || intermediate_size <= 0)
+        return W4A16_ERR_INVALID_ARG;
+    if (int st = check_k(hidden_size)) return st;
+    if (misaligned(gate_up_qweight, 4) || misaligned(gate_up_scales, 2) || misaligned(input_x, 16) ||
+        misaligned(output_mlp, 2))
+        return W4A16_ERR_ALIGNMENT;
+    GemmArgs g = {};
+    g.qweight[0] = gate_up_qweight; g.scales[0] = H(gate_up_scales); g.out[0] = H(output_mlp);
+    g.rows[0] = 2 * intermediate_size;
+    g.x = H(input_x);
+    g.M = M; g.K = hidden_size; g.mode = kSwiglu;
+    return gemm_launch(g, S(stream));
+}
+
+int w4a16_gemv_group_dots(const uint32_t* qweight, const int8_t* input_q8, const int32_t* input_sum8,
+                          int32_t* out_dots, int out_features, int in_features, w4a16_stream_t stream) {
+    if (!qweight || !input_q8 || !input_sum8 || !out_dots || out_features <= 0) return W4A16_ERR_INVALID_ARG;
+    if (int st = check_k(in_features)) return st;
+    if (misaligned(qweight, 4) || misaligned(input_sum8, 4) || misaligned(out_dots, 4)) return W4A16_ERR_ALIGNMENT;
+    return gemv_group_dots(qweight, input_q8, input_sum8, out_dots, out_features, in_features, S(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,345 @@
+// Batch-1 decode GEMV on W4 group-128 weights and Q8_1 activations (sm_100a).
+//
+// Replaces the reference's gemv_w4a8_u4_kernel / gemv_qkv_w4a8_u4_kernel /
+// gemv_dual_gate_up_swiglu_w4a8_u4_kernel, their 32-bit fall-backs and the two fp16-input
+// "standalone" kernels (src/kernels/gemv_w4a16.cu:74-858) with one kernel template.
+//
+// Work split.  Eight lanes share a weight row; each lane reads 16 bytes (32 weights) per
+// step, so a sub-warp consumes 256 elements of K per step.  A CTA holds
+// units_per_cta x ksplit sub-warps: `units_per_cta` output rows (row pairs for SwiGLU) and
+// `ksplit` slices of K, chosen on the host so that even a 1536 x 1536 projection gives
+// every SM a CTA and every lane only a handful of loads -- the whole matrix is then in
+// flight at once, which is what bounds these latency-limited shapes.
+//
+// Order inside a CTA: (1) issue the first batch of weight and scale loads into registers --
+// they do not depend on the previous kernel; (2) release dependents / wait for the prior
+// grid (programmatic dependent launch), then stage the activation in shared memory
+// (copy of the Q8_1 arrays, or quantise fp16 on the fly); (3) dp4a over the chunks,
+// fp32 accumulate per lane; (4) 3-step shuffle reduce over the sub-warp, shared-memory
+// reduce over the K slices; (5) epilogue (residual / QKV scatter / SwiGLU), fp16 store.
+#include <algorithm>
+#include <cstdlib>
+
+#include "w4a16_common.cuh"
+#include "w4a16_internal.hpp"
+
+namespace w4 {
+namespace {
+
+constexpr int kMaxThreads = 256;
+constexpr int kMaxSubwarps = kMaxThreads / kSubwarp;  // 32
+
+template <int MODE, int U, bool FP16_IN, bool ALIGNED16>
+__global__ void __launch_bounds__(kMaxThreads) gemv_w4_kernel(const GemvArgs a) {
+    constexpr int R = (MODE == kSwiglu) ? 2 : 1;  // weight rows per sub-warp
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int K = a.K;
+    int8_t* s_q8 = reinterpret_cast<int8_t*>(smem);
+    int32_t* s_seed = reinterpret_cast<int32_t*>(smem + K);
+    float* s_scale = reinterpret_cast<float*>(smem + K + (K / kChunk) * 4);
+    float* s_part = reinterpret_cast<float*>(smem + staged_x_bytes(K));
+
+    const int tid = threadIdx.x;
+    const int sub = tid >> 3, l = tid & 7;
+    const int u_local = sub % a.units_per_cta;
+    const int ks = sub / a.units_per_cta;
+    const int unit = blockIdx.x * a.units_per_cta + u_local;
+    const bool active = unit < a.units;
+
+    // Resolve the weight rows this sub-warp reads and where its output goes.
+    const uint32_t* wrow[R];
+    const __half* srow[R];
+    __half* out_ptr = nullptr;
+    const int words = K / 8, groups = K / kGroup;
+    if (active) {
+        if constexpr (MODE == kQkv) {
+            int t = 0, local = unit;
+            if (local >= a.rows[0]) { local -= a.rows[0]; t = 1; }
+            if (t == 1 && local >= a.rows[1]) { local -= a.rows[1]; t = 2; }
+            wrow[0] = a.qweight[t] + static_cast<size_t>(local) * words;
+            srow[0] = a.scales[t] + static_cast<size_t>(local) * groups;
+            out_ptr = a.out[t] + local;
+        } else {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const size_t row = static_cast<size_t>(unit) * R + r;
+                wrow[r] = a.qweight[0] + row * words;
+                srow[r] = a.scales[0] + row * groups;
+            }
+            out_ptr = a.out[0] + unit;
+        }
+    } else {
+#pragma unroll
+        for (int r = 0; r < R; ++r) { wrow[r] = nullptr; srow[r] = nullptr; }
+    }
+
+    const int total_steps = K / kStepElems;
+    const int s_begin = ks * a.steps_per_split;
+    const int s_end = active ? min(s_begin + a.steps_per_split, total_steps) : s_begin;
+
+    uint4 w[R][U];
+    uint16_t sb[R][U];
+    auto issue = [&](int s0) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int s = s0 + u;
+            if (s < s_end) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    w[r][u] = ld_weights<ALIGNED16>(wrow[r] + (s * kSubwarp + l) * 4);
+                    sb[r][u] = ld_scale_bits(srow[r] + 2 * s + (l >> 2));
+                }
+            }
+        }
+    };
+
+    issue(s_begin);
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+
+    if constexpr (FP16_IN) stage_x_from_fp16(a.x_fp16, K, s_q8, s_seed, s_scale);
+    else stage_x_from_q8_1(a.q8, a.xscale, a.sum8, K, a.vec_ok != 0, s_q8, s_seed, s_scale);
+    __syncthreads();
+
+    float acc[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = 0.0f;
+
+    for (int s0 = s_begin; s0 < s_end; s0 += U) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int s = s0 + u;
+            if (s < s_end) {
+                const int c = s * kSubwarp + l;  // 32-element chunk index along K
+                const uint4 xa = reinterpret_cast<const uint4*>(s_q8)[2 * c];
+                const uint4 xb = reinterpret_cast<const uint4*>(s_q8)[2 * c + 1];
+                const int32_t seed = s_seed[c];
+                const float xs = s_scale[c >> 2];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const int32_t d = chunk_dot(w[r][u], xa, xb, seed);
+                    const float ws = __half2float(__ushort_as_half(sb[r][u]));
+                    acc[r] = fmaf(static_cast<float>(d), ws * xs, acc[r]);
+                }
+            }
+        }
+        if (s0 + U < s_end) issue(s0 + U);
+    }
+
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 4);
+        acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 2);
+        acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 1);
+    }
+
+    if (a.ksplit > 1) {
+        if (l == 0 && ks < a.ksplit) {  // padding threads of a rounded-up block have ks >= ksplit
+#pragma unroll
+            for (int r = 0; r < R; ++r) s_part[(ks * a.units_per_cta + u_local) * R + r] = acc[r];
+        }
+        __syncthreads();
+        if (ks == 0 && l == 0) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                float t = 0.0f;
+                for (int k = 0; k < a.ksplit; ++k) t += s_part[(k * a.units_per_cta + u_local) * R + r];
+                acc[r] = t;
+            }
+        }
+    }
+
+    if (active && ks == 0 && l == 0) {
+        float y;
+        if constexpr (MODE == kSwiglu) {
+            const float gate = acc[0];
+            y = (gate / (1.0f + expf(-gate))) * acc[R - 1];
+        } else {
+            y = acc[0];
+            if constexpr (MODE == kPlain) {
+                if (a.residual != nullptr) y += __half2float(a.residual[unit]);
+            }
+        }
+        *out_ptr = __float2half_rn(y);
+    }
+}
+
+// Diagnostic: the per-group int32 dots, through the same staging and chunk_dot as above.
+__global__ void __launch_bounds__(kMaxThreads) gemv_group_dots_kernel(const uint32_t* __restrict__ qweight,
+                                                                       const int8_t* __restrict__ q8,
+                                                                       const int32_t* __restrict__ sum8,
+                                                                       int32_t* __restrict__ out, int N, int K,
+                                                                       int vec_ok, int aligned16) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    int8_t* s_q8 = reinterpret_cast<int8_t*>(smem);
+    int32_t* s_seed = reinterpret_cast<int32_t*>(smem + K);
+    // only the integer part is needed: q8 bytes and the per-chunk seeds
+    {
+        const int tid = threadIdx.x, nthr = blockDim.x;
+        if (vec_ok) {
+            for (int i = tid; i < K / 16; i += nthr)
+                reinterpret_cast<uint4*>(s_q8)[i] = reinterpret_cast<const uint4*>(q8)[i];
+            for (int c = tid; c < K / kChunk; c += nthr) {
+                const int4 v = reinterpret_cast<const int4*>(sum8)[c];
+                s_seed[c] = v.x + v.y + v.z + v.w;
+            }
+        } else {
+            for (int i = tid; i < K; i += nthr) s_q8[i] = q8[i];
+            for (int c = tid; c < K / kChunk; c += nthr)
+                s_seed[c] = sum8[4 * c] + sum8[4 * c + 1] + sum8[4 * c + 2] + sum8[4 * c + 3];
+        }
+    }
+    __syncthreads();
+    const int sub = threadIdx.x >> 3, l = threadIdx.x & 7;
+    const int row = blockIdx.x * kMaxSubwarps + sub;
+    const bool active = row < N;
+    const uint32_t* wrow = qweight + static_cast<size_t>(active ? row : 0) * (K / 8);
+    const int groups = K / kGroup;
+    for (int s = 0; s < K / kStepElems; ++s) {
+        const int c = s * kSubwarp + l;
+        int32_t d = 0;
+        if (active) {
+            const uint4 w = aligned16 ? ld_weights_16(wrow + c * 4) : ld_weights_4x4(wrow + c * 4);
+            const uint4 xa = reinterpret_cast<const uint4*>(s_q8)[2 * c];
+            const uint4 xb = reinterpret_cast<const uint4*>(s_q8)[2 * c + 1];
+            d = chunk_dot(w, xa, xb, s_seed[c]);
+        }
+        d += __shfl_xor_sync(0xFFFFFFFFu, d, 1);
+        d += __shfl_xor_sync(0xFFFFFFFFu, d, 2);
+        if (active && (l & 3) == 0) out[static_cast<size_t>(row) * groups + 2 * s + (l >> 2)] = d;
+    }
+}
+
+// ---- host side -------------------------------------------------------------------
+
+struct Plan {
+    int units_per_cta, ksplit, steps_per_split, U;
+};
+
+// Picks the CTA shape.  units: output rows (or pairs).  Goals, in order: at least ~1.3 CTAs
+// per SM when the matrix allows it; all 32 sub-warps of a CTA busy; at most 8 loads per lane
+// per batch so one batch covers a lane's whole K slice for the model's shapes.
+Plan make_plan(int units, int K, int sm_count) {
+    static const int force_units = env_int("W4A16_GEMV_UNITS", 0);
+    static const int force_ksplit = env_int("W4A16_GEMV_KSPLIT", 0);
+    const int steps = K / kStepElems;
+    const int target_ctas = (sm_count * 13 + 9) / 10;
+    int upc = 32;
+    while (upc > 4 && (units + upc - 1) / upc < target_ctas) upc /= 2;
+    if (force_units > 0) upc = std::min(32, std::max(1, force_units));
+    int cap = std::max(1, kMaxSubwarps / upc);   // most K slices the CTA can hold
+    cap = std::min(cap, steps);
+    int per = (steps + cap - 1) / cap;           // steps per slice if all slices were used
+    int ksplit = (steps + per - 1) / per;        // fewest slices that reach that depth
+    if (force_ksplit > 0) {
+        ksplit = std::min(std::min(force_ksplit, steps), kMaxSubwarps / upc);
+        ksplit = std::max(1, ksplit);
+        per = (steps + ksplit - 1) / ksplit;
+    }
+    Plan p;
+    p.units_per_cta = upc;
+    p.ksplit = ksplit;
+    p.steps_per_split = per;
+    p.U = per <= 4 ? 4 : 8;
+    return p;
+}
+
+template <int MODE, int U, bool FP16_IN>
+cudaError_t launch_aligned(const GemvArgs& a, bool aligned16, dim3 grid, dim3 block, size_t smem,
+                           cudaStream_t stream) {
+    if (aligned16)
+        return launch_kernel(gemv_w4_kernel<MODE, U, FP16_IN, true>, grid, block, smem, stream, pdl_enabled(), a);
+    return launch_kernel(gemv_w4_kernel<MODE, U, FP16_IN, false>, grid, block, smem, stream, pdl_enabled(), a);
+}
+template <int MODE, int U>
+cudaError_t launch_input(const GemvArgs& a, bool aligned16, dim3 grid, dim3 block, size_t smem, cudaStream_t stream) {
+    if constexpr (MODE != kQkv) {
+        if (a.x_fp16 != nullptr) return launch_aligned<MODE, U, true>(a, aligned16, grid, block, smem, stream);
+    }
+    return launch_aligned<MODE, U, false>(a, aligned16, grid, block, smem, stream);
+}
+template <int MODE>
+cudaError_t launch_mode(const GemvArgs& a, int U, bool aligned16, dim3 grid, dim3 block, size_t smem,
+                        cudaStream_t stream) {
+    if (U == 4) return launch_input<MODE, 4>(a, aligned16, grid, block, smem, stream);
+    return launch_input<MODE, 8>(a, aligned16, grid, block, smem, stream);
+}
+
+template <typename F>
+cudaError_t raise_smem(F* f) {
+    return cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+}
+template <int MODE, int U>
+cudaError_t raise_smem_mode() {
+    cudaError_t e = raise_smem(gemv_w4_kernel<MODE, U, false, true>);
+    if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, false, false>);
+    if constexpr (MODE != kQkv) {
+        if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, true, true>);
+        if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, true, false>);
+    }
+    return e;
+}
+
+}  // namespace
+
+int gemv_set_attributes() {
+    cudaError_t e = raise_smem_mode<kPlain, 4>();
+    if (e == cudaSuccess) e = raise_smem_mode<kPlain, 8>();
+    if (e == cudaSuccess) e = raise_smem_mode<kQkv, 4>();
+    if (e == cudaSuccess) e = raise_smem_mode<kQkv, 8>();
+    if (e == cudaSuccess) e = raise_smem_mode<kSwiglu, 4>();
+    if (e == cudaSuccess) e = raise_smem_mode<kSwiglu, 8>();
+    if (e == cudaSuccess) e = raise_smem(gemv_group_dots_kernel);
+    return static_cast<int>(e);
+}
+
+int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
+    const DeviceInfo* dev = nullptr;
+    if (int st = ensure_device_ready(&dev)) return st;
+
+    Plan p = make_plan(a.units, a.K, dev->sm_count);
+    if (mode == kQkv) {
+        // a CTA's rows must come from one tensor
+        while (p.units_per_cta > 1 && (a.rows[0] % p.units_per_cta || a.rows[1] % p.units_per_cta)) p.units_per_cta /= 2;
+    }
+    a.units_per_cta = p.units_per_cta;
+    a.ksplit = p.ksplit;
+    a.steps_per_split = p.steps_per_split;
+
+    bool aligned16 = true;
+    const int ntens = (mode == kQkv) ? 3 : 1;
+    for (int t = 0; t < ntens; ++t) aligned16 = aligned16 && (reinterpret_cast<uintptr_t>(a.qweight[t]) % 16 == 0);
+    a.vec_ok = (a.x_fp16 == nullptr) && (reinterpret_cast<uintptr_t>(a.q8) % 16 == 0) &&
+               (reinterpret_cast<uintptr_t>(a.sum8) % 16 == 0);
+
+    const int R = (mode == kSwiglu) ? 2 : 1;
+    const int threads = a.units_per_cta * a.ksplit * kSubwarp;
+    const int grid = (a.units + a.units_per_cta - 1) / a.units_per_cta;
+    const size_t smem = staged_x_bytes(a.K) + static_cast<size_t>(a.ksplit) * a.units_per_cta * R * sizeof(float);
+    if (smem > 200 * 1024) return W4A16_ERR_TOO_LARGE;
+    // fp16 staging quantises with whole warps
+    const int block = (threads + 31) / 32 * 32;
+
+    cudaError_t e;
+    switch (mode) {
+        case kPlain: e = launch_mode<kPlain>(a, p.U, aligned16, dim3(grid), dim3(block), smem, stream); break;
+        case kQkv: e = launch_mode<kQkv>(a, p.U, aligned16, dim3(grid), dim3(block), smem, stream); break;
+        default: e = launch_mode<kSwiglu>(a, p.U, aligned16, dim3(grid), dim3(block), smem, stream); break;
+    }
+    return static_cast<int>(e);
+}
+
+int gemv_group_dots(const uint32_t* qweight, const int8_t* q8, const int32_t* sum8, int32_t* out, int N, int K,
+                    cudaStream_t stream) {
+    const DeviceInfo* dev = nullptr;
+    if (int st = ensure_device_ready(&dev)) return st;
+    const int vec_ok = (reinterpret_cast<uintptr_t>(q8) % 16 == 0) && (reinterpret_cast<uintptr_t>(sum8) % 16 == 0);
+    const int aligned16 = reinterpret_cast<uintptr_t>(qweight) % 16 == 0;
+    const size_t smem = staged_x_bytes(K);
+    if (smem > 200 * 1024) return W4A16_ERR_TOO_LARGE;
+    const int grid = (N + kMaxSubwarps - 1) / kMaxSubwarps;
+    gemv_group_dots_kernel<<<grid, kMaxThreads, smem, stream>>>(qweight, q8, sum8, out, N, K, vec_ok, aligned16);
+    return static_cast<int>(cudaGetLastError());
+}
+
+}  // namespace w4

@@ -1,0 +1,168 @@
+// Device-side building blocks shared by the W4A16 kernels (sm_100a only).
+//
+// Layout facts used here (reference include/quant_primitives.cuh:10-32):
+//   packed word = q0 | q4<<4 | q1<<8 | q5<<12 | q2<<16 | q6<<20 | q3<<24 | q7<<28, so
+//   (w & 0x0F0F0F0F) holds elements 0..3 as bytes and ((w >> 4) & 0x0F0F0F0F) elements 4..7;
+//   weight = (q - 8) * scale;  Q8_1 activation = int8 q8[K], fp32 scale[K/128],
+//   int32 sum8[K/8] = -8 * (sum of the octet's q8).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+namespace w4 {
+
+constexpr int kGroup = 128;       // elements per quantisation group
+constexpr int kChunk = 32;        // elements covered by one 16-byte weight load
+constexpr int kSubwarp = 8;       // lanes that share one weight row (8 x 16 B = 256 elements per step)
+constexpr int kStepElems = 256;   // elements of a row consumed per sub-warp step
+
+// ---- loads -------------------------------------------------------------------
+
+// 16-byte streaming load of weights: read-only path, no L1 allocation.  volatile keeps
+// the issue order the code states (weight loads go out before the activation staging).
+__device__ __forceinline__ uint4 ld_weights_16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
+}
+// Same 16 bytes through four 4-byte loads, for weight tensors that are only 4-byte aligned.
+__device__ __forceinline__ uint4 ld_weights_4x4(const void* p) {
+    const uint32_t* q = static_cast<const uint32_t*>(p);
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v.x) : "l"(q));
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v.y) : "l"(q + 1));
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v.z) : "l"(q + 2));
+    asm volatile("ld.global.nc.L1::no_allocate.u32 %0, [%1];" : "=r"(v.w) : "l"(q + 3));
+    return v;
+}
+template <bool ALIGNED16>
+__device__ __forceinline__ uint4 ld_weights(const void* p) {
+    if constexpr (ALIGNED16) return ld_weights_16(p);
+    else return ld_weights_4x4(p);
+}
+__device__ __forceinline__ uint16_t ld_scale_bits(const __half* p) {
+    uint16_t v;
+    asm volatile("ld.global.nc.u16 %0, [%1];" : "=h"(v) : "l"(p));
+    return v;
+}
+
+// ---- programmatic dependent launch ---------------------------------------------
+// Both are no-ops for a kernel launched without the programmatic-serialisation attribute.
+__device__ __forceinline__ void pdl_wait_prior_grids() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_release_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+
+// ---- integer core -----------------------------------------------------------------
+
+// Sum over 8 elements of (q_j - 8) * x_j added to `seed`, when seed already carries the
+// -8 * sum(x) term; without it, this is the plain sum of q_j * x_j.
+__device__ __forceinline__ int32_t octet_dot(uint32_t packed, int32_t x_lo, int32_t x_hi, int32_t seed) {
+    const int32_t w_lo = static_cast<int32_t>(packed & 0x0F0F0F0Fu);
+    const int32_t w_hi = static_cast<int32_t>((packed >> 4) & 0x0F0F0F0Fu);
+    return __dp4a(w_hi, x_hi, __dp4a(w_lo, x_lo, seed));
+}
+
+// One 16-byte weight chunk (32 elements) against its 32 activation bytes.
+// chunk_seed = -8 * (sum of the 32 activation bytes), i.e. the four sum8 entries added up.
+__device__ __forceinline__ int32_t chunk_dot(const uint4& w, const uint4& xa, const uint4& xb, int32_t chunk_seed) {
+    int32_t d = octet_dot(w.x, static_cast<int32_t>(xa.x), static_cast<int32_t>(xa.y), chunk_seed);
+    d = octet_dot(w.y, static_cast<int32_t>(xa.z), static_cast<int32_t>(xa.w), d);
+    d = octet_dot(w.z, static_cast<int32_t>(xb.x), static_cast<int32_t>(xb.y), d);
+    d = octet_dot(w.w, static_cast<int32_t>(xb.z), static_cast<int32_t>(xb.w), d);
+    return d;
+}
+
+// ---- Q8_1 quantiser ------------------------------------------------------------------
+// One warp quantises one group of 128: lane l owns elements 4l..4l+3.
+// d = max(max|x| / 127, 1e-8), inv_d = 1 / d, q = clamp(rn(x * inv_d), -127, 127), all in
+// IEEE fp32 (explicit _rn intrinsics: the result does not depend on compiler flags).
+// Returns the four int8 packed little-endian; *d_out is the group scale (same in all lanes).
+__device__ __forceinline__ uint32_t quantize_group128_lane(const float v[4], float* d_out) {
+    float m = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+#pragma unroll
+    for (int mask = 16; mask > 0; mask >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, mask));
+    const float d = fmaxf(__fdiv_rn(m, 127.0f), 1e-8f);
+    const float inv_d = __fdiv_rn(1.0f, d);
+    uint32_t packed = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        int q = __float2int_rn(__fmul_rn(v[j], inv_d));
+        q = max(-127, min(127, q));
+        packed |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * j);
+    }
+    *d_out = d;
+    return packed;
+}
+// Sum of the four signed bytes of a packed word.
+__device__ __forceinline__ int32_t byte_sum(uint32_t packed) {
+    return __dp4a(static_cast<int32_t>(packed), 0x01010101, 0);
+}
+
+__device__ __forceinline__ void load_half4_as_float(const __half* p, float v[4]) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const __half2 a = *reinterpret_cast<const __half2*>(&raw.x);
+    const __half2 b = *reinterpret_cast<const __half2*>(&raw.y);
+    const float2 fa = __half22float2(a), fb = __half22float2(b);
+    v[0] = fa.x; v[1] = fa.y; v[2] = fb.x; v[3] = fb.y;
+}
+
+// Layout of the staged activation in shared memory (all 16-byte aligned):
+//   q8[K] int8 | chunk_seed[K/32] int32 | scale[K/128] fp32
+struct StagedX {
+    const int8_t* q8;
+    const int32_t* seed;
+    const float* scale;
+};
+__host__ __device__ inline size_t staged_x_bytes(int K) {
+    return static_cast<size_t>(K) + static_cast<size_t>(K / kChunk) * 4 + static_cast<size_t>(K / kGroup) * 4;
+}
+
+// Copies a pre-quantised Q8_1 activation from global into shared memory, folding the four
+// per-octet sum8 of each chunk into one seed.  vec_ok: q8 and sum8 are 16-byte aligned.
+__device__ __forceinline__ void stage_x_from_q8_1(const int8_t* __restrict__ g_q8, const float* __restrict__ g_scale,
+                                                  const int32_t* __restrict__ g_sum8, int K, bool vec_ok,
+                                                  int8_t* s_q8, int32_t* s_seed, float* s_scale) {
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    if (vec_ok) {
+        const uint4* src = reinterpret_cast<const uint4*>(g_q8);
+        uint4* dst = reinterpret_cast<uint4*>(s_q8);
+        for (int i = tid; i < K / 16; i += nthr) dst[i] = src[i];
+        const int4* s8 = reinterpret_cast<const int4*>(g_sum8);
+        for (int c = tid; c < K / kChunk; c += nthr) {
+            const int4 v = s8[c];
+            s_seed[c] = v.x + v.y + v.z + v.w;
+        }
+    } else {
+        for (int i = tid; i < K; i += nthr) s_q8[i] = g_q8[i];
+        for (int c = tid; c < K / kChunk; c += nthr)
+            s_seed[c] = g_sum8[4 * c] + g_sum8[4 * c + 1] + g_sum8[4 * c + 2] + g_sum8[4 * c + 3];
+    }
+    for (int g = tid; g < K / kGroup; g += nthr) s_scale[g] = g_scale[g];
+}
+
+// Quantises an fp16 activation into the same shared-memory layout (every CTA does it for
+// itself; the result is identical to what the stand-alone quantiser writes to global).
+// x must be 8-byte aligned.
+__device__ __forceinline__ void stage_x_from_fp16(const __half* __restrict__ g_x, int K, int8_t* s_q8,
+                                                  int32_t* s_seed, float* s_scale) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int g = warp; g < K / kGroup; g += nwarps) {
+        float v[4];
+        load_half4_as_float(g_x + g * kGroup + lane * 4, v);
+        float d;
+        const uint32_t packed = quantize_group128_lane(v, &d);
+        reinterpret_cast<uint32_t*>(s_q8)[g * (kGroup / 4) + lane] = packed;
+        int32_t s = byte_sum(packed);
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 4);
+        if ((lane & 7) == 0) s_seed[g * 4 + (lane >> 3)] = -8 * s;
+        if (lane == 0) s_scale[g] = d;
+    }
+}
+
+}  // namespace w4

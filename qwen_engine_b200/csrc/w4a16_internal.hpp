@@ -1,0 +1,90 @@
+// Internal C++ interface between the C-ABI translation unit and the kernel files.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+
+#include "../../include/w4a16_b200.h"
+
+namespace w4 {
+
+// Per-process switches and per-device facts.
+struct DeviceInfo {
+    int sm_count = 0;
+    int cc_major = 0;
+    bool ready = false;
+};
+int ensure_device_ready(const DeviceInfo** out);  // lazy per-device set-up; returns a status
+bool pdl_enabled();
+void set_pdl_enabled(bool on);
+int env_int(const char* name, int fallback);       // read once, cached by the caller
+
+// One launch with (optionally) the programmatic-serialisation attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 bool pdl, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// ---- Q8_1 quantisers (q8_1_quantize.cu) ----
+int quantize_fp16_to_q8_1(const __half* x, int8_t* q8, float* scale, int32_t* sum8, int n, cudaStream_t stream);
+int rmsnorm_q8_1(const __half* in, const __half* gamma, __half* out_opt, int8_t* q8, float* scale, int32_t* sum8,
+                 int hidden, cudaStream_t stream);
+int quantize_set_attributes();
+
+// ---- decode GEMV (gemv_decode.cu) ----
+enum GemvMode { kPlain = 0, kQkv = 1, kSwiglu = 2 };
+
+struct GemvArgs {
+    // PLAIN / SWIGLU use index 0 only; QKV uses q, k, v in 0, 1, 2.
+    const uint32_t* qweight[3];
+    const __half* scales[3];
+    __half* out[3];
+    int rows[3];  // weight rows of each tensor
+    // activation: either pre-quantised Q8_1 or fp16 (quantised in the kernel's prologue)
+    const int8_t* q8;
+    const float* xscale;
+    const int32_t* sum8;
+    const __half* x_fp16;
+    const __half* residual;  // PLAIN only, may be null, may alias out[0]
+    int K;
+    int units;  // outputs produced: rows (PLAIN, QKV total) or row pairs (SWIGLU)
+    // filled in by the planner
+    int units_per_cta;
+    int ksplit;
+    int steps_per_split;
+    int vec_ok;
+};
+int gemv_launch(GemvMode mode, GemvArgs args, cudaStream_t stream);
+int gemv_group_dots(const uint32_t* qweight, const int8_t* q8, const int32_t* sum8, int32_t* out, int N, int K,
+                    cudaStream_t stream);
+int gemv_set_attributes();
+
+// ---- M-token contraction (gemm_prefill.cu) ----
+struct GemmArgs {
+    const uint32_t* qweight[3];
+    const __half* scales[3];
+    __half* out[3];
+    int rows[3];
+    const __half* x;         // [M][K]
+    const __half* residual;  // [M][N] or null; may alias out[0]
+    int M;
+    int K;
+    int mode;  // GemvMode values
+};
+int gemm_launch(GemmArgs args, cudaStream_t stream);
+int gemm_set_attributes();
+
+}  // namespace w4

@@ -1,0 +1,147 @@
+"""Python mirror of the reference's `qwen::launch_*` functions for the W4 projection path
+(reference include/kernels.cuh), calling the C ABI of libw4a16_b200.so.
+
+Names, argument order and meaning follow the reference; tensors are torch CUDA tensors
+(torch is used for device memory and streams only).  Every call goes to the CUDA library;
+there is no other implementation behind these functions, and a nonzero status raises
+`W4A16Error` where the reference throws std::runtime_error.
+"""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from ._lib import QKVView, W4A16Error, check, load  # noqa: F401
+
+__all__ = [
+    "QKVProjectionView", "W4A16Error", "init", "set_pdl",
+    "launch_quantize_fp16_to_q8_1", "launch_rmsnorm_q8_1",
+    "launch_gemv_w4a16", "launch_gemv_w4a8", "launch_gemv_qkv_w4a8",
+    "launch_gemv_dual_gate_up_swiglu_w4a16", "launch_gemv_dual_gate_up_swiglu_w4a8",
+    "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
+    "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots",
+]
+
+# Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
+HIDDEN_SIZE, INTERMEDIATE_SIZE = 1536, 8960
+NUM_Q_HEADS, NUM_KV_HEADS, HEAD_DIM = 12, 2, 128
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    if t is None:
+        return None
+    if not t.is_cuda:
+        raise ValueError("device pointer expected: tensor is not on a CUDA device")
+    return t.data_ptr()
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+
+
+@dataclass
+class QKVProjectionView:
+    """reference include/kernels.cuh:23-27"""
+    q_weight: torch.Tensor
+    q_scale: torch.Tensor
+    d_q: torch.Tensor
+    k_weight: torch.Tensor
+    k_scale: torch.Tensor
+    d_k: torch.Tensor
+    v_weight: torch.Tensor
+    v_scale: torch.Tensor
+    d_v: torch.Tensor
+
+    def pod(self) -> QKVView:
+        return QKVView(*[_ptr(getattr(self, n)) for n, _ in QKVView._fields_])
+
+
+def init() -> None:
+    check("w4a16_init", load().w4a16_init())
+
+
+def set_pdl(enabled: bool) -> None:
+    """Programmatic dependent launch on (default) or off for all launchers."""
+    check("w4a16_set_option", load().w4a16_set_option(1, int(bool(enabled))))
+
+
+def launch_quantize_fp16_to_q8_1(input_x, out_q8, out_scale, out_sum8, num_elements, stream=None):
+    check("w4a16_quantize_fp16_to_q8_1", load().w4a16_quantize_fp16_to_q8_1(
+        _ptr(input_x), _ptr(out_q8), _ptr(out_scale), _ptr(out_sum8), num_elements, _stream(stream)))
+
+
+def launch_rmsnorm_q8_1(input, gamma, output_fp16_opt, out_q8, out_scale, out_sum8, stream=None,
+                        hidden_size=HIDDEN_SIZE):
+    check("w4a16_rmsnorm_q8_1", load().w4a16_rmsnorm_q8_1(
+        _ptr(input), _ptr(gamma), _ptr(output_fp16_opt), _ptr(out_q8), _ptr(out_scale), _ptr(out_sum8),
+        _stream(stream), hidden_size))
+
+
+def launch_gemv_w4a16(qweight, scales, input_x, residual, output_y, out_features, in_features, stream=None):
+    check("w4a16_gemv_w4a16", load().w4a16_gemv_w4a16(
+        _ptr(qweight), _ptr(scales), _ptr(input_x), _ptr(residual), _ptr(output_y), out_features, in_features,
+        _stream(stream)))
+
+
+def launch_gemv_w4a8(qweight, scales, input_q8, input_scale, input_sum8, residual, output_y, out_features,
+                     in_features, stream=None):
+    check("w4a16_gemv_w4a8", load().w4a16_gemv_w4a8(
+        _ptr(qweight), _ptr(scales), _ptr(input_q8), _ptr(input_scale), _ptr(input_sum8), _ptr(residual),
+        _ptr(output_y), out_features, in_features, _stream(stream)))
+
+
+def launch_gemv_qkv_w4a8(view: QKVProjectionView, input_q8, input_scale, input_sum8, stream=None,
+                         in_features=HIDDEN_SIZE, num_q_heads=NUM_Q_HEADS, num_kv_heads=NUM_KV_HEADS,
+                         head_dim=HEAD_DIM):
+    pod = view.pod()
+    check("w4a16_gemv_qkv_w4a8", load().w4a16_gemv_qkv_w4a8(
+        ctypes.byref(pod), _ptr(input_q8), _ptr(input_scale), _ptr(input_sum8), _stream(stream), in_features,
+        num_q_heads, num_kv_heads, head_dim))
+
+
+def launch_gemv_dual_gate_up_swiglu_w4a16(gate_up_qweight, gate_up_scales, input_x, output_mlp, hidden_size,
+                                          intermediate_size, stream=None):
+    check("w4a16_gemv_dual_gate_up_swiglu_w4a16", load().w4a16_gemv_dual_gate_up_swiglu_w4a16(
+        _ptr(gate_up_qweight), _ptr(gate_up_scales), _ptr(input_x), _ptr(output_mlp), hidden_size,
+        intermediate_size, _stream(stream)))
+
+
+def launch_gemv_dual_gate_up_swiglu_w4a8(gate_up_qweight, gate_up_scales, input_q8, input_scale, input_sum8,
+                                         output_mlp, hidden_size, intermediate_size, stream=None):
+    check("w4a16_gemv_dual_gate_up_swiglu_w4a8", load().w4a16_gemv_dual_gate_up_swiglu_w4a8(
+        _ptr(gate_up_qweight), _ptr(gate_up_scales), _ptr(input_q8), _ptr(input_scale), _ptr(input_sum8),
+        _ptr(output_mlp), hidden_size, intermediate_size, _stream(stream)))
+
+
+def launch_gemm_prefill_w4a16(qweight, scales, input_x, residual, output_y, M, N, K, stream=None, sm_count=0):
+    check("w4a16_gemm_prefill_w4a16", load().w4a16_gemm_prefill_w4a16(
+        _ptr(qweight), _ptr(scales), _ptr(input_x), _ptr(residual), _ptr(output_y), M, N, K, _stream(stream),
+        sm_count))
+
+
+def launch_gemm_prefill_qkv_w4a16(view: QKVProjectionView, input_x, M, stream=None, in_features=HIDDEN_SIZE,
+                                  num_q_heads=NUM_Q_HEADS, num_kv_heads=NUM_KV_HEADS, head_dim=HEAD_DIM,
+                                  sm_count=0):
+    pod = view.pod()
+    check("w4a16_gemm_prefill_qkv_w4a16", load().w4a16_gemm_prefill_qkv_w4a16(
+        ctypes.byref(pod), _ptr(input_x), M, _stream(stream), in_features, num_q_heads, num_kv_heads, head_dim,
+        sm_count))
+
+
+def launch_gemm_prefill_dual_gate_up_swiglu_w4a16(gate_up_qweight, gate_up_scales, input_x, output_mlp, M,
+                                                  stream=None, hidden_size=HIDDEN_SIZE,
+                                                  intermediate_size=INTERMEDIATE_SIZE):
+    check("w4a16_gemm_prefill_dual_gate_up_swiglu_w4a16", load().w4a16_gemm_prefill_dual_gate_up_swiglu_w4a16(
+        _ptr(gate_up_qweight), _ptr(gate_up_scales), _ptr(input_x), _ptr(output_mlp), M, _stream(stream),
+        hidden_size, intermediate_size))
+
+
+def gemv_group_dots(qweight, input_q8, input_sum8, out_dots, out_features, in_features, stream=None):
+    """Diagnostic: int32 per-group partial sums of the decode GEMV (no reference launcher)."""
+    check("w4a16_gemv_group_dots", load().w4a16_gemv_group_dots(
+        _ptr(qweight), _ptr(input_q8), _ptr(input_sum8), _ptr(out_dots), out_features, in_features,
+        _stream(stream)))

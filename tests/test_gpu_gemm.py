@@ -1,0 +1,104 @@
+"""Parity of the M-token contraction (small-M decode batches, prefill) with the CPU oracle.
+
+Arithmetic under test: fp16 weights dequantised as (q-8)*scale with one fp16 rounding, exact
+fp16 x fp16 products, fp32 accumulation, fp16 output (+ fp16 residual add / SwiGLU).
+Tolerance against the golden that sums the same products in double: max relative error
+<= 1e-2, median <= 2 fp16 ulp (util.assert_fp16_close).
+"""
+import numpy as np
+import pytest
+
+import oracle
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import qwen_engine_b200 as pkg
+    pkg.init()
+    return pkg
+
+
+def _inputs(seed, M, N, K):
+    from qwen_engine_b200 import synth
+    return (synth.packed_weights(seed, "g", N, K), synth.scales(seed, "g", N, K),
+            synth.activations(seed, "g", M, K))
+
+
+def _sample(rng, n, k):
+    k = min(n, k)
+    idx = np.unique(np.concatenate([[0, n - 1], rng.choice(n, size=k, replace=False)]))
+    return idx.astype(np.int32)
+
+
+CASES = [
+    # (M, N, K, residual)
+    (1, 1536, 1536, True), (2, 2048, 1536, False), (3, 100, 256, True), (5, 1536, 8960, True),
+    (8, 1536, 1536, True), (16, 1536, 1536, False), (33, 520, 512, True), (64, 1536, 8960, True),
+    (128, 1536, 1536, True), (200, 2048, 1536, False), (512, 1536, 8960, True),
+]
+
+
+@pytest.mark.parametrize("M,N,K,use_res", CASES)
+def test_gemm_prefill_matches_oracle(ops, M, N, K, use_res):
+    qw, sc, x = _inputs(M * 7 + N + K, M, N, K)
+    rng = np.random.default_rng(M + N)
+    res = rng.standard_normal((M, N)).astype(np.float16) if use_res else None
+    y = torch.full((M * N + 64,), float("nan"), dtype=torch.float16, device="cuda")
+    d_res = None
+    if use_res:
+        y[:M * N] = util.to_dev(res).reshape(-1)   # in place: residual == output
+        d_res = y
+    ops.launch_gemm_prefill_w4a16(util.to_dev(qw), util.to_dev(sc), util.to_dev(x), d_res, y, M, N, K)
+    torch.cuda.synchronize()
+    out = util.to_np(y)
+    assert np.isnan(out[M * N:]).all(), "wrote past the output"
+    out = out[:M * N].reshape(M, N)
+    m_idx, n_idx = _sample(rng, M, 24), _sample(rng, N, 96)
+    ref64, ref16 = oracle.gemm_prefill(qw, sc, x, m_idx, n_idx, residual=res)
+    got = out[np.ix_(m_idx, n_idx)]
+    util.assert_fp16_close(got, ref64, what=f"gemm M={M} N={N} K={K}")
+    assert np.isfinite(out).all()
+
+
+@pytest.mark.parametrize("M", [1, 4, 16, 70, 256])
+def test_gemm_prefill_qkv_matches_oracle(ops, M):
+    from qwen_engine_b200 import synth
+    K, nq, nkv, hd = 1536, 12, 2, 128
+    dims = [nq * hd, nkv * hd, nkv * hd]
+    x = synth.activations(M, "qkv", M, K)
+    ws = [(synth.packed_weights(M, f"t{i}", n, K), synth.scales(M, f"t{i}", n, K)) for i, n in enumerate(dims)]
+    outs = [torch.full((M * n + 8,), float("nan"), dtype=torch.float16, device="cuda") for n in dims]
+    dev = [(util.to_dev(w), util.to_dev(s)) for w, s in ws]
+    view = ops.QKVProjectionView(dev[0][0], dev[0][1], outs[0], dev[1][0], dev[1][1], outs[1],
+                                 dev[2][0], dev[2][1], outs[2])
+    ops.launch_gemm_prefill_qkv_w4a16(view, util.to_dev(x), M, None, K, nq, nkv, hd)
+    torch.cuda.synchronize()
+    rng = np.random.default_rng(M)
+    for (w, s), o, n in zip(ws, outs, dims):
+        got = util.to_np(o)
+        assert np.isnan(got[M * n:]).all()
+        got = got[:M * n].reshape(M, n)
+        m_idx, n_idx = _sample(rng, M, 16), _sample(rng, n, 64)
+        ref64, _ = oracle.gemm_prefill(w, s, x, m_idx, n_idx)
+        util.assert_fp16_close(got[np.ix_(m_idx, n_idx)], ref64, what=f"qkv M={M}")
+
+
+@pytest.mark.parametrize("M,H,I", [(1, 1536, 8960), (6, 256, 512), (16, 1536, 8960), (130, 1536, 8960), (40, 512, 100)])
+def test_gemm_prefill_swiglu_matches_oracle(ops, M, H, I):
+    qw, sc, x = _inputs(M + H + I, M, 2 * I, H)
+    y = torch.full((M * I + 8,), float("nan"), dtype=torch.float16, device="cuda")
+    ops.launch_gemm_prefill_dual_gate_up_swiglu_w4a16(util.to_dev(qw), util.to_dev(sc), util.to_dev(x), y, M, None,
+                                                      H, I)
+    torch.cuda.synchronize()
+    out = util.to_np(y)
+    assert np.isnan(out[M * I:]).all()
+    out = out[:M * I].reshape(M, I)
+    rng = np.random.default_rng(M + I)
+    m_idx, n_idx = _sample(rng, M, 16), _sample(rng, I, 96)
+    ref64, _ = oracle.gemm_prefill(qw, sc, x, m_idx, n_idx, swiglu=True)
+    util.assert_fp16_close(out[np.ix_(m_idx, n_idx)], ref64, what=f"swiglu M={M}")
