@@ -1,0 +1,466 @@
+#!/usr/bin/env python
+"""Benchmark of the W4A16 group-128 batch-1 decode projection sweep on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+One step = one pass of the 28-layer Qwen2.5-1.5B-shaped projection sweep (QKV, O, gate_up +
+SwiGLU, down, each with its Q8_1 quantiser in front), run as one CUDA graph through the C ABI
+(w4a16_sweep_*).  Weights are seeded synthetic tensors with the benchmark configuration's
+distributions; the 675 MB of packed weights streamed per step exceed L2, so every step reads
+them from HBM.  Prints ONE JSON line (rank 0).
+
+The oracle (oracle/) is used here only for the cpu_baseline leg / the reference arm and for
+a one-layer sanity check of the result.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "W4A16 G128 batch-1 decode projection sweep, achieved HBM bandwidth"
+UNIT = "GB/s"
+WORKLOAD = ("config 1: 28-layer Qwen2.5-1.5B projection sweep (QKV 1536->2048, O 1536->1536 +res, "
+            "gate_up 1536->17920 +SwiGLU, down 8960->1536 +res), W4A16 G128, batch 1, Q8_1 before each GEMV")
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=28, help=argparse.SUPPRESS)
+    ap.add_argument("--no-cpu-baseline", action="store_true", help=argparse.SUPPRESS)
+    return ap.parse_args()
+
+
+# ---- synthetic model -----------------------------------------------------------------
+
+def make_layers_np(num_layers: int, seed: int = 0x5EED0001):
+    from qwen_engine_b200 import synth
+    layers = []
+    for l in range(num_layers):
+        L = {}
+        for name in ("q", "k", "v", "o", "gate_up", "down"):
+            N, K = synth.SHAPES[name]
+            L[name] = (synth.packed_weights(seed, f"L{l}.{name}", N, K), synth.scales(seed, f"L{l}.{name}", N, K))
+        L["input_norm"] = np.ones(synth.HIDDEN, dtype=np.float16)
+        L["post_norm"] = np.ones(synth.HIDDEN, dtype=np.float16)
+        layers.append(L)
+    return layers
+
+
+def upload_layers(layers_np):
+    import torch
+    out = []
+    for L in layers_np:
+        D = {}
+        for k, v in L.items():
+            if isinstance(v, tuple):
+                D[k] = (torch.from_numpy(v[0].view(np.int32)).cuda(), torch.from_numpy(v[1]).cuda())
+            else:
+                D[k] = torch.from_numpy(v).cuda()
+        out.append(D)
+    return out
+
+
+# ---- clocks ---------------------------------------------------------------------------
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed regions run."""
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
+
+    def __init__(self, index: int, period_s: float = 0.01, pci_bus_id: str | None = None):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            try:
+                self.h = pynvml.nvmlDeviceGetHandleByPciBusId(pci_bus_id.encode()) if pci_bus_id else None
+            except Exception:
+                self.h = None
+            if self.h is None:
+                self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self._thr = threading.Thread(target=self._run, args=(period_s,), daemon=True)
+        except Exception:
+            self.nv = None
+
+    def _run(self, period):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                for bit, name in self.REASONS.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(period)
+
+    def start(self):
+        if self._thr:
+            self._thr.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thr:
+            self._thr.join(timeout=1.0)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# ---- CPU baseline (oracle port) ----------------------------------------------------------
+
+def time_cpu_sweep(layers_np, h0, budget_s: float = 12.0, max_reps: int = 20):
+    """Times the oracle's sweep on the host cores.  Returns (GB/s, cores, sample description, last h)."""
+    import oracle
+    from qwen_engine_b200 import synth
+    threads = oracle.default_threads()
+    nbytes = synth.layer_algorithmic_bytes() * len(layers_np)
+    oracle.decode_sweep(layers_np[:1], h0, threads=threads)  # warm the library and the page cache
+    reps, t0, h = 0, time.perf_counter(), None
+    while reps < max_reps and (reps == 0 or time.perf_counter() - t0 < budget_s):
+        h = oracle.decode_sweep(layers_np, h0, threads=threads)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return nbytes / dt / 1e9, threads, f"{reps} full {len(layers_np)}-layer sweeps of the oracle port, {dt * 1e3:.1f} ms each", h
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from qwen_engine_b200 import synth
+    layers_np = make_layers_np(args.layers)
+    h0 = synth.activations(7, "h0", synth.HIDDEN)
+    # one "step" = one oracle sweep; W warm-up and K timed steps, bounded so the run ends in minutes
+    import oracle
+    threads = oracle.default_threads()
+    nbytes = synth.layer_algorithmic_bytes() * len(layers_np)
+    steps, warm = max(1, min(args.steps, 20)), max(1, min(args.warmup, 3))
+    for _ in range(warm):
+        oracle.decode_sweep(layers_np, h0, threads=threads)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        oracle.decode_sweep(layers_np, h0, threads=threads)
+    dt = (time.perf_counter() - t0) / steps
+    val = nbytes / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
+        "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers": len(layers_np),
+                   "note": "reference's CPU check restated in C (tests/test_kernels.cu:308-363), all host threads; "
+                           "the reference has no separately callable CPU implementation of this path"},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
+                         "sample": f"{steps} full {len(layers_np)}-layer sweeps"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ---- GPU arm ---------------------------------------------------------------------------------
+
+def timed_events(torch, stream, fn, steps):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        fn()
+    e1.record(stream)
+    e1.synchronize()
+    return e0.elapsed_time(e1)  # ms
+
+
+def kernel_roofline(torch, ops, layers_dev, stream, peaks, reps=20):
+    """Average duration of the dominant kernel (gate_up + SwiGLU GEMV), timed alone: one CUDA graph
+    of 28 launches over the 28 layers' distinct weights (397 MB > L2, so every launch streams from
+    HBM), CUDA events around each replay."""
+    from qwen_engine_b200 import synth
+    H, I = synth.HIDDEN, synth.INTER
+    x = torch.from_numpy(synth.activations(3, "roof", H)).cuda()
+    q8 = torch.empty(H, dtype=torch.int8, device="cuda")
+    xs = torch.empty(H // 128, dtype=torch.float32, device="cuda")
+    s8 = torch.empty(H // 8, dtype=torch.int32, device="cuda")
+    out = torch.empty(I, dtype=torch.float16, device="cuda")
+    res = {}
+    with torch.cuda.stream(stream):
+        ops.launch_quantize_fp16_to_q8_1(x, q8, xs, s8, H)
+
+        def all_layers(name):
+            for L in layers_dev:
+                if name == "gate_up":
+                    ops.launch_gemv_dual_gate_up_swiglu_w4a8(L[name][0], L[name][1], q8, xs, s8, out, H, I)
+                elif name == "o":
+                    ops.launch_gemv_w4a8(L[name][0], L[name][1], q8, xs, s8, None, out, H, H)
+        all_layers("gate_up")
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            all_layers("gate_up")
+        for _ in range(3):
+            g.replay()
+        stream.synchronize()
+        ms = timed_events(torch, stream, g.replay, reps)
+    per_launch_s = ms * 1e-3 / (reps * len(layers_dev))
+    nbytes = synth.gemv_algorithmic_bytes(2 * I, H, n_out=I)
+    achieved = nbytes / per_launch_s / 1e9
+    peak = peaks.get("hbm_gbs")
+    src = "measured" if peak else "fallback"
+    peak = peak or 6650.0
+    res = {"bound": "hbm", "kernel": "gemv_w4_kernel<SwiGLU> (gate_up 17920x1536)", "achieved": achieved, "peak": peak,
+           "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": f"of {src} (burst copy)",
+           "bytes_per_launch": nbytes, "us_per_launch": per_launch_s * 1e6,
+           "how": f"CUDA graph of {len(layers_dev)} launches over distinct weights, {reps} replays, CUDA events"}
+    return res
+
+
+def time_reference_cuda(torch, layers_dev, stream, steps):
+    """Second comparison: the reference's own CUDA kernels rebuilt for sm_100a (oracle/_ref), the same
+    chain in one CUDA graph.  Returns None when that library is not present."""
+    sys.path.insert(0, str(ROOT))
+    from tests.util import RefKernels
+    if not RefKernels.available("fastmath"):
+        return None
+    import ctypes
+    from qwen_engine_b200 import synth
+    ref = RefKernels("fastmath")
+    H, I = synth.HIDDEN, synth.INTER
+    h = torch.from_numpy(synth.activations(7, "h0", H)).cuda()
+    q = torch.empty(H, dtype=torch.float16, device="cuda")
+    k = torch.empty(synth.KV_DIM, dtype=torch.float16, device="cuda")
+    v = torch.empty(synth.KV_DIM, dtype=torch.float16, device="cuda")
+    mlp = torch.empty(I, dtype=torch.float16, device="cuda")
+    q8 = torch.empty(I, dtype=torch.int8, device="cuda")
+    xs = torch.empty(I // 128, dtype=torch.float32, device="cuda")
+    s8 = torch.empty(I // 8, dtype=torch.int32, device="cuda")
+
+    def chain(sp):
+        for L in layers_dev:
+            ref.call("ref_rmsnorm_q8_1", h, L["input_norm"], None, q8, xs, s8, sp, H)
+            pod = RefKernels.QKVPod(L["q"][0].data_ptr(), L["q"][1].data_ptr(), q.data_ptr(), L["k"][0].data_ptr(),
+                                    L["k"][1].data_ptr(), k.data_ptr(), L["v"][0].data_ptr(), L["v"][1].data_ptr(),
+                                    v.data_ptr())
+            ref.call("ref_gemv_qkv_w4a8", pod, q8, xs, s8, sp, H, 12, 2, 128)
+            ref.call("ref_quantize_fp16_to_q8_1", q, q8, xs, s8, H, sp)
+            ref.call("ref_gemv_w4a8", L["o"][0], L["o"][1], q8, xs, s8, h, h, H, H, sp)
+            ref.call("ref_rmsnorm_q8_1", h, L["post_norm"], None, q8, xs, s8, sp, H)
+            ref.call("ref_gemv_dual_gate_up_swiglu_w4a8", L["gate_up"][0], L["gate_up"][1], q8, xs, s8, mlp, H, I, sp)
+            ref.call("ref_quantize_fp16_to_q8_1", mlp, q8, xs, s8, I, sp)
+            ref.call("ref_gemv_w4a8", L["down"][0], L["down"][1], q8, xs, s8, h, h, H, I, sp)
+
+    with torch.cuda.stream(stream):
+        sp = ctypes.c_void_p(stream.cuda_stream)
+        chain(sp)
+        stream.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            chain(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+        for _ in range(3):
+            g.replay()
+        stream.synchronize()
+        ms = timed_events(torch, stream, g.replay, steps)
+    us = ms * 1e3 / steps
+    nbytes = synth.layer_algorithmic_bytes() * len(layers_dev)
+    return {"what": "reference CUDA kernels (src/kernels/*.cu) rebuilt for sm_100a with its own flags, same chain "
+                    "in one CUDA graph", "us_per_sweep": us, "value": nbytes / (us * 1e-6) / 1e9, "unit": UNIT}
+
+
+def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
+    """Configuration 2: lm_head 1536 -> 151936 split by vocabulary rows over the ranks, fp16 logit slices
+    all-gathered over NVLink (NCCL).  Strong scaling: the total work is fixed."""
+    from qwen_engine_b200 import synth
+    N, K = synth.SHAPES["lm_head"]
+    rows = N // world
+    r0 = rank * rows
+    # every rank draws only its own slab: rows are generated per 1024-row block so that slabs agree
+    qw = synth.packed_weights(11, f"lm_head.r{r0}", rows, K)
+    sc = synth.scales(11, f"lm_head.r{r0}", rows, K)
+    d_qw, d_sc = torch.from_numpy(qw.view(np.int32)).cuda(), torch.from_numpy(sc).cuda()
+    x = torch.from_numpy(synth.activations(11, "lm_x", K)).cuda()
+    q8 = torch.empty(K, dtype=torch.int8, device="cuda")
+    xs = torch.empty(K // 128, dtype=torch.float32, device="cuda")
+    s8 = torch.empty(K // 8, dtype=torch.int32, device="cuda")
+    logits = torch.empty(rows * world, dtype=torch.float16, device="cuda")
+    mine = logits[r0:r0 + rows]
+    # rotate over enough copies of the slab that consecutive steps do not hit L2
+    copies = max(1, int(np.ceil(3 * 126e6 / (qw.nbytes + sc.nbytes))))
+    copies = min(copies, 24)
+    slabs = [(d_qw, d_sc)] + [(d_qw.clone(), d_sc.clone()) for _ in range(copies - 1)]
+    with torch.cuda.stream(stream):
+        ops.launch_quantize_fp16_to_q8_1(x, q8, xs, s8, K)
+        i = [0]
+
+        def step():
+            w, s = slabs[i[0] % copies]
+            i[0] += 1
+            ops.launch_gemv_w4a8(w, s, q8, xs, s8, None, mine, rows, K)
+            if world > 1:
+                dist.all_gather_into_tensor(logits, mine)
+        for _ in range(max(3, warmup)):
+            step()
+        stream.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ms = timed_events(torch, stream, step, steps)
+        torch.cuda.synchronize()
+    t = torch.tensor([ms], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us = float(t.item()) * 1e3 / steps
+    nbytes = synth.gemv_algorithmic_bytes(N, K)
+    return {"workload": f"config 2: lm_head {K}->{N}, rows split over {world} GPU(s), NCCL all-gather of fp16 slices",
+            "rows_per_gpu": rows, "us_per_step": us, "value": nbytes / (us * 1e-6) / 1e9, "unit": UNIT,
+            "scaling": "strong", "weight_copies_rotated": copies}
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the W4A16 kernels have no CPU path")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    import qwen_engine_b200 as ops
+    from qwen_engine_b200 import synth
+    ops.init()
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+
+    steps, warmup = max(1, args.steps), max(3, args.warmup)
+    layers_np = make_layers_np(args.layers)
+    layers_dev = upload_layers(layers_np)
+    stream = torch.cuda.Stream()
+    h0_np = synth.activations(7, "h0", synth.HIDDEN)
+    h_in = torch.from_numpy(h0_np).cuda()
+    h_out = torch.empty_like(h_in)
+    pin_in = torch.from_numpy(h0_np).pin_memory()
+    pin_out = torch.empty(synth.HIDDEN, dtype=torch.float16).pin_memory()
+    with torch.cuda.stream(stream):
+        sweep = ops.DecodeSweep(layers_dev, stream=stream)
+    nbytes = synth.layer_algorithmic_bytes() * len(layers_np)
+
+    props = torch.cuda.get_device_properties(local)
+    try:
+        bus_id = f"{props.pci_domain_id:08X}:{props.pci_bus_id:02X}:{props.pci_device_id:02X}.0"
+    except AttributeError:
+        bus_id = None
+    sampler = ClockSampler(local, pci_bus_id=bus_id)
+    sampler.start()
+
+    # ---- device-resident timing: W warm-up, then exactly K steps --------------------------
+    for _ in range(warmup):
+        sweep.run_device(h_in, h_out, stream)
+    stream.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = timed_events(torch, stream, lambda: sweep.run_device(h_in, h_out, stream), steps)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t = torch.tensor([ms], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    ms_per_step = ms / steps
+    value = world * nbytes / (ms_per_step * 1e-3) / 1e9
+
+    # ---- end to end: host buffers, copies and the host's read of the result inside the region ---
+    def e2e_step():
+        sweep.run_host(pin_in, pin_out, stream)
+        stream.synchronize()
+        _ = pin_out[0].item()
+    for _ in range(3):
+        e2e_step()
+    if world > 1:
+        dist.barrier()
+    ms_e2e = timed_events(torch, stream, e2e_step, steps)
+    t = torch.tensor([ms_e2e], device="cuda")
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_value = world * nbytes / (float(t.item()) / steps * 1e-3) / 1e9
+    clocks = sampler.stop()
+
+    final = pin_out.numpy().copy()
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
+        "ms_per_step": ms_per_step, "us_per_sweep": ms_per_step * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers": len(layers_np), "parallelism": f"replicas x{world}",
+                   "algorithmic_bytes_per_step": nbytes,
+                   "l2": "inputs larger than L2: 675 MB of packed weights are streamed per step",
+                   "pdl": bool(ops.load().w4a16_get_option(1))},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": synth.HIDDEN * 2,
+                "d2h_bytes_per_step": synth.HIDDEN * 2,
+                "how": "w4a16_sweep_run_host: pinned fp16 hidden state in, sweep graph, hidden state out, "
+                       "stream synchronise and host read every step; weights resident (model state)"},
+        "gpu_launches": sweep.launches * steps, "gpu_launches_per_step": sweep.launches,
+        "clocks": clocks,
+        "result_finite": bool(np.isfinite(final.astype(np.float32)).all()),
+    }
+
+    if rank == 0:
+        with torch.cuda.stream(stream):
+            line["roofline"] = kernel_roofline(torch, ops, layers_dev, stream, peaks)
+        line["roofline_sweep"] = {"achieved": value / world, "peak": peaks.get("hbm_gbs", 6650.0),
+                                  "frac": value / world / peaks.get("hbm_gbs", 6650.0), "unit": UNIT,
+                                  "note": "whole sweep (224 dependent launches) per GPU against the copy peak"}
+    if world > 1 or os.environ.get("W4A16_BENCH_LM_HEAD", "1") == "1":
+        lm = lm_head_nsplit(torch, dist, ops, rank, world, stream, min(steps, 200), warmup)
+        if rank == 0:
+            line["lm_head"] = lm
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        ref_cuda = time_reference_cuda(torch, layers_dev, stream, min(steps, 100))
+        if ref_cuda:
+            line["reference_cuda_sm100a"] = ref_cuda
+        gbs, cores, sample, h_cpu = time_cpu_sweep(layers_np, h0_np)
+        line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        # sanity: first layer of the device sweep against the oracle on the same input
+        import oracle
+        one = ops.DecodeSweep(layers_dev[:1], stream=stream)
+        one.run_host(pin_in, pin_out, stream)
+        stream.synchronize()
+        h1 = oracle.decode_sweep(layers_np[:1], h0_np)
+        err = np.abs(pin_out.numpy().astype(np.float64) - h1.astype(np.float64))
+        line["check_layer0_max_abs_err"] = float(err.max())
+        line["check_layer0_rms"] = float(np.sqrt(np.mean(h1.astype(np.float64) ** 2)))
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

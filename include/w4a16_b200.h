@@ -153,6 +153,63 @@ W4A16_API int w4a16_gemm_prefill_dual_gate_up_swiglu_w4a16(const uint32_t* gate_
                                                            w4a16_stream_t stream, int hidden_size,
                                                            int intermediate_size);
 
+/* ---- decode projection sweep -------------------------------------------------------- */
+
+/*
+ * The W4 projections of one batch-1 decode pass, in the order the reference engine issues
+ * them (reference src/engine.cu:361-451, execute_gqa_decode_layer / execute_decode_pass),
+ * captured once into a CUDA graph as the engine does (src/engine.cu:453-470).  Per layer:
+ *   rmsnorm_q8_1(h) -> QKV GEMV -> [attention stand-in: Q8_1 of the q output]
+ *   -> O GEMV (+h, in place) -> rmsnorm_q8_1(h) -> gate_up GEMV + SwiGLU
+ *   -> Q8_1 of the MLP activation -> down GEMV (+h, in place).
+ * Attention, RoPE and the KV cache are not part of this library; the attention output is
+ * replaced by the q projection so that every GEMV keeps a true data dependency.
+ * All pointers are device pointers owned by the caller and must stay valid while the
+ * sweep object lives.  The object owns one CUDA graph and no device memory.
+ */
+typedef struct w4a16_layer_weights {
+    const void* input_norm_gamma;          /* fp16 [hidden] */
+    const void* q_weight;  const void* q_scale;
+    const void* k_weight;  const void* k_scale;
+    const void* v_weight;  const void* v_scale;
+    const void* o_weight;  const void* o_scale;
+    const void* post_norm_gamma;           /* fp16 [hidden] */
+    const void* gate_up_weight; const void* gate_up_scale;
+    const void* down_weight;    const void* down_scale;
+} w4a16_layer_weights;
+
+typedef struct w4a16_sweep_desc {
+    int num_layers, hidden_size, intermediate_size, num_q_heads, num_kv_heads, head_dim;
+    const w4a16_layer_weights* layers;     /* host array [num_layers], copied */
+    void* workspace;                       /* device, >= w4a16_sweep_workspace_bytes(), 256-byte aligned */
+} w4a16_sweep_desc;
+
+typedef struct w4a16_sweep w4a16_sweep;
+
+/* Bytes of device workspace the sweep needs (hidden state, q/k/v, MLP activation, Q8_1 scratch). */
+W4A16_API int64_t w4a16_sweep_workspace_bytes(int hidden_size, int intermediate_size, int num_q_heads,
+                                              int num_kv_heads, int head_dim);
+
+/* Builds the sweep: one eager pass on `stream`, then graph capture.  Synchronises `stream`. */
+W4A16_API int w4a16_sweep_create(const w4a16_sweep_desc* desc, w4a16_stream_t stream, w4a16_sweep** out);
+W4A16_API int w4a16_sweep_destroy(w4a16_sweep* sweep);
+
+/* Kernels launched per w4a16_sweep_run_* call. */
+W4A16_API int w4a16_sweep_launches(const w4a16_sweep* sweep);
+
+/* One sweep with the hidden state in device memory: h_in fp16 [hidden] -> h_out fp16 [hidden]
+ * (two small device copies around the graph launch).  Asynchronous on `stream`. */
+W4A16_API int w4a16_sweep_run_device(w4a16_sweep* sweep, const void* d_h_in, void* d_h_out,
+                                     w4a16_stream_t stream);
+
+/* Same with HOST buffers (pinned for true asynchrony): copies h_in to the device, runs the
+ * sweep, copies the result back.  Asynchronous on `stream`; synchronise before reading. */
+W4A16_API int w4a16_sweep_run_host(w4a16_sweep* sweep, const void* h_h_in, void* h_h_out,
+                                   w4a16_stream_t stream);
+
+/* Device pointer of a workspace region, for tests: 0 hidden, 1 q, 2 k, 3 v, 4 mlp. */
+W4A16_API void* w4a16_sweep_buffer(const w4a16_sweep* sweep, int which);
+
 /* ---- diagnostics ----------------------------------------------------------------- */
 
 /*

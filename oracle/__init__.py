@@ -193,3 +193,30 @@ def rmsnorm(x, gamma, eps=1e-6, inv_rms_override=0.0):
     inv = lib().orc_rmsnorm(_p(x), _p(gamma), ctypes.c_int(x.size), ctypes.c_float(eps),
                             ctypes.c_float(inv_rms_override), _p(y))
     return y, float(inv)
+
+
+def decode_sweep(layers, h0, threads=None, collect=False):
+    """CPU restatement of the decode projection sweep (the chain the library's DecodeSweep runs;
+    reference order of launches: src/engine.cu:361-451 with the attention output replaced by the
+    q projection).  layers: list of dicts of numpy arrays -- 'input_norm', 'post_norm' fp16 gamma,
+    'q','k','v','o','gate_up','down' -> (packed, scales).  Returns the final hidden state fp16
+    (and, with collect=True, every intermediate per layer)."""
+    h = np.ascontiguousarray(h0, dtype=np.float16).copy()
+    trace = []
+    for L in layers:
+        xn, _ = rmsnorm(h, L["input_norm"])
+        q8, xs, _ = quantize_q8_1(xn)
+        q = gemv_q8(*L["q"], q8, xs, threads=threads, want64=False)[1]
+        k = gemv_q8(*L["k"], q8, xs, threads=threads, want64=False)[1]
+        v = gemv_q8(*L["v"], q8, xs, threads=threads, want64=False)[1]
+        a8, as_, _ = quantize_q8_1(q)
+        h_attn = gemv_q8(*L["o"], a8, as_, residual=h, threads=threads, want64=False)[1]
+        xn2, _ = rmsnorm(h_attn, L["post_norm"])
+        p8, ps, _ = quantize_q8_1(xn2)
+        mlp = gemv_q8(*L["gate_up"], p8, ps, swiglu=True, threads=threads, want64=False)[1]
+        m8, ms, _ = quantize_q8_1(mlp)
+        h_new = gemv_q8(*L["down"], m8, ms, residual=h_attn, threads=threads, want64=False)[1]
+        if collect:
+            trace.append({"h_in": h, "q": q, "k": k, "v": v, "h_attn": h_attn, "mlp": mlp, "h_out": h_new})
+        h = h_new
+    return (h, trace) if collect else h

@@ -18,7 +18,21 @@ class QKVView(ctypes.Structure):
                                         "v_weight", "v_scale", "d_v")]
 
 
-# name -> argtypes; every function returns int except the two noted below
+class LayerWeights(ctypes.Structure):
+    """Mirror of w4a16_layer_weights."""
+    _fields_ = [(n, c_void_p) for n in (
+        "input_norm_gamma", "q_weight", "q_scale", "k_weight", "k_scale", "v_weight", "v_scale",
+        "o_weight", "o_scale", "post_norm_gamma", "gate_up_weight", "gate_up_scale", "down_weight", "down_scale")]
+
+
+class SweepDesc(ctypes.Structure):
+    """Mirror of w4a16_sweep_desc."""
+    _fields_ = [("num_layers", c_int), ("hidden_size", c_int), ("intermediate_size", c_int),
+                ("num_q_heads", c_int), ("num_kv_heads", c_int), ("head_dim", c_int),
+                ("layers", POINTER(LayerWeights)), ("workspace", c_void_p)]
+
+
+# name -> argtypes; every function returns int except those in RESTYPES
 SIGNATURES = {
     "w4a16_version": [],
     "w4a16_init": [],
@@ -40,7 +54,15 @@ SIGNATURES = {
     "w4a16_gemm_prefill_dual_gate_up_swiglu_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                      c_int, c_int],
     "w4a16_gemv_group_dots": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "w4a16_sweep_workspace_bytes": [c_int, c_int, c_int, c_int, c_int],
+    "w4a16_sweep_create": [POINTER(SweepDesc), c_void_p, POINTER(c_void_p)],
+    "w4a16_sweep_destroy": [c_void_p],
+    "w4a16_sweep_launches": [c_void_p],
+    "w4a16_sweep_run_device": [c_void_p, c_void_p, c_void_p, c_void_p],
+    "w4a16_sweep_run_host": [c_void_p, c_void_p, c_void_p, c_void_p],
+    "w4a16_sweep_buffer": [c_void_p, c_int],
 }
+RESTYPES = {"w4a16_sweep_workspace_bytes": ctypes.c_int64, "w4a16_sweep_buffer": c_void_p}
 
 _lib = None
 
@@ -58,7 +80,7 @@ def load() -> ctypes.CDLL:
     for name, argtypes in SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError if the symbol is not exported
         fn.argtypes = argtypes
-        fn.restype = c_int
+        fn.restype = RESTYPES.get(name, c_int)
     lib.w4a16_status_string.argtypes = [c_int]
     lib.w4a16_status_string.restype = c_char_p
     _lib = lib

@@ -1,0 +1,223 @@
+// Host driver of the decode projection sweep: the W4 launches of one batch-1 decode pass in
+// the reference engine's order (reference src/engine.cu:361-451), captured once into a CUDA
+// graph like the engine's decode graph (src/engine.cu:453-470).  Host C++ only; the kernels
+// are the library's ordinary launchers.
+#include <memory>
+#include <new>
+#include <vector>
+
+#include "w4a16_internal.hpp"
+
+struct w4a16_sweep {
+    w4a16_sweep_desc desc{};
+    std::vector<w4a16_layer_weights> layers;
+    // workspace carve-up (device)
+    __half* h = nullptr;      // hidden state [hidden]
+    __half* q = nullptr;      // [nq*hd]
+    __half* k = nullptr;      // [nkv*hd]
+    __half* v = nullptr;      // [nkv*hd]
+    __half* mlp = nullptr;    // [inter]
+    int8_t* act_q8 = nullptr; // [max(hidden, inter)]
+    float* act_scale = nullptr;
+    int32_t* act_sum8 = nullptr;
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    int launches = 0;
+};
+
+namespace {
+
+using namespace w4;
+
+constexpr size_t kAlign = 256;
+size_t align_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
+
+struct Carve {
+    size_t h, q, k, v, mlp, q8, scale, sum8, total;
+};
+Carve carve(int hidden, int inter, int nq, int nkv, int hd) {
+    const size_t kmax = static_cast<size_t>(hidden > inter ? hidden : inter);
+    const size_t qdim = static_cast<size_t>(nq) * hd, kvdim = static_cast<size_t>(nkv) * hd;
+    Carve c{};
+    size_t off = 0;
+    c.h = off; off += align_up(hidden * sizeof(__half));
+    c.q = off; off += align_up((qdim > static_cast<size_t>(hidden) ? qdim : hidden) * sizeof(__half));
+    c.k = off; off += align_up(kvdim * sizeof(__half));
+    c.v = off; off += align_up(kvdim * sizeof(__half));
+    c.mlp = off; off += align_up(inter * sizeof(__half));
+    c.q8 = off; off += align_up(kmax);
+    c.scale = off; off += align_up(kmax / 128 * sizeof(float));
+    c.sum8 = off; off += align_up(kmax / 8 * sizeof(int32_t));
+    c.total = off;
+    return c;
+}
+
+// Issues the launches of one pass on `stream`; returns the first nonzero status.
+int issue_pass(w4a16_sweep* s, cudaStream_t stream, int* launches) {
+    const auto& d = s->desc;
+    const int H = d.hidden_size, I = d.intermediate_size;
+    const int qdim = d.num_q_heads * d.head_dim, kvdim = d.num_kv_heads * d.head_dim;
+    int n = 0;
+    for (const auto& L : s->layers) {
+        if (int st = rmsnorm_q8_1(s->h,
+                                  static_cast<const __half*>(L.input_norm_gamma), nullptr, s->act_q8, s->act_scale,
+                                  s->act_sum8, H, stream))
+            return st;
+        ++n;
+        GemvArgs a = {};
+        a.qweight[0] = static_cast<const uint32_t*>(L.q_weight); a.scales[0] = static_cast<const __half*>(L.q_scale);
+        a.qweight[1] = static_cast<const uint32_t*>(L.k_weight); a.scales[1] = static_cast<const __half*>(L.k_scale);
+        a.qweight[2] = static_cast<const uint32_t*>(L.v_weight); a.scales[2] = static_cast<const __half*>(L.v_scale);
+        a.out[0] = s->q; a.out[1] = s->k; a.out[2] = s->v;
+        a.rows[0] = qdim; a.rows[1] = kvdim; a.rows[2] = kvdim;
+        a.q8 = s->act_q8; a.xscale = s->act_scale; a.sum8 = s->act_sum8;
+        a.K = H; a.units = qdim + 2 * kvdim;
+        if (int st = gemv_launch(kQkv, a, stream)) return st;
+        ++n;
+        // attention stand-in: the q projection plays the attention output
+        if (int st = quantize_fp16_to_q8_1(s->q, s->act_q8, s->act_scale, s->act_sum8, qdim, stream)) return st;
+        ++n;
+        GemvArgs o = {};
+        o.qweight[0] = static_cast<const uint32_t*>(L.o_weight); o.scales[0] = static_cast<const __half*>(L.o_scale);
+        o.out[0] = s->h; o.rows[0] = H; o.residual = s->h;
+        o.q8 = s->act_q8; o.xscale = s->act_scale; o.sum8 = s->act_sum8;
+        o.K = qdim; o.units = H;
+        if (int st = gemv_launch(kPlain, o, stream)) return st;
+        ++n;
+        if (int st = rmsnorm_q8_1(s->h, static_cast<const __half*>(L.post_norm_gamma), nullptr, s->act_q8,
+                                  s->act_scale, s->act_sum8, H, stream))
+            return st;
+        ++n;
+        GemvArgs g = {};
+        g.qweight[0] = static_cast<const uint32_t*>(L.gate_up_weight);
+        g.scales[0] = static_cast<const __half*>(L.gate_up_scale);
+        g.out[0] = s->mlp; g.rows[0] = 2 * I;
+        g.q8 = s->act_q8; g.xscale = s->act_scale; g.sum8 = s->act_sum8;
+        g.K = H; g.units = I;
+        if (int st = gemv_launch(kSwiglu, g, stream)) return st;
+        ++n;
+        if (int st = quantize_fp16_to_q8_1(s->mlp, s->act_q8, s->act_scale, s->act_sum8, I, stream)) return st;
+        ++n;
+        GemvArgs dn = {};
+        dn.qweight[0] = static_cast<const uint32_t*>(L.down_weight);
+        dn.scales[0] = static_cast<const __half*>(L.down_scale);
+        dn.out[0] = s->h; dn.rows[0] = H; dn.residual = s->h;
+        dn.q8 = s->act_q8; dn.xscale = s->act_scale; dn.sum8 = s->act_sum8;
+        dn.K = I; dn.units = H;
+        if (int st = gemv_launch(kPlain, dn, stream)) return st;
+        ++n;
+    }
+    if (launches) *launches = n;
+    return 0;
+}
+
+}  // namespace
+
+extern "C" {
+
+int64_t w4a16_sweep_workspace_bytes(int hidden_size, int intermediate_size, int num_q_heads, int num_kv_heads,
+                                    int head_dim) {
+    if (hidden_size <= 0 || intermediate_size <= 0 || num_q_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0)
+        return W4A16_ERR_INVALID_ARG;
+    return static_cast<int64_t>(carve(hidden_size, intermediate_size, num_q_heads, num_kv_heads, head_dim).total);
+}
+
+int w4a16_sweep_create(const w4a16_sweep_desc* desc, w4a16_stream_t stream_, w4a16_sweep** out) {
+    if (!desc || !out || !desc->layers || !desc->workspace || desc->num_layers <= 0) return W4A16_ERR_INVALID_ARG;
+    const int H = desc->hidden_size, I = desc->intermediate_size;
+    const int qdim = desc->num_q_heads * desc->head_dim;
+    if (H <= 0 || I <= 0 || qdim <= 0 || desc->num_kv_heads <= 0) return W4A16_ERR_INVALID_ARG;
+    if (H % 256 || I % 256 || qdim % 256) return W4A16_ERR_SHAPE;
+    if (reinterpret_cast<uintptr_t>(desc->workspace) % kAlign) return W4A16_ERR_ALIGNMENT;
+    for (int l = 0; l < desc->num_layers; ++l) {
+        const w4a16_layer_weights& L = desc->layers[l];
+        const void* ptrs[] = {L.input_norm_gamma, L.q_weight, L.q_scale, L.k_weight, L.k_scale, L.v_weight, L.v_scale,
+                              L.o_weight, L.o_scale, L.post_norm_gamma, L.gate_up_weight, L.gate_up_scale,
+                              L.down_weight, L.down_scale};
+        for (const void* p : ptrs)
+            if (!p) return W4A16_ERR_INVALID_ARG;
+    }
+    if (int st = w4::ensure_device_ready(nullptr)) return st;
+
+    std::unique_ptr<w4a16_sweep> s(new (std::nothrow) w4a16_sweep);
+    if (!s) return static_cast<int>(cudaErrorMemoryAllocation);
+    s->desc = *desc;
+    s->layers.assign(desc->layers, desc->layers + desc->num_layers);
+    s->desc.layers = s->layers.data();
+    const Carve c = carve(H, I, desc->num_q_heads, desc->num_kv_heads, desc->head_dim);
+    uint8_t* base = static_cast<uint8_t*>(desc->workspace);
+    s->h = reinterpret_cast<__half*>(base + c.h);
+    s->q = reinterpret_cast<__half*>(base + c.q);
+    s->k = reinterpret_cast<__half*>(base + c.k);
+    s->v = reinterpret_cast<__half*>(base + c.v);
+    s->mlp = reinterpret_cast<__half*>(base + c.mlp);
+    s->act_q8 = reinterpret_cast<int8_t*>(base + c.q8);
+    s->act_scale = reinterpret_cast<float*>(base + c.scale);
+    s->act_sum8 = reinterpret_cast<int32_t*>(base + c.sum8);
+
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    cudaError_t e = cudaMemsetAsync(s->h, 0, H * sizeof(__half), stream);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    // one eager pass (sets kernel attributes, validates the launches), then capture
+    if (int st = issue_pass(s.get(), stream, &s->launches)) return st;
+    if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return static_cast<int>(e);
+    if ((e = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal)) != cudaSuccess)
+        return static_cast<int>(e);
+    const int st = issue_pass(s.get(), stream, nullptr);
+    e = cudaStreamEndCapture(stream, &s->graph);
+    if (st) {
+        if (s->graph) cudaGraphDestroy(s->graph);
+        return st;
+    }
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if ((e = cudaGraphInstantiate(&s->exec, s->graph, 0)) != cudaSuccess) {
+        cudaGraphDestroy(s->graph);
+        return static_cast<int>(e);
+    }
+    *out = s.release();
+    return 0;
+}
+
+int w4a16_sweep_destroy(w4a16_sweep* s) {
+    if (!s) return 0;
+    if (s->exec) cudaGraphExecDestroy(s->exec);
+    if (s->graph) cudaGraphDestroy(s->graph);
+    delete s;
+    return 0;
+}
+
+int w4a16_sweep_launches(const w4a16_sweep* s) { return s ? s->launches : W4A16_ERR_INVALID_ARG; }
+
+int w4a16_sweep_run_device(w4a16_sweep* s, const void* d_h_in, void* d_h_out, w4a16_stream_t stream_) {
+    if (!s || !d_h_in || !d_h_out) return W4A16_ERR_INVALID_ARG;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const size_t bytes = s->desc.hidden_size * sizeof(__half);
+    cudaError_t e = cudaMemcpyAsync(s->h, d_h_in, bytes, cudaMemcpyDeviceToDevice, stream);
+    if (e == cudaSuccess) e = cudaGraphLaunch(s->exec, stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(d_h_out, s->h, bytes, cudaMemcpyDeviceToDevice, stream);
+    return static_cast<int>(e);
+}
+
+int w4a16_sweep_run_host(w4a16_sweep* s, const void* h_h_in, void* h_h_out, w4a16_stream_t stream_) {
+    if (!s || !h_h_in || !h_h_out) return W4A16_ERR_INVALID_ARG;
+    cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+    const size_t bytes = s->desc.hidden_size * sizeof(__half);
+    cudaError_t e = cudaMemcpyAsync(s->h, h_h_in, bytes, cudaMemcpyHostToDevice, stream);
+    if (e == cudaSuccess) e = cudaGraphLaunch(s->exec, stream);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(h_h_out, s->h, bytes, cudaMemcpyDeviceToHost, stream);
+    return static_cast<int>(e);
+}
+
+void* w4a16_sweep_buffer(const w4a16_sweep* s, int which) {
+    if (!s) return nullptr;
+    switch (which) {
+        case 0: return s->h;
+        case 1: return s->q;
+        case 2: return s->k;
+        case 3: return s->v;
+        case 4: return s->mlp;
+        default: return nullptr;
+    }
+}
+
+}  // extern "C"

@@ -44,7 +44,7 @@ __global__ void __launch_bounds__(256) gemm_smallm_kernel(const SmallMArgs a) {
     const int K = a.g.K, M = a.g.M;
     const int sub = threadIdx.x >> 3, l = threadIdx.x & 7;
     const int unit = blockIdx.x * a.units_per_cta + sub;
-    const bool active = unit < a.units;
+    const bool active = sub < a.units_per_cta && unit < a.units;  // a rounded-up block has idle sub-warps
     const int words = K / 8, groups = K / kGroup;
 
     const uint32_t* wrow[R] = {};

@@ -13,15 +13,15 @@ from dataclasses import dataclass
 
 import torch
 
-from ._lib import QKVView, W4A16Error, check, load  # noqa: F401
+from ._lib import LayerWeights, QKVView, SweepDesc, W4A16Error, check, load  # noqa: F401
 
 __all__ = [
-    "QKVProjectionView", "W4A16Error", "init", "set_pdl",
+    "QKVProjectionView", "W4A16Error", "init", "set_pdl", "load",
     "launch_quantize_fp16_to_q8_1", "launch_rmsnorm_q8_1",
     "launch_gemv_w4a16", "launch_gemv_w4a8", "launch_gemv_qkv_w4a8",
     "launch_gemv_dual_gate_up_swiglu_w4a16", "launch_gemv_dual_gate_up_swiglu_w4a8",
     "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
-    "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots",
+    "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots", "DecodeSweep",
 ]
 
 # Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
@@ -145,3 +145,58 @@ def gemv_group_dots(qweight, input_q8, input_sum8, out_dots, out_features, in_fe
     check("w4a16_gemv_group_dots", load().w4a16_gemv_group_dots(
         _ptr(qweight), _ptr(input_q8), _ptr(input_sum8), _ptr(out_dots), out_features, in_features,
         _stream(stream)))
+
+
+class DecodeSweep:
+    """The W4 projections of one batch-1 decode pass as one CUDA graph (C ABI w4a16_sweep_*).
+
+    layers: list of dicts with keys input_norm, q, k, v, o, post_norm, gate_up, down; the norm
+    entries are fp16 gamma tensors, the others (qweight, scales) tensor pairs.  The object keeps
+    the tensors alive; the native sweep owns only its graph.
+    """
+
+    def __init__(self, layers, hidden=HIDDEN_SIZE, inter=INTERMEDIATE_SIZE, num_q_heads=NUM_Q_HEADS,
+                 num_kv_heads=NUM_KV_HEADS, head_dim=HEAD_DIM, stream=None):
+        lib = load()
+        self._layers = layers
+        self.hidden = hidden
+        nbytes = lib.w4a16_sweep_workspace_bytes(hidden, inter, num_q_heads, num_kv_heads, head_dim)
+        if nbytes < 0:
+            check("w4a16_sweep_workspace_bytes", int(nbytes))
+        self._ws = torch.zeros(nbytes + 256, dtype=torch.uint8, device="cuda")
+        ws_ptr = (self._ws.data_ptr() + 255) // 256 * 256
+        arr = (LayerWeights * len(layers))()
+        for i, L in enumerate(layers):
+            arr[i] = LayerWeights(
+                _ptr(L["input_norm"]), _ptr(L["q"][0]), _ptr(L["q"][1]), _ptr(L["k"][0]), _ptr(L["k"][1]),
+                _ptr(L["v"][0]), _ptr(L["v"][1]), _ptr(L["o"][0]), _ptr(L["o"][1]), _ptr(L["post_norm"]),
+                _ptr(L["gate_up"][0]), _ptr(L["gate_up"][1]), _ptr(L["down"][0]), _ptr(L["down"][1]))
+        desc = SweepDesc(len(layers), hidden, inter, num_q_heads, num_kv_heads, head_dim, arr, ws_ptr)
+        handle = ctypes.c_void_p()
+        check("w4a16_sweep_create", lib.w4a16_sweep_create(ctypes.byref(desc), _stream(stream), ctypes.byref(handle)))
+        self._h = handle
+        self.launches = lib.w4a16_sweep_launches(handle)
+
+    def run_device(self, h_in: torch.Tensor, h_out: torch.Tensor, stream=None):
+        check("w4a16_sweep_run_device", load().w4a16_sweep_run_device(self._h, _ptr(h_in), _ptr(h_out),
+                                                                      _stream(stream)))
+
+    def run_host(self, h_in: torch.Tensor, h_out: torch.Tensor, stream=None):
+        """h_in / h_out: pinned host fp16 tensors; asynchronous on the stream."""
+        assert not h_in.is_cuda and not h_out.is_cuda
+        check("w4a16_sweep_run_host", load().w4a16_sweep_run_host(self._h, h_in.data_ptr(), h_out.data_ptr(),
+                                                                  _stream(stream)))
+
+    def buffer_ptr(self, which: int) -> int:
+        return load().w4a16_sweep_buffer(self._h, which)
+
+    def close(self):
+        if self._h is not None:
+            load().w4a16_sweep_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
