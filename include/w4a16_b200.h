@@ -130,6 +130,24 @@ W4A16_API int w4a16_gemv_dual_gate_up_swiglu_w4a8(const uint32_t* gate_up_qweigh
                                                   void* output_mlp, int hidden_size,
                                                   int intermediate_size, w4a16_stream_t stream);
 
+/* ---- fused forms: RMSNorm + Q8_1 inside the GEMV -------------------------------------- */
+/*
+ * Each of these gives the same output bits as the pair of calls it replaces -- the reference's
+ * launch_rmsnorm_q8_1 (include/kernels.cuh:39-48, src/engine.cu:367-371, 414-418, 434-438) followed
+ * by the W4A8 GEMV -- with one launch less: every CTA normalises and quantises the fp16 vector
+ * for itself.  gamma == NULL skips the normalisation (plain quantisation, as w4a16_gemv_w4a16).
+ */
+W4A16_API int w4a16_gemv_rmsnorm_w4a16(const uint32_t* qweight, const void* scales, const void* input_x,
+                                       const void* gamma, const void* residual, void* output_y,
+                                       int out_features, int in_features, w4a16_stream_t stream);
+W4A16_API int w4a16_gemv_qkv_rmsnorm_w4a16(const w4a16_qkv_view* view, const void* input_x, const void* gamma,
+                                           w4a16_stream_t stream, int in_features, int num_q_heads,
+                                           int num_kv_heads, int head_dim);
+W4A16_API int w4a16_gemv_dual_gate_up_swiglu_rmsnorm_w4a16(const uint32_t* gate_up_qweight,
+                                                           const void* gate_up_scales, const void* input_x,
+                                                           const void* gamma, void* output_mlp, int hidden_size,
+                                                           int intermediate_size, w4a16_stream_t stream);
+
 /* ---- M-token contraction (small-M decode batches and prefill) ------------------- */
 
 /* reference include/kernels.cuh:119-130 launch_gemm_prefill_w4a16
@@ -182,7 +200,16 @@ typedef struct w4a16_sweep_desc {
     int num_layers, hidden_size, intermediate_size, num_q_heads, num_kv_heads, head_dim;
     const w4a16_layer_weights* layers;     /* host array [num_layers], copied */
     void* workspace;                       /* device, >= w4a16_sweep_workspace_bytes(), 256-byte aligned */
+    int flags;                             /* W4A16_SWEEP_* */
 } w4a16_sweep_desc;
+
+enum {
+    W4A16_SWEEP_SEPARATE = 0,    /* the reference's launch sequence: 8 launches per layer */
+    W4A16_SWEEP_FUSE_NORM = 1,   /* RMSNorm + Q8_1 inside the QKV and gate_up GEMVs */
+    W4A16_SWEEP_FUSE_QUANT_O = 2,    /* Q8_1 of the attention output inside the O GEMV */
+    W4A16_SWEEP_FUSE_QUANT_DOWN = 4, /* Q8_1 of the MLP activation inside the down GEMV */
+    W4A16_SWEEP_FUSE_ALL = 7     /* 4 launches per layer, same output bits */
+};
 
 typedef struct w4a16_sweep w4a16_sweep;
 

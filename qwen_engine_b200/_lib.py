@@ -29,7 +29,7 @@ class SweepDesc(ctypes.Structure):
     """Mirror of w4a16_sweep_desc."""
     _fields_ = [("num_layers", c_int), ("hidden_size", c_int), ("intermediate_size", c_int),
                 ("num_q_heads", c_int), ("num_kv_heads", c_int), ("head_dim", c_int),
-                ("layers", POINTER(LayerWeights)), ("workspace", c_void_p)]
+                ("layers", POINTER(LayerWeights)), ("workspace", c_void_p), ("flags", c_int)]
 
 
 # name -> argtypes; every function returns int except those in RESTYPES
@@ -47,6 +47,10 @@ SIGNATURES = {
     "w4a16_gemv_dual_gate_up_swiglu_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "w4a16_gemv_dual_gate_up_swiglu_w4a8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                             c_int, c_void_p],
+    "w4a16_gemv_rmsnorm_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "w4a16_gemv_qkv_rmsnorm_w4a16": [POINTER(QKVView), c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int],
+    "w4a16_gemv_dual_gate_up_swiglu_rmsnorm_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                     c_void_p],
     "w4a16_gemm_prefill_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                  c_int],
     "w4a16_gemm_prefill_qkv_w4a16": [POINTER(QKVView), c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,

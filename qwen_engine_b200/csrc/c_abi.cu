@@ -129,7 +129,7 @@ int w4a16_rmsnorm_q8_1(const void* input, const void* gamma, void* output_fp16_o
 
 static int gemv_plain(const uint32_t* qweight, const void* scales, const void* x_fp16, const int8_t* q8,
                       const float* xscale, const int32_t* sum8, const void* residual, void* y, int N, int K,
-                      w4a16_stream_t stream) {
+                      w4a16_stream_t stream, const void* gamma = nullptr) {
     if (!qweight || !scales || !y || N <= 0) return W4A16_ERR_INVALID_ARG;
     if (int st = check_k(K)) return st;
     if (misaligned(qweight, 4) || misaligned(scales, 2) || misaligned(y, 2) || misaligned(residual, 2) ||
@@ -137,9 +137,10 @@ static int gemv_plain(const uint32_t* qweight, const void* scales, const void* x
         return W4A16_ERR_ALIGNMENT;
     GemvArgs a = {};
     a.qweight[0] = qweight; a.scales[0] = H(scales); a.out[0] = H(y); a.rows[0] = N;
-    a.q8 = q8; a.xscale = xscale; a.sum8 = sum8; a.x_fp16 = H(x_fp16);
+    a.q8 = q8; a.xscale = xscale; a.sum8 = sum8; a.x_fp16 = H(x_fp16); a.gamma = H(gamma);
     a.residual = H(residual);
     a.K = K; a.units = N;
+    if (misaligned(gamma, 8)) return W4A16_ERR_ALIGNMENT;
     return gemv_launch(kPlain, a, S(stream));
 }
 
@@ -194,7 +195,7 @@ int w4a16_gemv_qkv_w4a8(const w4a16_qkv_view* view, const int8_t* input_q8, cons
 
 static int gemv_swiglu(const uint32_t* qweight, const void* scales, const void* x_fp16, const int8_t* q8,
                        const float* xscale, const int32_t* sum8, void* out, int hidden, int inter,
-                       w4a16_stream_t stream) {
+                       w4a16_stream_t stream, const void* gamma = nullptr) {
     if (!qweight || !scales || !out || inter <= 0) return W4A16_ERR_INVALID_ARG;
     if (int st = check_k(hidden)) return st;
     if (misaligned(qweight, 4) || misaligned(scales, 2) || misaligned(out, 2) || misaligned(x_fp16, 8) ||
@@ -202,8 +203,9 @@ static int gemv_swiglu(const uint32_t* qweight, const void* scales, const void* 
         return W4A16_ERR_ALIGNMENT;
     GemvArgs a = {};
     a.qweight[0] = qweight; a.scales[0] = H(scales); a.out[0] = H(out); a.rows[0] = 2 * inter;
-    a.q8 = q8; a.xscale = xscale; a.sum8 = sum8; a.x_fp16 = H(x_fp16);
+    a.q8 = q8; a.xscale = xscale; a.sum8 = sum8; a.x_fp16 = H(x_fp16); a.gamma = H(gamma);
     a.K = hidden; a.units = inter;
+    if (misaligned(gamma, 8)) return W4A16_ERR_ALIGNMENT;
     return gemv_launch(kSwiglu, a, S(stream));
 }
 
@@ -222,6 +224,36 @@ int w4a16_gemv_dual_gate_up_swiglu_w4a8(const uint32_t* gate_up_qweight, const v
     if (!input_q8 || !input_scale || !input_sum8) return W4A16_ERR_INVALID_ARG;
     return gemv_swiglu(gate_up_qweight, gate_up_scales, nullptr, input_q8, input_scale, input_sum8, output_mlp,
                        hidden_size, intermediate_size, stream);
+}
+
+int w4a16_gemv_rmsnorm_w4a16(const uint32_t* qweight, const void* scales, const void* input_x, const void* gamma,
+                             const void* residual, void* output_y, int out_features, int in_features,
+                             w4a16_stream_t stream) {
+    if (!input_x) return W4A16_ERR_INVALID_ARG;
+    return gemv_plain(qweight, scales, input_x, nullptr, nullptr, nullptr, residual, output_y, out_features,
+                      in_features, stream, gamma);
+}
+
+int w4a16_gemv_qkv_rmsnorm_w4a16(const w4a16_qkv_view* view, const void* input_x, const void* gamma,
+                                 w4a16_stream_t stream, int in_features, int num_q_heads, int num_kv_heads,
+                                 int head_dim) {
+    if (!input_x) return W4A16_ERR_INVALID_ARG;
+    if (int st = check_k(in_features)) return st;
+    if (misaligned(input_x, 8) || misaligned(gamma, 8)) return W4A16_ERR_ALIGNMENT;
+    GemvArgs a = {};
+    if (int st = fill_qkv(view, num_q_heads, num_kv_heads, head_dim, a.qweight, a.scales, a.out, a.rows)) return st;
+    a.x_fp16 = H(input_x); a.gamma = H(gamma);
+    a.K = in_features;
+    a.units = a.rows[0] + a.rows[1] + a.rows[2];
+    return gemv_launch(kQkv, a, S(stream));
+}
+
+int w4a16_gemv_dual_gate_up_swiglu_rmsnorm_w4a16(const uint32_t* gate_up_qweight, const void* gate_up_scales,
+                                                 const void* input_x, const void* gamma, void* output_mlp,
+                                                 int hidden_size, int intermediate_size, w4a16_stream_t stream) {
+    if (!input_x) return W4A16_ERR_INVALID_ARG;
+    return gemv_swiglu(gate_up_qweight, gate_up_scales, input_x, nullptr, nullptr, nullptr, output_mlp, hidden_size,
+                       intermediate_size, stream, gamma);
 }
 
 int w4a16_gemm_prefill_w4a16(const uint32_t* qweight, const void* scales, const void* input_x, const void* residual,

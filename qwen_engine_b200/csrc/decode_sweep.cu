@@ -58,52 +58,68 @@ int issue_pass(w4a16_sweep* s, cudaStream_t stream, int* launches) {
     const int H = d.hidden_size, I = d.intermediate_size;
     const int qdim = d.num_q_heads * d.head_dim, kvdim = d.num_kv_heads * d.head_dim;
     int n = 0;
+    const int flags = d.flags;
     for (const auto& L : s->layers) {
-        if (int st = rmsnorm_q8_1(s->h,
-                                  static_cast<const __half*>(L.input_norm_gamma), nullptr, s->act_q8, s->act_scale,
-                                  s->act_sum8, H, stream))
-            return st;
-        ++n;
         GemvArgs a = {};
         a.qweight[0] = static_cast<const uint32_t*>(L.q_weight); a.scales[0] = static_cast<const __half*>(L.q_scale);
         a.qweight[1] = static_cast<const uint32_t*>(L.k_weight); a.scales[1] = static_cast<const __half*>(L.k_scale);
         a.qweight[2] = static_cast<const uint32_t*>(L.v_weight); a.scales[2] = static_cast<const __half*>(L.v_scale);
         a.out[0] = s->q; a.out[1] = s->k; a.out[2] = s->v;
         a.rows[0] = qdim; a.rows[1] = kvdim; a.rows[2] = kvdim;
-        a.q8 = s->act_q8; a.xscale = s->act_scale; a.sum8 = s->act_sum8;
         a.K = H; a.units = qdim + 2 * kvdim;
+        if (flags & W4A16_SWEEP_FUSE_NORM) {
+            a.x_fp16 = s->h; a.gamma = static_cast<const __half*>(L.input_norm_gamma);
+        } else {
+            if (int st = rmsnorm_q8_1(s->h, static_cast<const __half*>(L.input_norm_gamma), nullptr, s->act_q8,
+                                      s->act_scale, s->act_sum8, H, stream))
+                return st;
+            ++n;
+            a.q8 = s->act_q8; a.xscale = s->act_scale; a.sum8 = s->act_sum8;
+        }
         if (int st = gemv_launch(kQkv, a, stream)) return st;
         ++n;
         // attention stand-in: the q projection plays the attention output
-        if (int st = quantize_fp16_to_q8_1(s->q, s->act_q8, s->act_scale, s->act_sum8, qdim, stream)) return st;
-        ++n;
         GemvArgs o = {};
         o.qweight[0] = static_cast<const uint32_t*>(L.o_weight); o.scales[0] = static_cast<const __half*>(L.o_scale);
         o.out[0] = s->h; o.rows[0] = H; o.residual = s->h;
-        o.q8 = s->act_q8; o.xscale = s->act_scale; o.sum8 = s->act_sum8;
         o.K = qdim; o.units = H;
+        if (flags & W4A16_SWEEP_FUSE_QUANT_O) {
+            o.x_fp16 = s->q;
+        } else {
+            if (int st = quantize_fp16_to_q8_1(s->q, s->act_q8, s->act_scale, s->act_sum8, qdim, stream)) return st;
+            ++n;
+            o.q8 = s->act_q8; o.xscale = s->act_scale; o.sum8 = s->act_sum8;
+        }
         if (int st = gemv_launch(kPlain, o, stream)) return st;
-        ++n;
-        if (int st = rmsnorm_q8_1(s->h, static_cast<const __half*>(L.post_norm_gamma), nullptr, s->act_q8,
-                                  s->act_scale, s->act_sum8, H, stream))
-            return st;
         ++n;
         GemvArgs g = {};
         g.qweight[0] = static_cast<const uint32_t*>(L.gate_up_weight);
         g.scales[0] = static_cast<const __half*>(L.gate_up_scale);
         g.out[0] = s->mlp; g.rows[0] = 2 * I;
-        g.q8 = s->act_q8; g.xscale = s->act_scale; g.sum8 = s->act_sum8;
         g.K = H; g.units = I;
+        if (flags & W4A16_SWEEP_FUSE_NORM) {
+            g.x_fp16 = s->h; g.gamma = static_cast<const __half*>(L.post_norm_gamma);
+        } else {
+            if (int st = rmsnorm_q8_1(s->h, static_cast<const __half*>(L.post_norm_gamma), nullptr, s->act_q8,
+                                      s->act_scale, s->act_sum8, H, stream))
+                return st;
+            ++n;
+            g.q8 = s->act_q8; g.xscale = s->act_scale; g.sum8 = s->act_sum8;
+        }
         if (int st = gemv_launch(kSwiglu, g, stream)) return st;
-        ++n;
-        if (int st = quantize_fp16_to_q8_1(s->mlp, s->act_q8, s->act_scale, s->act_sum8, I, stream)) return st;
         ++n;
         GemvArgs dn = {};
         dn.qweight[0] = static_cast<const uint32_t*>(L.down_weight);
         dn.scales[0] = static_cast<const __half*>(L.down_scale);
         dn.out[0] = s->h; dn.rows[0] = H; dn.residual = s->h;
-        dn.q8 = s->act_q8; dn.xscale = s->act_scale; dn.sum8 = s->act_sum8;
         dn.K = I; dn.units = H;
+        if (flags & W4A16_SWEEP_FUSE_QUANT_DOWN) {
+            dn.x_fp16 = s->mlp;
+        } else {
+            if (int st = quantize_fp16_to_q8_1(s->mlp, s->act_q8, s->act_scale, s->act_sum8, I, stream)) return st;
+            ++n;
+            dn.q8 = s->act_q8; dn.xscale = s->act_scale; dn.sum8 = s->act_sum8;
+        }
         if (int st = gemv_launch(kPlain, dn, stream)) return st;
         ++n;
     }
@@ -161,10 +177,16 @@ int w4a16_sweep_create(const w4a16_sweep_desc* desc, w4a16_stream_t stream_, w4a
     // one eager pass (sets kernel attributes, validates the launches), then capture
     if (int st = issue_pass(s.get(), stream, &s->launches)) return st;
     if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return static_cast<int>(e);
-    if ((e = cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal)) != cudaSuccess)
+    // capture on a stream of our own: the caller's may be the legacy default stream, which cannot capture
+    cudaStream_t cap = nullptr;
+    if ((e = cudaStreamCreateWithFlags(&cap, cudaStreamNonBlocking)) != cudaSuccess) return static_cast<int>(e);
+    if ((e = cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal)) != cudaSuccess) {
+        cudaStreamDestroy(cap);
         return static_cast<int>(e);
-    const int st = issue_pass(s.get(), stream, nullptr);
-    e = cudaStreamEndCapture(stream, &s->graph);
+    }
+    const int st = issue_pass(s.get(), cap, nullptr);
+    e = cudaStreamEndCapture(cap, &s->graph);
+    cudaStreamDestroy(cap);
     if (st) {
         if (s->graph) cudaGraphDestroy(s->graph);
         return st;

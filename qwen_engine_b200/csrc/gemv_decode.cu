@@ -28,8 +28,14 @@ namespace {
 
 constexpr int kMaxThreads = 256;
 constexpr int kMaxSubwarps = kMaxThreads / kSubwarp;  // 32
+constexpr float kRmsEps = 1e-6f;                      // reference include/config.cuh:20 RMS_NORM_EPS
 
-template <int MODE, int U, bool FP16_IN, bool ALIGNED16>
+// XIN: where the activation comes from.
+enum XIn { kXQ8 = 0,        // pre-quantised Q8_1 arrays in global memory
+           kXFp16 = 1,      // fp16 vector, quantised in the prologue
+           kXFp16Norm = 2 };  // fp16 vector, RMSNorm then quantised in the prologue
+
+template <int MODE, int U, int XIN, bool ALIGNED16>
 __global__ void __launch_bounds__(kMaxThreads) gemv_w4_kernel(const GemvArgs a) {
     constexpr int R = (MODE == kSwiglu) ? 2 : 1;  // weight rows per sub-warp
     extern __shared__ __align__(16) uint8_t smem[];
@@ -97,7 +103,8 @@ __global__ void __launch_bounds__(kMaxThreads) gemv_w4_kernel(const GemvArgs a) 
     pdl_release_dependents();
     pdl_wait_prior_grids();
 
-    if constexpr (FP16_IN) stage_x_from_fp16(a.x_fp16, K, s_q8, s_seed, s_scale);
+    if constexpr (XIN == kXFp16Norm) stage_x_from_fp16_rmsnorm(a.x_fp16, a.gamma, K, kRmsEps, s_q8, s_seed, s_scale);
+    else if constexpr (XIN == kXFp16) stage_x_from_fp16(a.x_fp16, K, s_q8, s_seed, s_scale);
     else stage_x_from_q8_1(a.q8, a.xscale, a.sum8, K, a.vec_ok != 0, s_q8, s_seed, s_scale);
     __syncthreads();
 
@@ -244,19 +251,20 @@ Plan make_plan(int units, int K, int sm_count) {
     return p;
 }
 
-template <int MODE, int U, bool FP16_IN>
+template <int MODE, int U, int XIN>
 cudaError_t launch_aligned(const GemvArgs& a, bool aligned16, dim3 grid, dim3 block, size_t smem,
                            cudaStream_t stream) {
     if (aligned16)
-        return launch_kernel(gemv_w4_kernel<MODE, U, FP16_IN, true>, grid, block, smem, stream, pdl_enabled(), a);
-    return launch_kernel(gemv_w4_kernel<MODE, U, FP16_IN, false>, grid, block, smem, stream, pdl_enabled(), a);
+        return launch_kernel(gemv_w4_kernel<MODE, U, XIN, true>, grid, block, smem, stream, pdl_enabled(), a);
+    return launch_kernel(gemv_w4_kernel<MODE, U, XIN, false>, grid, block, smem, stream, pdl_enabled(), a);
 }
 template <int MODE, int U>
 cudaError_t launch_input(const GemvArgs& a, bool aligned16, dim3 grid, dim3 block, size_t smem, cudaStream_t stream) {
-    if constexpr (MODE != kQkv) {
-        if (a.x_fp16 != nullptr) return launch_aligned<MODE, U, true>(a, aligned16, grid, block, smem, stream);
+    if (a.x_fp16 != nullptr) {
+        if (a.gamma != nullptr) return launch_aligned<MODE, U, kXFp16Norm>(a, aligned16, grid, block, smem, stream);
+        return launch_aligned<MODE, U, kXFp16>(a, aligned16, grid, block, smem, stream);
     }
-    return launch_aligned<MODE, U, false>(a, aligned16, grid, block, smem, stream);
+    return launch_aligned<MODE, U, kXQ8>(a, aligned16, grid, block, smem, stream);
 }
 template <int MODE>
 cudaError_t launch_mode(const GemvArgs& a, int U, bool aligned16, dim3 grid, dim3 block, size_t smem,
@@ -271,12 +279,12 @@ cudaError_t raise_smem(F* f) {
 }
 template <int MODE, int U>
 cudaError_t raise_smem_mode() {
-    cudaError_t e = raise_smem(gemv_w4_kernel<MODE, U, false, true>);
-    if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, false, false>);
-    if constexpr (MODE != kQkv) {
-        if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, true, true>);
-        if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, true, false>);
-    }
+    cudaError_t e = raise_smem(gemv_w4_kernel<MODE, U, kXQ8, true>);
+    if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, kXQ8, false>);
+    if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, kXFp16, true>);
+    if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, kXFp16, false>);
+    if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, kXFp16Norm, true>);
+    if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, kXFp16Norm, false>);
     return e;
 }
 

@@ -165,4 +165,53 @@ __device__ __forceinline__ void stage_x_from_fp16(const __half* __restrict__ g_x
     }
 }
 
+// RMSNorm fused in front of the quantiser, per CTA: y = fp16(fp16(x * inv_rms) * gamma) with
+// inv_rms = 1 / sqrt(mean(x^2) + eps) rounded to fp16 -- the arithmetic of the stand-alone
+// rmsnorm_q8_1 kernel (mean of squares in double), so both give the same Q8_1 arrays.
+// Needs blockDim.x to be a multiple of 32 and at most 256.
+__device__ __forceinline__ void stage_x_from_fp16_rmsnorm(const __half* __restrict__ g_x,
+                                                          const __half* __restrict__ g_gamma, int K, float eps,
+                                                          int8_t* s_q8, int32_t* s_seed, float* s_scale) {
+    __shared__ double s_red[8];
+    __shared__ float s_inv;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    double ss = 0.0;
+    for (int g = warp; g < K / kGroup; g += nwarps) {
+        float v[4];
+        load_half4_as_float(g_x + g * kGroup + lane * 4, v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) ss += static_cast<double>(v[j]) * static_cast<double>(v[j]);
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, m);
+    if (lane == 0) s_red[warp] = ss;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        double t = 0.0;
+        for (int w = 0; w < nwarps; ++w) t += s_red[w];
+        s_inv = static_cast<float>(1.0 / sqrt(t / static_cast<double>(K) + static_cast<double>(eps)));
+    }
+    __syncthreads();
+    const __half2 inv2 = __float2half2_rn(s_inv);
+    for (int g = warp; g < K / kGroup; g += nwarps) {
+        const uint2 xr = *reinterpret_cast<const uint2*>(g_x + g * kGroup + lane * 4);
+        const uint2 gr = *reinterpret_cast<const uint2*>(g_gamma + g * kGroup + lane * 4);
+        const __half2 y0 = __hmul2(__hmul2(*reinterpret_cast<const __half2*>(&xr.x), inv2),
+                                   *reinterpret_cast<const __half2*>(&gr.x));
+        const __half2 y1 = __hmul2(__hmul2(*reinterpret_cast<const __half2*>(&xr.y), inv2),
+                                   *reinterpret_cast<const __half2*>(&gr.y));
+        const float2 f0 = __half22float2(y0), f1 = __half22float2(y1);
+        const float v[4] = {f0.x, f0.y, f1.x, f1.y};
+        float d;
+        const uint32_t packed = quantize_group128_lane(v, &d);
+        reinterpret_cast<uint32_t*>(s_q8)[g * (kGroup / 4) + lane] = packed;
+        int32_t s = byte_sum(packed);
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+        s += __shfl_xor_sync(0xFFFFFFFFu, s, 4);
+        if ((lane & 7) == 0) s_seed[g * 4 + (lane >> 3)] = -8 * s;
+        if (lane == 0) s_scale[g] = d;
+    }
+}
+
 }  // namespace w4

@@ -58,6 +58,7 @@ struct GemvArgs {
     const float* xscale;
     const int32_t* sum8;
     const __half* x_fp16;
+    const __half* gamma;     // with x_fp16: RMSNorm gain applied before the quantiser (null = no norm)
     const __half* residual;  // PLAIN only, may be null, may alias out[0]
     int K;
     int units;  // outputs produced: rows (PLAIN, QKV total) or row pairs (SWIGLU)

@@ -22,6 +22,8 @@ __all__ = [
     "launch_gemv_dual_gate_up_swiglu_w4a16", "launch_gemv_dual_gate_up_swiglu_w4a8",
     "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
     "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots", "DecodeSweep",
+    "launch_gemv_rmsnorm_w4a16", "launch_gemv_qkv_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16",
+    "SWEEP_SEPARATE", "SWEEP_FUSE_ALL",
 ]
 
 # Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
@@ -117,6 +119,31 @@ def launch_gemv_dual_gate_up_swiglu_w4a8(gate_up_qweight, gate_up_scales, input_
         _ptr(output_mlp), hidden_size, intermediate_size, _stream(stream)))
 
 
+def launch_gemv_rmsnorm_w4a16(qweight, scales, input_x, gamma, residual, output_y, out_features, in_features,
+                              stream=None):
+    """launch_rmsnorm_q8_1 + launch_gemv_w4a8 in one launch (gamma None: quantise only)."""
+    check("w4a16_gemv_rmsnorm_w4a16", load().w4a16_gemv_rmsnorm_w4a16(
+        _ptr(qweight), _ptr(scales), _ptr(input_x), _ptr(gamma), _ptr(residual), _ptr(output_y), out_features,
+        in_features, _stream(stream)))
+
+
+def launch_gemv_qkv_rmsnorm_w4a16(view: QKVProjectionView, input_x, gamma, stream=None, in_features=HIDDEN_SIZE,
+                                  num_q_heads=NUM_Q_HEADS, num_kv_heads=NUM_KV_HEADS, head_dim=HEAD_DIM):
+    """launch_rmsnorm_q8_1 + launch_gemv_qkv_w4a8 in one launch."""
+    pod = view.pod()
+    check("w4a16_gemv_qkv_rmsnorm_w4a16", load().w4a16_gemv_qkv_rmsnorm_w4a16(
+        ctypes.byref(pod), _ptr(input_x), _ptr(gamma), _stream(stream), in_features, num_q_heads, num_kv_heads,
+        head_dim))
+
+
+def launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16(gate_up_qweight, gate_up_scales, input_x, gamma, output_mlp,
+                                                  hidden_size, intermediate_size, stream=None):
+    """launch_rmsnorm_q8_1 + launch_gemv_dual_gate_up_swiglu_w4a8 in one launch."""
+    check("w4a16_gemv_dual_gate_up_swiglu_rmsnorm_w4a16", load().w4a16_gemv_dual_gate_up_swiglu_rmsnorm_w4a16(
+        _ptr(gate_up_qweight), _ptr(gate_up_scales), _ptr(input_x), _ptr(gamma), _ptr(output_mlp), hidden_size,
+        intermediate_size, _stream(stream)))
+
+
 def launch_gemm_prefill_w4a16(qweight, scales, input_x, residual, output_y, M, N, K, stream=None, sm_count=0):
     check("w4a16_gemm_prefill_w4a16", load().w4a16_gemm_prefill_w4a16(
         _ptr(qweight), _ptr(scales), _ptr(input_x), _ptr(residual), _ptr(output_y), M, N, K, _stream(stream),
@@ -147,6 +174,9 @@ def gemv_group_dots(qweight, input_q8, input_sum8, out_dots, out_features, in_fe
         _stream(stream)))
 
 
+SWEEP_SEPARATE, SWEEP_FUSE_NORM, SWEEP_FUSE_QUANT_O, SWEEP_FUSE_QUANT_DOWN, SWEEP_FUSE_ALL = 0, 1, 2, 4, 7
+
+
 class DecodeSweep:
     """The W4 projections of one batch-1 decode pass as one CUDA graph (C ABI w4a16_sweep_*).
 
@@ -156,7 +186,7 @@ class DecodeSweep:
     """
 
     def __init__(self, layers, hidden=HIDDEN_SIZE, inter=INTERMEDIATE_SIZE, num_q_heads=NUM_Q_HEADS,
-                 num_kv_heads=NUM_KV_HEADS, head_dim=HEAD_DIM, stream=None):
+                 num_kv_heads=NUM_KV_HEADS, head_dim=HEAD_DIM, stream=None, flags=SWEEP_FUSE_ALL):
         lib = load()
         self._layers = layers
         self.hidden = hidden
@@ -171,7 +201,7 @@ class DecodeSweep:
                 _ptr(L["input_norm"]), _ptr(L["q"][0]), _ptr(L["q"][1]), _ptr(L["k"][0]), _ptr(L["k"][1]),
                 _ptr(L["v"][0]), _ptr(L["v"][1]), _ptr(L["o"][0]), _ptr(L["o"][1]), _ptr(L["post_norm"]),
                 _ptr(L["gate_up"][0]), _ptr(L["gate_up"][1]), _ptr(L["down"][0]), _ptr(L["down"][1]))
-        desc = SweepDesc(len(layers), hidden, inter, num_q_heads, num_kv_heads, head_dim, arr, ws_ptr)
+        desc = SweepDesc(len(layers), hidden, inter, num_q_heads, num_kv_heads, head_dim, arr, ws_ptr, flags)
         handle = ctypes.c_void_p()
         check("w4a16_sweep_create", lib.w4a16_sweep_create(ctypes.byref(desc), _stream(stream), ctypes.byref(handle)))
         self._h = handle

@@ -57,13 +57,14 @@ I_, H_ = 40, 512
 sw, ss = synth.packed_weights(24, "ref.sw", 2 * I_, H_), synth.scales(24, "ref.sw", 2 * I_, H_)
 data.update(swiglu_w=sw, swiglu_s=ss)
 
-nq, nkv, hd, Kq = 2, 1, 16, 256
+nq, nkv, hd, Kq = 2, 1, 64, 256   # q/k/v widths are multiples of the reference's 64-wide GEMM tile
 qkv_w = [synth.packed_weights(25, f"ref.qkv{i}", n, Kq) for i, n in enumerate((nq * hd, nkv * hd, nkv * hd))]
 qkv_s = [synth.scales(25, f"ref.qkv{i}", n, Kq) for i, n in enumerate((nq * hd, nkv * hd, nkv * hd))]
 qkv_x = synth.activations(25, "ref.qkv", Kq)
 for i in range(3):
     data[f"qkv_w{i}"], data[f"qkv_s{i}"] = qkv_w[i], qkv_s[i]
 data["qkv_x"] = qkv_x
+data["qkv_dims"] = np.array([nq, nkv, hd, Kq], dtype=np.int32)
 
 M = 8
 px = synth.activations(26, "ref.p", M, K)

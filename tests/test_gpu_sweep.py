@@ -1,0 +1,153 @@
+"""The decode projection sweep (C ABI w4a16_sweep_*) at the benchmark's full size against the CPU
+oracle, and its size-independent properties."""
+import numpy as np
+import pytest
+
+import oracle
+from tests import util
+
+pytestmark = pytest.mark.gpu
+torch = pytest.importorskip("torch")
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import qwen_engine_b200 as pkg
+    pkg.init()
+    return pkg
+
+
+@pytest.fixture(scope="module")
+def model():
+    import bench
+    layers_np = bench.make_layers_np(28)
+    return layers_np, bench.upload_layers(layers_np)
+
+
+def test_full_size_sweep_matches_oracle_layer_by_layer(ops, model):
+    """28 layers, benchmark shapes.  Each layer is run alone on the device from the oracle's hidden
+    state entering it (so a 1-ulp difference cannot snowball through later quantisers) and compared
+    with the oracle's hidden state leaving it."""
+    from qwen_engine_b200 import synth
+    layers_np, layers_dev = model
+    h0 = synth.activations(7, "h0", synth.HIDDEN)
+    _, trace = oracle.decode_sweep(layers_np, h0, collect=True)
+    h_in = torch.empty(synth.HIDDEN, dtype=torch.float16, device="cuda")
+    h_out = torch.empty_like(h_in)
+    worst = 0.0
+    for l, t in enumerate(trace):
+        one = ops.DecodeSweep(layers_dev[l:l + 1])
+        h_in.copy_(util.to_dev(t["h_in"]))
+        one.run_device(h_in, h_out)
+        torch.cuda.synchronize()
+        got = util.to_np(h_out)
+        # intermediate buffers of the layer: q projection and MLP activation
+        rep = util.error_report(got, t["h_out"].astype(np.float64))
+        assert rep["finite"]
+        # the oracle value is itself fp16-rounded: agreement within 2 fp16 steps of the final add,
+        # and the path's stated tolerance
+        assert rep["max_rel"] <= 1e-2, (l, rep)
+        assert rep["median_ulp"] <= 2.0, (l, rep)
+        worst = max(worst, rep["max_ulp"])
+        one.close()
+    assert worst <= 8.0
+
+
+def test_sweep_is_deterministic_and_host_path_equals_device_path(ops, model):
+    from qwen_engine_b200 import synth
+    _, layers_dev = model
+    sweep = ops.DecodeSweep(layers_dev, flags=ops.SWEEP_SEPARATE)
+    assert sweep.launches == 28 * 8
+    h0 = synth.activations(7, "h0", synth.HIDDEN)
+    h_in = util.to_dev(h0)
+    a, b = torch.empty_like(h_in), torch.empty_like(h_in)
+    sweep.run_device(h_in, a)
+    sweep.run_device(h_in, b)
+    pin_in, pin_out = torch.from_numpy(h0).pin_memory(), torch.empty(synth.HIDDEN, dtype=torch.float16).pin_memory()
+    sweep.run_host(pin_in, pin_out)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    assert np.array_equal(util.to_np(a).view(np.uint16), pin_out.numpy().view(np.uint16))
+    assert np.isfinite(pin_out.numpy().astype(np.float32)).all()
+    sweep.close()
+
+
+def test_row_split_consistency_at_full_size(ops):
+    """Rows are independent: the lm_head GEMV computed as 8 row slabs equals the one-launch result
+    bit for bit (the property the multi-GPU split relies on)."""
+    from qwen_engine_b200 import synth
+    N, K = synth.SHAPES["lm_head"]
+    qw, sc = synth.packed_weights(2, "lm", N, K), synth.scales(2, "lm", N, K)
+    x = util.to_dev(synth.activations(2, "lmx", K))
+    q8 = torch.empty(K, dtype=torch.int8, device="cuda")
+    xs = torch.empty(K // 128, dtype=torch.float32, device="cuda")
+    s8 = torch.empty(K // 8, dtype=torch.int32, device="cuda")
+    ops.launch_quantize_fp16_to_q8_1(x, q8, xs, s8, K)
+    d_qw, d_sc = util.to_dev(qw), util.to_dev(sc)
+    full = torch.empty(N, dtype=torch.float16, device="cuda")
+    ops.launch_gemv_w4a8(d_qw, d_sc, q8, xs, s8, None, full, N, K)
+    parts = torch.empty(N, dtype=torch.float16, device="cuda")
+    rows = N // 8
+    for r in range(8):
+        w_slab = d_qw[r * rows:(r + 1) * rows].contiguous()
+        s_slab = d_sc[r * rows:(r + 1) * rows].contiguous()
+        ops.launch_gemv_w4a8(w_slab, s_slab, q8, xs, s8, None, parts[r * rows:(r + 1) * rows], rows, K)
+    torch.cuda.synchronize()
+    assert torch.equal(full, parts)
+
+
+@pytest.mark.parametrize("flags", [1, 2, 4, 7])
+def test_fused_sweeps_give_the_bits_of_the_separate_launch_sequence(ops, model, flags):
+    """Folding the RMSNorm / Q8_1 launches into the GEMV prologues must not change a single bit."""
+    from qwen_engine_b200 import synth
+    _, layers_dev = model
+    h_in = util.to_dev(synth.activations(7, "h0", synth.HIDDEN))
+    ref_sweep = ops.DecodeSweep(layers_dev, flags=ops.SWEEP_SEPARATE)
+    fused = ops.DecodeSweep(layers_dev, flags=flags)
+    assert fused.launches == 28 * (8 - bin(flags).count("1") - (1 if flags & 1 else 0))
+    a, b = torch.empty_like(h_in), torch.empty_like(h_in)
+    ref_sweep.run_device(h_in, a)
+    fused.run_device(h_in, b)
+    torch.cuda.synchronize()
+    assert torch.equal(a, b)
+    ref_sweep.close()
+    fused.close()
+
+
+def test_fused_entry_points_equal_two_call_sequences(ops):
+    from qwen_engine_b200 import synth
+    H, I = 1536, 8960
+    x = util.to_dev((synth.activations(31, "fx", H).astype(np.float32) * 3).astype(np.float16))
+    gamma = util.to_dev((1 + 0.1 * synth.activations(32, "fg", H).astype(np.float32)).astype(np.float16))
+    q8 = torch.empty(H, dtype=torch.int8, device="cuda")
+    xs = torch.empty(H // 128, dtype=torch.float32, device="cuda")
+    s8 = torch.empty(H // 8, dtype=torch.int32, device="cuda")
+    ops.launch_rmsnorm_q8_1(x, gamma, None, q8, xs, s8, None, H)
+    # gate_up + SwiGLU
+    gw, gs = util.to_dev(synth.packed_weights(33, "gu", 2 * I, H)), util.to_dev(synth.scales(33, "gu", 2 * I, H))
+    y1, y2 = torch.empty(I, dtype=torch.float16, device="cuda"), torch.empty(I, dtype=torch.float16, device="cuda")
+    ops.launch_gemv_dual_gate_up_swiglu_w4a8(gw, gs, q8, xs, s8, y1, H, I)
+    ops.launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16(gw, gs, x, gamma, y2, H, I)
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y2)
+    # plain GEMV with residual (lm_head / O style)
+    N = 3000
+    w, s = util.to_dev(synth.packed_weights(34, "p", N, H)), util.to_dev(synth.scales(34, "p", N, H))
+    r = util.to_dev(synth.activations(35, "r", N))
+    z1, z2 = torch.empty(N, dtype=torch.float16, device="cuda"), torch.empty(N, dtype=torch.float16, device="cuda")
+    ops.launch_gemv_w4a8(w, s, q8, xs, s8, r, z1, N, H)
+    ops.launch_gemv_rmsnorm_w4a16(w, s, x, gamma, r, z2, N, H)
+    torch.cuda.synchronize()
+    assert torch.equal(z1, z2)
+    # fused QKV
+    dims = [1536, 256, 256]
+    ws = [(util.to_dev(synth.packed_weights(36, f"t{i}", n, H)), util.to_dev(synth.scales(36, f"t{i}", n, H)))
+          for i, n in enumerate(dims)]
+    oa = [torch.empty(n, dtype=torch.float16, device="cuda") for n in dims]
+    ob = [torch.empty(n, dtype=torch.float16, device="cuda") for n in dims]
+    mk = lambda o: ops.QKVProjectionView(ws[0][0], ws[0][1], o[0], ws[1][0], ws[1][1], o[1], ws[2][0], ws[2][1], o[2])
+    ops.launch_gemv_qkv_w4a8(mk(oa), q8, xs, s8)
+    ops.launch_gemv_qkv_rmsnorm_w4a16(mk(ob), x, gamma)
+    torch.cuda.synchronize()
+    for ta, tb in zip(oa, ob):
+        assert torch.equal(ta, tb)

@@ -42,25 +42,31 @@ def fp16_ulp(ref: np.ndarray) -> np.ndarray:
     return 2.0 ** (e - 10)
 
 
-def error_report(y: np.ndarray, ref64: np.ndarray) -> dict:
-    """y: fp16 result, ref64: exact value in double.
+def error_report(y: np.ndarray, ref64: np.ndarray, magnitude: np.ndarray | None = None) -> dict:
+    """y: fp16 result, ref64: exact value in double.  magnitude (optional): size of the operands the
+    result was rounded at -- for an epilogue that rounds the accumulator to fp16 BEFORE adding the
+    residual (the prefill GEMM), errors are judged at max(|ref|, |accumulator|), not at a sum that
+    may have cancelled.
     rel: |y - ref| / max(|ref|, 1e-2 * rms(ref))  -- relative error with a floor, so outputs that
     cancel to ~0 are judged against the vector's scale;  ulp: error in fp16 ulps at ref."""
     y64 = np.asarray(y, dtype=np.float64).reshape(-1)
     r = np.asarray(ref64, dtype=np.float64).reshape(-1)
     rms = float(np.sqrt(np.mean(r * r))) or 1.0
     err = np.abs(y64 - r)
-    rel = err / np.maximum(np.abs(r), 1e-2 * rms)
+    size = np.abs(r)
+    if magnitude is not None:
+        size = np.maximum(size, np.abs(np.asarray(magnitude, dtype=np.float64).reshape(-1)))
+    rel = err / np.maximum(size, 1e-2 * rms)
     # ulp measured at max(|ref|, 1e-3 rms): fp32 accumulation noise is absolute, so outputs that
     # cancel to nearly zero are not held to the spacing of fp16 at their own tiny magnitude
-    ulp = err / fp16_ulp(np.maximum(np.abs(r), 1e-3 * rms))
+    ulp = err / fp16_ulp(np.maximum(size, 1e-3 * rms))
     return {"max_rel": float(rel.max()), "median_ulp": float(np.median(ulp)), "max_ulp": float(ulp.max()),
             "max_abs": float(err.max()), "finite": bool(np.isfinite(y64).all())}
 
 
-def assert_fp16_close(y, ref64, max_rel=1e-2, median_ulp=2.0, what=""):
+def assert_fp16_close(y, ref64, max_rel=1e-2, median_ulp=2.0, what="", magnitude=None):
     """The stated tolerance of the path: max relative error <= 1e-2, median <= 2 fp16 ulp."""
-    rep = error_report(y, ref64)
+    rep = error_report(y, ref64, magnitude)
     assert rep["finite"], f"{what}: non-finite output"
     assert rep["max_rel"] <= max_rel, f"{what}: {rep}"
     assert rep["median_ulp"] <= median_ulp, f"{what}: {rep}"
