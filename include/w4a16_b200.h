@@ -130,6 +130,26 @@ W4A16_API int w4a16_gemv_dual_gate_up_swiglu_w4a8(const uint32_t* gate_up_qweigh
                                                   void* output_mlp, int hidden_size,
                                                   int intermediate_size, w4a16_stream_t stream);
 
+/*
+ * fp16-input GEMV that brings its own scratch.  No counterpart in the reference.
+ * Same arguments and same output bits as w4a16_gemv_w4a16, but the activation is quantised
+ * to Q8_1 once, into a fixed array inside the library's device image (50 176 bytes per GPU,
+ * held until the process exits), and the GEMV reads it from there.  It is meant for callers
+ * that have no spare device buffer to pass and are not allowed to allocate one -- an engine
+ * whose memory all went into one start-up arena, a plugin host that bans allocation calls on
+ * the inference path.  The function itself allocates nothing, on the host or the device.
+ *   - in_features above 32768 is refused with W4A16_ERR_TOO_LARGE (nothing is launched).
+ *   - The first call on each device looks up the array's device address; make that first
+ *     call before any stream capture.
+ *   - All calls share the one array: two calls that may run at the same time on the GPU
+ *     (different streams, no ordering between them) race on it.  Calls on one stream, or
+ *     otherwise ordered, are safe; leftovers of an earlier call are never read.
+ */
+W4A16_API int w4a16_gemv_w4a16_static_scratch(const uint32_t* qweight, const void* scales,
+                                              const void* input_x, const void* residual,
+                                              void* output_y, int out_features, int in_features,
+                                              w4a16_stream_t stream);
+
 /* ---- fused forms: RMSNorm + Q8_1 inside the GEMV -------------------------------------- */
 /*
  * Each of these gives the same output bits as the pair of calls it replaces -- the reference's

@@ -23,7 +23,7 @@ __all__ = [
     "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
     "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots", "DecodeSweep",
     "launch_gemv_rmsnorm_w4a16", "launch_gemv_qkv_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16",
-    "SWEEP_SEPARATE", "SWEEP_FUSE_ALL",
+    "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "gemv_w4a16_static_scratch",
 ]
 
 # Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
@@ -85,6 +85,16 @@ def launch_rmsnorm_q8_1(input, gamma, output_fp16_opt, out_q8, out_scale, out_su
 
 def launch_gemv_w4a16(qweight, scales, input_x, residual, output_y, out_features, in_features, stream=None):
     check("w4a16_gemv_w4a16", load().w4a16_gemv_w4a16(
+        _ptr(qweight), _ptr(scales), _ptr(input_x), _ptr(residual), _ptr(output_y), out_features, in_features,
+        _stream(stream)))
+
+
+def gemv_w4a16_static_scratch(qweight, scales, input_x, residual, output_y, out_features, in_features,
+                              stream=None):
+    """launch_gemv_w4a16 for callers that can neither pass nor allocate scratch: the Q8_1 form of
+    the activation goes into a fixed array inside the library (in_features <= 32768; calls that
+    overlap on the GPU race on that array)."""
+    check("w4a16_gemv_w4a16_static_scratch", load().w4a16_gemv_w4a16_static_scratch(
         _ptr(qweight), _ptr(scales), _ptr(input_x), _ptr(residual), _ptr(output_y), out_features, in_features,
         _stream(stream)))
 
