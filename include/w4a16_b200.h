@@ -270,6 +270,13 @@ W4A16_API int w4a16_gemv_group_dots(const uint32_t* qweight, const int8_t* input
                                     const int32_t* input_sum8, int32_t* out_dots, int out_features,
                                     int in_features, w4a16_stream_t stream);
 
+/*
+ * Debug counters kept on the current device.  which = 0: number of bounded waits of the
+ * tensor-core kernel that ran out (each one means a launch gave up and its output is invalid;
+ * 0 in normal operation).  Synchronises the device.
+ */
+W4A16_API int w4a16_debug_counter(int which, unsigned int* out);
+
 #ifdef __cplusplus
 }
 #endif

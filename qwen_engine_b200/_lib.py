@@ -59,6 +59,7 @@ SIGNATURES = {
     "w4a16_gemm_prefill_dual_gate_up_swiglu_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                                      c_int, c_int],
     "w4a16_gemv_group_dots": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "w4a16_debug_counter": [c_int, POINTER(ctypes.c_uint)],
     "w4a16_sweep_workspace_bytes": [c_int, c_int, c_int, c_int, c_int],
     "w4a16_sweep_create": [POINTER(SweepDesc), c_void_p, POINTER(c_void_p)],
     "w4a16_sweep_destroy": [c_void_p],

@@ -309,4 +309,10 @@ int w4a16_gemv_group_dots(const uint32_t* qweight, const int8_t* input_q8, const
     return gemv_group_dots(qweight, input_q8, input_sum8, out_dots, out_features, in_features, S(stream));
 }
 
+int w4a16_debug_counter(int which, unsigned int* out) {
+    if (!out || which != 0) return W4A16_ERR_INVALID_ARG;
+    if (int st = ensure_device_ready(nullptr)) return st;
+    return gemm_tc_timeouts(out);
+}
+
 }  // extern "C"

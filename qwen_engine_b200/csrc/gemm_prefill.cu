@@ -19,11 +19,16 @@ cudaError_t launch_smallm(const SmallMArgs& a, int mt, dim3 grid, dim3 block, cu
 
 }  // namespace
 
-int gemm_set_attributes() { return 0; }
+int gemm_set_attributes() { return gemm_tc_set_attributes(); }
 
 int gemm_launch(GemmArgs g, cudaStream_t stream) {
     const DeviceInfo* dev = nullptr;
     if (int st = ensure_device_ready(&dev)) return st;
+
+    // Token counts from one tensor-core tile upwards go to the tcgen05 kernel; below that (and for
+    // pointers or shapes TMA cannot address) the CUDA-core weight-streaming kernel runs.
+    static const int tc_min_m = env_int("W4A16_TC_MIN_M", 16);
+    if (g.M >= tc_min_m && gemm_tc_supported(g)) return gemm_tc_launch(g, dev->sm_count, stream);
 
     SmallMArgs a;
     a.g = g;

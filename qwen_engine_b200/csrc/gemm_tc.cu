@@ -1,0 +1,465 @@
+// M-token W4A16 contraction on the 5th-generation tensor cores (tcgen05 / TMEM), sm_100a.
+//
+// Replaces the reference's wmma prefill GEMMs (src/kernels/gemm_prefill.cu:319-610).
+// Arithmetic is the reference's: weights dequantised to fp16 as (q - 8) * scale with one fp16
+// rounding (include/quant_primitives.cuh:92-115), fp16 x fp16 products exact, fp32 accumulation,
+// epilogue fp16(acc) [+ fp16 residual add] / SwiGLU on the fp32 accumulators
+// (gemm_prefill.cu:257-275, 572-605).
+//
+// Formulation: D[n][m] = sum_k W[n][k] * X[m][k] with the WEIGHT rows on the 128-wide M side of
+// the MMA and the tokens on its N side (16..256), so a decode batch of 16 tokens fills the
+// tensor core as well as a prefill chunk does, and weights stream through each CTA exactly once.
+//
+//   warp 6      : TMA producer of raw packed weights, 128 rows x 128 B (= 256 k) per stage,
+//                 128B-swizzled so that row-per-thread reads are bank-conflict free
+//   warps 0-3   : dequantise raw nibbles -> fp16 A tile [128 x 64] in the K-major 128B-swizzled
+//                 layout the UMMA shared-memory descriptor expects; later the epilogue
+//   warp 5      : TMA producer of the token tile B [T x 64] fp16 (128B swizzle)
+//   warp 4      : allocates TMEM, issues tcgen05.mma (one thread), commits to mbarriers
+//   epilogue    : tcgen05.ld 32x32b (thread = weight row, registers = tokens), fp16 stores
+//
+// No cluster, no multicast.  Every mbarrier wait is bounded: on expiry the kernel raises an
+// abort flag, all roles leave their loops, TMEM is freed and the kernel returns; the host can
+// read the count of such events with w4a16_debug_counter(0).
+#include <cuda.h>
+
+#include <algorithm>
+#include <mutex>
+
+#include "gemm_smallm.cuh"
+#include "w4a16_common.cuh"
+#include "w4a16_internal.hpp"
+
+namespace w4 {
+
+__device__ unsigned int g_tc_wait_timeouts = 0;
+
+namespace {
+
+constexpr int kTileRows = 128;          // weight rows per CTA (UMMA M)
+constexpr int kBK = 64;                 // fp16 elements per k-block: one 128-byte swizzle row
+constexpr int kRawStages = 3;
+constexpr int kRawBytes = kTileRows * 128;   // 128 rows x 128 bytes of packed nibbles = 256 k
+constexpr int kABytes = kTileRows * 128;     // 128 rows x 64 fp16
+constexpr int kDequantThreads = 128;
+constexpr int kThreads = 224;           // 7 warps
+constexpr int kMaxStages = 8;
+constexpr unsigned kWaitLimit = 1u << 22;
+
+struct TcArgs {
+    CUtensorMap tmap_w[3];
+    CUtensorMap tmap_x;
+    const __half* scales[3];
+    __half* out[3];
+    int rows[3];
+    int out_ld[3];
+    int tiles[3];            // 128-row tiles per weight tensor
+    const __half* residual;
+    int M, K, T, stages, tmem_cols;
+};
+
+// ---- PTX wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait.  Returns false if the barrier did not flip within the limit or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (unsigned it = 0; it < kWaitLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (it > 2048) __nanosleep(64);
+    }
+    *abort_flag = 1;
+    atomicAdd(&g_tc_wait_timeouts, 1u);
+    return false;
+}
+__device__ __forceinline__ void fence_barrier_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, fp16 inputs, fp32 accumulate.
+__device__ __forceinline__ void tc_mma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 B apart, 8-row groups
+// 1024 B apart (stride byte offset), descriptor version 1 (sm_100).  `addr` may be advanced by
+// 32 B per 16-element K slice inside the 128-byte swizzle row.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);   // start address, 16-byte units
+    d |= static_cast<uint64_t>(1) << 16;                  // leading byte offset (unused with swizzle)
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;          // stride byte offset
+    d |= static_cast<uint64_t>(1) << 46;                  // version
+    d |= static_cast<uint64_t>(2) << 61;                  // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D fp32, A/B fp16, both K-major, M = 128, N = n.
+__device__ __forceinline__ uint32_t make_idesc(int n) {
+    return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kTileRows >> 4) << 24);
+}
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1) gemm_w4a16_tc_kernel(const __grid_constant__ TcArgs a) {
+    extern __shared__ uint8_t smem_raw_base[];
+    // 1024-byte alignment for the swizzled tiles
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_base) + 1023) & ~uintptr_t(1023));
+    const int T = a.T, S = a.stages, K = a.K;
+    const int G = K / kGroup;
+    const int b_bytes = T * 128;
+    uint8_t* s_raw = smem;                                  // kRawStages x 16 KB
+    uint8_t* s_a = s_raw + kRawStages * kRawBytes;          // S x 16 KB
+    uint8_t* s_b = s_a + S * kABytes;                       // S x T*128
+    __half* s_scale = reinterpret_cast<__half*>(s_b + S * b_bytes);   // [G][128]
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_scale) + ((G * kTileRows * 2 + 15) & ~15));
+    // barrier slots: raw_full[3] raw_empty[3] a_full[S] b_full[S] ab_empty[S] accum_full
+    const uint32_t bar0 = smem_u32(s_bar);
+    auto raw_full = [&](int i) { return bar0 + 8u * i; };
+    auto raw_empty = [&](int i) { return bar0 + 8u * (kRawStages + i); };
+    auto a_full = [&](int i) { return bar0 + 8u * (2 * kRawStages + i); };
+    auto b_full = [&](int i) { return bar0 + 8u * (2 * kRawStages + kMaxStages + i); };
+    auto ab_empty = [&](int i) { return bar0 + 8u * (2 * kRawStages + 2 * kMaxStages + i); };
+    const uint32_t accum_full = bar0 + 8u * (2 * kRawStages + 3 * kMaxStages);
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + (2 * kRawStages + 3 * kMaxStages + 1));
+    volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+    // which weight tensor / which rows
+    int t = 0, tile = blockIdx.x;
+    if constexpr (MODE == kQkv) {
+        if (tile >= a.tiles[0]) { tile -= a.tiles[0]; t = 1; }
+        if (t == 1 && tile >= a.tiles[1]) { tile -= a.tiles[1]; t = 2; }
+    }
+    const int n0 = tile * kTileRows;         // first weight row of this CTA inside tensor t
+    const int m0 = blockIdx.y * T;           // first token
+    const int rows_t = a.rows[t];
+    const int num_kb = K / kBK, num_sb = K / 256;
+
+    if (tid == 0) {
+        for (int i = 0; i < kRawStages; ++i) { mbar_init(raw_full(i), 1); mbar_init(raw_empty(i), 4); }
+        for (int i = 0; i < S; ++i) { mbar_init(a_full(i), 4); mbar_init(b_full(i), 1); mbar_init(ab_empty(i), 1); }
+        mbar_init(accum_full, 1);
+        *s_abort = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&a.tmap_x);
+        tma_prefetch_desc(&a.tmap_w[t]);
+    }
+    if (warp == 4) {
+        tmem_alloc(smem_u32(s_tmem), static_cast<uint32_t>(a.tmem_cols));
+        tmem_relinquish();
+    }
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+
+    if (warp < 4) {
+        // ---------------- dequantise: thread = weight row ----------------
+        const int r = tid;
+        // scales of the 128 rows, transposed to [group][row]
+        {
+            const __half* sc = a.scales[t];
+            for (int idx = tid; idx < kTileRows * G; idx += kDequantThreads) {
+                const int rr = idx / G, g = idx - rr * G;
+                const int row = n0 + rr;
+                s_scale[g * kTileRows + rr] = row < rows_t ? sc[static_cast<size_t>(row) * G + g] : __float2half(0.0f);
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        const int sw = r & 7;
+        bool ok = true;
+        for (int sb = 0; sb < num_sb && ok; ++sb) {
+            const int rs = sb % kRawStages;
+            ok = mbar_wait(raw_full(rs), (sb / kRawStages) & 1, s_abort);
+            if (!ok) break;
+            const uint8_t* raw_row = s_raw + rs * kRawBytes + r * 128;
+            const __half2 sc0 = __half2half2(s_scale[(2 * sb) * kTileRows + r]);
+            const __half2 sc1 = __half2half2(s_scale[(2 * sb + 1) * kTileRows + r]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int kb = sb * 4 + j;
+                const int s = kb % S;
+                ok = mbar_wait(ab_empty(s), ((kb / S) & 1) ^ 1, s_abort);
+                if (!ok) break;
+                const uint4 w0 = *reinterpret_cast<const uint4*>(raw_row + (((2 * j) ^ sw) << 4));
+                const uint4 w1 = *reinterpret_cast<const uint4*>(raw_row + (((2 * j + 1) ^ sw) << 4));
+                const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                const __half2 sc2 = (j < 2) ? sc0 : sc1;
+                uint8_t* a_row = s_a + s * kABytes + r * 128;
+#pragma unroll
+                for (int w = 0; w < 8; ++w) {
+                    __half2 h[4];
+                    dequant_word_fp16(words[w], sc2, h);
+                    *reinterpret_cast<uint4*>(a_row + ((w ^ sw) << 4)) = *reinterpret_cast<const uint4*>(h);
+                }
+                fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor core's async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(a_full(s));
+            }
+            __syncwarp();
+            if (lane == 0 && ok) mbar_arrive(raw_empty(rs));
+        }
+        // ---------------- epilogue: thread = weight row, registers = tokens ----------------
+        if (ok) ok = mbar_wait(accum_full, 0, s_abort);
+        tc_fence_after();
+        if (ok) {
+            const int n = n0 + r;
+            const bool row_ok = n < rows_t;
+            __half* out = a.out[t];
+            const int ld = a.out_ld[t];
+            for (int c0 = 0; c0 < T; c0 += 16) {
+                uint32_t v[16];
+                tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(c0), v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int m = m0 + c0 + j;
+                    const float acc = __uint_as_float(v[j]);
+                    if constexpr (MODE == kSwiglu) {
+                        const float up = __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
+                        if ((lane & 1) == 0 && row_ok && m < a.M) {
+                            const float y = (acc / (1.0f + expf(-acc))) * up;
+                            out[static_cast<size_t>(m) * ld + (n >> 1)] = __float2half_rn(y);
+                        }
+                    } else {
+                        if (row_ok && m < a.M) {
+                            __half y = __float2half_rn(acc);
+                            if constexpr (MODE == kPlain) {
+                                if (a.residual != nullptr) y = __hadd(y, a.residual[static_cast<size_t>(m) * ld + n]);
+                            }
+                            out[static_cast<size_t>(m) * ld + n] = y;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == 4) {
+        // ---------------- MMA issue ----------------
+        if (lane == 0) {
+            const uint32_t idesc = make_idesc(T);
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % S;
+                const uint32_t ph = (kb / S) & 1;
+                ok = mbar_wait(a_full(s), ph, s_abort) && mbar_wait(b_full(s), ph, s_abort);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t a_addr = smem_u32(s_a + s * kABytes);
+                const uint32_t b_addr = smem_u32(s_b + s * b_bytes);
+#pragma unroll
+                for (int ks = 0; ks < kBK / 16; ++ks) {
+                    tc_mma_f16(tmem_base, make_smem_desc(a_addr + ks * 32), make_smem_desc(b_addr + ks * 32), idesc,
+                               (kb | ks) != 0 ? 1u : 0u);
+                }
+                tc_commit(ab_empty(s));    // frees the stage when these MMAs have read it
+            }
+            if (ok) tc_commit(accum_full);
+        }
+        __syncwarp();
+    } else if (warp == 5) {
+        // ---------------- TMA: token tiles ----------------
+        if (lane == 0) {
+            bool ok = true;
+            for (int kb = 0; kb < num_kb && ok; ++kb) {
+                const int s = kb % S;
+                ok = mbar_wait(ab_empty(s), ((kb / S) & 1) ^ 1, s_abort);
+                if (!ok) break;
+                mbar_arrive_expect_tx(b_full(s), static_cast<uint32_t>(b_bytes));
+                tma_load_2d(smem_u32(s_b + s * b_bytes), &a.tmap_x, kb * kBK, m0, b_full(s));
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- TMA: raw packed weights ----------------
+        if (lane == 0) {
+            bool ok = true;
+            for (int sb = 0; sb < num_sb && ok; ++sb) {
+                const int rs = sb % kRawStages;
+                ok = mbar_wait(raw_empty(rs), ((sb / kRawStages) & 1) ^ 1, s_abort);
+                if (!ok) break;
+                mbar_arrive_expect_tx(raw_full(rs), kRawBytes);
+                tma_load_2d(smem_u32(s_raw + rs * kRawBytes), &a.tmap_w[t], sb * 128, n0, raw_full(rs));
+            }
+        }
+        __syncwarp();
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 4) tmem_dealloc(tmem_base, static_cast<uint32_t>(a.tmem_cols));
+}
+
+// ---- host side ----------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+bool encode_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
+               uint64_t row_bytes, uint32_t box_inner, uint32_t box_outer) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return false;
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+size_t tc_smem_bytes(int T, int S, int K) {
+    const size_t G = K / kGroup;
+    return 1024 + static_cast<size_t>(kRawStages) * kRawBytes + static_cast<size_t>(S) * (kABytes + T * 128) +
+           ((G * kTileRows * 2 + 15) & ~size_t(15)) + (2 * kRawStages + 3 * kMaxStages + 1) * 8 + 16;
+}
+
+}  // namespace
+
+int gemm_tc_set_attributes() {
+    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_tc_kernel<kPlain>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_w4a16_tc_kernel<kQkv>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_w4a16_tc_kernel<kSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    return static_cast<int>(e);
+}
+
+// Can the tensor-core kernel take this problem?  (alignment for TMA, tile-aligned QKV tensors)
+bool gemm_tc_supported(const GemmArgs& g) {
+    if (encode_tiled_fn() == nullptr) return false;
+    const int nt = g.mode == kQkv ? 3 : 1;
+    for (int t = 0; t < nt; ++t) {
+        if (reinterpret_cast<uintptr_t>(g.qweight[t]) % 16) return false;
+        if (g.mode == kQkv && g.rows[t] % kTileRows) return false;
+    }
+    if (reinterpret_cast<uintptr_t>(g.x) % 16) return false;
+    // scales tile must fit next to at least two pipeline stages
+    return tc_smem_bytes(16, 2, g.K) <= 227 * 1024;
+}
+
+int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
+    TcArgs a;
+    const int nt = g.mode == kQkv ? 3 : 1;
+    int total_tiles = 0;
+    for (int t = 0; t < 3; ++t) {
+        a.scales[t] = g.scales[t];
+        a.out[t] = g.out[t];
+        a.rows[t] = t < nt ? g.rows[t] : 0;
+        a.tiles[t] = (a.rows[t] + kTileRows - 1) / kTileRows;
+        total_tiles += a.tiles[t];
+        a.out_ld[t] = g.mode == kSwiglu ? g.rows[0] / 2 : a.rows[t];
+    }
+    a.residual = g.residual;
+    a.M = g.M;
+    a.K = g.K;
+    // tokens per tile: the smallest power of two >= M (16..256); halve it while the grid is thin
+    int T = 16;
+    while (T < g.M && T < 256) T *= 2;
+    while (T > 64 && total_tiles * ((g.M + T - 1) / T) < sm_count) T /= 2;
+    int S = kMaxStages;
+    while (S > 2 && tc_smem_bytes(T, S, g.K) > 227 * 1024) --S;
+    if (tc_smem_bytes(T, S, g.K) > 227 * 1024) return W4A16_ERR_TOO_LARGE;
+    a.T = T;
+    a.stages = S;
+    a.tmem_cols = T < 32 ? 32 : T;
+
+    for (int t = 0; t < nt; ++t) {
+        if (!encode_2d(&a.tmap_w[t], CU_TENSOR_MAP_DATA_TYPE_UINT8, g.qweight[t], static_cast<uint64_t>(g.K / 2),
+                       static_cast<uint64_t>(g.rows[t]), static_cast<uint64_t>(g.K / 2), 128, kTileRows))
+            return W4A16_ERR_INVALID_ARG;
+    }
+    for (int t = nt; t < 3; ++t) a.tmap_w[t] = a.tmap_w[0];
+    if (!encode_2d(&a.tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.x, static_cast<uint64_t>(g.K),
+                   static_cast<uint64_t>(g.M), static_cast<uint64_t>(g.K) * 2, kBK, static_cast<uint32_t>(T)))
+        return W4A16_ERR_INVALID_ARG;
+
+    const dim3 grid(total_tiles, (g.M + T - 1) / T), block(kThreads);
+    const size_t smem = tc_smem_bytes(T, S, g.K);
+    cudaError_t e;
+    switch (g.mode) {
+        case kPlain: e = launch_kernel(gemm_w4a16_tc_kernel<kPlain>, grid, block, smem, stream, pdl_enabled(), a); break;
+        case kQkv: e = launch_kernel(gemm_w4a16_tc_kernel<kQkv>, grid, block, smem, stream, pdl_enabled(), a); break;
+        default: e = launch_kernel(gemm_w4a16_tc_kernel<kSwiglu>, grid, block, smem, stream, pdl_enabled(), a); break;
+    }
+    return static_cast<int>(e);
+}
+
+int gemm_tc_timeouts(unsigned int* out) {
+    return static_cast<int>(cudaMemcpyFromSymbol(out, g_tc_wait_timeouts, sizeof(unsigned int)));
+}
+
+}  // namespace w4

@@ -87,5 +87,10 @@ struct GemmArgs {
 };
 int gemm_launch(GemmArgs args, cudaStream_t stream);
 int gemm_set_attributes();
+// tensor-core (tcgen05) form of the same contraction (gemm_tc.cu)
+bool gemm_tc_supported(const GemmArgs& g);
+int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream);
+int gemm_tc_set_attributes();
+int gemm_tc_timeouts(unsigned int* out);
 
 }  // namespace w4

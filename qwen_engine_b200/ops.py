@@ -23,7 +23,7 @@ __all__ = [
     "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
     "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots", "DecodeSweep",
     "launch_gemv_rmsnorm_w4a16", "launch_gemv_qkv_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16",
-    "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "gemv_w4a16_static_scratch",
+    "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "gemv_w4a16_static_scratch", "debug_counter",
 ]
 
 # Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
@@ -60,6 +60,13 @@ class QKVProjectionView:
 
     def pod(self) -> QKVView:
         return QKVView(*[_ptr(getattr(self, n)) for n, _ in QKVView._fields_])
+
+
+def debug_counter(which: int = 0) -> int:
+    """Device-side debug counters (0: bounded waits of the tensor-core kernel that ran out)."""
+    v = ctypes.c_uint(0)
+    check("w4a16_debug_counter", load().w4a16_debug_counter(which, ctypes.byref(v)))
+    return v.value
 
 
 def init() -> None:
