@@ -40,6 +40,9 @@ def parse():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--suite", default="sweep", choices=["sweep", "shapes"],
+                    help="sweep: the headline line; shapes: per-shape GEMV and M-token GEMM table (configs 0, 3, 4)")
+    ap.add_argument("--m-list", default="1,2,4,8,16,32,64,128,512,1024,4096")
     ap.add_argument("--layers", type=int, default=28, help=argparse.SUPPRESS)
     ap.add_argument("--no-cpu-baseline", action="store_true", help=argparse.SUPPRESS)
     return ap.parse_args()
@@ -286,34 +289,31 @@ def time_reference_cuda(torch, layers_dev, stream, steps):
 def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
     """Configuration 2: lm_head 1536 -> 151936 split by vocabulary rows over the ranks, fp16 logit slices
     all-gathered over NVLink (NCCL).  Strong scaling: the total work is fixed."""
-    from qwen_engine_b200 import synth
+    from qwen_engine_b200 import nsplit, synth
     N, K = synth.SHAPES["lm_head"]
-    rows = N // world
-    r0 = rank * rows
-    # every rank draws only its own slab: rows are generated per 1024-row block so that slabs agree
-    qw = synth.packed_weights(11, f"lm_head.r{r0}", rows, K)
-    sc = synth.scales(11, f"lm_head.r{r0}", rows, K)
-    d_qw, d_sc = torch.from_numpy(qw.view(np.int32)).cuda(), torch.from_numpy(sc).cuda()
+    slab = nsplit.slab_bounds(N, world, rank)
+    rows = slab.rows
+    # every rank draws only its own slab of the synthetic matrix
+    qw = synth.packed_weights(11, f"lm_head.r{slab.first}", rows, K)
+    sc = synth.scales(11, f"lm_head.r{slab.first}", rows, K)
     x = torch.from_numpy(synth.activations(11, "lm_x", K)).cuda()
     q8 = torch.empty(K, dtype=torch.int8, device="cuda")
     xs = torch.empty(K // 128, dtype=torch.float32, device="cuda")
     s8 = torch.empty(K // 8, dtype=torch.int32, device="cuda")
-    logits = torch.empty(rows * world, dtype=torch.float16, device="cuda")
-    mine = logits[r0:r0 + rows]
     # rotate over enough copies of the slab that consecutive steps do not hit L2
-    copies = max(1, int(np.ceil(3 * 126e6 / (qw.nbytes + sc.nbytes))))
-    copies = min(copies, 24)
-    slabs = [(d_qw, d_sc)] + [(d_qw.clone(), d_sc.clone()) for _ in range(copies - 1)]
+    copies = max(1, min(24, int(np.ceil(3 * 126e6 / (qw.nbytes + sc.nbytes)))))
+    launch = lambda w, s, a, b, c, out, r, k: ops.launch_gemv_w4a8(w, s, a, b, c, None, out, r, k)
+    shards = []
+    for _ in range(copies):
+        shards.append(nsplit.NSplitGemv(torch.from_numpy(qw.view(np.int32)).cuda(), torch.from_numpy(sc).cuda(),
+                                        N, K, launch))
     with torch.cuda.stream(stream):
         ops.launch_quantize_fp16_to_q8_1(x, q8, xs, s8, K)
         i = [0]
 
         def step():
-            w, s = slabs[i[0] % copies]
+            shards[i[0] % copies].forward(q8, xs, s8)
             i[0] += 1
-            ops.launch_gemv_w4a8(w, s, q8, xs, s8, None, mine, rows, K)
-            if world > 1:
-                dist.all_gather_into_tensor(logits, mine)
         for _ in range(max(3, warmup)):
             step()
         stream.synchronize()
@@ -332,10 +332,102 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
             "scaling": "strong", "weight_copies_rotated": copies}
 
 
+def run_shapes_suite(args):
+    """Per-shape table: batch-1 GEMV (Q8_1 in) and the M-token contraction for the four projection shapes
+    plus the scaled-up 28672 x 8192 shape.  Each measurement is one CUDA graph that walks `copies`
+    distinct weight sets (so small shapes are not served from L2), timed with CUDA events."""
+    import torch
+    import qwen_engine_b200 as ops
+    from qwen_engine_b200 import synth
+    torch.cuda.set_device(0)
+    ops.init()
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    stream = torch.cuda.Stream()
+    reps = max(3, min(args.steps, 20))
+    shapes = {"qkv": (2048, 1536), "o": (1536, 1536), "gate_up": (17920, 1536), "down": (1536, 8960),
+              "big": (28672, 8192)}
+    m_list = [int(v) for v in args.m_list.split(",") if v]
+    out = {"suite": "shapes", "gemv": {}, "gemm": {}, "peaks": {k: peaks.get(k) for k in ("hbm_gbs", "bf16_tflops")}}
+    g = torch.Generator(device="cuda").manual_seed(1)
+
+    def weights(N, K, copies):
+        ws = []
+        for _ in range(copies):
+            w = torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), dtype=torch.int32, device="cuda", generator=g)
+            sc = (torch.rand((N, K // 128), device="cuda", generator=g) * 0.018 + 0.002).half()
+            ws.append((w, sc))
+        return ws
+
+    def timed_graph(fn):
+        with torch.cuda.stream(stream):
+            fn()
+            stream.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=stream):
+                fn()
+            for _ in range(2):
+                gr.replay()
+            stream.synchronize()
+            ms = timed_events(torch, stream, gr.replay, reps)
+        return ms * 1e3 / reps   # us per graph
+
+    for name, (N, K) in shapes.items():
+        wbytes = synth.weight_bytes(N, K)
+        copies = max(2, min(28, int(np.ceil(3 * 126e6 / wbytes))))
+        ws = weights(N, K, copies)
+        x = torch.randn(K, device="cuda", generator=g).half()
+        q8 = torch.empty(K, dtype=torch.int8, device="cuda")
+        xs = torch.empty(K // 128, dtype=torch.float32, device="cuda")
+        s8 = torch.empty(K // 8, dtype=torch.int32, device="cuda")
+        with torch.cuda.stream(stream):
+            ops.launch_quantize_fp16_to_q8_1(x, q8, xs, s8, K)
+        n_out = N // 2 if name == "gate_up" else N
+        y = torch.empty(n_out, dtype=torch.float16, device="cuda")
+
+        def gemv_all():
+            for w, sc in ws:
+                if name == "gate_up":
+                    ops.launch_gemv_dual_gate_up_swiglu_w4a8(w, sc, q8, xs, s8, y, K, n_out)
+                else:
+                    ops.launch_gemv_w4a8(w, sc, q8, xs, s8, None, y, N, K)
+        us = timed_graph(gemv_all) / copies
+        nb = synth.gemv_algorithmic_bytes(N, K, n_out=n_out)
+        out["gemv"][name] = {"N": N, "K": K, "us": us, "GB/s": nb / us / 1e3, "copies": copies}
+
+        for M in m_list:
+            if name == "big" and M not in (16, 128, 1024, 4096):
+                continue
+            xm = torch.randn((M, K), device="cuda", generator=g).half()
+            ym = torch.empty((M, n_out), dtype=torch.float16, device="cuda")
+            use = ws[:max(2, min(copies, 8))] if M >= 512 else ws
+
+            def gemm_all():
+                for w, sc in use:
+                    if name == "gate_up":
+                        ops.launch_gemm_prefill_dual_gate_up_swiglu_w4a16(w, sc, xm, ym, M, None, K, n_out)
+                    else:
+                        ops.launch_gemm_prefill_w4a16(w, sc, xm, None, ym, M, N, K)
+            us = timed_graph(gemm_all) / len(use)
+            flops = 2.0 * M * N * K
+            nb = wbytes + 2 * M * K + 2 * M * n_out
+            out["gemm"][f"{name}.M{M}"] = {"us": us, "TFLOP/s": flops / us / 1e6, "GB/s": nb / us / 1e3}
+        del ws
+        torch.cuda.empty_cache()
+    out["tc_wait_timeouts"] = ops.debug_counter(0)
+    print(json.dumps(out), flush=True)
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.suite == "shapes":
+        run_shapes_suite(args)
         return
 
     import torch

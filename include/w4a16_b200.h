@@ -273,7 +273,8 @@ W4A16_API int w4a16_gemv_group_dots(const uint32_t* qweight, const int8_t* input
 /*
  * Debug counters kept on the current device.  which = 0: number of bounded waits of the
  * tensor-core kernel that ran out (each one means a launch gave up and its output is invalid;
- * 0 in normal operation).  Synchronises the device.
+ * 0 in normal operation); 1..16: cycle sums of that kernel's roles, zero unless the library was
+ * built with -DW4A16_TC_PROFILE.  Synchronises the device.
  */
 W4A16_API int w4a16_debug_counter(int which, unsigned int* out);
 

@@ -48,6 +48,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     if not force and up_to_date():
         return LIB
     cmd = [nvcc(), *NVCC_FLAGS]
+    if os.environ.get("W4A16_TC_PROFILE"):
+        cmd += ["-DW4A16_TC_PROFILE"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-o", str(LIB), *[str(CSRC / s) for s in SOURCES]]

@@ -10,12 +10,15 @@
 // the MMA and the tokens on its N side (16..256), so a decode batch of 16 tokens fills the
 // tensor core as well as a prefill chunk does, and weights stream through each CTA exactly once.
 //
-//   warp 6      : TMA producer of raw packed weights, 128 rows x 128 B (= 256 k) per stage,
+//   warps 0..4*NG-1 : NG groups of 4 warps dequantise raw nibbles -> fp16 A tile [128 x 64] in the
+//                 K-major 128B-swizzled layout the UMMA shared-memory descriptor expects; inside a
+//                 group a thread owns a weight row, and group g takes k-blocks g, g+NG, ... so the
+//                 fixed cost of a k-block (barrier waits, proxy fence, arrive) is paid by 4 warps
+//                 while the other groups work on the next k-blocks; later all of them run the epilogue
+//   next warp   : allocates TMEM, issues tcgen05.mma (one thread), commits to mbarriers
+//   next warp   : TMA producer of the token tile B [T x 64] fp16 (128B swizzle)
+//   last warp   : TMA producer of raw packed weights, 128 rows x 128 B (= 256 k) per stage,
 //                 128B-swizzled so that row-per-thread reads are bank-conflict free
-//   warps 0-3   : dequantise raw nibbles -> fp16 A tile [128 x 64] in the K-major 128B-swizzled
-//                 layout the UMMA shared-memory descriptor expects; later the epilogue
-//   warp 5      : TMA producer of the token tile B [T x 64] fp16 (128B swizzle)
-//   warp 4      : allocates TMEM, issues tcgen05.mma (one thread), commits to mbarriers
 //   epilogue    : tcgen05.ld 32x32b (thread = weight row, registers = tokens), fp16 stores
 //
 // No cluster, no multicast.  Every mbarrier wait is bounded: on expiry the kernel raises an
@@ -33,6 +36,17 @@
 namespace w4 {
 
 __device__ unsigned int g_tc_wait_timeouts = 0;
+#ifdef W4A16_TC_PROFILE
+// Cycle counts of CTA (0,0), per role, summed over its k-blocks (build with -DW4A16_TC_PROFILE).
+__device__ unsigned long long g_tc_prof[16];
+#define TC_PROF_DECL(name) long long name = 0
+#define TC_PROF_T() clock64()
+#define TC_PROF_ADD(acc, t0) acc += clock64() - (t0)
+#else
+#define TC_PROF_DECL(name)
+#define TC_PROF_T() 0
+#define TC_PROF_ADD(acc, t0)
+#endif
 
 namespace {
 
@@ -41,8 +55,6 @@ constexpr int kBK = 64;                 // fp16 elements per k-block: one 128-by
 constexpr int kRawStages = 3;
 constexpr int kRawBytes = kTileRows * 128;   // 128 rows x 128 bytes of packed nibbles = 256 k
 constexpr int kABytes = kTileRows * 128;     // 128 rows x 64 fp16
-constexpr int kDequantThreads = 128;
-constexpr int kThreads = 224;           // 7 warps
 constexpr int kMaxStages = 8;
 constexpr unsigned kWaitLimit = 1u << 22;
 
@@ -156,8 +168,19 @@ __device__ __forceinline__ uint32_t make_idesc(int n) {
     return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(kTileRows >> 4) << 24);
 }
 
-template <int MODE>
-__global__ void __launch_bounds__(kThreads, 1) gemm_w4a16_tc_kernel(const __grid_constant__ TcArgs a) {
+// One lane polls the barrier for its warp (512 threads polling would keep the mbarrier unit busy and
+// delay the single MMA-issuing thread); __syncwarp then orders the other lanes' reads after it.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int lane) {
+    int ok = 1;
+    if (lane == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+    __syncwarp();
+    return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
+}
+
+template <int MODE, int NG>
+__global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(const __grid_constant__ TcArgs a) {
+    constexpr int kDqWarps = 4 * NG;             // dequantising warps: NG groups of 4
+    constexpr int kDqThreads = kDqWarps * 32;
     extern __shared__ uint8_t smem_raw_base[];
     // 1024-byte alignment for the swizzled tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_base) + 1023) & ~uintptr_t(1023));
@@ -169,12 +192,11 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a16_tc_kernel(const __grid
     uint8_t* s_b = s_a + S * kABytes;                       // S x T*128
     __half* s_scale = reinterpret_cast<__half*>(s_b + S * b_bytes);   // [G][128]
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_scale) + ((G * kTileRows * 2 + 15) & ~15));
-    // barrier slots: raw_full[3] raw_empty[3] a_full[S] b_full[S] ab_empty[S] accum_full
+    // barrier slots: raw_full[3] raw_empty[3] full[S] (A dequantised AND B landed) ab_empty[S] accum_full
     const uint32_t bar0 = smem_u32(s_bar);
     auto raw_full = [&](int i) { return bar0 + 8u * i; };
     auto raw_empty = [&](int i) { return bar0 + 8u * (kRawStages + i); };
-    auto a_full = [&](int i) { return bar0 + 8u * (2 * kRawStages + i); };
-    auto b_full = [&](int i) { return bar0 + 8u * (2 * kRawStages + kMaxStages + i); };
+    auto full = [&](int i) { return bar0 + 8u * (2 * kRawStages + i); };
     auto ab_empty = [&](int i) { return bar0 + 8u * (2 * kRawStages + 2 * kMaxStages + i); };
     const uint32_t accum_full = bar0 + 8u * (2 * kRawStages + 3 * kMaxStages);
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + (2 * kRawStages + 3 * kMaxStages + 1));
@@ -194,15 +216,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a16_tc_kernel(const __grid
     const int num_kb = K / kBK, num_sb = K / 256;
 
     if (tid == 0) {
-        for (int i = 0; i < kRawStages; ++i) { mbar_init(raw_full(i), 1); mbar_init(raw_empty(i), 4); }
-        for (int i = 0; i < S; ++i) { mbar_init(a_full(i), 4); mbar_init(b_full(i), 1); mbar_init(ab_empty(i), 1); }
+        for (int i = 0; i < kRawStages; ++i) { mbar_init(raw_full(i), 1); mbar_init(raw_empty(i), kDqWarps); }
+        for (int i = 0; i < S; ++i) { mbar_init(full(i), 4 + 1); mbar_init(ab_empty(i), 1); }   // 4 warps + the TMA thread
         mbar_init(accum_full, 1);
         *s_abort = 0;
         fence_barrier_init();
         tma_prefetch_desc(&a.tmap_x);
         tma_prefetch_desc(&a.tmap_w[t]);
     }
-    if (warp == 4) {
+    if (warp == kDqWarps) {
         tmem_alloc(smem_u32(s_tmem), static_cast<uint32_t>(a.tmem_cols));
         tmem_relinquish();
     }
@@ -213,34 +235,44 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a16_tc_kernel(const __grid
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
 
-    if (warp < 4) {
-        // ---------------- dequantise: thread = weight row ----------------
-        const int r = tid;
+    if (warp < kDqWarps) {
+        // ---------------- dequantise: group = warp / 4, thread = weight row inside the group ----------------
+        const int r = (warp & 3) * 32 + lane;    // weight row inside the tile == TMEM lane of the epilogue
+        const int part = warp >> 2;              // group index; also the epilogue's column share
         // scales of the 128 rows, transposed to [group][row]
         {
             const __half* sc = a.scales[t];
-            for (int idx = tid; idx < kTileRows * G; idx += kDequantThreads) {
+            for (int idx = tid; idx < kTileRows * G; idx += kDqThreads) {
                 const int rr = idx / G, g = idx - rr * G;
                 const int row = n0 + rr;
                 s_scale[g * kTileRows + rr] = row < rows_t ? sc[static_cast<size_t>(row) * G + g] : __float2half(0.0f);
             }
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");
         }
         const int sw = r & 7;
         bool ok = true;
+        int rs = 0;
+        uint32_t rph = 0;
+        // ring position of this group's first k-block (k-block index == part), then += NG per visit
+        int s = part;
+        uint32_t ph = 0;
+        while (s >= S) { s -= S; ph ^= 1; }
+        TC_PROF_DECL(q_raw); TC_PROF_DECL(q_empty); TC_PROF_DECL(q_work); TC_PROF_DECL(q_sync);
         for (int sb = 0; sb < num_sb && ok; ++sb) {
-            const int rs = sb % kRawStages;
-            ok = mbar_wait(raw_full(rs), (sb / kRawStages) & 1, s_abort);
+            [[maybe_unused]] long long d0 = TC_PROF_T();
+            ok = warp_wait(raw_full(rs), rph, s_abort, lane);
+            TC_PROF_ADD(q_raw, d0);
             if (!ok) break;
             const uint8_t* raw_row = s_raw + rs * kRawBytes + r * 128;
             const __half2 sc0 = __half2half2(s_scale[(2 * sb) * kTileRows + r]);
             const __half2 sc1 = __half2half2(s_scale[(2 * sb + 1) * kTileRows + r]);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int kb = sb * 4 + j;
-                const int s = kb % S;
-                ok = mbar_wait(ab_empty(s), ((kb / S) & 1) ^ 1, s_abort);
+            for (int j = part; j < 4; j += NG) {     // this group's k-blocks of the 256-element super-block
+                [[maybe_unused]] long long d1 = TC_PROF_T();
+                ok = warp_wait(ab_empty(s), ph ^ 1, s_abort, lane);
+                TC_PROF_ADD(q_empty, d1);
                 if (!ok) break;
+                [[maybe_unused]] long long d2 = TC_PROF_T();
                 const uint4 w0 = *reinterpret_cast<const uint4*>(raw_row + (((2 * j) ^ sw) << 4));
                 const uint4 w1 = *reinterpret_cast<const uint4*>(raw_row + (((2 * j + 1) ^ sw) << 4));
                 const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
@@ -252,25 +284,40 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a16_tc_kernel(const __grid
                     dequant_word_fp16(words[w], sc2, h);
                     *reinterpret_cast<uint4*>(a_row + ((w ^ sw) << 4)) = *reinterpret_cast<const uint4*>(h);
                 }
+                TC_PROF_ADD(q_work, d2);
+                [[maybe_unused]] long long d3 = TC_PROF_T();
                 fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor core's async proxy
                 __syncwarp();
-                if (lane == 0) mbar_arrive(a_full(s));
+                if (lane == 0) mbar_arrive(full(s));
+                TC_PROF_ADD(q_sync, d3);
+                s += NG;
+                while (s >= S) { s -= S; ph ^= 1; }
             }
             __syncwarp();
             if (lane == 0 && ok) mbar_arrive(raw_empty(rs));
+            if (++rs == kRawStages) { rs = 0; rph ^= 1; }
         }
+#ifdef W4A16_TC_PROFILE
+        if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp & 3) == 0) {
+            const int gq = 4 + 3 * part;
+            if (gq + 2 < 16) { g_tc_prof[gq] = q_raw + q_empty; g_tc_prof[gq + 1] = q_work; g_tc_prof[gq + 2] = q_sync; }
+        }
+#endif
         // ---------------- epilogue: thread = weight row, registers = tokens ----------------
-        if (ok) ok = mbar_wait(accum_full, 0, s_abort);
+        if (ok) ok = warp_wait(accum_full, 0, s_abort, lane);
         tc_fence_after();
         if (ok) {
             const int n = n0 + r;
             const bool row_ok = n < rows_t;
             __half* out = a.out[t];
             const int ld = a.out_ld[t];
-            for (int c0 = 0; c0 < T; c0 += 16) {
+            // the NG warps that share a TMEM lane quarter take the 16-column chunks in turn
+            for (int c0 = part * 16; c0 < T; c0 += 16 * NG) {
                 uint32_t v[16];
-                tmem_ld16(tmem_base + (static_cast<uint32_t>(warp * 32) << 16) + static_cast<uint32_t>(c0), v);
+                const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+                tmem_ld16(lane_base + static_cast<uint32_t>(c0), v);
                 tmem_ld_wait();
+
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int m = m0 + c0 + j;
@@ -293,52 +340,70 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a16_tc_kernel(const __grid
                 }
             }
         }
-    } else if (warp == 4) {
+    } else if (warp == kDqWarps) {
         // ---------------- MMA issue ----------------
         if (lane == 0) {
+            // One thread issues every MMA, so its instruction stream is the critical path of a k-block:
+            // descriptors are advanced by plain adds on their low word (the start-address field counts
+            // 16-byte units and cannot carry out of its 14 bits for shared-memory addresses), ring
+            // positions by compare-and-reset.
             const uint32_t idesc = make_idesc(T);
+            const uint64_t a_desc0 = make_smem_desc(smem_u32(s_a));
+            const uint64_t b_desc0 = make_smem_desc(smem_u32(s_b));
+            const uint32_t a_step = kABytes >> 4, b_step = static_cast<uint32_t>(b_bytes) >> 4;
+            uint64_t a_desc = a_desc0, b_desc = b_desc0;
+            int s = 0;
+            uint32_t ph = 0;
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % S;
-                const uint32_t ph = (kb / S) & 1;
-                ok = mbar_wait(a_full(s), ph, s_abort) && mbar_wait(b_full(s), ph, s_abort);
+            TC_PROF_DECL(p_wait); TC_PROF_DECL(p_mma); TC_PROF_DECL(p_commit);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                [[maybe_unused]] long long c0 = TC_PROF_T();
+                ok = mbar_wait(full(s), ph, s_abort);
+                TC_PROF_ADD(p_wait, c0);
                 if (!ok) break;
-                tc_fence_after();
-                const uint32_t a_addr = smem_u32(s_a + s * kABytes);
-                const uint32_t b_addr = smem_u32(s_b + s * b_bytes);
+                [[maybe_unused]] long long c1 = TC_PROF_T();
 #pragma unroll
-                for (int ks = 0; ks < kBK / 16; ++ks) {
-                    tc_mma_f16(tmem_base, make_smem_desc(a_addr + ks * 32), make_smem_desc(b_addr + ks * 32), idesc,
-                               (kb | ks) != 0 ? 1u : 0u);
-                }
+                for (int ks = 0; ks < kBK / 16; ++ks)
+                    tc_mma_f16(tmem_base, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
+                TC_PROF_ADD(p_mma, c1);
+                [[maybe_unused]] long long c2 = TC_PROF_T();
                 tc_commit(ab_empty(s));    // frees the stage when these MMAs have read it
+                TC_PROF_ADD(p_commit, c2);
+                a_desc += a_step;
+                b_desc += b_step;
+                if (++s == S) { s = 0; ph ^= 1; a_desc = a_desc0; b_desc = b_desc0; }
             }
             if (ok) tc_commit(accum_full);
+#ifdef W4A16_TC_PROFILE
+            if (blockIdx.x == 0 && blockIdx.y == 0) {
+                g_tc_prof[0] = p_wait; g_tc_prof[1] = p_mma; g_tc_prof[2] = p_commit; g_tc_prof[3] = num_kb;
+            }
+#endif
         }
         __syncwarp();
-    } else if (warp == 5) {
+    } else if (warp == kDqWarps + 1) {
         // ---------------- TMA: token tiles ----------------
         if (lane == 0) {
-            bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % S;
-                ok = mbar_wait(ab_empty(s), ((kb / S) & 1) ^ 1, s_abort);
-                if (!ok) break;
-                mbar_arrive_expect_tx(b_full(s), static_cast<uint32_t>(b_bytes));
-                tma_load_2d(smem_u32(s_b + s * b_bytes), &a.tmap_x, kb * kBK, m0, b_full(s));
+            int s = 0;
+            uint32_t ph = 0;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait(ab_empty(s), ph ^ 1, s_abort)) break;
+                mbar_arrive_expect_tx(full(s), static_cast<uint32_t>(b_bytes));
+                tma_load_2d(smem_u32(s_b + s * b_bytes), &a.tmap_x, kb * kBK, m0, full(s));
+                if (++s == S) { s = 0; ph ^= 1; }
             }
         }
         __syncwarp();
     } else {
         // ---------------- TMA: raw packed weights ----------------
         if (lane == 0) {
-            bool ok = true;
-            for (int sb = 0; sb < num_sb && ok; ++sb) {
-                const int rs = sb % kRawStages;
-                ok = mbar_wait(raw_empty(rs), ((sb / kRawStages) & 1) ^ 1, s_abort);
-                if (!ok) break;
+            int rs = 0;
+            uint32_t rph = 0;
+            for (int sb = 0; sb < num_sb; ++sb) {
+                if (!mbar_wait(raw_empty(rs), rph ^ 1, s_abort)) break;
                 mbar_arrive_expect_tx(raw_full(rs), kRawBytes);
                 tma_load_2d(smem_u32(s_raw + rs * kRawBytes), &a.tmap_w[t], sb * 128, n0, raw_full(rs));
+                if (++rs == kRawStages) { rs = 0; rph ^= 1; }
             }
         }
         __syncwarp();
@@ -346,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_w4a16_tc_kernel(const __grid
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 4) tmem_dealloc(tmem_base, static_cast<uint32_t>(a.tmem_cols));
+    if (warp == kDqWarps) tmem_dealloc(tmem_base, static_cast<uint32_t>(a.tmem_cols));
 }
 
 // ---- host side ----------------------------------------------------------------------------
@@ -389,12 +454,33 @@ size_t tc_smem_bytes(int T, int S, int K) {
 
 }  // namespace
 
+namespace {
+template <int MODE, int NG>
+cudaError_t raise_tc_smem() {
+    return cudaFuncSetAttribute(gemm_w4a16_tc_kernel<MODE, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+}
+template <int NG>
+cudaError_t raise_tc_smem_modes() {
+    cudaError_t e = raise_tc_smem<kPlain, NG>();
+    if (e == cudaSuccess) e = raise_tc_smem<kQkv, NG>();
+    if (e == cudaSuccess) e = raise_tc_smem<kSwiglu, NG>();
+    return e;
+}
+template <int NG>
+cudaError_t launch_tc(int mode, dim3 grid, size_t smem, cudaStream_t stream, const TcArgs& a) {
+    const dim3 block((4 * NG + 3) * 32);
+    switch (mode) {
+        case kPlain: return launch_kernel(gemm_w4a16_tc_kernel<kPlain, NG>, grid, block, smem, stream, pdl_enabled(), a);
+        case kQkv: return launch_kernel(gemm_w4a16_tc_kernel<kQkv, NG>, grid, block, smem, stream, pdl_enabled(), a);
+        default: return launch_kernel(gemm_w4a16_tc_kernel<kSwiglu, NG>, grid, block, smem, stream, pdl_enabled(), a);
+    }
+}
+}  // namespace
+
 int gemm_tc_set_attributes() {
-    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_tc_kernel<kPlain>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemm_w4a16_tc_kernel<kQkv>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemm_w4a16_tc_kernel<kSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = raise_tc_smem_modes<1>();
+    if (e == cudaSuccess) e = raise_tc_smem_modes<2>();
+    if (e == cudaSuccess) e = raise_tc_smem_modes<4>();
     return static_cast<int>(e);
 }
 
@@ -430,12 +516,14 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     int T = 16;
     while (T < g.M && T < 256) T *= 2;
     while (T > 64 && total_tiles * ((g.M + T - 1) / T) < sm_count) T /= 2;
-    int S = kMaxStages;
+    static const int stages_env = env_int("W4A16_TC_STAGES", 0);
+    int S = stages_env > 0 ? std::min(stages_env, kMaxStages) : kMaxStages;
     while (S > 2 && tc_smem_bytes(T, S, g.K) > 227 * 1024) --S;
     if (tc_smem_bytes(T, S, g.K) > 227 * 1024) return W4A16_ERR_TOO_LARGE;
     a.T = T;
     a.stages = S;
     a.tmem_cols = T < 32 ? 32 : T;
+
 
     for (int t = 0; t < nt; ++t) {
         if (!encode_2d(&a.tmap_w[t], CU_TENSOR_MAP_DATA_TYPE_UINT8, g.qweight[t], static_cast<uint64_t>(g.K / 2),
@@ -447,15 +535,26 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
                    static_cast<uint64_t>(g.M), static_cast<uint64_t>(g.K) * 2, kBK, static_cast<uint32_t>(T)))
         return W4A16_ERR_INVALID_ARG;
 
-    const dim3 grid(total_tiles, (g.M + T - 1) / T), block(kThreads);
+    const dim3 grid(total_tiles, (g.M + T - 1) / T);
     const size_t smem = tc_smem_bytes(T, S, g.K);
+    // A dequantising group revisits a ring slot every NG k-blocks and waits on a parity: it must never
+    // be two uses of a slot ahead of the tensor core, which holds exactly when NG <= stages.
+    static const int groups_env = env_int("W4A16_TC_GROUPS", 4);
+    const int groups = S >= 4 ? std::min(groups_env, 4) : std::min(groups_env, 2);
     cudaError_t e;
-    switch (g.mode) {
-        case kPlain: e = launch_kernel(gemm_w4a16_tc_kernel<kPlain>, grid, block, smem, stream, pdl_enabled(), a); break;
-        case kQkv: e = launch_kernel(gemm_w4a16_tc_kernel<kQkv>, grid, block, smem, stream, pdl_enabled(), a); break;
-        default: e = launch_kernel(gemm_w4a16_tc_kernel<kSwiglu>, grid, block, smem, stream, pdl_enabled(), a); break;
-    }
+    if (groups == 1) e = launch_tc<1>(g.mode, grid, smem, stream, a);
+    else if (groups == 2) e = launch_tc<2>(g.mode, grid, smem, stream, a);
+    else e = launch_tc<4>(g.mode, grid, smem, stream, a);
     return static_cast<int>(e);
+}
+
+int gemm_tc_prof(unsigned long long* out) {
+#ifdef W4A16_TC_PROFILE
+    return static_cast<int>(cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(unsigned long long) * 16));
+#else
+    for (int i = 0; i < 16; ++i) out[i] = 0;
+    return 0;
+#endif
 }
 
 int gemm_tc_timeouts(unsigned int* out) {

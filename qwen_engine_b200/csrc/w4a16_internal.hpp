@@ -92,5 +92,6 @@ bool gemm_tc_supported(const GemmArgs& g);
 int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream);
 int gemm_tc_set_attributes();
 int gemm_tc_timeouts(unsigned int* out);
+int gemm_tc_prof(unsigned long long* out);   // zeros unless built with -DW4A16_TC_PROFILE
 
 }  // namespace w4

@@ -1,0 +1,77 @@
+"""Output-row split of a W4 GEMV over the GPUs of one node (one process per GPU).
+
+The projection path shards along output rows only: rows are independent, a split along K would
+need a reduction and would break the fused residual / SwiGLU epilogues.  Each rank owns one
+contiguous slab of rows of `qweight` and `scales` in its OWN allocation (slab offsets of the
+scale tensor are not 16-byte multiples inside a global tensor), activations are replicated, and
+the fp16 output slices are all-gathered (NCCL over NVLink on GPUs; any torch.distributed backend
+works, which is how the host logic is tested with gloo on CPU).
+
+The reference engine is single-GPU; this has no counterpart there.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass(frozen=True)
+class Slab:
+    first: int      # first global row of this rank
+    rows: int       # rows this rank owns (may be 0 on trailing ranks)
+    stride: int     # rows reserved per rank in the gathered buffer (same on all ranks)
+
+
+def slab_bounds(n_rows: int, world: int, rank: int, align: int = 1) -> Slab:
+    """Contiguous, `align`-row-aligned slabs (align=2 keeps gate/up row pairs on one rank, align=head_dim
+    keeps attention heads whole).  All ranks reserve `stride` rows so that one equal-sized all-gather works
+    for any n_rows."""
+    if n_rows <= 0 or world <= 0 or not 0 <= rank < world or align <= 0:
+        raise ValueError("bad split arguments")
+    stride = math.ceil(n_rows / world / align) * align
+    first = min(rank * stride, n_rows)
+    return Slab(first, min(first + stride, n_rows) - first, stride)
+
+
+class NSplitGemv:
+    """y[N] = W[N][K] . x, rows split over the ranks of `group`, logits gathered on every rank.
+
+    launch(qweight_slab, scales_slab, q8, xscale, sum8, out_slice, rows, K) runs the local GEMV; on GPUs
+    it is `launch_gemv_w4a8` of this package.
+    """
+
+    def __init__(self, qweight_slab: torch.Tensor, scales_slab: torch.Tensor, n_rows: int, in_features: int,
+                 launch, group=None, align: int = 1):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.n_rows, self.K = n_rows, in_features
+        self.slab = slab_bounds(n_rows, self.world, self.rank, align)
+        if qweight_slab.shape[0] != self.slab.rows or scales_slab.shape[0] != self.slab.rows:
+            raise ValueError(f"rank {self.rank} expects a slab of {self.slab.rows} rows")
+        self.qweight, self.scales, self.launch = qweight_slab, scales_slab, launch
+        # gathered buffer: world x stride halves; rank r's slice starts at r * stride
+        self.gathered = torch.empty(self.world * self.slab.stride, dtype=torch.float16, device=qweight_slab.device)
+
+    def local_slice(self) -> torch.Tensor:
+        s = self.slab
+        return self.gathered[self.rank * s.stride: self.rank * s.stride + s.stride]
+
+    def forward(self, q8, xscale, sum8) -> torch.Tensor:
+        """Returns the full fp16 output [n_rows] (a view of the gathered buffer when no padding exists)."""
+        mine = self.local_slice()
+        if self.slab.rows > 0:
+            self.launch(self.qweight, self.scales, q8, xscale, sum8, mine, self.slab.rows, self.K)
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.gathered, mine, group=self.group)
+        if self.world * self.slab.stride == self.n_rows:
+            return self.gathered
+        # padded layout -> compact
+        parts = []
+        for r in range(self.world):
+            rows = min(max(self.n_rows - r * self.slab.stride, 0), self.slab.stride)
+            parts.append(self.gathered[r * self.slab.stride: r * self.slab.stride + rows])
+        return torch.cat(parts)
