@@ -310,12 +310,12 @@ int w4a16_gemv_group_dots(const uint32_t* qweight, const int8_t* input_q8, const
 }
 
 int w4a16_debug_counter(int which, unsigned int* out) {
-    if (!out || which < 0 || which > 16) return W4A16_ERR_INVALID_ARG;
+    if (!out || which < 0 || which > 32) return W4A16_ERR_INVALID_ARG;
     if (int st = ensure_device_ready(nullptr)) return st;
     if (which == 0) return gemm_tc_timeouts(out);
-    // 1..16: per-role cycle sums of the tensor-core kernel's CTA (0,0); zero unless the library was
+    // 1..32: per-role cycle sums of the tensor-core kernel's CTA (0,0); zero unless the library was
     // built with -DW4A16_TC_PROFILE
-    unsigned long long prof[16];
+    unsigned long long prof[32];
     if (int st = gemm_tc_prof(prof)) return st;
     *out = static_cast<unsigned int>(prof[which - 1]);
     return 0;

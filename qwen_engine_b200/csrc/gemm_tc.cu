@@ -38,7 +38,7 @@ namespace w4 {
 __device__ unsigned int g_tc_wait_timeouts = 0;
 #ifdef W4A16_TC_PROFILE
 // Cycle counts of CTA (0,0), per role, summed over its k-blocks (build with -DW4A16_TC_PROFILE).
-__device__ unsigned long long g_tc_prof[16];
+__device__ unsigned long long g_tc_prof[32];
 #define TC_PROF_DECL(name) long long name = 0
 #define TC_PROF_T() clock64()
 #define TC_PROF_ADD(acc, t0) acc += clock64() - (t0)
@@ -87,6 +87,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Non-blocking test of a phase (try_wait may park the thread for a while when the phase is still open).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
         : "r"(bar), "r"(parity)
@@ -342,11 +354,14 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
         }
     } else if (warp == kDqWarps) {
         // ---------------- MMA issue ----------------
-        if (lane == 0) {
-            // One thread issues every MMA, so its instruction stream is the critical path of a k-block:
-            // descriptors are advanced by plain adds on their low word (the start-address field counts
-            // 16-byte units and cannot carry out of its 14 bits for shared-memory addresses), ring
-            // positions by compare-and-reset.
+        // The whole warp walks the loop with warp-uniform values (so descriptors and ring positions can
+        // live in uniform registers); one elected lane issues the tensor-core instructions.  The
+        // instruction stream of this warp is the critical path of a k-block, hence: descriptors are
+        // advanced by plain adds on their low word (the start-address field counts 16-byte units and
+        // cannot carry out of its 14 bits for shared-memory addresses), ring positions by
+        // compare-and-reset, and the barrier of the NEXT k-block is tested before this k-block's MMAs
+        // are issued so that the test's latency overlaps the issue.
+        {
             const uint32_t idesc = make_idesc(T);
             const uint64_t a_desc0 = make_smem_desc(smem_u32(s_a));
             const uint64_t b_desc0 = make_smem_desc(smem_u32(s_b));
@@ -355,28 +370,43 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            TC_PROF_DECL(p_wait); TC_PROF_DECL(p_mma); TC_PROF_DECL(p_commit);
+            TC_PROF_DECL(p_wait); TC_PROF_DECL(p_mma); TC_PROF_DECL(p_commit); TC_PROF_DECL(p_test);
+            bool ready = mbar_test_wait(full(0), 0);
+            [[maybe_unused]] long long loop_t0 = TC_PROF_T();
             for (int kb = 0; kb < num_kb; ++kb) {
                 [[maybe_unused]] long long c0 = TC_PROF_T();
-                ok = mbar_wait(full(s), ph, s_abort);
+                if (!ready) ok = warp_wait(full(s), ph, s_abort, lane);
                 TC_PROF_ADD(p_wait, c0);
                 if (!ok) break;
+                // position of the next k-block, and an early look at its barrier
+                int sn = s + 1;
+                uint32_t phn = ph;
+                if (sn == S) { sn = 0; phn ^= 1; }
                 [[maybe_unused]] long long c1 = TC_PROF_T();
+                if (lane == 0) {
 #pragma unroll
-                for (int ks = 0; ks < kBK / 16; ++ks)
-                    tc_mma_f16(tmem_base, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
-                TC_PROF_ADD(p_mma, c1);
-                [[maybe_unused]] long long c2 = TC_PROF_T();
-                tc_commit(ab_empty(s));    // frees the stage when these MMAs have read it
-                TC_PROF_ADD(p_commit, c2);
+                    for (int ks = 0; ks < kBK / 16; ++ks)
+                        tc_mma_f16(tmem_base, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
+                    TC_PROF_ADD(p_mma, c1);
+                    [[maybe_unused]] long long c2 = TC_PROF_T();
+                    tc_commit(ab_empty(s));    // frees the stage when these MMAs have read it
+                    TC_PROF_ADD(p_commit, c2);
+                }
+                [[maybe_unused]] long long c3 = TC_PROF_T();
+                ready = (kb + 1 < num_kb) ? mbar_test_wait(full(sn), phn) : true;
+                ready = __all_sync(0xFFFFFFFFu, ready);
+                TC_PROF_ADD(p_test, c3);
                 a_desc += a_step;
                 b_desc += b_step;
-                if (++s == S) { s = 0; ph ^= 1; a_desc = a_desc0; b_desc = b_desc0; }
+                if (sn == 0) { a_desc = a_desc0; b_desc = b_desc0; }
+                s = sn;
+                ph = phn;
             }
-            if (ok) tc_commit(accum_full);
+            if (ok && lane == 0) tc_commit(accum_full);
 #ifdef W4A16_TC_PROFILE
-            if (blockIdx.x == 0 && blockIdx.y == 0) {
+            if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) {
                 g_tc_prof[0] = p_wait; g_tc_prof[1] = p_mma; g_tc_prof[2] = p_commit; g_tc_prof[3] = num_kb;
+                g_tc_prof[16] = clock64() - loop_t0; g_tc_prof[19] = p_test;
             }
 #endif
         }
@@ -386,12 +416,20 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
+            TC_PROF_DECL(x_wait);
+            [[maybe_unused]] long long x_t0 = TC_PROF_T();
             for (int kb = 0; kb < num_kb; ++kb) {
-                if (!mbar_wait(ab_empty(s), ph ^ 1, s_abort)) break;
+                [[maybe_unused]] long long w0 = TC_PROF_T();
+                const bool okx = mbar_wait(ab_empty(s), ph ^ 1, s_abort);
+                TC_PROF_ADD(x_wait, w0);
+                if (!okx) break;
                 mbar_arrive_expect_tx(full(s), static_cast<uint32_t>(b_bytes));
                 tma_load_2d(smem_u32(s_b + s * b_bytes), &a.tmap_x, kb * kBK, m0, full(s));
                 if (++s == S) { s = 0; ph ^= 1; }
             }
+#ifdef W4A16_TC_PROFILE
+            if (blockIdx.x == 0 && blockIdx.y == 0) { g_tc_prof[17] = x_wait; g_tc_prof[18] = clock64() - x_t0; }
+#endif
         }
         __syncwarp();
     } else {
@@ -550,9 +588,9 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
 
 int gemm_tc_prof(unsigned long long* out) {
 #ifdef W4A16_TC_PROFILE
-    return static_cast<int>(cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(unsigned long long) * 16));
+    return static_cast<int>(cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(unsigned long long) * 32));
 #else
-    for (int i = 0; i < 16; ++i) out[i] = 0;
+    for (int i = 0; i < 32; ++i) out[i] = 0;
     return 0;
 #endif
 }
