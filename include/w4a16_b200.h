@@ -228,7 +228,11 @@ enum {
     W4A16_SWEEP_FUSE_NORM = 1,   /* RMSNorm + Q8_1 inside the QKV and gate_up GEMVs */
     W4A16_SWEEP_FUSE_QUANT_O = 2,    /* Q8_1 of the attention output inside the O GEMV */
     W4A16_SWEEP_FUSE_QUANT_DOWN = 4, /* Q8_1 of the MLP activation inside the down GEMV */
-    W4A16_SWEEP_FUSE_ALL = 7     /* 4 launches per layer, same output bits */
+    W4A16_SWEEP_FUSE_ALL = 7,    /* 4 launches per layer, same output bits */
+    W4A16_SWEEP_PERSISTENT = 8   /* the whole pass as ONE persistent kernel (one CTA per SM): weights of all
+                                    layers stream through a shared-memory ring while the CTAs exchange the
+                                    small activation vectors through tagged 8-byte words; needs
+                                    hidden <= 4096, intermediate and q width <= 9216, 16-byte aligned weights */
 };
 
 typedef struct w4a16_sweep w4a16_sweep;
@@ -253,6 +257,10 @@ W4A16_API int w4a16_sweep_run_device(w4a16_sweep* sweep, const void* d_h_in, voi
  * sweep, copies the result back.  Asynchronous on `stream`; synchronise before reading. */
 W4A16_API int w4a16_sweep_run_host(w4a16_sweep* sweep, const void* h_h_in, void* h_h_out,
                                    w4a16_stream_t stream);
+
+/* 0 after a clean pass; nonzero if a bounded wait of the persistent kernel ran out (1 ring, 2 exchange):
+ * the pass's output is then invalid.  Synchronises the device.  Always 0 for graph-mode sweeps. */
+W4A16_API int w4a16_sweep_status(w4a16_sweep* sweep, int* out);
 
 /* Device pointer of a workspace region, for tests: 0 hidden, 1 q, 2 k, 3 v, 4 mlp. */
 W4A16_API void* w4a16_sweep_buffer(const w4a16_sweep* sweep, int which);

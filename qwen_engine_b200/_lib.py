@@ -67,6 +67,7 @@ SIGNATURES = {
     "w4a16_sweep_run_device": [c_void_p, c_void_p, c_void_p, c_void_p],
     "w4a16_sweep_run_host": [c_void_p, c_void_p, c_void_p, c_void_p],
     "w4a16_sweep_buffer": [c_void_p, c_int],
+    "w4a16_sweep_status": [c_void_p, POINTER(c_int)],
 }
 RESTYPES = {"w4a16_sweep_workspace_bytes": ctypes.c_int64, "w4a16_sweep_buffer": c_void_p}
 

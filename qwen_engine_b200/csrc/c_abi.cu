@@ -310,9 +310,15 @@ int w4a16_gemv_group_dots(const uint32_t* qweight, const int8_t* input_q8, const
 }
 
 int w4a16_debug_counter(int which, unsigned int* out) {
-    if (!out || which < 0 || which > 32) return W4A16_ERR_INVALID_ARG;
+    if (!out || which < 0 || which > 49) return W4A16_ERR_INVALID_ARG;
     if (int st = ensure_device_ready(nullptr)) return st;
     if (which == 0) return gemm_tc_timeouts(out);
+    if (which >= 33) {   // 33..48: persistent sweep, CTA 0: kind*4 + phase, in kilo-cycles; 49: reset them
+        unsigned long long ps[16];
+        if (int st = psweep_prof(ps, which == 49)) return st;
+        *out = which == 49 ? 0u : static_cast<unsigned int>(ps[which - 33] / 1000);
+        return 0;
+    }
     // 1..32: per-role cycle sums of the tensor-core kernel's CTA (0,0); zero unless the library was
     // built with -DW4A16_TC_PROFILE
     unsigned long long prof[32];

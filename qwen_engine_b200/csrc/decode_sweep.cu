@@ -23,6 +23,12 @@ struct w4a16_sweep {
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     int launches = 0;
+    // persistent form
+    bool persistent = false;
+    w4::PSweepArgs pargs{};
+    uint32_t epoch = 0;
+    uint32_t launch_count = 0;
+    int sm_count = 0;
 };
 
 namespace {
@@ -30,10 +36,13 @@ namespace {
 using namespace w4;
 
 constexpr size_t kAlign = 256;
+constexpr size_t kMaxPersistentLayers = 256;   // capacity of the persistent kernel's layer table in the workspace
 size_t align_up(size_t v) { return (v + kAlign - 1) / kAlign * kAlign; }
 
 struct Carve {
     size_t h, q, k, v, mlp, q8, scale, sum8, total;
+    // persistent form: exchange buffers (8-byte tagged words), device copy of the layer table, status word
+    size_t ll_h_attn, ll_h_down, ll_q, ll_mlp, layer_table, status, counters;
 };
 Carve carve(int hidden, int inter, int nq, int nkv, int hd) {
     const size_t kmax = static_cast<size_t>(hidden > inter ? hidden : inter);
@@ -48,6 +57,13 @@ Carve carve(int hidden, int inter, int nq, int nkv, int hd) {
     c.q8 = off; off += align_up(kmax);
     c.scale = off; off += align_up(kmax / 128 * sizeof(float));
     c.sum8 = off; off += align_up(kmax / 8 * sizeof(int32_t));
+    c.ll_h_attn = off; off += align_up(hidden / 2 * 8);
+    c.ll_h_down = off; off += align_up(hidden / 2 * 8);
+    c.ll_q = off; off += align_up(qdim / 2 * 8);
+    c.ll_mlp = off; off += align_up(inter / 2 * 8);
+    c.status = off; off += align_up(sizeof(int));
+    c.counters = off; off += align_up(4 * kMaxPersistentLayers * 32);   // one 32-byte cell per projection
+    c.layer_table = off; off += align_up(kMaxPersistentLayers * w4::psweep_layer_bytes());
     c.total = off;
     return c;
 }
@@ -127,6 +143,15 @@ int issue_pass(w4a16_sweep* s, cudaStream_t stream, int* launches) {
     return 0;
 }
 
+// One pass over the resident hidden state: graph replay, or the persistent kernel with fresh tags.
+int run_pass(w4a16_sweep* s, cudaStream_t stream) {
+    if (!s->persistent) return static_cast<int>(cudaGraphLaunch(s->exec, stream));
+    s->pargs.epoch = s->epoch;
+    s->pargs.counter_target = ++s->launch_count * static_cast<uint32_t>(s->sm_count);
+    s->epoch += 4u * static_cast<uint32_t>(s->desc.num_layers);
+    return w4::psweep_launch(s->pargs, s->sm_count, stream);
+}
+
 }  // namespace
 
 extern "C" {
@@ -174,6 +199,57 @@ int w4a16_sweep_create(const w4a16_sweep_desc* desc, w4a16_stream_t stream_, w4a
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     cudaError_t e = cudaMemsetAsync(s->h, 0, H * sizeof(__half), stream);
     if (e != cudaSuccess) return static_cast<int>(e);
+
+    if (desc->flags & W4A16_SWEEP_PERSISTENT) {
+        const int kvdim = desc->num_kv_heads * desc->head_dim;
+        if (!w4::psweep_supported(H, I, qdim, kvdim) || static_cast<size_t>(desc->num_layers) > kMaxPersistentLayers)
+            return W4A16_ERR_SHAPE;
+        for (const auto& L : s->layers) {
+            const void* w16[] = {L.q_weight, L.k_weight, L.v_weight, L.o_weight, L.gate_up_weight, L.down_weight};
+            const void* s4[] = {L.q_scale, L.k_scale, L.v_scale, L.o_scale, L.gate_up_scale, L.down_scale};
+            for (const void* p : w16)
+                if (reinterpret_cast<uintptr_t>(p) % 16) return W4A16_ERR_ALIGNMENT;   // bulk copies
+            for (const void* p : s4)
+                if (reinterpret_cast<uintptr_t>(p) % 4) return W4A16_ERR_ALIGNMENT;    // 4-byte async copies
+            if (reinterpret_cast<uintptr_t>(L.input_norm_gamma) % 8 || reinterpret_cast<uintptr_t>(L.post_norm_gamma) % 8)
+                return W4A16_ERR_ALIGNMENT;
+        }
+        const w4::DeviceInfo* dev = nullptr;
+        if (int st = w4::ensure_device_ready(&dev)) return st;
+        if (int st = w4::psweep_set_attributes()) return st;
+        std::vector<uint8_t> table(s->layers.size() * w4::psweep_layer_bytes());
+        for (size_t l = 0; l < s->layers.size(); ++l)
+            w4::psweep_fill_layer(table.data() + l * w4::psweep_layer_bytes(), s->layers[l]);
+        uint8_t* d_table = base + c.layer_table;
+        if ((e = cudaMemcpyAsync(d_table, table.data(), table.size(), cudaMemcpyHostToDevice, stream)) != cudaSuccess)
+            return static_cast<int>(e);
+        // tags start above zero, so zeroed exchange buffers never look published
+        if ((e = cudaMemsetAsync(base + c.ll_h_attn, 0, c.layer_table - c.ll_h_attn, stream)) != cudaSuccess)
+            return static_cast<int>(e);
+        if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return static_cast<int>(e);   // `table` is a local
+        s->persistent = true;
+        s->sm_count = dev->sm_count;
+        w4::PSweepArgs& a = s->pargs;
+        a.layers = d_table;
+        a.num_layers = desc->num_layers; a.H = H; a.I = I; a.qdim = qdim; a.kvdim = kvdim;
+        a.h_in = s->h; a.h_out = s->h;
+        a.ll_h_attn = reinterpret_cast<uint2*>(base + c.ll_h_attn);
+        a.ll_h_down = reinterpret_cast<uint2*>(base + c.ll_h_down);
+        a.ll_q = reinterpret_cast<uint2*>(base + c.ll_q);
+        a.ll_mlp = reinterpret_cast<uint2*>(base + c.ll_mlp);
+        a.k_out = s->k; a.v_out = s->v;
+        a.status = reinterpret_cast<int*>(base + c.status);
+        a.counters = reinterpret_cast<uint32_t*>(base + c.counters);
+        s->launches = 1;
+        // one eager pass: validates the launch
+        a.epoch = s->epoch;
+        a.counter_target = ++s->launch_count * static_cast<uint32_t>(s->sm_count);
+        if (int st = w4::psweep_launch(a, s->sm_count, stream)) return st;
+        s->epoch += 4u * static_cast<uint32_t>(desc->num_layers);
+        if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return static_cast<int>(e);
+        *out = s.release();
+        return 0;
+    }
     // one eager pass (sets kernel attributes, validates the launches), then capture
     if (int st = issue_pass(s.get(), stream, &s->launches)) return st;
     if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return static_cast<int>(e);
@@ -215,7 +291,7 @@ int w4a16_sweep_run_device(w4a16_sweep* s, const void* d_h_in, void* d_h_out, w4
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     const size_t bytes = s->desc.hidden_size * sizeof(__half);
     cudaError_t e = cudaMemcpyAsync(s->h, d_h_in, bytes, cudaMemcpyDeviceToDevice, stream);
-    if (e == cudaSuccess) e = cudaGraphLaunch(s->exec, stream);
+    if (e == cudaSuccess) e = static_cast<cudaError_t>(run_pass(s, stream));
     if (e == cudaSuccess) e = cudaMemcpyAsync(d_h_out, s->h, bytes, cudaMemcpyDeviceToDevice, stream);
     return static_cast<int>(e);
 }
@@ -225,9 +301,16 @@ int w4a16_sweep_run_host(w4a16_sweep* s, const void* h_h_in, void* h_h_out, w4a1
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     const size_t bytes = s->desc.hidden_size * sizeof(__half);
     cudaError_t e = cudaMemcpyAsync(s->h, h_h_in, bytes, cudaMemcpyHostToDevice, stream);
-    if (e == cudaSuccess) e = cudaGraphLaunch(s->exec, stream);
+    if (e == cudaSuccess) e = static_cast<cudaError_t>(run_pass(s, stream));
     if (e == cudaSuccess) e = cudaMemcpyAsync(h_h_out, s->h, bytes, cudaMemcpyDeviceToHost, stream);
     return static_cast<int>(e);
+}
+
+int w4a16_sweep_status(w4a16_sweep* s, int* out) {
+    if (!s || !out) return W4A16_ERR_INVALID_ARG;
+    *out = 0;
+    if (!s->persistent) return 0;
+    return static_cast<int>(cudaMemcpy(out, s->pargs.status, sizeof(int), cudaMemcpyDeviceToHost));
 }
 
 void* w4a16_sweep_buffer(const w4a16_sweep* s, int which) {

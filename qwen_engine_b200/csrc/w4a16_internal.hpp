@@ -94,4 +94,28 @@ int gemm_tc_set_attributes();
 int gemm_tc_timeouts(unsigned int* out);
 int gemm_tc_prof(unsigned long long* out);   // zeros unless built with -DW4A16_TC_PROFILE
 
+// ---- persistent one-kernel decode sweep (sweep_persistent.cu) ----
+struct PSweepArgs {
+    const void* layers;   // device array of the kernel's per-layer pointer table
+    int num_layers, H, I, qdim, kvdim;
+    const __half* h_in;   // plain fp16 [H]
+    __half* h_out;        // plain fp16 [H] (may alias h_in)
+    uint2* ll_h_attn;     // [H/2]     tagged words published by the O projection
+    uint2* ll_h_down;     // [H/2]     ... by the down projection
+    uint2* ll_q;          // [qdim/2]
+    uint2* ll_mlp;        // [I/2]
+    __half* k_out;        // plain [kvdim]
+    __half* v_out;        // plain [kvdim]
+    uint32_t epoch;       // tags of this launch are epoch + stage + 1
+    uint32_t* counters;   // [4 * num_layers] at 32-byte spacing: CTAs that have published each stage, ever
+    uint32_t counter_target;   // value a stage counter reaches when all CTAs of THIS launch have published
+    int* status;          // 0 ok; 1 ring wait ran out; 2 tag poll ran out
+};
+size_t psweep_layer_bytes();
+bool psweep_supported(int H, int I, int qdim, int kvdim);
+int psweep_set_attributes();
+void psweep_fill_layer(void* dst, const w4a16_layer_weights& L);
+int psweep_launch(const PSweepArgs& args, int sm_count, cudaStream_t stream);
+int psweep_prof(unsigned long long* out, bool reset);   // zeros unless built with -DW4A16_TC_PROFILE
+
 }  // namespace w4

@@ -23,7 +23,7 @@ __all__ = [
     "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
     "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots", "DecodeSweep",
     "launch_gemv_rmsnorm_w4a16", "launch_gemv_qkv_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16",
-    "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "gemv_w4a16_static_scratch", "debug_counter",
+    "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "gemv_w4a16_static_scratch", "debug_counter",
 ]
 
 # Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
@@ -192,6 +192,7 @@ def gemv_group_dots(qweight, input_q8, input_sum8, out_dots, out_features, in_fe
 
 
 SWEEP_SEPARATE, SWEEP_FUSE_NORM, SWEEP_FUSE_QUANT_O, SWEEP_FUSE_QUANT_DOWN, SWEEP_FUSE_ALL = 0, 1, 2, 4, 7
+SWEEP_PERSISTENT = 8
 
 
 class DecodeSweep:
@@ -233,6 +234,12 @@ class DecodeSweep:
         assert not h_in.is_cuda and not h_out.is_cuda
         check("w4a16_sweep_run_host", load().w4a16_sweep_run_host(self._h, h_in.data_ptr(), h_out.data_ptr(),
                                                                   _stream(stream)))
+
+    def status(self) -> int:
+        """0 after clean passes; nonzero if a bounded wait of the persistent kernel ran out."""
+        v = ctypes.c_int(0)
+        check("w4a16_sweep_status", load().w4a16_sweep_status(self._h, ctypes.byref(v)))
+        return v.value
 
     def buffer_ptr(self, which: int) -> int:
         return load().w4a16_sweep_buffer(self._h, which)
