@@ -40,8 +40,11 @@ def parse():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--suite", default="sweep", choices=["sweep", "shapes"],
-                    help="sweep: the headline line; shapes: per-shape GEMV and M-token GEMM table (configs 0, 3, 4)")
+    ap.add_argument("--suite", default="sweep", choices=["sweep", "shapes", "single"],
+                    help="sweep: the headline line; shapes: per-shape GEMV and M-token GEMM table (configs 0, 3, 4); "
+                         "single: a few launches of one kernel (for ncu captures)")
+    ap.add_argument("--shape", default="gate_up", help="single: qkv | o | gate_up | down | lm_head | big")
+    ap.add_argument("--m", type=int, default=0, help="single: 0 = batch-1 GEMV on Q8_1, else M tokens through the GEMM")
     ap.add_argument("--m-list", default="1,2,4,8,16,32,64,128,512,1024,4096")
     ap.add_argument("--layers", type=int, default=28, help=argparse.SUPPRESS)
     ap.add_argument("--no-cpu-baseline", action="store_true", help=argparse.SUPPRESS)
@@ -228,8 +231,11 @@ def kernel_roofline(torch, ops, layers_dev, stream, peaks, reps=20):
     peak = peaks.get("hbm_gbs")
     src = "measured" if peak else "fallback"
     peak = peak or 6650.0
+    # dram__bytes_read.sum + dram__bytes_write.sum of this kernel per launch, from the ncu capture summarised
+    # in profiles/gemv_gate_up_swiglu_17920x1536.md
+    traffic = 14225408
     res = {"bound": "hbm", "kernel": "gemv_w4_kernel<SwiGLU> (gate_up 17920x1536)", "achieved": achieved, "peak": peak,
-           "unit": "GB/s", "frac": achieved / peak, "traffic": None, "peak_source": f"of {src} (burst copy)",
+           "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "peak_source": f"of {src} (burst copy)",
            "bytes_per_launch": nbytes, "us_per_launch": per_launch_s * 1e6,
            "how": f"CUDA graph of {len(layers_dev)} launches over distinct weights, {reps} replays, CUDA events"}
     return res
@@ -421,8 +427,55 @@ def run_shapes_suite(args):
     print(json.dumps(out), flush=True)
 
 
+def run_single(args):
+    """A handful of launches of one kernel over distinct weight copies (so DRAM counters mean something)."""
+    import torch
+    import qwen_engine_b200 as ops
+    from qwen_engine_b200 import synth
+    torch.cuda.set_device(0)
+    ops.init()
+    shapes = {"qkv": (2048, 1536), "o": (1536, 1536), "gate_up": (17920, 1536), "down": (1536, 8960),
+              "lm_head": (151936, 1536), "big": (28672, 8192)}
+    N, K = shapes[args.shape]
+    g = torch.Generator(device="cuda").manual_seed(1)
+    copies = max(2, min(12, int(np.ceil(2 * 126e6 / synth.weight_bytes(N, K)))))
+    ws = [(torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), dtype=torch.int32, device="cuda", generator=g),
+           (torch.rand((N, K // 128), device="cuda", generator=g) * 0.018 + 0.002).half()) for _ in range(copies)]
+    n_out = N // 2 if args.shape == "gate_up" else N
+    reps = max(1, min(args.steps, 12))
+    if args.m == 0:
+        x = torch.randn(K, device="cuda", generator=g).half()
+        q8 = torch.empty(K, dtype=torch.int8, device="cuda")
+        xs = torch.empty(K // 128, dtype=torch.float32, device="cuda")
+        s8 = torch.empty(K // 8, dtype=torch.int32, device="cuda")
+        y = torch.empty(n_out, dtype=torch.float16, device="cuda")
+        ops.launch_quantize_fp16_to_q8_1(x, q8, xs, s8, K)
+        for i in range(reps):
+            w, sc = ws[i % copies]
+            if args.shape == "gate_up":
+                ops.launch_gemv_dual_gate_up_swiglu_w4a8(w, sc, q8, xs, s8, y, K, n_out)
+            else:
+                ops.launch_gemv_w4a8(w, sc, q8, xs, s8, None, y, N, K)
+    else:
+        M = args.m
+        xm = torch.randn((M, K), device="cuda", generator=g).half()
+        ym = torch.empty((M, n_out), dtype=torch.float16, device="cuda")
+        for i in range(reps):
+            w, sc = ws[i % copies]
+            if args.shape == "gate_up":
+                ops.launch_gemm_prefill_dual_gate_up_swiglu_w4a16(w, sc, xm, ym, M, None, K, n_out)
+            else:
+                ops.launch_gemm_prefill_w4a16(w, sc, xm, None, ym, M, N, K)
+    torch.cuda.synchronize()
+    print(json.dumps({"suite": "single", "shape": args.shape, "m": args.m, "launches": reps, "copies": copies,
+                      "tc_wait_timeouts": ops.debug_counter(0)}), flush=True)
+
+
 def main():
     args = parse()
+    if args.suite == "single":
+        run_single(args)
+        return
     if args.impl == "reference":
         run_reference_arm(args)
         return
@@ -459,7 +512,7 @@ def main():
     h_out = torch.empty_like(h_in)
     pin_in = torch.from_numpy(h0_np).pin_memory()
     pin_out = torch.empty(synth.HIDDEN, dtype=torch.float16).pin_memory()
-    sweep_flags = int(os.environ.get("W4A16_SWEEP_FLAGS", str(ops.SWEEP_FUSE_ALL)))
+    sweep_flags = int(os.environ.get("W4A16_SWEEP_FLAGS", str(ops.SWEEP_DEFAULT)))
     with torch.cuda.stream(stream):
         sweep = ops.DecodeSweep(layers_dev, stream=stream, flags=sweep_flags)
     nbytes = synth.layer_algorithmic_bytes() * len(layers_np)

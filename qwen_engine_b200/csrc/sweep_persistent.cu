@@ -402,7 +402,7 @@ __device__ void consumer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
     int chunk_parity = 0;
     const int num_stages = a.num_layers * 4;
 #ifdef W4A16_TC_PROFILE
-    long long ps_all0 = 0, ps_all1 = 0, ps_all2 = 0, ps_all3 = 0, ps_gu0 = 0, ps_gu1 = 0, ps_gu2 = 0, ps_gu3 = 0,
+    long long ps_ctr = 0; long long ps_all0 = 0, ps_all1 = 0, ps_all2 = 0, ps_all3 = 0, ps_gu0 = 0, ps_gu1 = 0, ps_gu2 = 0, ps_gu3 = 0,
               ps_dn0 = 0, ps_dn1 = 0, ps_dn2 = 0, ps_dn3 = 0;
 #endif
     for (int st = 0; st < num_stages; ++st) {
@@ -428,6 +428,9 @@ __device__ void consumer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
             consumer_sync();
             if (*s_abort) return;
         }
+#ifdef W4A16_TC_PROFILE
+        ps_ctr += clock64() - t_in;
+#endif
         bool ok;
         switch (p.kind) {
             case 0: ok = stage_input_norm(a, a.ll_h_down, st == 0 ? a.h_in : nullptr, in_tag, L.gamma_in, s, s_abort, tid); break;
@@ -590,6 +593,7 @@ __device__ void consumer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
     if (blockIdx.x == 0 && tid == 0) {
         g_ps_prof[0] += ps_all0; g_ps_prof[1] += ps_all1; g_ps_prof[2] += ps_all2; g_ps_prof[3] += ps_all3;
         g_ps_prof[4] += ps_gu0; g_ps_prof[5] += ps_gu1; g_ps_prof[6] += ps_gu2; g_ps_prof[7] += ps_gu3;
+        g_ps_prof[12] += ps_ctr;
         g_ps_prof[8] += ps_dn0; g_ps_prof[9] += ps_dn1; g_ps_prof[10] += ps_dn2; g_ps_prof[11] += ps_dn3;
     }
 #endif

@@ -23,7 +23,7 @@ __all__ = [
     "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
     "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots", "DecodeSweep",
     "launch_gemv_rmsnorm_w4a16", "launch_gemv_qkv_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16",
-    "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "gemv_w4a16_static_scratch", "debug_counter",
+    "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
 ]
 
 # Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
@@ -193,6 +193,8 @@ def gemv_group_dots(qweight, input_q8, input_sum8, out_dots, out_features, in_fe
 
 SWEEP_SEPARATE, SWEEP_FUSE_NORM, SWEEP_FUSE_QUANT_O, SWEEP_FUSE_QUANT_DOWN, SWEEP_FUSE_ALL = 0, 1, 2, 4, 7
 SWEEP_PERSISTENT = 8
+# the fastest measured form on B200: RMSNorm inside QKV / gate_up, Q8_1 inside O, a separate quantiser before down
+SWEEP_DEFAULT = SWEEP_FUSE_NORM | SWEEP_FUSE_QUANT_O
 
 
 class DecodeSweep:
@@ -204,7 +206,7 @@ class DecodeSweep:
     """
 
     def __init__(self, layers, hidden=HIDDEN_SIZE, inter=INTERMEDIATE_SIZE, num_q_heads=NUM_Q_HEADS,
-                 num_kv_heads=NUM_KV_HEADS, head_dim=HEAD_DIM, stream=None, flags=SWEEP_FUSE_ALL):
+                 num_kv_heads=NUM_KV_HEADS, head_dim=HEAD_DIM, stream=None, flags=SWEEP_DEFAULT):
         lib = load()
         self._layers = layers
         self.hidden = hidden
