@@ -309,33 +309,65 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
     # rotate over enough copies of the slab that consecutive steps do not hit L2
     copies = max(1, min(24, int(np.ceil(3 * 126e6 / (qw.nbytes + sc.nbytes)))))
     launch = lambda w, s, a, b, c, out, r, k: ops.launch_gemv_w4a8(w, s, a, b, c, None, out, r, k)
-    shards = []
-    for _ in range(copies):
-        shards.append(nsplit.NSplitGemv(torch.from_numpy(qw.view(np.int32)).cuda(), torch.from_numpy(sc).cuda(),
-                                        N, K, launch))
+    peer_launch = lambda w, s, a, b, c, out, peers, r, k: ops.gemv_w4a8_peers(w, s, a, b, c, out, peers, r, k)
+    d_qw, d_sc = torch.from_numpy(qw.view(np.int32)).cuda(), torch.from_numpy(sc).cuda()
+    slabs = [(d_qw, d_sc)] + [(d_qw.clone(), d_sc.clone()) for _ in range(copies - 1)]
+    nbytes = synth.gemv_algorithmic_bytes(N, K)
     with torch.cuda.stream(stream):
         ops.launch_quantize_fp16_to_q8_1(x, q8, xs, s8, K)
-        i = [0]
+    stream.synchronize()
 
-        def step():
-            shards[i[0] % copies].forward(q8, xs, s8)
-            i[0] += 1
-        for _ in range(max(3, warmup)):
-            step()
-        stream.synchronize()
+    def measure(use_peers):
+        shards = [nsplit.NSplitGemv(w, s, N, K, launch, peer_launch=peer_launch if use_peers else None)
+                  for w, s in slabs]
+        with torch.cuda.stream(stream):
+            def one_round():      # one step per weight copy: GEMV on the local slab, then the exchange
+                for sh in shards:
+                    sh.forward(q8, xs, s8)
+            for _ in range(2):
+                one_round()
+            stream.synchronize()
+            result = shards[0].forward(q8, xs, s8).clone()
+            # replayed as one CUDA graph where the exchange captures, so the host's launch cost is not timed
+            rounds = max(1, (steps + copies - 1) // copies)
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    one_round()
+                run, how = graph.replay, "cuda graph"
+            except Exception:
+                torch.cuda.synchronize()
+                run, how = one_round, "eager"
+            for _ in range(max(1, warmup // copies)):
+                run()
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            ms = timed_events(torch, stream, run, rounds)
+            torch.cuda.synchronize()
+        t = torch.tensor([ms], device="cuda")
         if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        ms = timed_events(torch, stream, step, steps)
-        torch.cuda.synchronize()
-    t = torch.tensor([ms], device="cuda")
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t.item()) * 1e3 / (rounds * copies)
+        return us, how, result
+
+    us_nccl, how_nccl, y_nccl = measure(False)
+    out = {"workload": f"config 2: lm_head {K}->{N}, rows split over {world} GPU(s)", "rows_per_gpu": rows,
+           "unit": UNIT, "scaling": "strong", "weight_copies_rotated": copies,
+           "nccl_all_gather": {"us_per_step": us_nccl, "value": nbytes / (us_nccl * 1e-6) / 1e9, "timed_as": how_nccl}}
+    best = us_nccl
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    us = float(t.item()) * 1e3 / steps
-    nbytes = synth.gemv_algorithmic_bytes(N, K)
-    return {"workload": f"config 2: lm_head {K}->{N}, rows split over {world} GPU(s), NCCL all-gather of fp16 slices",
-            "rows_per_gpu": rows, "us_per_step": us, "value": nbytes / (us * 1e-6) / 1e9, "unit": UNIT,
-            "scaling": "strong", "weight_copies_rotated": copies}
+        try:
+            us_peer, how_peer, y_peer = measure(True)
+            out["peer_store_epilogue"] = {"us_per_step": us_peer, "value": nbytes / (us_peer * 1e-6) / 1e9,
+                                          "timed_as": how_peer, "equals_nccl_result": bool(torch.equal(y_nccl, y_peer))}
+            best = min(best, us_peer)
+        except Exception as e:   # no peer access / symmetric memory on this box
+            out["peer_store_epilogue"] = {"unavailable": str(e)[:200]}
+    out["us_per_step"] = best
+    out["value"] = nbytes / (best * 1e-6) / 1e9
+    return out
 
 
 def run_shapes_suite(args):

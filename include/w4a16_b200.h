@@ -107,6 +107,20 @@ W4A16_API int w4a16_gemv_w4a8(const uint32_t* qweight, const void* scales, const
                               const void* residual, void* output_y, int out_features,
                               int in_features, w4a16_stream_t stream);
 
+/*
+ * w4a16_gemv_w4a8 whose epilogue also stores the output slice into up to 7 more buffers -- the same
+ * slice position in the gathered output of every PEER GPU, whose memory is mapped into this process
+ * (CUDA IPC / symmetric memory); the stores are plain stores that travel over NVLink.  With the rows of
+ * a large projection (lm_head) split over the GPUs of a node, this replaces the all-gather that would
+ * follow the GEMV; the caller orders the ranks afterwards (a barrier on the stream) before reading.
+ * No counterpart in the reference, which is single-GPU.  peer_outputs[i] points at element 0 of THIS
+ * rank's slice inside peer i's buffer.
+ */
+W4A16_API int w4a16_gemv_w4a8_peers(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                                    const float* input_scale, const int32_t* input_sum8, void* output_y,
+                                    void* const* peer_outputs, int num_peers, int out_features,
+                                    int in_features, w4a16_stream_t stream);
+
 /* reference include/kernels.cuh:84-94 launch_gemv_qkv_w4a8 (src/kernels/gemv_w4a16.cu:123-194,
  * 387-513, 893-926): q, k and v projections in one launch. */
 W4A16_API int w4a16_gemv_qkv_w4a8(const w4a16_qkv_view* view, const int8_t* input_q8,

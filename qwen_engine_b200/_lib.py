@@ -44,6 +44,8 @@ SIGNATURES = {
     "w4a16_gemv_w4a16_static_scratch": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "w4a16_gemv_w4a8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                         c_void_p],
+    "w4a16_gemv_w4a8_peers": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(c_void_p), c_int,
+                              c_int, c_int, c_void_p],
     "w4a16_gemv_qkv_w4a8": [POINTER(QKVView), c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int],
     "w4a16_gemv_dual_gate_up_swiglu_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "w4a16_gemv_dual_gate_up_swiglu_w4a8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,

@@ -129,7 +129,8 @@ int w4a16_rmsnorm_q8_1(const void* input, const void* gamma, void* output_fp16_o
 
 static int gemv_plain(const uint32_t* qweight, const void* scales, const void* x_fp16, const int8_t* q8,
                       const float* xscale, const int32_t* sum8, const void* residual, void* y, int N, int K,
-                      w4a16_stream_t stream, const void* gamma = nullptr) {
+                      w4a16_stream_t stream, const void* gamma = nullptr, void* const* peers = nullptr,
+                      int num_peers = 0) {
     if (!qweight || !scales || !y || N <= 0) return W4A16_ERR_INVALID_ARG;
     if (int st = check_k(K)) return st;
     if (misaligned(qweight, 4) || misaligned(scales, 2) || misaligned(y, 2) || misaligned(residual, 2) ||
@@ -141,6 +142,13 @@ static int gemv_plain(const uint32_t* qweight, const void* scales, const void* x
     a.residual = H(residual);
     a.K = K; a.units = N;
     if (misaligned(gamma, 8)) return W4A16_ERR_ALIGNMENT;
+    if (num_peers < 0 || num_peers > 7 || (num_peers > 0 && !peers)) return W4A16_ERR_INVALID_ARG;
+    for (int p = 0; p < num_peers; ++p) {
+        if (!peers[p]) return W4A16_ERR_INVALID_ARG;
+        if (misaligned(peers[p], 2)) return W4A16_ERR_ALIGNMENT;
+        a.peer_out[p] = H(peers[p]);
+    }
+    a.num_peers = num_peers;
     return gemv_launch(kPlain, a, S(stream));
 }
 
@@ -157,6 +165,15 @@ int w4a16_gemv_w4a8(const uint32_t* qweight, const void* scales, const int8_t* i
     if (!input_q8 || !input_scale || !input_sum8) return W4A16_ERR_INVALID_ARG;
     return gemv_plain(qweight, scales, nullptr, input_q8, input_scale, input_sum8, residual, output_y, out_features,
                       in_features, stream);
+}
+
+int w4a16_gemv_w4a8_peers(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                          const float* input_scale, const int32_t* input_sum8, void* output_y,
+                          void* const* peer_outputs, int num_peers, int out_features, int in_features,
+                          w4a16_stream_t stream) {
+    if (!input_q8 || !input_scale || !input_sum8) return W4A16_ERR_INVALID_ARG;
+    return gemv_plain(qweight, scales, nullptr, input_q8, input_scale, input_sum8, nullptr, output_y, out_features,
+                      in_features, stream, nullptr, peer_outputs, num_peers);
 }
 
 static int fill_qkv(const w4a16_qkv_view* v, int nq, int nkv, int hd, const uint32_t* qw[3], const __half* sc[3],

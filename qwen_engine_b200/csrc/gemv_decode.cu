@@ -167,7 +167,11 @@ __global__ void __launch_bounds__(kMaxThreads) gemv_w4_kernel(const GemvArgs a) 
                 if (a.residual != nullptr) y += __half2float(a.residual[unit]);
             }
         }
-        *out_ptr = __float2half_rn(y);
+        const __half yh = __float2half_rn(y);
+        *out_ptr = yh;
+        if constexpr (MODE == kPlain) {
+            for (int p = 0; p < a.num_peers; ++p) a.peer_out[p][unit] = yh;   // slice into every peer's buffer
+        }
     }
 }
 

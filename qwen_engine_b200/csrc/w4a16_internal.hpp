@@ -60,6 +60,10 @@ struct GemvArgs {
     const __half* x_fp16;
     const __half* gamma;     // with x_fp16: RMSNorm gain applied before the quantiser (null = no norm)
     const __half* residual;  // PLAIN only, may be null, may alias out[0]
+    // PLAIN only: the same output slice is also stored into these buffers (peer GPUs' memory mapped into
+    // this process: plain stores travel over NVLink)
+    __half* peer_out[7];
+    int num_peers;
     int K;
     int units;  // outputs produced: rows (PLAIN, QKV total) or row pairs (SWIGLU)
     // filled in by the planner

@@ -44,7 +44,10 @@ class NSplitGemv:
     """
 
     def __init__(self, qweight_slab: torch.Tensor, scales_slab: torch.Tensor, n_rows: int, in_features: int,
-                 launch, group=None, align: int = 1):
+                 launch, group=None, align: int = 1, peer_launch=None):
+        """peer_launch (optional, GPUs with peer access only): launch(qw, sc, q8, xs, s8, out_slice, peer_ptrs,
+        rows, K) whose epilogue also writes the slice into every peer's gathered buffer; the gathered buffer
+        then lives in symmetric memory and the all-gather becomes a barrier."""
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -54,7 +57,18 @@ class NSplitGemv:
             raise ValueError(f"rank {self.rank} expects a slab of {self.slab.rows} rows")
         self.qweight, self.scales, self.launch = qweight_slab, scales_slab, launch
         # gathered buffer: world x stride halves; rank r's slice starts at r * stride
-        self.gathered = torch.empty(self.world * self.slab.stride, dtype=torch.float16, device=qweight_slab.device)
+        self.peer_launch = peer_launch if self.world > 1 else None
+        self.symm = None
+        if self.peer_launch is not None:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.gathered = symm_mem.empty(self.world * self.slab.stride, dtype=torch.float16,
+                                           device=qweight_slab.device)
+            self.symm = symm_mem.rendezvous(self.gathered, group=group if group is not None else dist.group.WORLD)
+            off = self.rank * self.slab.stride * 2          # this rank's slice, in bytes, inside every buffer
+            self.peer_ptrs = [int(self.symm.buffer_ptrs[r]) + off for r in range(self.world) if r != self.rank]
+        else:
+            self.gathered = torch.empty(self.world * self.slab.stride, dtype=torch.float16,
+                                        device=qweight_slab.device)
 
     def local_slice(self) -> torch.Tensor:
         s = self.slab
@@ -63,10 +77,16 @@ class NSplitGemv:
     def forward(self, q8, xscale, sum8) -> torch.Tensor:
         """Returns the full fp16 output [n_rows] (a view of the gathered buffer when no padding exists)."""
         mine = self.local_slice()
-        if self.slab.rows > 0:
-            self.launch(self.qweight, self.scales, q8, xscale, sum8, mine, self.slab.rows, self.K)
-        if self.world > 1:
-            dist.all_gather_into_tensor(self.gathered, mine, group=self.group)
+        if self.peer_launch is not None:
+            if self.slab.rows > 0:
+                self.peer_launch(self.qweight, self.scales, q8, xscale, sum8, mine, self.peer_ptrs, self.slab.rows,
+                                 self.K)
+            self.symm.barrier()      # every rank's stores have landed before anyone reads the gathered vector
+        else:
+            if self.slab.rows > 0:
+                self.launch(self.qweight, self.scales, q8, xscale, sum8, mine, self.slab.rows, self.K)
+            if self.world > 1:
+                dist.all_gather_into_tensor(self.gathered, mine, group=self.group)
         if self.world * self.slab.stride == self.n_rows:
             return self.gathered
         # padded layout -> compact

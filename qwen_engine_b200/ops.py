@@ -23,7 +23,7 @@ __all__ = [
     "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
     "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots", "DecodeSweep",
     "launch_gemv_rmsnorm_w4a16", "launch_gemv_qkv_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16",
-    "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
+    "gemv_w4a8_peers", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
 ]
 
 # Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
@@ -111,6 +111,16 @@ def launch_gemv_w4a8(qweight, scales, input_q8, input_scale, input_sum8, residua
     check("w4a16_gemv_w4a8", load().w4a16_gemv_w4a8(
         _ptr(qweight), _ptr(scales), _ptr(input_q8), _ptr(input_scale), _ptr(input_sum8), _ptr(residual),
         _ptr(output_y), out_features, in_features, _stream(stream)))
+
+
+def gemv_w4a8_peers(qweight, scales, input_q8, input_scale, input_sum8, output_y, peer_ptrs, out_features,
+                    in_features, stream=None):
+    """launch_gemv_w4a8 that also stores its output slice at the device addresses `peer_ptrs` (the slice's
+    place in each peer GPU's gathered buffer, mapped into this process)."""
+    arr = (ctypes.c_void_p * max(1, len(peer_ptrs)))(*peer_ptrs)
+    check("w4a16_gemv_w4a8_peers", load().w4a16_gemv_w4a8_peers(
+        _ptr(qweight), _ptr(scales), _ptr(input_q8), _ptr(input_scale), _ptr(input_sum8), _ptr(output_y), arr,
+        len(peer_ptrs), out_features, in_features, _stream(stream)))
 
 
 def launch_gemv_qkv_w4a8(view: QKVProjectionView, input_q8, input_scale, input_sum8, stream=None,
