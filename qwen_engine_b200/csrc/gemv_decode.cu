@@ -251,7 +251,8 @@ Plan make_plan(int units, int K, int sm_count) {
     p.units_per_cta = upc;
     p.ksplit = ksplit;
     p.steps_per_split = per;
-    p.U = per <= 4 ? 4 : 8;
+    static const int force_u = env_int("W4A16_GEMV_U", 0);
+    p.U = force_u == 4 || force_u == 8 ? force_u : (per <= 4 ? 4 : 8);
     return p;
 }
 
