@@ -211,7 +211,7 @@ int w4a16_sweep_create(const w4a16_sweep_desc* desc, w4a16_stream_t stream_, w4a
                 if (reinterpret_cast<uintptr_t>(p) % 16) return W4A16_ERR_ALIGNMENT;   // bulk copies
             for (const void* p : s4)
                 if (reinterpret_cast<uintptr_t>(p) % 4) return W4A16_ERR_ALIGNMENT;    // 4-byte async copies
-            if (reinterpret_cast<uintptr_t>(L.input_norm_gamma) % 8 || reinterpret_cast<uintptr_t>(L.post_norm_gamma) % 8)
+            if (reinterpret_cast<uintptr_t>(L.input_norm_gamma) % 16 || reinterpret_cast<uintptr_t>(L.post_norm_gamma) % 16)
                 return W4A16_ERR_ALIGNMENT;
         }
         const w4::DeviceInfo* dev = nullptr;

@@ -272,23 +272,39 @@ struct ConsumerSmem {
     float* inv;        // [1]
 };
 
-// Quantises one group held by a warp (lane owns 4 consecutive elements) into the staged layout.
-__device__ __forceinline__ void quantize_group_to_smem(const float v[4], int g, int lane, const ConsumerSmem& s) {
-    float d;
-    const uint32_t packed = quantize_group128_lane(v, &d);
-    reinterpret_cast<uint32_t*>(s.q8)[g * (kGroup / 4) + lane] = packed;
-    int32_t sum = byte_sum(packed);
+// Half-warp form of the group quantiser: 16 lanes per group of 128, lane owns 8 consecutive elements, so the
+// two halves of a warp quantise two groups at once.  Same arithmetic (and bits) as quantize_group128_lane.
+// hl = lane & 15.  Inactive half-warps pass on = false and still take part in the shuffles.
+__device__ __forceinline__ void quantize_group_halfwarp(const float v[8], int g, int hl, bool on, const ConsumerSmem& s) {
+    float m = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[j]));
+#pragma unroll
+    for (int mask = 8; mask > 0; mask >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, mask));
+    const float d = fmaxf(__fdiv_rn(m, 127.0f), 1e-8f);
+    const float inv_d = __fdiv_rn(1.0f, d);
+    uint32_t packed[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        int q = __float2int_rn(__fmul_rn(v[j], inv_d));
+        q = max(-127, min(127, q));
+        packed[j >> 2] |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * (j & 3));
+    }
+    int32_t sum = byte_sum(packed[0]) + byte_sum(packed[1]);     // 8 of the 32 elements of a chunk
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
-    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
-    if ((lane & 7) == 0) s.seed[g * 4 + (lane >> 3)] = -8 * sum;
-    if (lane == 0) s.xscale[g] = d;
+    if (on) {
+        reinterpret_cast<uint2*>(s.q8)[g * (kGroup / 8) + hl] = make_uint2(packed[0], packed[1]);
+        if ((hl & 3) == 0) s.seed[g * 4 + (hl >> 2)] = -8 * sum;
+        if (hl == 0) s.xscale[g] = d;
+    }
 }
 
 // Input of a stage WITH RMSNorm (QKV, gate_up): the residual stream, H elements.  Fetches it into
 // s.h (the later residual add reads it there), then normalises + quantises from there.
 __device__ bool stage_input_norm(const PSweepArgs& a, const uint2* ll, const __half* plain, uint32_t tag,
-                                 const __half* gamma, const ConsumerSmem& s, volatile int* s_abort, int tid) {
+                                 const uint4* gamma_regs, int ngam, const ConsumerSmem& s, volatile int* s_abort,
+                                 int tid) {
     const int H = a.H, words = H / 2;
     const int lane = tid & 31, warp = tid >> 5;
     double ss = 0.0;
@@ -318,23 +334,35 @@ __device__ bool stage_input_norm(const PSweepArgs& a, const uint2* ll, const __h
     for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, m);
     if (lane == 0) s.red[warp] = ss;
     consumer_sync();
-    if (tid == 0) {
-        double t = 0.0;
-        for (int w = 0; w < kConsumerWarps; ++w) t += s.red[w];
-        *s.inv = static_cast<float>(1.0 / sqrt(t / static_cast<double>(H) + static_cast<double>(kEps)));
-    }
-    consumer_sync();
-    const __half2 inv2 = __float2half2_rn(*s.inv);
-    for (int g = warp; g < H / kGroup; g += kConsumerWarps) {
-        const uint2 xr = *reinterpret_cast<const uint2*>(s.h + g * kGroup + lane * 4);
-        const uint2 gr = *reinterpret_cast<const uint2*>(gamma + g * kGroup + lane * 4);
-        const __half2 y0 = __hmul2(__hmul2(*reinterpret_cast<const __half2*>(&xr.x), inv2),
-                                   *reinterpret_cast<const __half2*>(&gr.x));
-        const __half2 y1 = __hmul2(__hmul2(*reinterpret_cast<const __half2*>(&xr.y), inv2),
-                                   *reinterpret_cast<const __half2*>(&gr.y));
-        const float2 f0 = __half22float2(y0), f1 = __half22float2(y1);
-        const float v[4] = {f0.x, f0.y, f1.x, f1.y};
-        quantize_group_to_smem(v, g, lane, s);
+    // every warp adds the per-warp sums itself (same order everywhere): no second barrier, no serial thread
+    double t = lane < kConsumerWarps ? s.red[lane] : 0.0;
+#pragma unroll
+    for (int m = 8; m > 0; m >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, m);
+    t = __shfl_sync(0xFFFFFFFFu, t, 0);
+    const float inv = static_cast<float>(1.0 / sqrt(t / static_cast<double>(H) + static_cast<double>(kEps)));
+    const __half2 inv2 = __float2half2_rn(inv);
+    // quantise: half-warp per group, the gain was fetched before the wait (gamma_regs[i] = group 2*(warp + i*W) + half)
+    const int hl = lane & 15, half = lane >> 4;
+    const int groups = H / kGroup;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (i < ngam) {
+            const int g = 2 * (warp + i * kConsumerWarps) + half;
+            const bool on = g < groups;
+            const uint4 xr = *reinterpret_cast<const uint4*>(s.h + (on ? g : 0) * kGroup + hl * 8);
+            const uint4 gr = gamma_regs[i];
+            const uint32_t xw[4] = {xr.x, xr.y, xr.z, xr.w}, gw[4] = {gr.x, gr.y, gr.z, gr.w};
+            float v[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const __half2 y = __hmul2(__hmul2(*reinterpret_cast<const __half2*>(&xw[k]), inv2),
+                                          *reinterpret_cast<const __half2*>(&gw[k]));
+                const float2 f = __half22float2(y);
+                v[2 * k] = f.x;
+                v[2 * k + 1] = f.y;
+            }
+            quantize_group_halfwarp(v, g, hl, on, s);
+        }
     }
     return true;
 }
@@ -344,24 +372,30 @@ __device__ bool stage_input_norm(const PSweepArgs& a, const uint2* ll, const __h
 __device__ bool stage_input_plain(const PSweepArgs& a, const uint2* ll, int n, uint32_t tag, const ConsumerSmem& s,
                                   volatile int* s_abort, int tid) {
     const int lane = tid & 31, warp = tid >> 5;
+    const int hl = lane & 15, half = lane >> 4;
     const int groups = n / kGroup;
-    constexpr int MAXG = (kMaxK / kGroup + kConsumerWarps - 1) / kConsumerWarps;   // groups per warp at most
-    uint32_t data[2 * MAXG];
-    // word 2i / 2i+1 of this thread: elements 4*lane .. 4*lane+3 of group (warp + i * warps)
-    auto idx = [warp, lane](int w) { return (warp + (w >> 1) * kConsumerWarps) * (kGroup / 2) + 2 * lane + (w & 1); };
+    // half-warp per group: group of round i = 2 * (warp + i * warps) + half; lane owns elements 8*hl .. 8*hl+7
+    constexpr int MAXR = (kMaxK / kGroup + 2 * kConsumerWarps - 1) / (2 * kConsumerWarps);   // rounds per warp
+    uint32_t data[4 * MAXR];
+    auto grp = [warp, half](int i) { return 2 * (warp + i * kConsumerWarps) + half; };
+    auto idx = [grp, hl](int w) { return grp(w >> 2) * (kGroup / 2) + 4 * hl + (w & 3); };
     int count = 0;
 #pragma unroll
-    for (int i = 0; i < MAXG; ++i)
-        if (warp + i * kConsumerWarps < groups) count = 2 * i + 2;
-    if (!poll_words<2 * MAXG>(ll, idx, count, tag, data, s_abort, a.status)) return false;
+    for (int i = 0; i < MAXR; ++i)
+        if (grp(i) < groups) count = 4 * i + 4;
+    if (!poll_words<4 * MAXR>(ll, idx, count, tag, data, s_abort, a.status)) return false;
+    const int rounds = (groups + 2 * kConsumerWarps - 1) / (2 * kConsumerWarps);
 #pragma unroll
-    for (int i = 0; i < MAXG; ++i) {
-        const int g = warp + i * kConsumerWarps;
-        if (g < groups) {
-            const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&data[2 * i]));
-            const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&data[2 * i + 1]));
-            const float v[4] = {f0.x, f0.y, f1.x, f1.y};
-            quantize_group_to_smem(v, g, lane, s);
+    for (int i = 0; i < MAXR; ++i) {
+        if (i < rounds) {       // uniform across the warp: both halves shuffle together
+            float v[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&data[4 * i + k]));
+                v[2 * k] = f.x;
+                v[2 * k + 1] = f.y;
+            }
+            quantize_group_halfwarp(v, grp(i), hl, grp(i) < groups, s);
         }
     }
     return true;
@@ -412,6 +446,20 @@ __device__ void consumer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
         const uint32_t out_tag = a.epoch + static_cast<uint32_t>(st) + 1;
         // ---- 1. the activation vector of this projection ----
         [[maybe_unused]] long long t_in = PS_T();
+        // RMSNorm gains of this thread's groups: constant data, fetched before the wait
+        uint4 gamma_regs[2] = {};
+        int ngam = 0;
+        if (p.kind == 0 || p.kind == 2) {
+            const __half* gamma = p.kind == 0 ? L.gamma_in : L.gamma_post;
+            const int groups = a.H / kGroup;
+            ngam = (groups + 2 * kConsumerWarps - 1) / (2 * kConsumerWarps);   // <= 2 for H <= 4096... checked on the host
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int g = 2 * ((tid >> 5) + i * kConsumerWarps) + ((tid & 31) >> 4);
+                if (i < ngam && g < groups)
+                    gamma_regs[i] = *reinterpret_cast<const uint4*>(gamma + g * kGroup + (tid & 15) * 8);
+            }
+        }
         if (st > 0) {
             // one thread waits until every CTA has published the previous projection
             if (tid == 0) {
@@ -433,9 +481,9 @@ __device__ void consumer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
 #endif
         bool ok;
         switch (p.kind) {
-            case 0: ok = stage_input_norm(a, a.ll_h_down, st == 0 ? a.h_in : nullptr, in_tag, L.gamma_in, s, s_abort, tid); break;
+            case 0: ok = stage_input_norm(a, a.ll_h_down, st == 0 ? a.h_in : nullptr, in_tag, gamma_regs, ngam, s, s_abort, tid); break;
             case 1: ok = stage_input_plain(a, a.ll_q, a.qdim, in_tag, s, s_abort, tid); break;
-            case 2: ok = stage_input_norm(a, a.ll_h_attn, nullptr, in_tag, L.gamma_post, s, s_abort, tid); break;
+            case 2: ok = stage_input_norm(a, a.ll_h_attn, nullptr, in_tag, gamma_regs, ngam, s, s_abort, tid); break;
             default: ok = stage_input_plain(a, a.ll_mlp, a.I, in_tag, s, s_abort, tid); break;
         }
         if (!ok) return;
