@@ -25,9 +25,10 @@ int gemm_launch(GemmArgs g, cudaStream_t stream) {
     const DeviceInfo* dev = nullptr;
     if (int st = ensure_device_ready(&dev)) return st;
 
-    // Token counts from one tensor-core tile upwards go to the tcgen05 kernel; below that (and for
-    // pointers or shapes TMA cannot address) the CUDA-core weight-streaming kernel runs.
-    static const int tc_min_m = env_int("W4A16_TC_MIN_M", 16);
+    // The tcgen05 kernel pads the token count to its smallest tile (16) and is already faster than the
+    // CUDA-core weight-streaming kernel from a handful of tokens (measured crossover on B200: 3-5 tokens
+    // depending on the shape); the CUDA-core kernel serves 1-3 tokens and pointers or shapes TMA cannot address.
+    static const int tc_min_m = env_int("W4A16_TC_MIN_M", 4);
     if (g.M >= tc_min_m && gemm_tc_supported(g)) return gemm_tc_launch(g, dev->sm_count, stream);
 
     SmallMArgs a;

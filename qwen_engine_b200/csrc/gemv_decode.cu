@@ -175,6 +175,91 @@ __global__ void __launch_bounds__(kMaxThreads) gemv_w4_kernel(const GemvArgs a) 
     }
 }
 
+// Streaming form for very tall matrices (lm_head): a persistent grid, each CTA walks row blocks of 32 with
+// the weights of the NEXT block already in flight while the current one is reduced, and the lane's share
+// of the quantised activation lives in registers for the whole launch (a lane always meets the same
+// 16-byte chunks l, l+8, ... of every row).  PLAIN mode, 16-byte aligned weights, K <= 256 * STEPS.
+template <int XIN, int STEPS, bool SWIGLU>
+__global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const GemvArgs a, const int num_blocks) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int K = a.K;
+    int8_t* s_q8 = reinterpret_cast<int8_t*>(smem);
+    int32_t* s_seed = reinterpret_cast<int32_t*>(smem + K);
+    float* s_scale = reinterpret_cast<float*>(smem + K + (K / kChunk) * 4);
+
+    const int tid = threadIdx.x, sub = tid >> 3, l = tid & 7;
+    const int words = K / 8, groups = K / kGroup, steps = K / kStepElems;
+    const int N = SWIGLU ? 2 * a.units : a.units;   // weight rows (SwiGLU: gate/up pairs = adjacent sub-warps)
+
+    uint4 w0[STEPS], w1[STEPS];
+    uint16_t sb0[STEPS], sb1[STEPS];
+    auto issue = [&](uint4 (&w)[STEPS], uint16_t (&sb)[STEPS], int blk) {
+        const int row = blk * kMaxSubwarps + sub;
+        const bool on_row = row < N;
+        const uint32_t* wrow = a.qweight[0] + static_cast<size_t>(on_row ? row : 0) * words;
+        const __half* srow = a.scales[0] + static_cast<size_t>(on_row ? row : 0) * groups;
+#pragma unroll
+        for (int i = 0; i < STEPS; ++i) {
+            if (on_row && i < steps) {
+                w[i] = ld_weights_16(wrow + (i * kSubwarp + l) * 4);
+                sb[i] = ld_scale_bits(srow + 2 * i + (l >> 2));
+            } else {
+                w[i] = make_uint4(0, 0, 0, 0);
+                sb[i] = 0;
+            }
+        }
+    };
+
+    int blk = blockIdx.x;
+    if (blk < num_blocks) issue(w0, sb0, blk);
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    if constexpr (XIN == kXFp16Norm) stage_x_from_fp16_rmsnorm(a.x_fp16, a.gamma, K, kRmsEps, s_q8, s_seed, s_scale);
+    else if constexpr (XIN == kXFp16) stage_x_from_fp16(a.x_fp16, K, s_q8, s_seed, s_scale);
+    else stage_x_from_q8_1(a.q8, a.xscale, a.sum8, K, a.vec_ok != 0, s_q8, s_seed, s_scale);
+    __syncthreads();
+
+    uint4 xa[STEPS], xb[STEPS];
+    int32_t seed[STEPS];
+    float xs[STEPS];
+#pragma unroll
+    for (int i = 0; i < STEPS; ++i) {
+        const int c = (i < steps ? i : 0) * kSubwarp + l;
+        xa[i] = reinterpret_cast<const uint4*>(s_q8)[2 * c];
+        xb[i] = reinterpret_cast<const uint4*>(s_q8)[2 * c + 1];
+        seed[i] = s_seed[c];
+        xs[i] = i < steps ? s_scale[c >> 2] : 0.0f;     // a zero factor switches an unused slot off
+    }
+
+    for (; blk < num_blocks; blk += gridDim.x) {
+        const int nxt = blk + gridDim.x;
+        if (nxt < num_blocks) issue(w1, sb1, nxt);
+        float acc = 0.0f;
+#pragma unroll
+        for (int i = 0; i < STEPS; ++i) {
+            const int32_t d = chunk_dot(w0[i], xa[i], xb[i], seed[i]);
+            acc = fmaf(static_cast<float>(d), __half2float(__ushort_as_half(sb0[i])) * xs[i], acc);
+        }
+        acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 4);
+        acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 2);
+        acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
+        const int row = blk * kMaxSubwarps + sub;
+        if constexpr (SWIGLU) {
+            const float up = __shfl_xor_sync(0xFFFFFFFFu, acc, 8);   // the odd row's sum sits 8 lanes over
+            if (l == 0 && (sub & 1) == 0 && row < N)
+                a.out[0][row >> 1] = __float2half_rn((acc / (1.0f + expf(-acc))) * up);
+        } else if (l == 0 && row < N) {
+            float y = acc;
+            if (a.residual != nullptr) y += __half2float(a.residual[row]);
+            const __half yh = __float2half_rn(y);
+            a.out[0][row] = yh;
+            for (int p = 0; p < a.num_peers; ++p) a.peer_out[p][row] = yh;
+        }
+#pragma unroll
+        for (int i = 0; i < STEPS; ++i) { w0[i] = w1[i]; sb0[i] = sb1[i]; }
+    }
+}
+
 // Diagnostic: the per-group int32 dots, through the same staging and chunk_dot as above.
 __global__ void __launch_bounds__(kMaxThreads) gemv_group_dots_kernel(const uint32_t* __restrict__ qweight,
                                                                        const int8_t* __restrict__ q8,
@@ -334,6 +419,30 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
     const int block = (threads + 31) / 32 * 32;
 
     cudaError_t e;
+    // very tall PLAIN matrices: persistent streaming kernel (two CTAs per SM, >= 8 row blocks each)
+    static const int stream_on = env_int("W4A16_GEMV_STREAM", 1);
+    const int steps = a.K / kStepElems;
+    const int weight_rows = mode == kSwiglu ? 2 * a.units : a.units;
+    const int num_blocks = (weight_rows + kMaxSubwarps - 1) / kMaxSubwarps;
+    static const int stream_min_blocks = env_int("W4A16_GEMV_STREAM_MIN", 16);   // row blocks per SM from which it pays
+    static const int stream_swiglu = env_int("W4A16_GEMV_STREAM_SWIGLU", 0);
+    const bool tall = num_blocks >= stream_min_blocks * dev->sm_count;
+    if (stream_on && aligned16 && steps <= 8 &&
+        ((mode == kPlain && tall) || (mode == kSwiglu && (tall || (stream_swiglu && num_blocks >= 3 * dev->sm_count))))) {
+        const dim3 sgrid(std::min(num_blocks, 2 * dev->sm_count)), sblock(kMaxThreads);
+        const size_t ssmem = staged_x_bytes(a.K);
+        const bool pdl = pdl_enabled();
+#define W4_STREAM2(XINV, SW)                                                                                               \
+    (steps <= 4 ? launch_kernel(gemv_w4_stream_kernel<XINV, 4, SW>, sgrid, sblock, ssmem, stream, pdl, a, num_blocks)     \
+     : steps <= 6 ? launch_kernel(gemv_w4_stream_kernel<XINV, 6, SW>, sgrid, sblock, ssmem, stream, pdl, a, num_blocks)  \
+                  : launch_kernel(gemv_w4_stream_kernel<XINV, 8, SW>, sgrid, sblock, ssmem, stream, pdl, a, num_blocks))
+#define W4_STREAM(XINV) (mode == kSwiglu ? W4_STREAM2(XINV, true) : W4_STREAM2(XINV, false))
+        if (a.x_fp16 != nullptr) e = a.gamma != nullptr ? W4_STREAM(kXFp16Norm) : W4_STREAM(kXFp16);
+        else e = W4_STREAM(kXQ8);
+#undef W4_STREAM
+#undef W4_STREAM2
+        return static_cast<int>(e);
+    }
     switch (mode) {
         case kPlain: e = launch_mode<kPlain>(a, p.U, aligned16, dim3(grid), dim3(block), smem, stream); break;
         case kQkv: e = launch_mode<kQkv>(a, p.U, aligned16, dim3(grid), dim3(block), smem, stream); break;
