@@ -107,6 +107,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false if the barrier did not flip within the limit or another role gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_test_wait(bar, parity)) return true;   // already complete: no need to park the thread
     for (unsigned it = 0; it < kWaitLimit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;

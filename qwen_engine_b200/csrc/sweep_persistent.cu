@@ -89,7 +89,17 @@ __device__ __forceinline__ bool bar_try_wait(uint32_t bar, uint32_t parity) {
         : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool bar_test_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (bar_test_wait(bar, parity)) return true;   // the common case (data already there) without parking the thread
     for (unsigned it = 0; it < kPollLimit; ++it) {
         if (bar_try_wait(bar, parity)) return true;
         if (*abort_flag) return false;

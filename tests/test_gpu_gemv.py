@@ -89,7 +89,9 @@ SHAPES = [
     (17, 256, True),       # ragged N
     (1000, 2560, True),
     (5000, 1536, False),
-    (151936, 1536, False),  # lm_head
+    (151936, 1536, False),  # lm_head: tall enough for the persistent streaming kernel
+    (80000, 1536, True),    # streaming kernel with an in-place residual and a ragged last row block
+    (76001, 1024, False),   # streaming kernel, 4 steps per lane, odd row count
 ]
 
 
