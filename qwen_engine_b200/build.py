@@ -50,6 +50,8 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     cmd = [nvcc(), *NVCC_FLAGS]
     if os.environ.get("W4A16_TC_PROFILE"):
         cmd += ["-DW4A16_TC_PROFILE"]
+    if os.environ.get("W4A16_GEMV_PROFILE"):
+        cmd += ["-DW4A16_GEMV_PROFILE"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
     cmd += ["-o", str(LIB), *[str(CSRC / s) for s in SOURCES]]

@@ -327,8 +327,13 @@ int w4a16_gemv_group_dots(const uint32_t* qweight, const int8_t* input_q8, const
 }
 
 int w4a16_debug_counter(int which, unsigned int* out) {
-    if (!out || which < 0 || which > 49) return W4A16_ERR_INVALID_ARG;
+    if (!out || which < 0) return W4A16_ERR_INVALID_ARG;
     if (int st = ensure_device_ready(nullptr)) return st;
+    // 50: reset, 51: count, 1000 + i: word i of the decode-GEMV timeline (-DW4A16_GEMV_PROFILE builds)
+    if (which == 50) return gemv_prof(-1, out);
+    if (which == 51) return gemv_prof(-2, out);
+    if (which >= 1000) return gemv_prof(which - 1000, out);
+    if (which > 49) return W4A16_ERR_INVALID_ARG;
     if (which == 0) return gemm_tc_timeouts(out);
     if (which >= 33) {   // 33..48: persistent sweep, CTA 0: kind*4 + phase, in kilo-cycles; 49: reset them
         unsigned long long ps[16];

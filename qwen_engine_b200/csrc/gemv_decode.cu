@@ -35,8 +35,43 @@ enum XIn { kXQ8 = 0,        // pre-quantised Q8_1 arrays in global memory
            kXFp16 = 1,      // fp16 vector, quantised in the prologue
            kXFp16Norm = 2 };  // fp16 vector, RMSNorm then quantised in the prologue
 
+// Optional timeline of the decode GEMV (-DW4A16_GEMV_PROFILE): thread 0 of CTA 0 of every launch appends one
+// record {globaltimer at entry, after the wait for the prior grid, at the end; latest end time of any CTA
+// of the launches before it; cycles spent waiting, staging x, in the dot loop, in the reduction + epilogue}.  Read with w4a16_debug_counter.
+#ifdef W4A16_GEMV_PROFILE
+constexpr int kProfRecords = 1024;
+__device__ unsigned int g_gemv_prof[kProfRecords * 8];
+__device__ unsigned int g_gemv_prof_n;
+__device__ unsigned int g_gemv_last_end;   // latest end time of any CTA of any GEMV so far
+__device__ __forceinline__ unsigned int gtimer() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return static_cast<unsigned int>(t);
+}
+#define GP_DECL() const bool gp_on = blockIdx.x == 0 && threadIdx.x == 0; unsigned int gp[8]; long long gp_c = 0; \
+    if (gp_on) { gp[0] = gtimer(); gp_c = clock64(); }
+#define GP_MARK(i) if (gp_on) { const long long c_ = clock64(); gp[i] = static_cast<unsigned int>(c_ - gp_c); gp_c = c_; }
+#define GP_GT(i) if (gp_on) { gp[i] = gtimer(); }
+#define GP_PREV_END(i) if (gp_on) { gp[i] = *reinterpret_cast<volatile unsigned int*>(&g_gemv_last_end); }
+#define GP_END() if (threadIdx.x == 0) { atomicMax(&g_gemv_last_end, gtimer()); }
+#define GP_FLUSH() if (gp_on) { const unsigned int n_ = atomicAdd(&g_gemv_prof_n, 1u); if (n_ < kProfRecords) { \
+    for (int i_ = 0; i_ < 8; ++i_) g_gemv_prof[n_ * 8 + i_] = gp[i_]; } }
+#else
+#define GP_DECL()
+#define GP_MARK(i)
+#define GP_GT(i)
+#define GP_PREV_END(i)
+#define GP_END()
+#define GP_FLUSH()
+#endif
+
+// Register caps: two 256-thread CTAs per SM need <= 128; the single-row forms with 8 loads per lane run as
+// 224-thread CTAs (down projection) of which three must fit an SM for the whole grid to be resident at once.
+constexpr int gemv_reg_cap(int mode, int u) { return (mode != kSwiglu && u == 8) ? 96 : 128; }
+
 template <int MODE, int U, int XIN, bool ALIGNED16>
-__global__ void __launch_bounds__(kMaxThreads) gemv_w4_kernel(const GemvArgs a) {
+__global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs a) {
+    GP_DECL();
     constexpr int R = (MODE == kSwiglu) ? 2 : 1;  // weight rows per sub-warp
     extern __shared__ __align__(16) uint8_t smem[];
     const int K = a.K;
@@ -100,13 +135,40 @@ __global__ void __launch_bounds__(kMaxThreads) gemv_w4_kernel(const GemvArgs a) 
     };
 
     issue(s_begin);
+    // Everything that does not depend on the prior grid goes before the wait: the weights above and the
+    // RMSNorm gain.  After it, every global round trip is on the critical path between two GEMVs, so the
+    // residual element is requested first and the activation is staged with one round trip.
+    [[maybe_unused]] uint4 gam[kStageRounds];
+    [[maybe_unused]] bool regs_form = false;
+    if constexpr (XIN != kXQ8) {
+        regs_form = stage_regs_ok(a.x_fp16, XIN == kXFp16Norm ? static_cast<const void*>(a.gamma) : nullptr, K);
+        if constexpr (XIN == kXFp16Norm) {
+            if (regs_form) prefetch_gamma(a.gamma, K, gam);
+        }
+    }
     pdl_release_dependents();
+    GP_MARK(4);
     pdl_wait_prior_grids();
+    GP_MARK(4);
+    GP_GT(1);
+    GP_PREV_END(3);
 
-    if constexpr (XIN == kXFp16Norm) stage_x_from_fp16_rmsnorm(a.x_fp16, a.gamma, K, kRmsEps, s_q8, s_seed, s_scale);
-    else if constexpr (XIN == kXFp16) stage_x_from_fp16(a.x_fp16, K, s_q8, s_seed, s_scale);
-    else stage_x_from_q8_1(a.q8, a.xscale, a.sum8, K, a.vec_ok != 0, s_q8, s_seed, s_scale);
+    [[maybe_unused]] __half res_pre = __ushort_as_half(0);
+    if constexpr (MODE == kPlain) {
+        if (active && ks == 0 && l == 0 && a.residual != nullptr) res_pre = a.residual[unit];
+    }
+    if constexpr (XIN == kXFp16Norm) {
+        if (regs_form) stage_x_fp16_regs<true>(a.x_fp16, gam, K, kRmsEps, s_q8, s_seed, s_scale);
+        else stage_x_from_fp16_rmsnorm(a.x_fp16, a.gamma, K, kRmsEps, s_q8, s_seed, s_scale);
+    } else if constexpr (XIN == kXFp16) {
+        if (regs_form) stage_x_fp16_regs<false>(a.x_fp16, gam, K, kRmsEps, s_q8, s_seed, s_scale);
+        else stage_x_from_fp16(a.x_fp16, K, s_q8, s_seed, s_scale);
+    } else {
+        if (!stage_x_from_q8_1_regs<(R * U >= 16)>(a.q8, a.xscale, a.sum8, K, a.vec_ok != 0, s_q8, s_seed, s_scale))
+            stage_x_from_q8_1(a.q8, a.xscale, a.sum8, K, a.vec_ok != 0, s_q8, s_seed, s_scale);
+    }
     __syncthreads();
+    GP_MARK(5);
 
     float acc[R];
 #pragma unroll
@@ -133,6 +195,7 @@ __global__ void __launch_bounds__(kMaxThreads) gemv_w4_kernel(const GemvArgs a) 
         if (s0 + U < s_end) issue(s0 + U);
     }
 
+    GP_MARK(6);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 4);
@@ -164,7 +227,7 @@ __global__ void __launch_bounds__(kMaxThreads) gemv_w4_kernel(const GemvArgs a) 
         } else {
             y = acc[0];
             if constexpr (MODE == kPlain) {
-                if (a.residual != nullptr) y += __half2float(a.residual[unit]);
+                if (a.residual != nullptr) y += __half2float(res_pre);
             }
         }
         const __half yh = __float2half_rn(y);
@@ -173,7 +236,28 @@ __global__ void __launch_bounds__(kMaxThreads) gemv_w4_kernel(const GemvArgs a) 
             for (int p = 0; p < a.num_peers; ++p) a.peer_out[p][unit] = yh;   // slice into every peer's buffer
         }
     }
+    GP_MARK(7);
+    GP_GT(2);
+    GP_FLUSH();
+    GP_END();
 }
+
+}  // namespace
+
+// Timeline records of the decode GEMV (zeros unless built with -DW4A16_GEMV_PROFILE).  which: -1 resets the
+// record count, -2 returns it, otherwise word `which` of the record table.
+int gemv_prof(int which, unsigned int* out) {
+#ifdef W4A16_GEMV_PROFILE
+    if (which == -1) { const unsigned int z = 0; *out = 0; return static_cast<int>(cudaMemcpyToSymbol(g_gemv_prof_n, &z, sizeof(z))); }
+    if (which == -2) return static_cast<int>(cudaMemcpyFromSymbol(out, g_gemv_prof_n, sizeof(unsigned int)));
+    if (which >= kProfRecords * 8) return W4A16_ERR_INVALID_ARG;
+    return static_cast<int>(cudaMemcpyFromSymbol(out, g_gemv_prof, sizeof(unsigned int), sizeof(unsigned int) * which));
+#else
+    (void)which; *out = 0; return 0;
+#endif
+}
+
+namespace {
 
 // Streaming form for very tall matrices (lm_head): a persistent grid, each CTA walks row blocks of 32 with
 // the weights of the NEXT block already in flight while the current one is reduced, and the lane's share
@@ -312,12 +396,22 @@ struct Plan {
     int units_per_cta, ksplit, steps_per_split, U;
 };
 
+// Warps of one kernel variant that fit an SM at once.  Registers are handed out per scheduler partition
+// (16384 each, whole warps), so a variant capped at 96 registers holds 5 warps per partition, one at 128
+// holds 4, and the 4-load forms (<= 80 registers) hold 6.
+int resident_warps_per_sm(GemvMode mode, int U) {
+    if (mode == kSwiglu) return 16;
+    return U == 8 ? 20 : 24;
+}
+
 // Picks the CTA shape.  units: output rows (or pairs).  Goals, in order: at least ~1.3 CTAs
 // per SM when the matrix allows it; all 32 sub-warps of a CTA busy; at most 8 loads per lane
-// per batch so one batch covers a lane's whole K slice for the model's shapes.
-Plan make_plan(int units, int K, int sm_count) {
+// per batch so one batch covers a lane's whole K slice for the model's shapes; and the whole grid
+// resident at once (a second wave of CTAs would start its weight loads only after the wait).
+Plan make_plan(GemvMode mode, int units, int K, int sm_count) {
     static const int force_units = env_int("W4A16_GEMV_UNITS", 0);
     static const int force_ksplit = env_int("W4A16_GEMV_KSPLIT", 0);
+    static const int force_u = env_int("W4A16_GEMV_U", 0);
     const int steps = K / kStepElems;
     const int target_ctas = (sm_count * 13 + 9) / 10;
     int upc = 32;
@@ -327,17 +421,26 @@ Plan make_plan(int units, int K, int sm_count) {
     cap = std::min(cap, steps);
     int per = (steps + cap - 1) / cap;           // steps per slice if all slices were used
     int ksplit = (steps + per - 1) / per;        // fewest slices that reach that depth
+    auto pick_u = [&](int depth) { return force_u == 4 || force_u == 8 ? force_u : (depth <= 4 ? 4 : 8); };
     if (force_ksplit > 0) {
         ksplit = std::min(std::min(force_ksplit, steps), kMaxSubwarps / upc);
         ksplit = std::max(1, ksplit);
         per = (steps + ksplit - 1) / ksplit;
+    } else {
+        const int grid = (units + upc - 1) / upc;
+        while (ksplit > 1) {
+            const int warps = (upc * ksplit * kSubwarp + 31) / 32;
+            const int ctas_per_sm = resident_warps_per_sm(mode, pick_u(per)) / warps;
+            if (grid <= ctas_per_sm * sm_count || per >= 8) break;
+            per = (steps + (ksplit - 1) - 1) / (ksplit - 1);   // one slice fewer, deeper slices
+            ksplit = (steps + per - 1) / per;
+        }
     }
     Plan p;
     p.units_per_cta = upc;
     p.ksplit = ksplit;
     p.steps_per_split = per;
-    static const int force_u = env_int("W4A16_GEMV_U", 0);
-    p.U = force_u == 4 || force_u == 8 ? force_u : (per <= 4 ? 4 : 8);
+    p.U = pick_u(per);
     return p;
 }
 
@@ -395,7 +498,7 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
     const DeviceInfo* dev = nullptr;
     if (int st = ensure_device_ready(&dev)) return st;
 
-    Plan p = make_plan(a.units, a.K, dev->sm_count);
+    Plan p = make_plan(mode, a.units, a.K, dev->sm_count);
     if (mode == kQkv) {
         // a CTA's rows must come from one tensor
         while (p.units_per_cta > 1 && (a.rows[0] % p.units_per_cta || a.rows[1] % p.units_per_cta)) p.units_per_cta /= 2;

@@ -214,4 +214,159 @@ __device__ __forceinline__ void stage_x_from_fp16_rmsnorm(const __half* __restri
     }
 }
 
+// ---- low-latency staging (the forms the decode GEMV uses when the shape allows) ---------------
+// Between two dependent GEMVs every global round trip in the prologue is on the critical path
+// (about 0.4 us each on B200), so these forms issue ALL of a thread's global loads back to back
+// before the first use, take the RMSNorm gain before the wait for the prior grid, and give each
+// group of 128 to a half-warp (lane = 8 consecutive elements = one 16-byte load = one sum8 octet)
+// so that K = 1536 is one round for a 192-thread CTA.  Same arithmetic, same bits as the loops above.
+constexpr int kStageRounds = 1;   // groups per half-warp held in registers (K <= 128 * blockDim / 16)
+
+// Half-warp quantiser: 16 lanes per group, lane hl owns elements 8*hl .. 8*hl+7.  Both halves of a
+// warp must call it together (shuffles); `on` = this half-warp has a real group.
+__device__ __forceinline__ void quantize_group_halfwarp_to_smem(const float v[8], int g, int hl, bool on, int8_t* s_q8,
+                                                                int32_t* s_seed, float* s_scale) {
+    float m = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[j]));
+#pragma unroll
+    for (int mask = 8; mask > 0; mask >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, mask));
+    const float d = fmaxf(__fdiv_rn(m, 127.0f), 1e-8f);
+    const float inv_d = __fdiv_rn(1.0f, d);
+    uint32_t packed[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        int q = __float2int_rn(__fmul_rn(v[j], inv_d));
+        q = max(-127, min(127, q));
+        packed[j >> 2] |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * (j & 3));
+    }
+    int32_t sum = byte_sum(packed[0]) + byte_sum(packed[1]);   // one octet; four lanes make a chunk
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+    sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+    if (on) {
+        reinterpret_cast<uint2*>(s_q8)[g * (kGroup / 8) + hl] = make_uint2(packed[0], packed[1]);
+        if ((hl & 3) == 0) s_seed[g * 4 + (hl >> 2)] = -8 * sum;
+        if (hl == 0) s_scale[g] = d;
+    }
+}
+
+// True when the register form applies: few enough groups for kStageRounds rounds and 16-byte aligned vectors.
+__device__ __forceinline__ bool stage_regs_ok(const void* x, const void* gamma, int K) {
+    const int nhw = blockDim.x >> 4;
+    return (K / kGroup) <= kStageRounds * nhw &&
+           ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(gamma)) & 15u) == 0;
+}
+
+// The RMSNorm gain words this thread will need; a weight, so it may be read before the prior grid is done.
+__device__ __forceinline__ void prefetch_gamma(const __half* __restrict__ g_gamma, int K, uint4 (&gam)[kStageRounds]) {
+    const int hw = threadIdx.x >> 4, hl = threadIdx.x & 15, nhw = blockDim.x >> 4;
+#pragma unroll
+    for (int r = 0; r < kStageRounds; ++r) {
+        const int g = hw + r * nhw;
+        gam[r] = g < K / kGroup ? __ldg(reinterpret_cast<const uint4*>(g_gamma + g * kGroup + hl * 8)) : make_uint4(0, 0, 0, 0);
+    }
+}
+
+// fp16 activation (optionally RMSNorm'ed with the prefetched gain) -> staged Q8_1.  One global round trip.
+template <bool NORM>
+__device__ __forceinline__ void stage_x_fp16_regs(const __half* g_x, const uint4 (&gam)[kStageRounds], int K, float eps,
+                                                  int8_t* s_q8, int32_t* s_seed, float* s_scale) {
+    __shared__ double s_red[8];
+    const int hw = threadIdx.x >> 4, hl = threadIdx.x & 15, nhw = blockDim.x >> 4;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    const int groups = K / kGroup;
+    uint4 xr[kStageRounds];
+#pragma unroll
+    for (int r = 0; r < kStageRounds; ++r) {
+        const int g = hw + r * nhw;
+        xr[r] = g < groups ? *reinterpret_cast<const uint4*>(g_x + g * kGroup + hl * 8) : make_uint4(0, 0, 0, 0);
+    }
+    __half2 inv2 = __float2half2_rn(1.0f);
+    if constexpr (NORM) {
+        double ss = 0.0;
+#pragma unroll
+        for (int r = 0; r < kStageRounds; ++r) {
+            const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xr[r]);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xw[k]));
+                ss += static_cast<double>(f.x) * static_cast<double>(f.x);
+                ss += static_cast<double>(f.y) * static_cast<double>(f.y);
+            }
+        }
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, m);
+        if (lane == 0) s_red[warp] = ss;
+        __syncthreads();
+        double t = 0.0;
+        for (int w = 0; w < nwarps; ++w) t += s_red[w];   // every thread, same order: no second barrier
+        inv2 = __float2half2_rn(static_cast<float>(1.0 / sqrt(t / static_cast<double>(K) + static_cast<double>(eps))));
+    }
+    const int rounds = (groups + nhw - 1) / nhw;
+#pragma unroll
+    for (int r = 0; r < kStageRounds; ++r) {
+        if (r < rounds) {   // uniform over the CTA: both halves of a warp shuffle together
+            const int g = hw + r * nhw;
+            const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xr[r]);
+            const uint32_t* gw = reinterpret_cast<const uint32_t*>(&gam[r]);
+            float v[8];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                __half2 y = *reinterpret_cast<const __half2*>(&xw[k]);
+                if constexpr (NORM) y = __hmul2(__hmul2(y, inv2), *reinterpret_cast<const __half2*>(&gw[k]));
+                const float2 f = __half22float2(y);
+                v[2 * k] = f.x;
+                v[2 * k + 1] = f.y;
+            }
+            quantize_group_halfwarp_to_smem(v, g, hl, g < groups, s_q8, s_seed, s_scale);
+        }
+    }
+}
+
+// Pre-quantised Q8_1 -> shared memory with every global load of the thread in flight at once.
+// Returns false (nothing done) when the vector is too long for the register budget or not 16-byte aligned.
+// LEAN: two round trips (bytes, then sums and scales) for callers that are short of registers.
+template <bool LEAN>
+__device__ __forceinline__ bool stage_x_from_q8_1_regs(const int8_t* g_q8, const float* g_scale, const int32_t* g_sum8,
+                                                       int K, bool vec_ok, int8_t* s_q8, int32_t* s_seed, float* s_scale) {
+    constexpr int MAXQ = 4, MAXS = 2;
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    if (!vec_ok || K / 16 > MAXQ * nthr || K / kChunk > MAXS * nthr || K / kGroup > nthr) return false;
+    uint4 q[MAXQ];
+    int4 sv[MAXS];
+    float sc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < MAXQ; ++i) {
+        const int idx = tid + i * nthr;
+        if (idx < K / 16) q[i] = reinterpret_cast<const uint4*>(g_q8)[idx];
+    }
+    if constexpr (LEAN) {
+#pragma unroll
+        for (int i = 0; i < MAXQ; ++i) {
+            const int idx = tid + i * nthr;
+            if (idx < K / 16) reinterpret_cast<uint4*>(s_q8)[idx] = q[i];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MAXS; ++i) {
+        const int idx = tid + i * nthr;
+        if (idx < K / kChunk) sv[i] = reinterpret_cast<const int4*>(g_sum8)[idx];
+    }
+    if (tid < K / kGroup) sc = g_scale[tid];
+    if constexpr (!LEAN) {
+#pragma unroll
+        for (int i = 0; i < MAXQ; ++i) {
+            const int idx = tid + i * nthr;
+            if (idx < K / 16) reinterpret_cast<uint4*>(s_q8)[idx] = q[i];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MAXS; ++i) {
+        const int idx = tid + i * nthr;
+        if (idx < K / kChunk) s_seed[idx] = sv[i].x + sv[i].y + sv[i].z + sv[i].w;
+    }
+    if (tid < K / kGroup) s_scale[tid] = sc;
+    return true;
+}
+
 }  // namespace w4

@@ -97,6 +97,7 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream);
 int gemm_tc_set_attributes();
 int gemm_tc_timeouts(unsigned int* out);
 int gemm_tc_prof(unsigned long long* out);   // zeros unless built with -DW4A16_TC_PROFILE
+int gemv_prof(int which, unsigned int* out);  // decode GEMV timeline (gemv_decode.cu); zeros unless -DW4A16_GEMV_PROFILE
 
 // ---- persistent one-kernel decode sweep (sweep_persistent.cu) ----
 struct PSweepArgs {
