@@ -182,6 +182,22 @@ W4A16_API int w4a16_gemv_dual_gate_up_swiglu_rmsnorm_w4a16(const uint32_t* gate_
                                                            const void* gamma, void* output_mlp, int hidden_size,
                                                            int intermediate_size, w4a16_stream_t stream);
 
+/*
+ * The same launch, which in addition leaves the Q8_1 form of output_mlp in output_q8 [intermediate],
+ * output_scale [intermediate/128] and output_sum8 [intermediate/8] -- what launch_quantize_fp16_to_q8_1
+ * (include/kernels.cuh:50-57, src/engine.cu:441-444) would compute from output_mlp, bit for bit -- so the
+ * down projection can start from w4a16_gemv_w4a8 without a quantiser launch in between.  The CTAs of one
+ * group of 128 outputs form a thread-block cluster and agree on the group's scale through distributed
+ * shared memory.  intermediate_size must be a multiple of 128 (W4A16_ERR_SHAPE otherwise).
+ * No reference counterpart.
+ */
+W4A16_API int w4a16_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1(const uint32_t* gate_up_qweight,
+                                                                const void* gate_up_scales, const void* input_x,
+                                                                const void* gamma, void* output_mlp,
+                                                                int8_t* output_q8, float* output_scale,
+                                                                int32_t* output_sum8, int hidden_size,
+                                                                int intermediate_size, w4a16_stream_t stream);
+
 /* ---- M-token contraction (small-M decode batches and prefill) ------------------- */
 
 /* reference include/kernels.cuh:119-130 launch_gemm_prefill_w4a16
@@ -243,6 +259,10 @@ enum {
     W4A16_SWEEP_FUSE_QUANT_O = 2,    /* Q8_1 of the attention output inside the O GEMV */
     W4A16_SWEEP_FUSE_QUANT_DOWN = 4, /* Q8_1 of the MLP activation inside the down GEMV */
     W4A16_SWEEP_FUSE_ALL = 7,    /* 4 launches per layer, same output bits */
+    W4A16_SWEEP_QUANT_IN_GATE_UP = 16, /* the gate_up launch writes the Q8_1 form of its own output (clusters
+                                    of four CTAs share one group of 128): no quantiser launch and no
+                                    re-quantisation in front of down; needs intermediate % 128 == 0; takes
+                                    precedence over FUSE_QUANT_DOWN; same output bits */
     W4A16_SWEEP_PERSISTENT = 8   /* the whole pass as ONE persistent kernel (one CTA per SM): weights of all
                                     layers stream through a shared-memory ring while the CTAs exchange the
                                     small activation vectors through tagged 8-byte words; needs

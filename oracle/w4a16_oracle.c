@@ -456,9 +456,13 @@ ORC_API void orc_gemm_prefill(const uint32_t* packed, const uint16_t* scales, co
 /* src/kernels/rmsnorm_rope.cu:214-233 (CPU twin tests/test_kernels.cu:81-96):*/
 /*   inv_rms = rsqrt(mean(x^2) + eps) in fp32, rounded to fp16;               */
 /*   y = fp16(fp16(x * inv_rms_h) * gamma)   (two fp16 multiplies).           */
-/* The sum of squares is taken in double here; the kernels add in fp32 in an  */
-/* order of their own, so inv_rms_h can differ by one fp16 ulp in rare cases. */
-/* The caller passes inv_rms_override > 0 to pin it to the device's value.    */
+/* The sum of squares is taken in double (squares of fp16 values are exact     */
+/* there and the sum is off by parts in 2^50 at most, so the summation order   */
+/* does not reach the fp32 mean); the mean,                                    */
+/* + eps, square root and reciprocal are IEEE fp32 as in the reference, whose */
+/* kernels add in fp32 in an order of their own, so its inv_rms_h can differ  */
+/* by one fp16 ulp in rare cases.  The caller passes inv_rms_override > 0 to  */
+/* pin it to a device's value.                                                */
 /* ------------------------------------------------------------------------- */
 ORC_API float orc_rmsnorm(const uint16_t* x, const uint16_t* gamma, int n, float eps,
                           float inv_rms_override, uint16_t* y) {
@@ -467,7 +471,8 @@ ORC_API float orc_rmsnorm(const uint16_t* x, const uint16_t* gamma, int n, float
         double v = (double)h2f(x[i]);
         ss += v * v;
     }
-    float inv_rms = (float)(1.0 / sqrt(ss / (double)n + (double)eps));
+    float mean = (float)ss / (float)n;
+    float inv_rms = 1.0f / sqrtf(mean + eps);
     if (inv_rms_override > 0.0f) inv_rms = inv_rms_override;
     float ih = h2f(f2h(inv_rms));
     for (int i = 0; i < n; ++i) {

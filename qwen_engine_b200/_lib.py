@@ -54,6 +54,8 @@ SIGNATURES = {
     "w4a16_gemv_qkv_rmsnorm_w4a16": [POINTER(QKVView), c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int],
     "w4a16_gemv_dual_gate_up_swiglu_rmsnorm_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                                      c_void_p],
+    "w4a16_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                          c_void_p, c_void_p, c_int, c_int, c_void_p],
     "w4a16_gemm_prefill_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                  c_int],
     "w4a16_gemm_prefill_qkv_w4a16": [POINTER(QKVView), c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,

@@ -212,7 +212,8 @@ int w4a16_gemv_qkv_w4a8(const w4a16_qkv_view* view, const int8_t* input_q8, cons
 
 static int gemv_swiglu(const uint32_t* qweight, const void* scales, const void* x_fp16, const int8_t* q8,
                        const float* xscale, const int32_t* sum8, void* out, int hidden, int inter,
-                       w4a16_stream_t stream, const void* gamma = nullptr) {
+                       w4a16_stream_t stream, const void* gamma = nullptr, int8_t* q8_out = nullptr,
+                       float* xscale_out = nullptr, int32_t* sum8_out = nullptr) {
     if (!qweight || !scales || !out || inter <= 0) return W4A16_ERR_INVALID_ARG;
     if (int st = check_k(hidden)) return st;
     if (misaligned(qweight, 4) || misaligned(scales, 2) || misaligned(out, 2) || misaligned(x_fp16, 8) ||
@@ -222,7 +223,8 @@ static int gemv_swiglu(const uint32_t* qweight, const void* scales, const void* 
     a.qweight[0] = qweight; a.scales[0] = H(scales); a.out[0] = H(out); a.rows[0] = 2 * inter;
     a.q8 = q8; a.xscale = xscale; a.sum8 = sum8; a.x_fp16 = H(x_fp16); a.gamma = H(gamma);
     a.K = hidden; a.units = inter;
-    if (misaligned(gamma, 8)) return W4A16_ERR_ALIGNMENT;
+    a.q8_out = q8_out; a.xscale_out = xscale_out; a.sum8_out = sum8_out;
+    if (misaligned(gamma, 8) || misaligned(xscale_out, 4) || misaligned(sum8_out, 4)) return W4A16_ERR_ALIGNMENT;
     return gemv_launch(kSwiglu, a, S(stream));
 }
 
@@ -271,6 +273,15 @@ int w4a16_gemv_dual_gate_up_swiglu_rmsnorm_w4a16(const uint32_t* gate_up_qweight
     if (!input_x) return W4A16_ERR_INVALID_ARG;
     return gemv_swiglu(gate_up_qweight, gate_up_scales, input_x, nullptr, nullptr, nullptr, output_mlp, hidden_size,
                        intermediate_size, stream, gamma);
+}
+
+int w4a16_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1(const uint32_t* gate_up_qweight, const void* gate_up_scales,
+                                                      const void* input_x, const void* gamma, void* output_mlp,
+                                                      int8_t* output_q8, float* output_scale, int32_t* output_sum8,
+                                                      int hidden_size, int intermediate_size, w4a16_stream_t stream) {
+    if (!input_x || !output_q8 || !output_scale || !output_sum8) return W4A16_ERR_INVALID_ARG;
+    return gemv_swiglu(gate_up_qweight, gate_up_scales, input_x, nullptr, nullptr, nullptr, output_mlp, hidden_size,
+                       intermediate_size, stream, gamma, output_q8, output_scale, output_sum8);
 }
 
 int w4a16_gemm_prefill_w4a16(const uint32_t* qweight, const void* scales, const void* input_x, const void* residual,

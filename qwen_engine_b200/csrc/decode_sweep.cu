@@ -20,6 +20,9 @@ struct w4a16_sweep {
     int8_t* act_q8 = nullptr; // [max(hidden, inter)]
     float* act_scale = nullptr;
     int32_t* act_sum8 = nullptr;
+    int8_t* mlp_q8 = nullptr; // Q8_1 of the MLP activation when the gate_up launch writes it itself
+    float* mlp_scale = nullptr;
+    int32_t* mlp_sum8 = nullptr;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     int launches = 0;
@@ -43,6 +46,7 @@ struct Carve {
     size_t h, q, k, v, mlp, q8, scale, sum8, total;
     // persistent form: exchange buffers (8-byte tagged words), device copy of the layer table, status word
     size_t ll_h_attn, ll_h_down, ll_q, ll_mlp, layer_table, status, counters;
+    size_t mlp_q8, mlp_scale, mlp_sum8;
 };
 Carve carve(int hidden, int inter, int nq, int nkv, int hd) {
     const size_t kmax = static_cast<size_t>(hidden > inter ? hidden : inter);
@@ -64,6 +68,9 @@ Carve carve(int hidden, int inter, int nq, int nkv, int hd) {
     c.status = off; off += align_up(sizeof(int));
     c.counters = off; off += align_up(4 * kMaxPersistentLayers * 32);   // one 32-byte cell per projection
     c.layer_table = off; off += align_up(kMaxPersistentLayers * w4::psweep_layer_bytes());
+    c.mlp_q8 = off; off += align_up(inter);
+    c.mlp_scale = off; off += align_up(inter / 128 * sizeof(float));
+    c.mlp_sum8 = off; off += align_up(inter / 8 * sizeof(int32_t));
     c.total = off;
     return c;
 }
@@ -122,6 +129,8 @@ int issue_pass(w4a16_sweep* s, cudaStream_t stream, int* launches) {
             ++n;
             g.q8 = s->act_q8; g.xscale = s->act_scale; g.sum8 = s->act_sum8;
         }
+        const bool quant_in_gate_up = (flags & W4A16_SWEEP_QUANT_IN_GATE_UP) != 0;
+        if (quant_in_gate_up) { g.q8_out = s->mlp_q8; g.xscale_out = s->mlp_scale; g.sum8_out = s->mlp_sum8; }
         if (int st = gemv_launch(kSwiglu, g, stream)) return st;
         ++n;
         GemvArgs dn = {};
@@ -129,7 +138,9 @@ int issue_pass(w4a16_sweep* s, cudaStream_t stream, int* launches) {
         dn.scales[0] = static_cast<const __half*>(L.down_scale);
         dn.out[0] = s->h; dn.rows[0] = H; dn.residual = s->h;
         dn.K = I; dn.units = H;
-        if (flags & W4A16_SWEEP_FUSE_QUANT_DOWN) {
+        if (quant_in_gate_up) {
+            dn.q8 = s->mlp_q8; dn.xscale = s->mlp_scale; dn.sum8 = s->mlp_sum8;
+        } else if (flags & W4A16_SWEEP_FUSE_QUANT_DOWN) {
             dn.x_fp16 = s->mlp;
         } else {
             if (int st = quantize_fp16_to_q8_1(s->mlp, s->act_q8, s->act_scale, s->act_sum8, I, stream)) return st;
@@ -195,6 +206,10 @@ int w4a16_sweep_create(const w4a16_sweep_desc* desc, w4a16_stream_t stream_, w4a
     s->act_q8 = reinterpret_cast<int8_t*>(base + c.q8);
     s->act_scale = reinterpret_cast<float*>(base + c.scale);
     s->act_sum8 = reinterpret_cast<int32_t*>(base + c.sum8);
+    s->mlp_q8 = reinterpret_cast<int8_t*>(base + c.mlp_q8);
+    s->mlp_scale = reinterpret_cast<float*>(base + c.mlp_scale);
+    s->mlp_sum8 = reinterpret_cast<int32_t*>(base + c.mlp_sum8);
+    if ((desc->flags & W4A16_SWEEP_QUANT_IN_GATE_UP) && I % 128) return W4A16_ERR_SHAPE;
 
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     cudaError_t e = cudaMemsetAsync(s->h, 0, H * sizeof(__half), stream);

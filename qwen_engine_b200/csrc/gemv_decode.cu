@@ -158,10 +158,20 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
         if (active && ks == 0 && l == 0 && a.residual != nullptr) res_pre = a.residual[unit];
     }
     if constexpr (XIN == kXFp16Norm) {
+#ifdef W4A16_GEMV_PROFILE
+        if (regs_form) stage_x_fp16_regs<true>(a.x_fp16, gam, K, kRmsEps, s_q8, s_seed, s_scale,
+                                               gp_on ? &g_gemv_prof[8000 + 8 * MODE] : nullptr);
+#else
         if (regs_form) stage_x_fp16_regs<true>(a.x_fp16, gam, K, kRmsEps, s_q8, s_seed, s_scale);
+#endif
         else stage_x_from_fp16_rmsnorm(a.x_fp16, a.gamma, K, kRmsEps, s_q8, s_seed, s_scale);
     } else if constexpr (XIN == kXFp16) {
+#ifdef W4A16_GEMV_PROFILE
+        if (regs_form) stage_x_fp16_regs<false>(a.x_fp16, gam, K, kRmsEps, s_q8, s_seed, s_scale,
+                                                gp_on ? &g_gemv_prof[8000 + 8 * 3] : nullptr);
+#else
         if (regs_form) stage_x_fp16_regs<false>(a.x_fp16, gam, K, kRmsEps, s_q8, s_seed, s_scale);
+#endif
         else stage_x_from_fp16(a.x_fp16, K, s_q8, s_seed, s_scale);
     } else {
         if (!stage_x_from_q8_1_regs<(R * U >= 16)>(a.q8, a.xscale, a.sum8, K, a.vec_ok != 0, s_q8, s_seed, s_scale))
@@ -219,6 +229,7 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
         }
     }
 
+    [[maybe_unused]] float y_rounded = 0.0f;   // SWIGLU: the fp16 output as a float, for the Q8_1 epilogue
     if (active && ks == 0 && l == 0) {
         float y;
         if constexpr (MODE == kSwiglu) {
@@ -232,8 +243,55 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
         }
         const __half yh = __float2half_rn(y);
         *out_ptr = yh;
+        y_rounded = __half2float(yh);
         if constexpr (MODE == kPlain) {
             for (int p = 0; p < a.num_peers; ++p) a.peer_out[p][unit] = yh;   // slice into every peer's buffer
+        }
+    }
+
+    if constexpr (MODE == kSwiglu) {
+        // Q8_1 of the output vector in the same launch.  The launch guarantees 32 outputs per CTA, no K
+        // split and clusters of four CTAs, i.e. one quantisation group of 128 per cluster: the CTAs swap
+        // their |max| through distributed shared memory, one cluster barrier, then each quantises its own
+        // 32 outputs (one chunk: 32 bytes, four sum8 entries) with the group's scale.  Same arithmetic as
+        // quantize_group128_lane, so the arrays equal the stand-alone quantiser's bit for bit.
+        if (a.q8_out != nullptr) {
+            __shared__ float s_y[kMaxSubwarps];
+            __shared__ float s_cluster_max[4];
+            if (l == 0) s_y[sub] = y_rounded;
+            __syncthreads();
+            uint32_t rank;
+            asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+            float v = 0.0f;
+            if (tid < 32) {
+                v = s_y[tid];
+                float m = fabsf(v);
+#pragma unroll
+                for (int mask = 16; mask > 0; mask >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, mask));
+                if (tid < 4) {   // lane t puts this CTA's maximum into slot `rank` of CTA t
+                    const uint32_t local = static_cast<uint32_t>(__cvta_generic_to_shared(&s_cluster_max[rank]));
+                    uint32_t remote;
+                    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(static_cast<uint32_t>(tid)));
+                    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(m) : "memory");
+                }
+            }
+            asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+            asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            if (tid < 32) {
+                const float m = fmaxf(fmaxf(s_cluster_max[0], s_cluster_max[1]), fmaxf(s_cluster_max[2], s_cluster_max[3]));
+                const float d = fmaxf(__fdiv_rn(m, 127.0f), 1e-8f);
+                const float inv_d = __fdiv_rn(1.0f, d);
+                int q = __float2int_rn(__fmul_rn(v, inv_d));
+                q = max(-127, min(127, q));
+                const int first = blockIdx.x * kMaxSubwarps;
+                a.q8_out[first + tid] = static_cast<int8_t>(q);
+                int sum = q;
+                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+                sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 4);
+                if ((tid & 7) == 0) a.sum8_out[(first + tid) >> 3] = -8 * sum;
+                if (rank == 0 && tid == 0) a.xscale_out[first / kGroup] = d;
+            }
         }
     }
     GP_MARK(7);
@@ -447,9 +505,12 @@ Plan make_plan(GemvMode mode, int units, int K, int sm_count) {
 template <int MODE, int U, int XIN>
 cudaError_t launch_aligned(const GemvArgs& a, bool aligned16, dim3 grid, dim3 block, size_t smem,
                            cudaStream_t stream) {
+    const int cluster_x = a.q8_out != nullptr ? 4 : 1;   // Q8_1 epilogue: four CTAs = one group of 128 outputs
     if (aligned16)
-        return launch_kernel(gemv_w4_kernel<MODE, U, XIN, true>, grid, block, smem, stream, pdl_enabled(), a);
-    return launch_kernel(gemv_w4_kernel<MODE, U, XIN, false>, grid, block, smem, stream, pdl_enabled(), a);
+        return launch_kernel_cluster(gemv_w4_kernel<MODE, U, XIN, true>, grid, block, smem, stream, pdl_enabled(),
+                                     cluster_x, a);
+    return launch_kernel_cluster(gemv_w4_kernel<MODE, U, XIN, false>, grid, block, smem, stream, pdl_enabled(),
+                                 cluster_x, a);
 }
 template <int MODE, int U>
 cudaError_t launch_input(const GemvArgs& a, bool aligned16, dim3 grid, dim3 block, size_t smem, cudaStream_t stream) {
@@ -499,6 +560,16 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
     if (int st = ensure_device_ready(&dev)) return st;
 
     Plan p = make_plan(mode, a.units, a.K, dev->sm_count);
+    const bool q8_epilogue = a.q8_out != nullptr || a.xscale_out != nullptr || a.sum8_out != nullptr;
+    if (q8_epilogue) {
+        if (mode != kSwiglu || !a.q8_out || !a.xscale_out || !a.sum8_out) return W4A16_ERR_INVALID_ARG;
+        if (a.units % kGroup != 0) return W4A16_ERR_SHAPE;
+        // the epilogue's layout: 32 outputs per CTA, the whole of K in each sub-warp
+        p.units_per_cta = kMaxSubwarps;
+        p.ksplit = 1;
+        p.steps_per_split = a.K / kStepElems;
+        p.U = 8;
+    }
     if (mode == kQkv) {
         // a CTA's rows must come from one tensor
         while (p.units_per_cta > 1 && (a.rows[0] % p.units_per_cta || a.rows[1] % p.units_per_cta)) p.units_per_cta /= 2;
@@ -530,7 +601,7 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
     static const int stream_min_blocks = env_int("W4A16_GEMV_STREAM_MIN", 16);   // row blocks per SM from which it pays
     static const int stream_swiglu = env_int("W4A16_GEMV_STREAM_SWIGLU", 0);
     const bool tall = num_blocks >= stream_min_blocks * dev->sm_count;
-    if (stream_on && aligned16 && steps <= 8 &&
+    if (stream_on && !q8_epilogue && aligned16 && steps <= 8 &&
         ((mode == kPlain && tall) || (mode == kSwiglu && (tall || (stream_swiglu && num_blocks >= 3 * dev->sm_count))))) {
         const dim3 sgrid(std::min(num_blocks, 2 * dev->sm_count)), sblock(kMaxThreads);
         const size_t ssmem = staged_x_bytes(a.K);

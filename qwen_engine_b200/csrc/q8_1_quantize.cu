@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_q8_1_kernel(const __half
     if (tid == 0) {
         double t = 0.0;
         for (int w = 0; w < kNormThreads / 32; ++w) t += s_warp[w];
-        s_inv = static_cast<float>(1.0 / sqrt(t / static_cast<double>(hidden) + static_cast<double>(eps)));
+        s_inv = inv_rms_from_sumsq(t, hidden, eps);
     }
     __syncthreads();
     const __half2 inv2 = __float2half2_rn(s_inv);

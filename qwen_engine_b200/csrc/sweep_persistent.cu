@@ -349,7 +349,7 @@ __device__ bool stage_input_norm(const PSweepArgs& a, const uint2* ll, const __h
 #pragma unroll
     for (int m = 8; m > 0; m >>= 1) t += __shfl_xor_sync(0xFFFFFFFFu, t, m);
     t = __shfl_sync(0xFFFFFFFFu, t, 0);
-    const float inv = static_cast<float>(1.0 / sqrt(t / static_cast<double>(H) + static_cast<double>(kEps)));
+    const float inv = inv_rms_from_sumsq(t, H, kEps);
     const __half2 inv2 = __float2half2_rn(inv);
     // quantise: half-warp per group, the gain was fetched before the wait (gamma_regs[i] = group 2*(warp + i*W) + half)
     const int hl = lane & 15, half = lane >> 4;

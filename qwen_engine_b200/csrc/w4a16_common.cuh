@@ -66,14 +66,32 @@ __device__ __forceinline__ int32_t octet_dot(uint32_t packed, int32_t x_lo, int3
     return __dp4a(w_hi, x_hi, __dp4a(w_lo, x_lo, seed));
 }
 
+// dp4a with unsigned bytes on the weight side and signed bytes on the activation side.
+__device__ __forceinline__ int32_t dp4a_u8s8(uint32_t a, int32_t b, int32_t c) {
+    int32_t d;
+    asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));
+    return d;
+}
+
 // One 16-byte weight chunk (32 elements) against its 32 activation bytes.
 // chunk_seed = -8 * (sum of the 32 activation bytes), i.e. the four sum8 entries added up.
+// The high nibbles are not shifted down: masked in place they are the unsigned bytes 16*q, their
+// dot product is exactly 16 times the wanted one, and the factor leaves with one arithmetic shift
+// at the end (the sum is a multiple of 16 and far from overflow: |.| <= 16*15*127*16).  That is four
+// instructions per weight word instead of five and two independent dp4a chains instead of one; the
+// integer result is the same as octet_dot's.
 __device__ __forceinline__ int32_t chunk_dot(const uint4& w, const uint4& xa, const uint4& xb, int32_t chunk_seed) {
-    int32_t d = octet_dot(w.x, static_cast<int32_t>(xa.x), static_cast<int32_t>(xa.y), chunk_seed);
-    d = octet_dot(w.y, static_cast<int32_t>(xa.z), static_cast<int32_t>(xa.w), d);
-    d = octet_dot(w.z, static_cast<int32_t>(xb.x), static_cast<int32_t>(xb.y), d);
-    d = octet_dot(w.w, static_cast<int32_t>(xb.z), static_cast<int32_t>(xb.w), d);
-    return d;
+    constexpr uint32_t kLo = 0x0F0F0F0Fu, kHi = 0xF0F0F0F0u;
+    int32_t lo = chunk_seed, hi = 0;
+    lo = dp4a_u8s8(w.x & kLo, static_cast<int32_t>(xa.x), lo);
+    hi = dp4a_u8s8(w.x & kHi, static_cast<int32_t>(xa.y), hi);
+    lo = dp4a_u8s8(w.y & kLo, static_cast<int32_t>(xa.z), lo);
+    hi = dp4a_u8s8(w.y & kHi, static_cast<int32_t>(xa.w), hi);
+    lo = dp4a_u8s8(w.z & kLo, static_cast<int32_t>(xb.x), lo);
+    hi = dp4a_u8s8(w.z & kHi, static_cast<int32_t>(xb.y), hi);
+    lo = dp4a_u8s8(w.w & kLo, static_cast<int32_t>(xb.z), lo);
+    hi = dp4a_u8s8(w.w & kHi, static_cast<int32_t>(xb.w), hi);
+    return lo + (hi >> 4);
 }
 
 // ---- Q8_1 quantiser ------------------------------------------------------------------
@@ -119,6 +137,15 @@ struct StagedX {
 };
 __host__ __device__ inline size_t staged_x_bytes(int K) {
     return static_cast<size_t>(K) + static_cast<size_t>(K / kChunk) * 4 + static_cast<size_t>(K / kGroup) * 4;
+}
+
+// RMSNorm scale from the sum of squares.  The sum is taken in double (squares of fp16 values are exact there
+// and their sum is off by parts in 2^50 at most, so the order of the additions does not reach the fp32 mean
+// and every kernel of this library gets the same value); everything after it is IEEE fp32
+// as in the reference (src/kernels/rmsnorm_rope.cu:214-233): mean, + eps, square root, reciprocal.
+__device__ __forceinline__ float inv_rms_from_sumsq(double sumsq, int n, float eps) {
+    const float mean = __fdiv_rn(__double2float_rn(sumsq), static_cast<float>(n));
+    return __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(mean, eps)));
 }
 
 // Copies a pre-quantised Q8_1 activation from global into shared memory, folding the four
@@ -189,7 +216,7 @@ __device__ __forceinline__ void stage_x_from_fp16_rmsnorm(const __half* __restri
     if (threadIdx.x == 0) {
         double t = 0.0;
         for (int w = 0; w < nwarps; ++w) t += s_red[w];
-        s_inv = static_cast<float>(1.0 / sqrt(t / static_cast<double>(K) + static_cast<double>(eps)));
+        s_inv = inv_rms_from_sumsq(t, K, eps);
     }
     __syncthreads();
     const __half2 inv2 = __float2half2_rn(s_inv);
@@ -270,7 +297,11 @@ __device__ __forceinline__ void prefetch_gamma(const __half* __restrict__ g_gamm
 // fp16 activation (optionally RMSNorm'ed with the prefetched gain) -> staged Q8_1.  One global round trip.
 template <bool NORM>
 __device__ __forceinline__ void stage_x_fp16_regs(const __half* g_x, const uint4 (&gam)[kStageRounds], int K, float eps,
-                                                  int8_t* s_q8, int32_t* s_seed, float* s_scale) {
+                                                  int8_t* s_q8, int32_t* s_seed, float* s_scale,
+                                                  unsigned int* marks = nullptr) {
+    // marks (profiling builds): cycle stamps of thread 0 after the load arrived / the reduction / the inverse / the end
+    long long mk_t = marks ? clock64() : 0;
+    auto mark = [&](int i) { if (marks) { const long long c = clock64(); marks[i] = static_cast<unsigned int>(c - mk_t); mk_t = c; } };
     __shared__ double s_red[8];
     const int hw = threadIdx.x >> 4, hl = threadIdx.x & 15, nhw = blockDim.x >> 4;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -282,6 +313,8 @@ __device__ __forceinline__ void stage_x_fp16_regs(const __half* g_x, const uint4
         xr[r] = g < groups ? *reinterpret_cast<const uint4*>(g_x + g * kGroup + hl * 8) : make_uint4(0, 0, 0, 0);
     }
     __half2 inv2 = __float2half2_rn(1.0f);
+    if (marks) { if (xr[0].x == 0xFFFFFFFFu) marks[7] = 1; }   // consume the load so the stamp sees its arrival
+    mark(0);
     if constexpr (NORM) {
         double ss = 0.0;
 #pragma unroll
@@ -298,9 +331,12 @@ __device__ __forceinline__ void stage_x_fp16_regs(const __half* g_x, const uint4
         for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, m);
         if (lane == 0) s_red[warp] = ss;
         __syncthreads();
+        mark(1);
         double t = 0.0;
         for (int w = 0; w < nwarps; ++w) t += s_red[w];   // every thread, same order: no second barrier
-        inv2 = __float2half2_rn(static_cast<float>(1.0 / sqrt(t / static_cast<double>(K) + static_cast<double>(eps))));
+        inv2 = __float2half2_rn(inv_rms_from_sumsq(t, K, eps));
+        if (marks) { if (__low2float(inv2) == 12345.0f) marks[7] = 2; }
+        mark(2);
     }
     const int rounds = (groups + nhw - 1) / nhw;
 #pragma unroll
@@ -321,6 +357,7 @@ __device__ __forceinline__ void stage_x_fp16_regs(const __half* g_x, const uint4
             quantize_group_halfwarp_to_smem(v, g, hl, g < groups, s_q8, s_seed, s_scale);
         }
     }
+    mark(3);
 }
 
 // Pre-quantised Q8_1 -> shared memory with every global load of the thread in flight at once.

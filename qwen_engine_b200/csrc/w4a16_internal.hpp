@@ -3,6 +3,7 @@
 
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
+#include <utility>
 
 #include <cstdint>
 
@@ -21,21 +22,37 @@ bool pdl_enabled();
 void set_pdl_enabled(bool on);
 int env_int(const char* name, int fallback);       // read once, cached by the caller
 
-// One launch with (optionally) the programmatic-serialisation attribute.
+// One launch with (optionally) the programmatic-serialisation attribute and a cluster width along x.
 template <typename... KArgs, typename... Args>
-inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                                 bool pdl, Args&&... args) {
+inline cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                         cudaStream_t stream, bool pdl, int cluster_x, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (pdl) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_x > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = static_cast<unsigned>(cluster_x);
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+        ++n;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cfg.numAttrs = n;
     return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 bool pdl, Args&&... args) {
+    return launch_kernel_cluster(kernel, grid, block, smem, stream, pdl, 1, std::forward<Args>(args)...);
 }
 
 // ---- Q8_1 quantisers (q8_1_quantize.cu) ----
@@ -64,6 +81,11 @@ struct GemvArgs {
     // this process: plain stores travel over NVLink)
     __half* peer_out[7];
     int num_peers;
+    // SWIGLU only, all three or none: the Q8_1 form of the output vector, written by the same launch
+    // (clusters of four CTAs = one group of 128 outputs; needs units % 128 == 0)
+    int8_t* q8_out;
+    float* xscale_out;
+    int32_t* sum8_out;
     int K;
     int units;  // outputs produced: rows (PLAIN, QKV total) or row pairs (SWIGLU)
     // filled in by the planner

@@ -22,8 +22,8 @@ __all__ = [
     "launch_gemv_dual_gate_up_swiglu_w4a16", "launch_gemv_dual_gate_up_swiglu_w4a8",
     "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
     "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots", "DecodeSweep",
-    "launch_gemv_rmsnorm_w4a16", "launch_gemv_qkv_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16",
-    "gemv_w4a8_peers", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
+    "launch_gemv_rmsnorm_w4a16", "launch_gemv_qkv_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1",
+    "gemv_w4a8_peers", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_QUANT_IN_GATE_UP", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
 ]
 
 # Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
@@ -171,6 +171,17 @@ def launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16(gate_up_qweight, gate_up_scale
         intermediate_size, _stream(stream)))
 
 
+def launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1(gate_up_qweight, gate_up_scales, input_x, gamma, output_mlp,
+                                                       output_q8, output_scale, output_sum8, hidden_size,
+                                                       intermediate_size, stream=None):
+    """The launch above, which also leaves the Q8_1 form of output_mlp (the down projection's input)."""
+    check("w4a16_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1",
+          load().w4a16_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1(
+              _ptr(gate_up_qweight), _ptr(gate_up_scales), _ptr(input_x), _ptr(gamma), _ptr(output_mlp),
+              _ptr(output_q8), _ptr(output_scale), _ptr(output_sum8), hidden_size, intermediate_size,
+              _stream(stream)))
+
+
 def launch_gemm_prefill_w4a16(qweight, scales, input_x, residual, output_y, M, N, K, stream=None, sm_count=0):
     check("w4a16_gemm_prefill_w4a16", load().w4a16_gemm_prefill_w4a16(
         _ptr(qweight), _ptr(scales), _ptr(input_x), _ptr(residual), _ptr(output_y), M, N, K, _stream(stream),
@@ -203,6 +214,7 @@ def gemv_group_dots(qweight, input_q8, input_sum8, out_dots, out_features, in_fe
 
 SWEEP_SEPARATE, SWEEP_FUSE_NORM, SWEEP_FUSE_QUANT_O, SWEEP_FUSE_QUANT_DOWN, SWEEP_FUSE_ALL = 0, 1, 2, 4, 7
 SWEEP_PERSISTENT = 8
+SWEEP_QUANT_IN_GATE_UP = 16
 # the fastest measured form on B200: RMSNorm inside QKV / gate_up, Q8_1 inside O, a separate quantiser before down
 SWEEP_DEFAULT = SWEEP_FUSE_NORM | SWEEP_FUSE_QUANT_O
 

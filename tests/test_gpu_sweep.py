@@ -114,6 +114,52 @@ def test_fused_sweeps_give_the_bits_of_the_separate_launch_sequence(ops, model, 
     fused.close()
 
 
+@pytest.mark.parametrize("flags", [16, 19, 23])
+def test_sweep_with_q8_1_written_by_gate_up_gives_the_same_bits(ops, model, flags):
+    """The gate_up launch quantising its own output (clusters of four CTAs per group of 128) replaces the
+    quantiser launch in front of down without changing a bit of the hidden state."""
+    from qwen_engine_b200 import synth
+    _, layers_dev = model
+    h_in = util.to_dev(synth.activations(7, "h0", synth.HIDDEN))
+    ref_sweep = ops.DecodeSweep(layers_dev, flags=ops.SWEEP_SEPARATE)
+    fused = ops.DecodeSweep(layers_dev, flags=flags)
+    assert fused.launches == 28 * (8 - (2 if flags & 1 else 0) - (1 if flags & 2 else 0) - 1)
+    a, b = torch.empty_like(h_in), torch.empty_like(h_in)
+    ref_sweep.run_device(h_in, a)
+    for _ in range(3):      # replays must agree with each other too
+        fused.run_device(h_in, b)
+        torch.cuda.synchronize()
+        assert torch.equal(a, b)
+    ref_sweep.close()
+    fused.close()
+
+
+@pytest.mark.parametrize("H,I,norm", [(1536, 8960, True), (1024, 1280, True), (512, 128, False), (2048, 4864, True)])
+def test_gate_up_q8_1_epilogue_equals_the_standalone_quantiser(ops, H, I, norm):
+    from qwen_engine_b200 import synth
+    x = util.to_dev((synth.activations(41, "fx", H).astype(np.float32) * 3).astype(np.float16))
+    gamma = util.to_dev((1 + 0.1 * synth.activations(42, "fg", H).astype(np.float32)).astype(np.float16)) if norm else None
+    gw, gs = util.to_dev(synth.packed_weights(43, "gu", 2 * I, H)), util.to_dev(synth.scales(43, "gu", 2 * I, H))
+    y = torch.empty(I, dtype=torch.float16, device="cuda")
+    q8 = torch.full((I,), 99, dtype=torch.int8, device="cuda")
+    xs = torch.full((I // 128,), -1.0, dtype=torch.float32, device="cuda")
+    s8 = torch.full((I // 8,), 12345, dtype=torch.int32, device="cuda")
+    ops.launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1(gw, gs, x, gamma, y, q8, xs, s8, H, I)
+    # the two-launch form: fused gate_up (same output to within the summation order), then the quantiser on y
+    y_ref = torch.empty_like(y)
+    ops.launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16(gw, gs, x, gamma, y_ref, H, I)
+    q8r, xsr, s8r = torch.empty_like(q8), torch.empty_like(xs), torch.empty_like(s8)
+    ops.launch_quantize_fp16_to_q8_1(y, q8r, xsr, s8r, I)
+    torch.cuda.synchronize()
+    assert torch.equal(q8, q8r) and torch.equal(xs, xsr) and torch.equal(s8, s8r)
+    util.assert_fp16_close(util.to_np(y), util.to_np(y_ref).astype(np.float64), what="gate_up with Q8_1 epilogue")
+    if I // 32 >= 193:   # same CTA shape as the plain launch: same bits
+        assert torch.equal(y, y_ref)
+    # a width that is not a whole number of groups is refused
+    with pytest.raises(ops.W4A16Error):
+        ops.launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1(gw, gs, x, gamma, y, q8, xs, s8, H, I - 64)
+
+
 def test_fused_entry_points_equal_two_call_sequences(ops):
     from qwen_engine_b200 import synth
     H, I = 1536, 8960

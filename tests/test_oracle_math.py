@@ -92,8 +92,9 @@ def test_rmsnorm_against_numpy():
     x = (rng.standard_normal(1536) * 2).astype(np.float16)
     g = (1 + 0.1 * rng.standard_normal(1536)).astype(np.float16)
     y, inv = oracle.rmsnorm(x, g)
-    inv_ref = np.float32(1.0 / np.sqrt(np.mean(x.astype(np.float64) ** 2) + np.float64(np.float32(1e-6))))
-    assert inv == pytest.approx(float(inv_ref), rel=1e-7)
+    mean = np.float32(np.sum(x.astype(np.float64) ** 2)) / np.float32(1536)
+    inv_ref = np.float32(1) / np.sqrt(mean + np.float32(1e-6), dtype=np.float32)
+    assert np.float32(inv) == inv_ref      # IEEE fp32 after the double-precision sum
     ih = np.float16(inv_ref)
     expect = ((x * ih).astype(np.float16) * g).astype(np.float16)
     assert np.array_equal(y.view(np.uint16), expect.view(np.uint16))
