@@ -68,6 +68,7 @@ struct TcArgs {
     int tiles[3];            // 128-row tiles per weight tensor
     const __half* residual;
     int M, K, T, stages, tmem_cols;
+    int ksplit;              // CTAs (one cluster along grid z) that share the K range of one output tile
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------
@@ -162,6 +163,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr)
         : "memory");
 }
+// Cluster-wide barrier (all threads of all CTAs of the cluster) and stores into another CTA's shared memory.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_map_shared(uint32_t local_addr, uint32_t cta_rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_addr), "r"(cta_rank));
+    return remote;
+}
+__device__ __forceinline__ void st_shared_cluster_u32(uint32_t addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 B apart, 8-row groups
@@ -216,6 +230,13 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#ifdef W4A16_TC_PROFILE
+    const long long t_entry = clock64();
+    const bool tl_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0;
+#define TC_TL(i) if (tl_on) g_tc_prof[i] = clock64() - t_entry;
+#else
+#define TC_TL(i)
+#endif
 
     // which weight tensor / which rows
     int t = 0, tile = blockIdx.x;
@@ -226,7 +247,12 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
     const int n0 = tile * kTileRows;         // first weight row of this CTA inside tensor t
     const int m0 = blockIdx.y * T;           // first token
     const int rows_t = a.rows[t];
-    const int num_kb = K / kBK, num_sb = K / 256;
+    // K range of this CTA: whole 256-element super-blocks, spread over the cluster as evenly as they go
+    const int ksplit = a.ksplit, krank = blockIdx.z;
+    const int total_sb = K / 256;
+    const int sb_begin = krank * (total_sb / ksplit) + min(krank, total_sb % ksplit);
+    const int num_sb = total_sb / ksplit + (krank < total_sb % ksplit ? 1 : 0);
+    const int num_kb = num_sb * (256 / kBK), kb_begin = sb_begin * (256 / kBK);
 
     if (tid == 0) {
         for (int i = 0; i < kRawStages; ++i) { mbar_init(raw_full(i), 1); mbar_init(raw_empty(i), kDqWarps); }
@@ -247,6 +273,7 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
+    TC_TL(20);
 
     if (warp < kDqWarps) {
         // ---------------- dequantise: group = warp / 4, thread = weight row inside the group ----------------
@@ -255,13 +282,16 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
         // scales of the 128 rows, transposed to [group][row]
         {
             const __half* sc = a.scales[t];
-            for (int idx = tid; idx < kTileRows * G; idx += kDqThreads) {
-                const int rr = idx / G, g = idx - rr * G;
+            const int g_local = 2 * num_sb, g_begin = 2 * sb_begin;    // this CTA's groups of 128 only
+            for (int idx = tid; idx < kTileRows * g_local; idx += kDqThreads) {
+                const int rr = idx / g_local, g = idx - rr * g_local;
                 const int row = n0 + rr;
-                s_scale[g * kTileRows + rr] = row < rows_t ? sc[static_cast<size_t>(row) * G + g] : __float2half(0.0f);
+                s_scale[g * kTileRows + rr] =
+                    row < rows_t ? sc[static_cast<size_t>(row) * G + g_begin + g] : __float2half(0.0f);
             }
             asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");
         }
+        TC_TL(21);
         const int sw = r & 7;
         bool ok = true;
         int rs = 0;
@@ -317,9 +347,35 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
         }
 #endif
         // ---------------- epilogue: thread = weight row, registers = tokens ----------------
+        TC_TL(22);
         if (ok) ok = warp_wait(accum_full, 0, s_abort, lane);
         tc_fence_after();
-        if (ok) {
+        TC_TL(23);
+        // Split K: the CTAs of the cluster hold partial sums of the same output tile.  After a first cluster
+        // barrier (everyone's main loop is over, so the leader's pipeline buffers are free) the others store
+        // their fp32 partials into the leader's shared memory, [rank-1][token][row] (conflict-free for row-per-thread); after a second barrier the
+        // leader adds them in rank order and finishes alone.  Every thread of every CTA passes both barriers,
+        // also when a bounded wait gave up.
+        float* s_part = reinterpret_cast<float*>(smem);
+        if (ksplit > 1) {
+            cluster_sync_all();
+            TC_TL(24);
+            if (krank != 0 && ok) {
+                const uint32_t remote0 = cluster_map_shared(smem_u32(s_part), 0);
+                for (int c0 = part * 16; c0 < T; c0 += 16 * NG) {
+                    uint32_t v[16];
+                    const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+                    tmem_ld16(lane_base + static_cast<uint32_t>(c0), v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        st_shared_cluster_u32(remote0 + 4u * static_cast<uint32_t>(((krank - 1) * T + c0 + j) * kTileRows + r), v[j]);
+                }
+            }
+            cluster_sync_all();
+            TC_TL(25);
+        }
+        if (ok && krank == 0) {
             const int n = n0 + r;
             const bool row_ok = n < rows_t;
             __half* out = a.out[t];
@@ -331,6 +387,16 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
                 tmem_ld16(lane_base + static_cast<uint32_t>(c0), v);
                 tmem_ld_wait();
 
+                TC_TL(28);
+                // the other CTAs' partial sums, slice after slice (16 independent loads in flight each)
+                for (int k = 1; k < ksplit; ++k) {
+                    float p[16];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) p[j] = s_part[((k - 1) * T + c0 + j) * kTileRows + r];
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + p[j]);
+                }
+                TC_TL(29);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int m = m0 + c0 + j;
@@ -412,6 +478,7 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
 #endif
         }
         __syncwarp();
+        if (ksplit > 1) { cluster_sync_all(); cluster_sync_all(); }
     } else if (warp == kDqWarps + 1) {
         // ---------------- TMA: token tiles ----------------
         if (lane == 0) {
@@ -425,7 +492,7 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
                 TC_PROF_ADD(x_wait, w0);
                 if (!okx) break;
                 mbar_arrive_expect_tx(full(s), static_cast<uint32_t>(b_bytes));
-                tma_load_2d(smem_u32(s_b + s * b_bytes), &a.tmap_x, kb * kBK, m0, full(s));
+                tma_load_2d(smem_u32(s_b + s * b_bytes), &a.tmap_x, (kb_begin + kb) * kBK, m0, full(s));
                 if (++s == S) { s = 0; ph ^= 1; }
             }
 #ifdef W4A16_TC_PROFILE
@@ -433,6 +500,7 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
 #endif
         }
         __syncwarp();
+        if (ksplit > 1) { cluster_sync_all(); cluster_sync_all(); }
     } else {
         // ---------------- TMA: raw packed weights ----------------
         if (lane == 0) {
@@ -441,15 +509,18 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
             for (int sb = 0; sb < num_sb; ++sb) {
                 if (!mbar_wait(raw_empty(rs), rph ^ 1, s_abort)) break;
                 mbar_arrive_expect_tx(raw_full(rs), kRawBytes);
-                tma_load_2d(smem_u32(s_raw + rs * kRawBytes), &a.tmap_w[t], sb * 128, n0, raw_full(rs));
+                tma_load_2d(smem_u32(s_raw + rs * kRawBytes), &a.tmap_w[t], (sb_begin + sb) * 128, n0, raw_full(rs));
                 if (++rs == kRawStages) { rs = 0; rph ^= 1; }
             }
         }
         __syncwarp();
+        if (ksplit > 1) { cluster_sync_all(); cluster_sync_all(); }
     }
 
+    TC_TL(26);
     tc_fence_before();
     __syncthreads();
+    TC_TL(27);
     if (warp == kDqWarps) tmem_dealloc(tmem_base, static_cast<uint32_t>(a.tmem_cols));
 }
 
@@ -508,10 +579,17 @@ cudaError_t raise_tc_smem_modes() {
 template <int NG>
 cudaError_t launch_tc(int mode, dim3 grid, size_t smem, cudaStream_t stream, const TcArgs& a) {
     const dim3 block((4 * NG + 3) * 32);
+    const dim3 cluster(1, 1, static_cast<unsigned>(a.ksplit));   // the K slices of one output tile
     switch (mode) {
-        case kPlain: return launch_kernel(gemm_w4a16_tc_kernel<kPlain, NG>, grid, block, smem, stream, pdl_enabled(), a);
-        case kQkv: return launch_kernel(gemm_w4a16_tc_kernel<kQkv, NG>, grid, block, smem, stream, pdl_enabled(), a);
-        default: return launch_kernel(gemm_w4a16_tc_kernel<kSwiglu, NG>, grid, block, smem, stream, pdl_enabled(), a);
+        case kPlain:
+            return launch_kernel_cluster(gemm_w4a16_tc_kernel<kPlain, NG>, grid, block, smem, stream, pdl_enabled(),
+                                         cluster, a);
+        case kQkv:
+            return launch_kernel_cluster(gemm_w4a16_tc_kernel<kQkv, NG>, grid, block, smem, stream, pdl_enabled(),
+                                         cluster, a);
+        default:
+            return launch_kernel_cluster(gemm_w4a16_tc_kernel<kSwiglu, NG>, grid, block, smem, stream, pdl_enabled(),
+                                         cluster, a);
     }
 }
 }  // namespace
@@ -562,6 +640,19 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     a.T = T;
     a.stages = S;
     a.tmem_cols = T < 32 ? 32 : T;
+    // Split K over a cluster when the output tiles alone leave most SMs idle (decode batches on the per-layer
+    // shapes): each tensor-core instruction costs its issuing thread a fixed time however few tokens it
+    // carries, so a thin grid is bound by K / 16 instructions in a row per CTA.  Up to 8 CTAs (the portable
+    // cluster size) share a tile; their fp32 partials must fit the leader's pipeline buffers.
+    static const int ksplit_env = env_int("W4A16_TC_KSPLIT", 0);
+    const int ctas = total_tiles * ((g.M + T - 1) / T);
+    int ksplit = 1;
+    if (ctas * 2 <= sm_count) ksplit = std::min(8, sm_count / ctas);
+    if (ksplit_env > 0) ksplit = std::min(ksplit_env, 8);
+    ksplit = std::min(ksplit, g.K / 256);
+    const size_t ring_bytes = static_cast<size_t>(kRawStages) * kRawBytes + static_cast<size_t>(S) * (kABytes + T * 128);
+    while (ksplit > 1 && static_cast<size_t>(ksplit - 1) * T * kTileRows * sizeof(float) > ring_bytes) --ksplit;
+    a.ksplit = std::max(1, ksplit);
 
 
     for (int t = 0; t < nt; ++t) {
@@ -574,7 +665,7 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
                    static_cast<uint64_t>(g.M), static_cast<uint64_t>(g.K) * 2, kBK, static_cast<uint32_t>(T)))
         return W4A16_ERR_INVALID_ARG;
 
-    const dim3 grid(total_tiles, (g.M + T - 1) / T);
+    const dim3 grid(total_tiles, (g.M + T - 1) / T, a.ksplit);
     const size_t smem = tc_smem_bytes(T, S, g.K);
     // A dequantising group revisits a ring slot every NG k-blocks and waits on a parity: it must never
     // be two uses of a slot ahead of the tensor core, which holds exactly when NG <= stages.

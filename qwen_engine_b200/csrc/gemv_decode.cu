@@ -505,7 +505,7 @@ Plan make_plan(GemvMode mode, int units, int K, int sm_count) {
 template <int MODE, int U, int XIN>
 cudaError_t launch_aligned(const GemvArgs& a, bool aligned16, dim3 grid, dim3 block, size_t smem,
                            cudaStream_t stream) {
-    const int cluster_x = a.q8_out != nullptr ? 4 : 1;   // Q8_1 epilogue: four CTAs = one group of 128 outputs
+    const dim3 cluster_x(a.q8_out != nullptr ? 4 : 1, 1, 1);   // Q8_1 epilogue: four CTAs = one group of 128 outputs
     if (aligned16)
         return launch_kernel_cluster(gemv_w4_kernel<MODE, U, XIN, true>, grid, block, smem, stream, pdl_enabled(),
                                      cluster_x, a);

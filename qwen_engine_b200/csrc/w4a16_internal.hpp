@@ -22,10 +22,10 @@ bool pdl_enabled();
 void set_pdl_enabled(bool on);
 int env_int(const char* name, int fallback);       // read once, cached by the caller
 
-// One launch with (optionally) the programmatic-serialisation attribute and a cluster width along x.
+// One launch with (optionally) the programmatic-serialisation attribute and thread-block cluster dimensions.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
-                                         cudaStream_t stream, bool pdl, int cluster_x, Args&&... args) {
+                                         cudaStream_t stream, bool pdl, dim3 cluster, Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -38,11 +38,11 @@ inline cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, di
         attr[n].val.programmaticStreamSerializationAllowed = 1;
         ++n;
     }
-    if (cluster_x > 1) {
+    if (cluster.x * cluster.y * cluster.z > 1) {
         attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = static_cast<unsigned>(cluster_x);
-        attr[n].val.clusterDim.y = 1;
-        attr[n].val.clusterDim.z = 1;
+        attr[n].val.clusterDim.x = cluster.x;
+        attr[n].val.clusterDim.y = cluster.y;
+        attr[n].val.clusterDim.z = cluster.z;
         ++n;
     }
     cfg.attrs = attr;
@@ -52,7 +52,7 @@ inline cudaError_t launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, di
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                  bool pdl, Args&&... args) {
-    return launch_kernel_cluster(kernel, grid, block, smem, stream, pdl, 1, std::forward<Args>(args)...);
+    return launch_kernel_cluster(kernel, grid, block, smem, stream, pdl, dim3(1, 1, 1), std::forward<Args>(args)...);
 }
 
 // ---- Q8_1 quantisers (q8_1_quantize.cu) ----
