@@ -614,7 +614,7 @@ def main():
             line["roofline"] = kernel_roofline(torch, ops, layers_dev, stream, peaks)
         line["roofline_sweep"] = {"achieved": value / world, "peak": peaks.get("hbm_gbs", 6650.0),
                                   "frac": value / world / peaks.get("hbm_gbs", 6650.0), "unit": UNIT,
-                                  "note": "whole sweep (224 dependent launches) per GPU against the copy peak"}
+                                  "note": f"whole sweep ({sweep.launches} dependent launches) per GPU against the copy peak"}
     if world > 1 or os.environ.get("W4A16_BENCH_LM_HEAD", "1") == "1":
         lm = lm_head_nsplit(torch, dist, ops, rank, world, stream, min(steps, 200), warmup)
         if rank == 0:

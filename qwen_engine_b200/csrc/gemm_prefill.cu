@@ -17,18 +17,85 @@ cudaError_t launch_smallm(const SmallMArgs& a, int mt, dim3 grid, dim3 block, cu
     }
 }
 
+// ---- few-token form (gemm_smallm_v2_kernel) ----
+template <int MODE, int U, int MT>
+cudaError_t launch_v2_one(const SmallMArgs& a, const SmallMPlan& p, dim3 grid, dim3 block, size_t smem, cudaStream_t stream) {
+    return launch_kernel(gemm_smallm_v2_kernel<MODE, U, MT>, grid, block, smem, stream, pdl_enabled(), a, p);
+}
+template <int MODE>
+cudaError_t launch_v2(const SmallMArgs& a, const SmallMPlan& p, int U, int mt, dim3 grid, dim3 block, size_t smem,
+                      cudaStream_t stream) {
+    if (U == 4) {
+        if (mt == 1) return launch_v2_one<MODE, 4, 1>(a, p, grid, block, smem, stream);
+        if (mt == 2) return launch_v2_one<MODE, 4, 2>(a, p, grid, block, smem, stream);
+        return launch_v2_one<MODE, 4, 4>(a, p, grid, block, smem, stream);
+    }
+    if (mt == 1) return launch_v2_one<MODE, 8, 1>(a, p, grid, block, smem, stream);
+    if (mt == 2) return launch_v2_one<MODE, 8, 2>(a, p, grid, block, smem, stream);
+    return launch_v2_one<MODE, 8, 4>(a, p, grid, block, smem, stream);
+}
+template <int MODE, int U, int MT>
+cudaError_t raise_v2() {
+    return cudaFuncSetAttribute(gemm_smallm_v2_kernel<MODE, U, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+}
+template <int MODE>
+cudaError_t raise_v2_mode() {
+    cudaError_t e = raise_v2<MODE, 4, 1>();
+    if (e == cudaSuccess) e = raise_v2<MODE, 4, 2>();
+    if (e == cudaSuccess) e = raise_v2<MODE, 4, 4>();
+    if (e == cudaSuccess) e = raise_v2<MODE, 8, 1>();
+    if (e == cudaSuccess) e = raise_v2<MODE, 8, 2>();
+    if (e == cudaSuccess) e = raise_v2<MODE, 8, 4>();
+    return e;
+}
+
+// CTA shape of the few-token form: as the decode GEMV's -- enough CTAs for every SM, all sub-warps busy,
+// the K range of a sub-warp at most 8 steps deep, and the whole grid resident (16 warps per SM at the
+// kernel's 128 registers).  Returns false when a K slice would be deeper than 8 steps.
+bool plan_v2(const GemmArgs& g, int units, int sm_count, SmallMPlan* out, int* U) {
+    const int steps = g.K / kStepElems;
+    const int target = (sm_count * 13 + 9) / 10;
+    int upc = 32;
+    while (upc > 4 && (units + upc - 1) / upc < target) upc /= 2;
+    if (g.mode == kQkv)
+        while (upc > 1 && (g.rows[0] % upc || g.rows[1] % upc)) upc /= 2;
+    int cap = std::min(std::max(1, 32 / upc), steps);
+    int per = (steps + cap - 1) / cap;
+    int ksplit = (steps + per - 1) / per;
+    const int grid = (units + upc - 1) / upc;
+    while (ksplit > 1 && per < 8) {
+        const int warps = (upc * ksplit * kSubwarp + 31) / 32;
+        if (grid <= (16 / warps) * sm_count) break;
+        per = (steps + (ksplit - 1) - 1) / (ksplit - 1);
+        ksplit = (steps + per - 1) / per;
+    }
+    if (per > 8) return false;
+    out->units_per_cta = upc;
+    out->ksplit = ksplit;
+    out->steps_per_split = per;
+    *U = per <= 4 ? 4 : 8;
+    return true;
+}
+
 }  // namespace
 
-int gemm_set_attributes() { return gemm_tc_set_attributes(); }
+int gemm_set_attributes() {
+    cudaError_t e = raise_v2_mode<kPlain>();
+    if (e == cudaSuccess) e = raise_v2_mode<kQkv>();
+    if (e == cudaSuccess) e = raise_v2_mode<kSwiglu>();
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return gemm_tc_set_attributes();
+}
 
 int gemm_launch(GemmArgs g, cudaStream_t stream) {
     const DeviceInfo* dev = nullptr;
     if (int st = ensure_device_ready(&dev)) return st;
 
-    // The tcgen05 kernel pads the token count to its smallest tile (16) and is already faster than the
-    // CUDA-core weight-streaming kernel from a handful of tokens (measured crossover on B200: 3-5 tokens
-    // depending on the shape); the CUDA-core kernel serves 1-3 tokens and pointers or shapes TMA cannot address.
-    static const int tc_min_m = env_int("W4A16_TC_MIN_M", 4);
+    // The tcgen05 kernel pads the token count to its smallest tile (16); measured on B200 it overtakes the
+    // CUDA-core few-token form at 5 tokens on the K = 1536 shapes and at 4 on K = 8960 (where the few-token
+    // form stages only two tokens per pass).  The CUDA-core forms also take what TMA cannot address.
+    static const int tc_min_m_env = env_int("W4A16_TC_MIN_M", 0);
+    const int tc_min_m = tc_min_m_env > 0 ? tc_min_m_env : (g.K > 4096 ? 4 : 5);
     if (g.M >= tc_min_m && gemm_tc_supported(g)) return gemm_tc_launch(g, dev->sm_count, stream);
 
     SmallMArgs a;
@@ -39,6 +106,33 @@ int gemm_launch(GemmArgs g, cudaStream_t stream) {
         a.out_ld[0] = g.rows[0]; a.out_ld[1] = g.rows[1]; a.out_ld[2] = g.rows[2];
     } else {
         a.out_ld[0] = a.units; a.out_ld[1] = a.out_ld[2] = 0;
+    }
+    // few tokens, 16-byte aligned tensors: the form that streams like the decode GEMV
+    static const int v2_on = env_int("W4A16_SMALLM_V2", 1);
+    bool aligned = reinterpret_cast<uintptr_t>(g.x) % 16 == 0;
+    for (int t = 0; t < (g.mode == kQkv ? 3 : 1); ++t) aligned = aligned && reinterpret_cast<uintptr_t>(g.qweight[t]) % 16 == 0;
+    SmallMPlan plan;
+    int U = 8;
+    if (v2_on && aligned && plan_v2(g, a.units, dev->sm_count, &plan, &U)) {
+        const int R = g.mode == kSwiglu ? 2 : 1;
+        // tokens per pass: as many as the shared-memory budget of a CTA (about a third of an SM) allows
+        int mt = g.M >= 4 ? 4 : (g.M >= 2 ? 2 : 1);
+        auto smem_for = [&](int t) {
+            return (static_cast<size_t>(t) * smallm_x_stride(g.K) + static_cast<size_t>(plan.ksplit) * plan.units_per_cta * R * t) * sizeof(float);
+        };
+        if (g.mode == kSwiglu && U == 8) mt = std::min(mt, 2);   // row pairs with 8 loads each: the registers are full
+        while (mt > 1 && smem_for(mt) > 72 * 1024) mt /= 2;
+        if (smem_for(mt) <= 160 * 1024) {
+            const int threads = plan.units_per_cta * plan.ksplit * kSubwarp;
+            const dim3 grid2((a.units + plan.units_per_cta - 1) / plan.units_per_cta), block2((threads + 31) / 32 * 32);
+            cudaError_t e2;
+            switch (g.mode) {
+                case kPlain: e2 = launch_v2<kPlain>(a, plan, U, mt, grid2, block2, smem_for(mt), stream); break;
+                case kQkv: e2 = launch_v2<kQkv>(a, plan, U, mt, grid2, block2, smem_for(mt), stream); break;
+                default: e2 = launch_v2<kSwiglu>(a, plan, U, mt, grid2, block2, smem_for(mt), stream); break;
+            }
+            return static_cast<int>(e2);
+        }
     }
     int upc = 32;
     const int target = (dev->sm_count * 13 + 9) / 10;

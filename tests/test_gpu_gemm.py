@@ -71,10 +71,13 @@ def test_gemm_prefill_matches_oracle(ops, M, N, K, use_res):
     assert np.isfinite(out).all()
 
 
-@pytest.mark.parametrize("M", [1, 4, 16, 70, 256])
-def test_gemm_prefill_qkv_matches_oracle(ops, M):
+@pytest.mark.parametrize("M,K,nq,nkv,hd", [(1, 1536, 12, 2, 128), (4, 1536, 12, 2, 128), (16, 1536, 12, 2, 128),
+                                           (70, 1536, 12, 2, 128), (256, 1536, 12, 2, 128),
+                                           # k/v widths below the tensor-core tile: the CUDA-core form at any
+                                           # token count (several token passes, ragged last one, deep K slices)
+                                           (19, 1536, 4, 1, 64), (7, 8960, 4, 1, 64), (2, 256, 2, 1, 32)])
+def test_gemm_prefill_qkv_matches_oracle(ops, M, K, nq, nkv, hd):
     from qwen_engine_b200 import synth
-    K, nq, nkv, hd = 1536, 12, 2, 128
     dims = [nq * hd, nkv * hd, nkv * hd]
     x = synth.activations(M, "qkv", M, K)
     ws = [(synth.packed_weights(M, f"t{i}", n, K), synth.scales(M, f"t{i}", n, K)) for i, n in enumerate(dims)]
