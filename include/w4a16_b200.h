@@ -121,6 +121,55 @@ W4A16_API int w4a16_gemv_w4a8_peers(const uint32_t* qweight, const void* scales,
                                     void* const* peer_outputs, int num_peers, int out_features,
                                     int in_features, w4a16_stream_t stream);
 
+/* ---- token selection after lm_head ------------------------------------------------------ */
+/* Same layout as the reference's DeviceControlBlock (include/tensor.cuh:28-34); lives in device memory. */
+typedef struct w4a16_sample_control {
+    int32_t token_id;      /* written by the samplers */
+    int32_t seq_pos;       /* Philox counter word 1; incremented by the samplers */
+    float temperature;     /* <= 1e-5: greedy argmax; else Gumbel-max on logit / temperature */
+    uint32_t reserved;
+    uint64_t rng_seed;     /* Philox key; advanced by 0x9E3779B97F4A7C15 per token */
+} w4a16_sample_control;
+
+/*
+ * reference include/kernels.cuh:210-219 launch_sample_and_advance (src/kernels/sampling.cu:60-232): token =
+ * index of the largest score, lowest index among equals; score = logit, or logit / temperature + Gumbel noise
+ * from Philox-4x32-10 keyed by (rng_seed; vocabulary index, seq_pos); writes the token into the control
+ * block and *d_token_out (either may be NULL) and advances seq_pos and rng_seed.  The two scratch arrays hold
+ * 256 entries, as in the reference.  Arithmetic is IEEE fp32 with the accurate logf (the reference's
+ * fast-math build uses approximations, so at temperature > 0 the two can pick different tokens when two scores
+ * agree to the last bits; greedy selection is identical).
+ */
+W4A16_API int w4a16_sample_and_advance(const void* logits, float* sample_scratch_val, int32_t* sample_scratch_idx,
+                                       void* d_control, int32_t* d_token_out, w4a16_stream_t stream,
+                                       int vocab_size);
+
+/*
+ * lm_head and token selection in one pass over the weights (no reference counterpart; replaces the pair
+ * launch_gemv_w4a8 + launch_sample_and_advance at src/engine.cu:440-450): every CTA of the GEMV scores the
+ * rows it produced and leaves ONE (score, index) candidate; w4a16_sample_finish reduces the candidates,
+ * writes the token and advances the control block.  The fp16 logits are stored only if output_logits is not
+ * NULL.  The token equals w4a16_sample_and_advance on the logits w4a16_gemv_w4a8 would write.
+ * candidate_val / candidate_idx: w4a16_sample_slots(out_features) entries.  index_offset is the vocabulary
+ * index of row 0 -- with the rows of lm_head split over GPUs every rank passes its slab's first row, the
+ * ranks exchange their candidates (8 bytes per slot instead of the logits) and one w4a16_sample_finish over
+ * all of them gives the token.  Needs 16-byte aligned weights and in_features <= 2048 (W4A16_ERR_SHAPE).
+ */
+W4A16_API int w4a16_sample_slots(int out_features);
+W4A16_API int w4a16_gemv_w4a8_sample_candidates(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                                                const float* input_scale, const int32_t* input_sum8,
+                                                void* output_logits, float* candidate_val, int32_t* candidate_idx,
+                                                const void* d_control, int index_offset, int out_features,
+                                                int in_features, w4a16_stream_t stream);
+W4A16_API int w4a16_sample_finish(const float* candidate_val, const int32_t* candidate_idx, int count,
+                                  void* d_control, int32_t* d_token_out, w4a16_stream_t stream);
+/* Both steps on one GPU; the scratch arrays hold w4a16_sample_slots(out_features) entries. */
+W4A16_API int w4a16_gemv_w4a8_sample_and_advance(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                                                 const float* input_scale, const int32_t* input_sum8,
+                                                 void* output_logits, float* sample_scratch_val,
+                                                 int32_t* sample_scratch_idx, void* d_control, int32_t* d_token_out,
+                                                 int out_features, int in_features, w4a16_stream_t stream);
+
 /* reference include/kernels.cuh:84-94 launch_gemv_qkv_w4a8 (src/kernels/gemv_w4a16.cu:123-194,
  * 387-513, 893-926): q, k and v projections in one launch. */
 W4A16_API int w4a16_gemv_qkv_w4a8(const w4a16_qkv_view* view, const int8_t* input_q8,

@@ -61,6 +61,8 @@ def lib() -> ctypes.CDLL:
     if _lib is None:
         _lib = ctypes.CDLL(str(build()))
         _lib.orc_rmsnorm.restype = ctypes.c_float
+        _lib.orc_sample.restype = ctypes.c_int32
+        _lib.orc_philox_first.restype = ctypes.c_uint32
     return _lib
 
 
@@ -193,6 +195,22 @@ def rmsnorm(x, gamma, eps=1e-6, inv_rms_override=0.0):
     inv = lib().orc_rmsnorm(_p(x), _p(gamma), ctypes.c_int(x.size), ctypes.c_float(eps),
                             ctypes.c_float(inv_rms_override), _p(y))
     return y, float(inv)
+
+
+def philox_first(seed, c0, c1):
+    """First output word of Philox-4x32-10 for counter (c0, c1, 0, 0) and the 64-bit key `seed`."""
+    return int(lib().orc_philox_first(ctypes.c_uint64(seed), ctypes.c_uint32(c0), ctypes.c_uint32(c1)))
+
+
+def sample(logits, temperature=0.0, seed=0, seq_pos=0, index_offset=0):
+    """Greedy / Gumbel-max token selection over fp16 logits: (token, best score, scores float32 [n])."""
+    logits = np.ascontiguousarray(logits, dtype=np.float16).reshape(-1)
+    scores = np.empty(logits.size, dtype=np.float32)
+    best = ctypes.c_float(0.0)
+    tok = lib().orc_sample(_p(logits), ctypes.c_int(logits.size), ctypes.c_float(temperature),
+                           ctypes.c_uint64(seed), ctypes.c_uint32(seq_pos), ctypes.c_int32(index_offset),
+                           ctypes.byref(best), _p(scores))
+    return int(tok), float(best.value), scores
 
 
 def decode_sweep(layers, h0, threads=None, collect=False):

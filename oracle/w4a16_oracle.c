@@ -482,4 +482,53 @@ ORC_API float orc_rmsnorm(const uint16_t* x, const uint16_t* gamma, int n, float
     return inv_rms;
 }
 
-ORC_API int orc_version(void) { return 1; }
+/* ------------------------------------------------------------------------- */
+/* Token selection after lm_head.  src/kernels/sampling.cu:13-57 (uniform     */
+/* number from Philox-4x32-10: counter = (vocabulary index, sequence          */
+/* position, 0, 0), key = the seed's two halves, first output word;           */
+/* u = (word + 1) / 2^32 clamped to [1e-7, 1 - 1e-7]), :86-100 (score = logit */
+/* for temperature <= 1e-5, else logit / temperature - log(-log(u)); a larger */
+/* score wins, scanning in index order so that the lowest index wins among    */
+/* equals; the running best starts at -1e30 with index 0).                    */
+/* Philox as published: Salmon, Moraes, Dror, Shaw, SC'11.  fp32 arithmetic   */
+/* with libm's logf; scores_out (optional, n floats) receives every score.    */
+/* ------------------------------------------------------------------------- */
+static uint32_t philox4x32_10_first(uint64_t seed, uint32_t c0, uint32_t c1) {
+    uint32_t c2 = 0, c3 = 0;
+    uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+    for (int round = 0; round < 10; ++round) {
+        uint64_t p0 = (uint64_t)0xD2511F53u * c0;
+        uint64_t p1 = (uint64_t)0xCD9E8D57u * c2;
+        uint32_t n0 = (uint32_t)(p1 >> 32) ^ c1 ^ k0;
+        uint32_t n1 = (uint32_t)p1;
+        uint32_t n2 = (uint32_t)(p0 >> 32) ^ c3 ^ k1;
+        uint32_t n3 = (uint32_t)p0;
+        c0 = n0; c1 = n1; c2 = n2; c3 = n3;
+        k0 += 0x9E3779B9u;
+        k1 += 0xBB67AE85u;
+    }
+    return c0;
+}
+ORC_API uint32_t orc_philox_first(uint64_t seed, uint32_t c0, uint32_t c1) { return philox4x32_10_first(seed, c0, c1); }
+ORC_API int32_t orc_sample(const uint16_t* logits, int n, float temperature, uint64_t seed, uint32_t seq_pos,
+                           int32_t index_offset, float* best_out, float* scores_out) {
+    float best = -1e30f;
+    int32_t best_idx = 0;
+    for (int i = 0; i < n; ++i) {
+        float v = h2f(logits[i]);
+        if (temperature > 1e-5f) {
+            uint32_t r = philox4x32_10_first(seed, (uint32_t)(i + index_offset), seq_pos);
+            float u = ((float)r + 1.0f) / 4294967296.0f;
+            if (u < 1e-7f) u = 1e-7f;
+            if (u > 1.0f - 1e-7f) u = 1.0f - 1e-7f;
+            float gumbel = -logf(-logf(u));
+            v = (v / temperature) + gumbel;
+        }
+        if (scores_out) scores_out[i] = v;
+        if (v > best) { best = v; best_idx = i + index_offset; }
+    }
+    if (best_out) *best_out = best;
+    return best_idx;
+}
+
+ORC_API int orc_version(void) { return 2; }

@@ -152,6 +152,68 @@ static int gemv_plain(const uint32_t* qweight, const void* scales, const void* x
     return gemv_launch(kPlain, a, S(stream));
 }
 
+// ---- token selection ----
+int w4a16_sample_and_advance(const void* logits, float* sample_scratch_val, int32_t* sample_scratch_idx,
+                             void* d_control, int32_t* d_token_out, w4a16_stream_t stream, int vocab_size) {
+    if (!logits || !sample_scratch_val || !sample_scratch_idx || vocab_size <= 0) return W4A16_ERR_INVALID_ARG;
+    if (misaligned(logits, 2) || misaligned(sample_scratch_val, 4) || misaligned(sample_scratch_idx, 4) ||
+        misaligned(d_control, 8) || misaligned(d_token_out, 4))
+        return W4A16_ERR_ALIGNMENT;
+    if (int st = ensure_device_ready(nullptr)) return st;
+    if (int st = sample_stage1(H(logits), sample_scratch_val, sample_scratch_idx, d_control, vocab_size, 0, S(stream)))
+        return st;
+    return sample_stage2(sample_scratch_val, sample_scratch_idx, sample_stage1_blocks(), d_control, d_token_out, S(stream));
+}
+
+int w4a16_sample_slots(int out_features) {
+    if (out_features <= 0) return W4A16_ERR_INVALID_ARG;
+    return gemv_sample_slots(out_features);
+}
+
+int w4a16_gemv_w4a8_sample_candidates(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                                      const float* input_scale, const int32_t* input_sum8, void* output_logits,
+                                      float* candidate_val, int32_t* candidate_idx, const void* d_control,
+                                      int index_offset, int out_features, int in_features, w4a16_stream_t stream) {
+    if (!qweight || !scales || !input_q8 || !input_scale || !input_sum8 || !candidate_val || !candidate_idx ||
+        out_features <= 0 || index_offset < 0)
+        return W4A16_ERR_INVALID_ARG;
+    if (int st = check_k(in_features)) return st;
+    if (misaligned(qweight, 16) || misaligned(scales, 2) || misaligned(output_logits, 2) || misaligned(input_scale, 4) ||
+        misaligned(input_sum8, 4) || misaligned(candidate_val, 4) || misaligned(candidate_idx, 4) ||
+        misaligned(d_control, 8))
+        return W4A16_ERR_ALIGNMENT;
+    GemvArgs a = {};
+    a.qweight[0] = qweight; a.scales[0] = H(scales); a.out[0] = H(output_logits); a.rows[0] = out_features;
+    a.q8 = input_q8; a.xscale = input_scale; a.sum8 = input_sum8;
+    a.K = in_features; a.units = out_features;
+    a.sample_val = candidate_val; a.sample_idx = candidate_idx; a.sample_control = d_control;
+    a.sample_index_offset = index_offset;
+    return gemv_launch(kPlain, a, S(stream));
+}
+
+int w4a16_sample_finish(const float* candidate_val, const int32_t* candidate_idx, int count, void* d_control,
+                        int32_t* d_token_out, w4a16_stream_t stream) {
+    if (!candidate_val || !candidate_idx || count <= 0) return W4A16_ERR_INVALID_ARG;
+    if (misaligned(candidate_val, 4) || misaligned(candidate_idx, 4) || misaligned(d_control, 8) || misaligned(d_token_out, 4))
+        return W4A16_ERR_ALIGNMENT;
+    if (int st = ensure_device_ready(nullptr)) return st;
+    return sample_stage2(candidate_val, candidate_idx, count, d_control, d_token_out, S(stream));
+}
+
+int w4a16_gemv_w4a8_sample_and_advance(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                                       const float* input_scale, const int32_t* input_sum8, void* output_logits,
+                                       float* sample_scratch_val, int32_t* sample_scratch_idx, void* d_control,
+                                       int32_t* d_token_out, int out_features, int in_features,
+                                       w4a16_stream_t stream) {
+    if (int st = w4a16_gemv_w4a8_sample_candidates(qweight, scales, input_q8, input_scale, input_sum8, output_logits,
+                                                   sample_scratch_val, sample_scratch_idx, d_control, 0, out_features,
+                                                   in_features, stream))
+        return st;
+    const int slots = gemv_sample_slots(out_features);
+    if (slots < 0) return slots;
+    return sample_stage2(sample_scratch_val, sample_scratch_idx, slots, d_control, d_token_out, S(stream));
+}
+
 int w4a16_gemv_w4a16(const uint32_t* qweight, const void* scales, const void* input_x, const void* residual,
                      void* output_y, int out_features, int in_features, w4a16_stream_t stream) {
     if (!input_x) return W4A16_ERR_INVALID_ARG;

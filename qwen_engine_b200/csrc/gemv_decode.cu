@@ -20,6 +20,7 @@
 #include <algorithm>
 #include <cstdlib>
 
+#include "sampling.cuh"
 #include "w4a16_common.cuh"
 #include "w4a16_internal.hpp"
 
@@ -356,6 +357,25 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const Ge
     if (blk < num_blocks) issue(w0, sb0, blk);
     pdl_release_dependents();
     pdl_wait_prior_grids();
+
+    // Token selection in the epilogue (PLAIN only): the fp16-rounded outputs of eight row blocks are parked in
+    // shared memory and then scored by all 256 threads at once (the Gumbel draw costs ~150 instructions per
+    // row; left to the one lane per row that holds the sum it would double the kernel's instruction count).
+    [[maybe_unused]] const bool sampling = !SWIGLU && a.sample_val != nullptr;
+    __shared__ float s_scores[2][kMaxThreads];
+    [[maybe_unused]] float temperature = 0.0f, best = kSampleFloor;
+    [[maybe_unused]] uint64_t rng_seed = 0;
+    [[maybe_unused]] uint32_t seq_pos = 0;
+    [[maybe_unused]] int32_t best_idx = 0;
+    [[maybe_unused]] int it = 0, buf = 0;
+    if constexpr (!SWIGLU) {
+        if (sampling && a.sample_control != nullptr) {
+            const SampleControl* c = static_cast<const SampleControl*>(a.sample_control);
+            temperature = c->temperature;
+            rng_seed = c->rng_seed;
+            seq_pos = static_cast<uint32_t>(c->seq_pos);
+        }
+    }
     if constexpr (XIN == kXFp16Norm) stage_x_from_fp16_rmsnorm(a.x_fp16, a.gamma, K, kRmsEps, s_q8, s_seed, s_scale);
     else if constexpr (XIN == kXFp16) stage_x_from_fp16(a.x_fp16, K, s_q8, s_seed, s_scale);
     else stage_x_from_q8_1(a.q8, a.xscale, a.sum8, K, a.vec_ok != 0, s_q8, s_seed, s_scale);
@@ -390,15 +410,44 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const Ge
             const float up = __shfl_xor_sync(0xFFFFFFFFu, acc, 8);   // the odd row's sum sits 8 lanes over
             if (l == 0 && (sub & 1) == 0 && row < N)
                 a.out[0][row >> 1] = __float2half_rn((acc / (1.0f + expf(-acc))) * up);
-        } else if (l == 0 && row < N) {
-            float y = acc;
-            if (a.residual != nullptr) y += __half2float(a.residual[row]);
-            const __half yh = __float2half_rn(y);
-            a.out[0][row] = yh;
-            for (int p = 0; p < a.num_peers; ++p) a.peer_out[p][row] = yh;
+        } else {
+            if (l == 0 && row < N) {
+                float y = acc;
+                if (a.residual != nullptr) y += __half2float(a.residual[row]);
+                const __half yh = __float2half_rn(y);
+                if (a.out[0] != nullptr) a.out[0][row] = yh;
+                for (int p = 0; p < a.num_peers; ++p) a.peer_out[p][row] = yh;
+                if (sampling) s_scores[buf][(it & 7) * kMaxSubwarps + sub] = __half2float(yh);
+            }
+            if (sampling) {
+                if ((it & 7) == 7 || nxt >= num_blocks) {      // uniform over the CTA
+                    __syncthreads();
+                    const int it_j = (it & ~7) + (tid >> 5);   // thread = (iteration of the group, row of the block)
+                    const int row_j = (static_cast<int>(blockIdx.x) + it_j * static_cast<int>(gridDim.x)) * kMaxSubwarps + (tid & 31);
+                    if (it_j <= it && row_j < N) {
+                        const int32_t index = row_j + a.sample_index_offset;
+                        sample_take(best, best_idx,
+                                    sample_score(s_scores[buf][tid], static_cast<uint32_t>(index), temperature, rng_seed, seq_pos),
+                                    index);
+                    }
+                    buf ^= 1;   // the next eight blocks park in the other half: one barrier per group is enough
+                }
+                ++it;
+            }
         }
 #pragma unroll
         for (int i = 0; i < STEPS; ++i) { w0[i] = w1[i]; sb0[i] = sb1[i]; }
+    }
+    if constexpr (!SWIGLU) {
+        if (sampling) {
+            __shared__ float s_v[32];
+            __shared__ int32_t s_i[32];
+            sample_block_reduce(best, best_idx, s_v, s_i);
+            if (tid == 0) {
+                a.sample_val[blockIdx.x] = best;
+                a.sample_idx[blockIdx.x] = best_idx;
+            }
+        }
     }
 }
 
@@ -555,6 +604,13 @@ int gemv_set_attributes() {
     return static_cast<int>(e);
 }
 
+int gemv_sample_slots(int out_features) {
+    const DeviceInfo* dev = nullptr;
+    if (int st = ensure_device_ready(&dev)) return st;
+    const int num_blocks = (out_features + kMaxSubwarps - 1) / kMaxSubwarps;
+    return std::min(num_blocks, 2 * dev->sm_count);   // the streaming form's grid
+}
+
 int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
     const DeviceInfo* dev = nullptr;
     if (int st = ensure_device_ready(&dev)) return st;
@@ -601,8 +657,10 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
     static const int stream_min_blocks = env_int("W4A16_GEMV_STREAM_MIN", 16);   // row blocks per SM from which it pays
     static const int stream_swiglu = env_int("W4A16_GEMV_STREAM_SWIGLU", 0);
     const bool tall = num_blocks >= stream_min_blocks * dev->sm_count;
-    if (stream_on && !q8_epilogue && aligned16 && steps <= 8 &&
-        ((mode == kPlain && tall) || (mode == kSwiglu && (tall || (stream_swiglu && num_blocks >= 3 * dev->sm_count))))) {
+    const bool sampling = a.sample_val != nullptr || a.sample_idx != nullptr;
+    if (sampling && (mode != kPlain || !a.sample_val || !a.sample_idx || !aligned16 || steps > 8)) return W4A16_ERR_SHAPE;
+    if ((sampling || stream_on) && !q8_epilogue && aligned16 && steps <= 8 &&
+        ((mode == kPlain && (tall || sampling)) || (mode == kSwiglu && (tall || (stream_swiglu && num_blocks >= 3 * dev->sm_count))))) {
         const dim3 sgrid(std::min(num_blocks, 2 * dev->sm_count)), sblock(kMaxThreads);
         const size_t ssmem = staged_x_bytes(a.K);
         const bool pdl = pdl_enabled();

@@ -86,6 +86,12 @@ struct GemvArgs {
     int8_t* q8_out;
     float* xscale_out;
     int32_t* sum8_out;
+    // PLAIN only, streaming form: token selection in the epilogue.  Every CTA leaves its best (score, index)
+    // candidate in sample_val / sample_idx [gemv_sample_slots()]; out[0] may then be null (logits not stored).
+    float* sample_val;
+    int32_t* sample_idx;
+    const void* sample_control;   // SampleControl (temperature, seed, position) in device memory, may be null
+    int sample_index_offset;      // added to the row number: vocabulary index of row 0 (row-split lm_head)
     int K;
     int units;  // outputs produced: rows (PLAIN, QKV total) or row pairs (SWIGLU)
     // filled in by the planner
@@ -98,6 +104,14 @@ int gemv_launch(GemvMode mode, GemvArgs args, cudaStream_t stream);
 int gemv_group_dots(const uint32_t* qweight, const int8_t* q8, const int32_t* sum8, int32_t* out, int N, int K,
                     cudaStream_t stream);
 int gemv_set_attributes();
+int gemv_sample_slots(int out_features);   // candidates the sampling epilogue writes for a matrix of that height
+
+// ---- token selection (sampling.cu) ----
+int sample_stage1_blocks();
+int sample_stage1(const __half* logits, float* part_val, int32_t* part_idx, const void* control, int vocab,
+                  int index_offset, cudaStream_t stream);
+int sample_stage2(const float* part_val, const int32_t* part_idx, int count, void* control, int32_t* token_out,
+                  cudaStream_t stream);
 
 // ---- M-token contraction (gemm_prefill.cu) ----
 struct GemmArgs {

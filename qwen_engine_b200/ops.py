@@ -23,7 +23,7 @@ __all__ = [
     "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
     "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots", "DecodeSweep",
     "launch_gemv_rmsnorm_w4a16", "launch_gemv_qkv_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1",
-    "gemv_w4a8_peers", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_QUANT_IN_GATE_UP", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
+    "gemv_w4a8_peers", "make_sample_control", "read_sample_control", "launch_sample_and_advance", "sample_slots", "launch_gemv_w4a8_sample_candidates", "launch_sample_finish", "launch_gemv_w4a8_sample_and_advance", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_QUANT_IN_GATE_UP", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
 ]
 
 # Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
@@ -121,6 +121,64 @@ def gemv_w4a8_peers(qweight, scales, input_q8, input_scale, input_sum8, output_y
     check("w4a16_gemv_w4a8_peers", load().w4a16_gemv_w4a8_peers(
         _ptr(qweight), _ptr(scales), _ptr(input_q8), _ptr(input_scale), _ptr(input_sum8), _ptr(output_y), arr,
         len(peer_ptrs), out_features, in_features, _stream(stream)))
+
+
+# ---- token selection after lm_head ------------------------------------------------------------
+
+VOCAB_SIZE = 151936
+
+
+def make_sample_control(temperature=0.0, rng_seed=0, seq_pos=0, token_id=0) -> "torch.Tensor":
+    """A device copy of the control block {int32 token_id, int32 seq_pos, float temperature, uint32 reserved,
+    uint64 rng_seed} (the reference's DeviceControlBlock, include/tensor.cuh:28-34) as an int32 tensor [6]."""
+    import struct
+    raw = struct.pack("<iifIQ", token_id, seq_pos, temperature, 0, rng_seed & 0xFFFFFFFFFFFFFFFF)
+    return torch.frombuffer(bytearray(raw), dtype=torch.int32).cuda()
+
+
+def read_sample_control(control) -> dict:
+    import struct
+    token_id, seq_pos, temperature, _, rng_seed = struct.unpack("<iifIQ", control.cpu().numpy().tobytes())
+    return {"token_id": token_id, "seq_pos": seq_pos, "temperature": temperature, "rng_seed": rng_seed}
+
+
+def launch_sample_and_advance(logits, sample_scratch_val, sample_scratch_idx, d_control, d_token_out, stream=None,
+                              vocab_size=VOCAB_SIZE):
+    """Mirror of launch_sample_and_advance (reference include/kernels.cuh:210-219)."""
+    check("w4a16_sample_and_advance", load().w4a16_sample_and_advance(
+        _ptr(logits), _ptr(sample_scratch_val), _ptr(sample_scratch_idx), _ptr(d_control), _ptr(d_token_out),
+        _stream(stream), vocab_size))
+
+
+def sample_slots(out_features: int) -> int:
+    n = load().w4a16_sample_slots(out_features)
+    if n < 0:
+        check("w4a16_sample_slots", n)
+    return n
+
+
+def launch_gemv_w4a8_sample_candidates(qweight, scales, input_q8, input_scale, input_sum8, output_logits, candidate_val,
+                                       candidate_idx, d_control, index_offset, out_features, in_features, stream=None):
+    """lm_head GEMV that leaves one (score, index) candidate per CTA; output_logits may be None."""
+    check("w4a16_gemv_w4a8_sample_candidates", load().w4a16_gemv_w4a8_sample_candidates(
+        _ptr(qweight), _ptr(scales), _ptr(input_q8), _ptr(input_scale), _ptr(input_sum8), _ptr(output_logits),
+        _ptr(candidate_val), _ptr(candidate_idx), _ptr(d_control), index_offset, out_features, in_features,
+        _stream(stream)))
+
+
+def launch_sample_finish(candidate_val, candidate_idx, count, d_control, d_token_out, stream=None):
+    check("w4a16_sample_finish", load().w4a16_sample_finish(
+        _ptr(candidate_val), _ptr(candidate_idx), count, _ptr(d_control), _ptr(d_token_out), _stream(stream)))
+
+
+def launch_gemv_w4a8_sample_and_advance(qweight, scales, input_q8, input_scale, input_sum8, output_logits,
+                                        sample_scratch_val, sample_scratch_idx, d_control, d_token_out, out_features,
+                                        in_features, stream=None):
+    """launch_gemv_w4a8 (lm_head) + launch_sample_and_advance in one pass over the weights."""
+    check("w4a16_gemv_w4a8_sample_and_advance", load().w4a16_gemv_w4a8_sample_and_advance(
+        _ptr(qweight), _ptr(scales), _ptr(input_q8), _ptr(input_scale), _ptr(input_sum8), _ptr(output_logits),
+        _ptr(sample_scratch_val), _ptr(sample_scratch_idx), _ptr(d_control), _ptr(d_token_out), out_features,
+        in_features, _stream(stream)))
 
 
 def launch_gemv_qkv_w4a8(view: QKVProjectionView, input_q8, input_scale, input_sum8, stream=None,

@@ -1,0 +1,150 @@
+"""Token selection after lm_head: the stand-alone sampler and the lm_head GEMV that samples in its epilogue,
+against the CPU oracle (oracle.sample) and against each other."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import qwen_engine_b200 as pkg
+    pkg.init()
+    return pkg
+
+
+def _scratch(n):
+    return (torch.full((n,), float("nan"), dtype=torch.float32, device="cuda"),
+            torch.full((n,), -7, dtype=torch.int32, device="cuda"))
+
+
+def _check_token(tok, logits, temperature, seed, seq_pos):
+    """Greedy: the oracle's token exactly.  With noise the device's logf may differ from libm's in the last
+    bit, so the chosen entry must score within a few ulp of the oracle's best."""
+    ref_tok, ref_best, scores = oracle.sample(logits, temperature, seed, seq_pos)
+    if temperature <= 1e-5:
+        assert tok == ref_tok
+    else:
+        assert tok == ref_tok or abs(scores[tok] - ref_best) <= 4e-6 * max(1.0, abs(ref_best))
+
+
+@pytest.mark.parametrize("vocab", [151936, 1000, 77, 1])
+@pytest.mark.parametrize("temperature,seed,seq_pos", [(0.0, 0, 0), (0.7, 0x1234567890ABCDEF, 17), (1.3, 42, 100000)])
+def test_sample_and_advance_matches_oracle(ops, vocab, temperature, seed, seq_pos):
+    rng = np.random.default_rng(vocab)
+    logits = (rng.standard_normal(vocab) * 4).astype(np.float16)
+    if vocab > 50:   # ties at the top: the lowest index must win
+        top = np.float16(logits.max() + 1)
+        logits[[vocab // 3, vocab // 2, vocab - 1]] = top
+    d_logits = util.to_dev(logits)
+    val, idx = _scratch(256)
+    control = ops.make_sample_control(temperature, seed, seq_pos)
+    token = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    ops.launch_sample_and_advance(d_logits, val, idx, control, token, None, vocab)
+    torch.cuda.synchronize()
+    tok = int(token.item())
+    _check_token(tok, logits, temperature, seed, seq_pos)
+    if temperature == 0.0 and vocab > 50:
+        assert tok == vocab // 3
+    after = ops.read_sample_control(control)
+    assert after["token_id"] == tok and after["seq_pos"] == seq_pos + 1
+    assert after["rng_seed"] == (seed + 0x9E3779B97F4A7C15) % 2**64
+    # without a control block: greedy, token only through the pointer
+    ops.launch_sample_and_advance(d_logits, val, idx, None, token, None, vocab)
+    torch.cuda.synchronize()
+    assert int(token.item()) == oracle.sample(logits)[0]
+
+
+@pytest.mark.parametrize("N,K", [(151936, 1536), (5000, 1024), (97, 512), (32, 256)])
+@pytest.mark.parametrize("temperature,seed,seq_pos", [(0.0, 0, 0), (0.9, 987654321, 3)])
+def test_lm_head_with_sampling_epilogue(ops, N, K, temperature, seed, seq_pos):
+    from qwen_engine_b200 import synth
+    qw, sc = synth.packed_weights(N + K, "lm", N, K), synth.scales(N + K, "lm", N, K)
+    if N >= 97:   # two identical rows: identical logits, the lower index must win if they are the best
+        qw[N - 1] = qw[5]
+        sc[N - 1] = sc[5]
+    x = synth.activations(N, "x", K)
+    q8, xs, s8 = oracle.quantize_q8_1(x)
+    d = [util.to_dev(t) for t in (qw, sc, q8, xs, s8)]
+    # the plain launch, for the logits themselves
+    logits = torch.empty(N, dtype=torch.float16, device="cuda")
+    ops.launch_gemv_w4a8(d[0], d[1], d[2], d[3], d[4], None, logits, N, K)
+    # the fused launch, with and without storing the logits
+    slots = ops.sample_slots(N)
+    assert 1 <= slots <= 2 * torch.cuda.get_device_properties(0).multi_processor_count
+    tokens, controls, fused_logits = [], [], None
+    for keep_logits in (True, False):
+        fval, fidx = _scratch(slots)
+        c2 = ops.make_sample_control(temperature, seed, seq_pos)
+        t2 = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+        logits2 = torch.full((N,), float("nan"), dtype=torch.float16, device="cuda") if keep_logits else None
+        ops.launch_gemv_w4a8_sample_and_advance(d[0], d[1], d[2], d[3], d[4], logits2, fval, fidx, c2, t2, N, K)
+        torch.cuda.synchronize()
+        tokens.append(int(t2.item()))
+        controls.append(ops.read_sample_control(c2))
+        if keep_logits:
+            fused_logits = logits2
+    assert tokens[0] == tokens[1] and controls[0] == controls[1]
+    # the logits it stores are the plain launch's: bit for bit where both use one K slice per row (lm_head),
+    # within the path's tolerance where the plain launch splits K inside the CTA
+    if K == 1536 and N >= 100000:
+        assert torch.equal(fused_logits, logits)
+    else:
+        util.assert_fp16_close(util.to_np(fused_logits), util.to_np(logits).astype(np.float64), what="fused logits")
+    # the stand-alone sampler on those logits: same arithmetic on the device, so the same token and control block
+    val, idx = _scratch(256)
+    c1 = ops.make_sample_control(temperature, seed, seq_pos)
+    t1 = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    ops.launch_sample_and_advance(fused_logits, val, idx, c1, t1, None, N)
+    torch.cuda.synchronize()
+    assert int(t1.item()) == tokens[0]
+    assert ops.read_sample_control(c1) == controls[0]
+    _check_token(tokens[0], util.to_np(fused_logits), temperature, seed, seq_pos)
+
+
+def test_row_split_lm_head_candidates_give_the_same_token(ops):
+    """Two slabs of the vocabulary, each scored with its own index offset; the candidates of both go through
+    one finishing reduction -- the exchange a row-split lm_head needs is 8 bytes per candidate."""
+    from qwen_engine_b200 import synth
+    N, K = 20000, 1536
+    qw, sc = synth.packed_weights(3, "lm2", N, K), synth.scales(3, "lm2", N, K)
+    x = synth.activations(4, "x2", K)
+    q8, xs, s8 = oracle.quantize_q8_1(x)
+    dq8, dxs, ds8 = util.to_dev(q8), util.to_dev(xs), util.to_dev(s8)
+    for temperature, seed in ((0.0, 0), (1.1, 5555)):
+        ref_val, ref_idx = _scratch(ops.sample_slots(N))
+        c0 = ops.make_sample_control(temperature, seed, 9)
+        t0 = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+        ops.launch_gemv_w4a8_sample_and_advance(util.to_dev(qw), util.to_dev(sc), dq8, dxs, ds8, None, ref_val, ref_idx,
+                                                c0, t0, N, K)
+        bounds = [0, 12000, N]
+        vals, idxs = [], []
+        c = ops.make_sample_control(temperature, seed, 9)
+        for lo, hi in zip(bounds[:-1], bounds[1:]):
+            n = hi - lo
+            v, i = _scratch(ops.sample_slots(n))
+            ops.launch_gemv_w4a8_sample_candidates(util.to_dev(qw[lo:hi]), util.to_dev(sc[lo:hi]), dq8, dxs, ds8, None,
+                                                   v, i, c, lo, n, K)
+            vals.append(v)
+            idxs.append(i)
+        allv, alli = torch.cat(vals), torch.cat(idxs)
+        t = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+        ops.launch_sample_finish(allv, alli, allv.numel(), c, t)
+        torch.cuda.synchronize()
+        assert int(t.item()) == int(t0.item())
+        assert ops.read_sample_control(c) == ops.read_sample_control(c0)
+
+
+def test_sampling_epilogue_refuses_what_it_cannot_run(ops):
+    from qwen_engine_b200 import synth
+    N, K = 64, 4096   # deeper than the streaming form's eight steps
+    qw, sc = util.to_dev(synth.packed_weights(1, "r", N, K)), util.to_dev(synth.scales(1, "r", N, K))
+    q8, xs, s8 = oracle.quantize_q8_1(synth.activations(2, "r", K))
+    v, i = _scratch(64)
+    with pytest.raises(ops.W4A16Error):
+        ops.launch_gemv_w4a8_sample_candidates(qw, sc, util.to_dev(q8), util.to_dev(xs), util.to_dev(s8), None, v, i,
+                                               None, 0, N, K)

@@ -98,3 +98,21 @@ def test_rmsnorm_against_numpy():
     ih = np.float16(inv_ref)
     expect = ((x * ih).astype(np.float16) * g).astype(np.float16)
     assert np.array_equal(y.view(np.uint16), expect.view(np.uint16))
+
+
+def test_philox_known_answer_and_sampler_rules():
+    """Philox-4x32-10: the published known-answer vector for an all-zero counter and key (Random123), then the
+    selection rules of the reference's sampler (src/kernels/sampling.cu:86-100): greedy at temperature <= 1e-5,
+    lowest index among equal scores, index offset only moves the counter and the reported index."""
+    assert oracle.philox_first(0, 0, 0) == 0x6627E8D5
+    logits = np.array([0.5, 2.0, 2.0, -1.0], dtype=np.float16)
+    tok, best, scores = oracle.sample(logits)
+    assert (tok, best) == (1, 2.0) and np.array_equal(scores, logits.astype(np.float32))
+    assert oracle.sample(logits, 1e-5)[0] == 1
+    t1, _, s1 = oracle.sample(logits, 0.8, seed=99, seq_pos=4)
+    t2, _, s2 = oracle.sample(logits[2:], 0.8, seed=99, seq_pos=4, index_offset=2)
+    assert np.array_equal(s1[2:], s2)                      # same counters -> same noise
+    assert t2 == 2 + int(np.argmax(s2))
+    assert not np.array_equal(s1, oracle.sample(logits, 0.8, seed=99, seq_pos=5)[2])
+    u = np.exp(-np.exp(-(s1 - logits.astype(np.float32) / np.float32(0.8))))   # invert the Gumbel transform
+    assert np.all((u > 0) & (u < 1))
