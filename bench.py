@@ -367,6 +367,75 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
             out["peer_store_epilogue"] = {"unavailable": str(e)[:200]}
     out["us_per_step"] = best
     out["value"] = nbytes / (best * 1e-6) / 1e9
+
+    # ---- token selection after lm_head: logits + stand-alone sampler vs. candidates from the GEMV's epilogue ----
+    try:
+        slots = ops.sample_slots(rows)
+        temperature = float(os.environ.get("W4A16_BENCH_TEMPERATURE", "0.8"))
+        ctl_a = ops.make_sample_control(temperature, 1234, 0)
+        ctl_b = ops.make_sample_control(temperature, 1234, 0)
+        val = torch.empty(256, dtype=torch.float32, device="cuda")
+        idx = torch.empty(256, dtype=torch.int32, device="cuda")
+        tok_a = torch.zeros(1, dtype=torch.int32, device="cuda")
+        gathers = [nsplit.NSplitGemv(w, s, N, K, launch) for w, s in slabs]
+        cand = lambda w, s, a, b, c, v, i, ctl, off, r, k: ops.launch_gemv_w4a8_sample_candidates(
+            w, s, a, b, c, None, v, i, ctl, off, r, k)
+        samplers = [nsplit.NSplitSampler(w, s, N, K, slots, cand, ops.launch_sample_finish) for w, s in slabs]
+
+        def unfused_round():
+            for g in gathers:
+                logits = g.forward(q8, xs, s8)
+                ops.launch_sample_and_advance(logits, val, idx, ctl_a, tok_a, None, N)
+
+        def fused_round():
+            for sm in samplers:
+                sm.forward(q8, xs, s8, ctl_b)
+
+        def time_rounds(fn):
+            with torch.cuda.stream(stream):
+                fn()
+                stream.synchronize()
+                try:
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=stream):
+                        fn()
+                    run, how = graph.replay, "cuda graph"
+                except Exception:
+                    torch.cuda.synchronize()
+                    run, how = fn, "eager"
+                rounds = max(1, (steps + copies - 1) // copies)
+                for _ in range(2):
+                    run()
+                stream.synchronize()
+                if world > 1:
+                    dist.barrier()
+                torch.cuda.synchronize()
+                ms = timed_events(torch, stream, run, rounds)
+                torch.cuda.synchronize()
+            t = torch.tensor([ms], device="cuda")
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item()) * 1e3 / (rounds * copies), how
+
+        # same control state on both sides: one step each from a fresh control block, tokens compared
+        ca, cb = ops.make_sample_control(temperature, 99, 5), ops.make_sample_control(temperature, 99, 5)
+        with torch.cuda.stream(stream):
+            lg = gathers[0].forward(q8, xs, s8)
+            ops.launch_sample_and_advance(lg, val, idx, ca, tok_a, None, N)
+            tok_f = samplers[0].forward(q8, xs, s8, cb).clone()
+        stream.synchronize()
+        same = int(tok_a.item()) == int(tok_f.item())
+        us_a, how_a = time_rounds(unfused_round)
+        us_b, how_b = time_rounds(fused_round)
+        out["token_selection"] = {
+            "temperature": temperature, "candidates_per_gpu": slots,
+            "logits_gather_then_sampler": {"us_per_step": us_a, "timed_as": how_a,
+                                           "exchange_bytes_per_gpu": rows * 2 if world > 1 else 0},
+            "sampling_epilogue": {"us_per_step": us_b, "timed_as": how_b,
+                                  "exchange_bytes_per_gpu": slots * 8 if world > 1 else 0},
+            "same_token": bool(same)}
+    except Exception as e:
+        out["token_selection"] = {"unavailable": str(e)[:200]}
     return out
 
 

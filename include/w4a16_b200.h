@@ -121,6 +121,18 @@ W4A16_API int w4a16_gemv_w4a8_peers(const uint32_t* qweight, const void* scales,
                                     void* const* peer_outputs, int num_peers, int out_features,
                                     int in_features, w4a16_stream_t stream);
 
+/* ---- embedding lookup on the W4 table ---------------------------------------------------- */
+/*
+ * reference include/kernels.cuh launch_embed_lookup_w4a16 (src/kernels/rmsnorm_rope.cu:15-69): row `token` of
+ * the packed table (the tied lm_head matrix) dequantised to fp16, (q - 8) * scale with one fp16 rounding
+ * (include/quant_primitives.cuh:92-115).  Token i is d_token_ids[i] if d_token_ids is given, else the
+ * control block's token_id; ids outside [0, vocab_size) read row 0, as in the reference.  out_hidden:
+ * fp16 [num_tokens][hidden_size], 16-byte aligned; hidden_size a multiple of 128.
+ */
+W4A16_API int w4a16_embed_lookup_w4a16(const uint32_t* embed_qweight, const void* embed_scales,
+                                       const int32_t* d_token_ids, void* out_hidden, const void* d_control,
+                                       int num_tokens, w4a16_stream_t stream, int hidden_size, int vocab_size);
+
 /* ---- token selection after lm_head ------------------------------------------------------ */
 /* Same layout as the reference's DeviceControlBlock (include/tensor.cuh:28-34); lives in device memory. */
 typedef struct w4a16_sample_control {

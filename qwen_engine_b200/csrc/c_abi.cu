@@ -152,6 +152,20 @@ static int gemv_plain(const uint32_t* qweight, const void* scales, const void* x
     return gemv_launch(kPlain, a, S(stream));
 }
 
+int w4a16_embed_lookup_w4a16(const uint32_t* embed_qweight, const void* embed_scales, const int32_t* d_token_ids,
+                             void* out_hidden, const void* d_control, int num_tokens, w4a16_stream_t stream,
+                             int hidden_size, int vocab_size) {
+    if (!embed_qweight || !embed_scales || !out_hidden || num_tokens <= 0 || vocab_size <= 0) return W4A16_ERR_INVALID_ARG;
+    if (!d_token_ids && !d_control) return W4A16_ERR_INVALID_ARG;
+    if (hidden_size <= 0 || hidden_size % 128) return W4A16_ERR_SHAPE;
+    if (misaligned(embed_qweight, 4) || misaligned(embed_scales, 2) || misaligned(out_hidden, 16) ||
+        misaligned(d_token_ids, 4) || misaligned(d_control, 8))
+        return W4A16_ERR_ALIGNMENT;
+    if (int st = ensure_device_ready(nullptr)) return st;
+    return embed_lookup(embed_qweight, H(embed_scales), d_token_ids, H(out_hidden), d_control, num_tokens, hidden_size,
+                        vocab_size, S(stream));
+}
+
 // ---- token selection ----
 int w4a16_sample_and_advance(const void* logits, float* sample_scratch_val, int32_t* sample_scratch_idx,
                              void* d_control, int32_t* d_token_out, w4a16_stream_t stream, int vocab_size) {

@@ -322,8 +322,9 @@ namespace {
 // the weights of the NEXT block already in flight while the current one is reduced, and the lane's share
 // of the quantised activation lives in registers for the whole launch (a lane always meets the same
 // 16-byte chunks l, l+8, ... of every row).  PLAIN mode, 16-byte aligned weights, K <= 256 * STEPS.
-template <int XIN, int STEPS, bool SWIGLU>
+template <int XIN, int STEPS, bool SWIGLU, bool SAMPLE = false>
 __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const GemvArgs a, const int num_blocks) {
+    static_assert(!(SWIGLU && SAMPLE), "token selection follows a plain projection");
     extern __shared__ __align__(16) uint8_t smem[];
     const int K = a.K;
     int8_t* s_q8 = reinterpret_cast<int8_t*>(smem);
@@ -361,15 +362,15 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const Ge
     // Token selection in the epilogue (PLAIN only): the fp16-rounded outputs of eight row blocks are parked in
     // shared memory and then scored by all 256 threads at once (the Gumbel draw costs ~150 instructions per
     // row; left to the one lane per row that holds the sum it would double the kernel's instruction count).
-    [[maybe_unused]] const bool sampling = !SWIGLU && a.sample_val != nullptr;
-    __shared__ float s_scores[2][kMaxThreads];
+    constexpr bool sampling = SAMPLE;
+    __shared__ float s_scores[SAMPLE ? 2 : 1][SAMPLE ? kMaxThreads : 1];
     [[maybe_unused]] float temperature = 0.0f, best = kSampleFloor;
     [[maybe_unused]] uint64_t rng_seed = 0;
     [[maybe_unused]] uint32_t seq_pos = 0;
     [[maybe_unused]] int32_t best_idx = 0;
     [[maybe_unused]] int it = 0, buf = 0;
-    if constexpr (!SWIGLU) {
-        if (sampling && a.sample_control != nullptr) {
+    if constexpr (SAMPLE) {
+        if (a.sample_control != nullptr) {
             const SampleControl* c = static_cast<const SampleControl*>(a.sample_control);
             temperature = c->temperature;
             rng_seed = c->rng_seed;
@@ -417,9 +418,9 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const Ge
                 const __half yh = __float2half_rn(y);
                 if (a.out[0] != nullptr) a.out[0][row] = yh;
                 for (int p = 0; p < a.num_peers; ++p) a.peer_out[p][row] = yh;
-                if (sampling) s_scores[buf][(it & 7) * kMaxSubwarps + sub] = __half2float(yh);
+                if constexpr (sampling) s_scores[buf][(it & 7) * kMaxSubwarps + sub] = __half2float(yh);
             }
-            if (sampling) {
+            if constexpr (sampling) {
                 if ((it & 7) == 7 || nxt >= num_blocks) {      // uniform over the CTA
                     __syncthreads();
                     const int it_j = (it & ~7) + (tid >> 5);   // thread = (iteration of the group, row of the block)
@@ -438,15 +439,13 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const Ge
 #pragma unroll
         for (int i = 0; i < STEPS; ++i) { w0[i] = w1[i]; sb0[i] = sb1[i]; }
     }
-    if constexpr (!SWIGLU) {
-        if (sampling) {
-            __shared__ float s_v[32];
-            __shared__ int32_t s_i[32];
-            sample_block_reduce(best, best_idx, s_v, s_i);
-            if (tid == 0) {
-                a.sample_val[blockIdx.x] = best;
-                a.sample_idx[blockIdx.x] = best_idx;
-            }
+    if constexpr (SAMPLE) {
+        __shared__ float s_v[32];
+        __shared__ int32_t s_i[32];
+        sample_block_reduce(best, best_idx, s_v, s_i);
+        if (tid == 0) {
+            a.sample_val[blockIdx.x] = best;
+            a.sample_idx[blockIdx.x] = best_idx;
         }
     }
 }
@@ -664,15 +663,15 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
         const dim3 sgrid(std::min(num_blocks, 2 * dev->sm_count)), sblock(kMaxThreads);
         const size_t ssmem = staged_x_bytes(a.K);
         const bool pdl = pdl_enabled();
-#define W4_STREAM2(XINV, SW)                                                                                               \
-    (steps <= 4 ? launch_kernel(gemv_w4_stream_kernel<XINV, 4, SW>, sgrid, sblock, ssmem, stream, pdl, a, num_blocks)     \
-     : steps <= 6 ? launch_kernel(gemv_w4_stream_kernel<XINV, 6, SW>, sgrid, sblock, ssmem, stream, pdl, a, num_blocks)  \
-                  : launch_kernel(gemv_w4_stream_kernel<XINV, 8, SW>, sgrid, sblock, ssmem, stream, pdl, a, num_blocks))
-#define W4_STREAM(XINV) (mode == kSwiglu ? W4_STREAM2(XINV, true) : W4_STREAM2(XINV, false))
+#define W4_STREAM3(XINV, SW, SA)                                                                                                \
+    (steps <= 4 ? launch_kernel(gemv_w4_stream_kernel<XINV, 4, SW, SA>, sgrid, sblock, ssmem, stream, pdl, a, num_blocks)     \
+     : steps <= 6 ? launch_kernel(gemv_w4_stream_kernel<XINV, 6, SW, SA>, sgrid, sblock, ssmem, stream, pdl, a, num_blocks)  \
+                  : launch_kernel(gemv_w4_stream_kernel<XINV, 8, SW, SA>, sgrid, sblock, ssmem, stream, pdl, a, num_blocks))
+#define W4_STREAM(XINV) (mode == kSwiglu ? W4_STREAM3(XINV, true, false) : sampling ? W4_STREAM3(XINV, false, true) : W4_STREAM3(XINV, false, false))
         if (a.x_fp16 != nullptr) e = a.gamma != nullptr ? W4_STREAM(kXFp16Norm) : W4_STREAM(kXFp16);
         else e = W4_STREAM(kXQ8);
 #undef W4_STREAM
-#undef W4_STREAM2
+#undef W4_STREAM3
         return static_cast<int>(e);
     }
     switch (mode) {

@@ -106,6 +106,10 @@ int gemv_group_dots(const uint32_t* qweight, const int8_t* q8, const int32_t* su
 int gemv_set_attributes();
 int gemv_sample_slots(int out_features);   // candidates the sampling epilogue writes for a matrix of that height
 
+// ---- embedding lookup (embed_lookup.cu) ----
+int embed_lookup(const uint32_t* qweight, const __half* scales, const int32_t* token_ids, __half* out,
+                 const void* control, int num_tokens, int hidden, int vocab, cudaStream_t stream);
+
 // ---- token selection (sampling.cu) ----
 int sample_stage1_blocks();
 int sample_stage1(const __half* logits, float* part_val, int32_t* part_idx, const void* control, int vocab,

@@ -95,3 +95,51 @@ class NSplitGemv:
             rows = min(max(self.n_rows - r * self.slab.stride, 0), self.slab.stride)
             parts.append(self.gathered[r * self.slab.stride: r * self.slab.stride + rows])
         return torch.cat(parts)
+
+
+class NSplitSampler:
+    """Token selection for a row-split lm_head without gathering the logits: every rank scores its own slab
+    in the GEMV's epilogue (vocabulary indices offset by the slab's first row), the ranks all-gather their
+    (score, index) candidates -- 8 bytes each, `slots` per rank -- and every rank reduces all of them to the
+    same token.
+
+    candidates(qweight_slab, scales_slab, q8, xscale, sum8, cand_val, cand_idx, control, index_offset, rows, K)
+    runs the local GEMV with the sampling epilogue; finish(cand_val, cand_idx, count, control, token_out)
+    reduces.  On GPUs they are launch_gemv_w4a8_sample_candidates / launch_sample_finish with logits=None.
+    A rank without rows contributes candidates that can never win (-inf score).
+    """
+
+    def __init__(self, qweight_slab: torch.Tensor, scales_slab: torch.Tensor, n_rows: int, in_features: int,
+                 slots: int, candidates, finish, group=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.n_rows, self.K, self.slots = n_rows, in_features, slots
+        self.slab = slab_bounds(n_rows, self.world, self.rank)
+        if qweight_slab.shape[0] != self.slab.rows or scales_slab.shape[0] != self.slab.rows:
+            raise ValueError(f"rank {self.rank} expects a slab of {self.slab.rows} rows")
+        self.qweight, self.scales = qweight_slab, scales_slab
+        self.candidates, self.finish = candidates, finish
+        dev = qweight_slab.device
+        # [world][2][slots] 32-bit words: scores (as bits) then indices, so that one all-gather moves both
+        self.gathered = torch.zeros((self.world, 2, slots), dtype=torch.int32, device=dev)
+        self.token = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def forward(self, q8, xscale, sum8, control) -> torch.Tensor:
+        """Returns the int32 token tensor [1] (the same value on every rank); advances `control`."""
+        mine = self.gathered[self.rank]
+        val, idx = mine[0].view(torch.float32), mine[1]
+        if self.slab.rows > 0:
+            self.candidates(self.qweight, self.scales, q8, xscale, sum8, val, idx, control, self.slab.first,
+                            self.slab.rows, self.K)
+        else:
+            val.fill_(float("-inf"))
+            idx.zero_()
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.gathered.view(-1), mine.reshape(-1), group=self.group)
+            allv = self.gathered[:, 0, :].contiguous().view(torch.float32).view(-1)
+            alli = self.gathered[:, 1, :].contiguous().view(-1)
+        else:
+            allv, alli = val, idx
+        self.finish(allv, alli, allv.numel(), control, self.token)
+        return self.token

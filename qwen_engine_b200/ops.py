@@ -23,7 +23,7 @@ __all__ = [
     "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
     "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots", "DecodeSweep",
     "launch_gemv_rmsnorm_w4a16", "launch_gemv_qkv_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1",
-    "gemv_w4a8_peers", "make_sample_control", "read_sample_control", "launch_sample_and_advance", "sample_slots", "launch_gemv_w4a8_sample_candidates", "launch_sample_finish", "launch_gemv_w4a8_sample_and_advance", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_QUANT_IN_GATE_UP", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
+    "gemv_w4a8_peers", "make_sample_control", "launch_embed_lookup_w4a16", "read_sample_control", "launch_sample_and_advance", "sample_slots", "launch_gemv_w4a8_sample_candidates", "launch_sample_finish", "launch_gemv_w4a8_sample_and_advance", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_QUANT_IN_GATE_UP", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
 ]
 
 # Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
@@ -140,6 +140,14 @@ def read_sample_control(control) -> dict:
     import struct
     token_id, seq_pos, temperature, _, rng_seed = struct.unpack("<iifIQ", control.cpu().numpy().tobytes())
     return {"token_id": token_id, "seq_pos": seq_pos, "temperature": temperature, "rng_seed": rng_seed}
+
+
+def launch_embed_lookup_w4a16(embed_qweight, embed_scales, d_token_ids, out_hidden, d_control, num_tokens, stream=None,
+                              hidden_size=HIDDEN_SIZE, vocab_size=VOCAB_SIZE):
+    """Mirror of launch_embed_lookup_w4a16 (reference include/kernels.cuh); vocab_size bounds the token ids."""
+    check("w4a16_embed_lookup_w4a16", load().w4a16_embed_lookup_w4a16(
+        _ptr(embed_qweight), _ptr(embed_scales), _ptr(d_token_ids), _ptr(out_hidden), _ptr(d_control), num_tokens,
+        _stream(stream), hidden_size, vocab_size))
 
 
 def launch_sample_and_advance(logits, sample_scratch_val, sample_scratch_idx, d_control, d_token_out, stream=None,

@@ -148,3 +148,26 @@ def test_sampling_epilogue_refuses_what_it_cannot_run(ops):
     with pytest.raises(ops.W4A16Error):
         ops.launch_gemv_w4a8_sample_candidates(qw, sc, util.to_dev(q8), util.to_dev(xs), util.to_dev(s8), None, v, i,
                                                None, 0, N, K)
+
+
+@pytest.mark.parametrize("H,vocab,M", [(1536, 3000, 1), (1536, 3000, 9), (256, 40, 3)])
+def test_embed_lookup_matches_the_dequantised_rows(ops, H, vocab, M):
+    """Row gather from the W4 table: (q - 8) * scale with one fp16 rounding -- exact, so bit for bit."""
+    from qwen_engine_b200 import synth
+    qw, sc = synth.packed_weights(H + vocab, "emb", vocab, H), synth.scales(H + vocab, "emb", vocab, H)
+    nib = oracle.unpack_nibbles(qw).astype(np.float32) - 8.0                          # [vocab][H], exact in fp16
+    table = (nib.astype(np.float16) * np.repeat(sc, 128, axis=1)).astype(np.float16)   # fp16 * fp16, rounded once
+    ids = np.array([(7 * i + 3) % vocab for i in range(M)], dtype=np.int32)
+    ids[-1] = vocab + 5 if M > 1 else ids[-1]            # out of range -> row 0, as the reference
+    out = torch.full((M * H + 8,), float("nan"), dtype=torch.float16, device="cuda")
+    ops.launch_embed_lookup_w4a16(util.to_dev(qw), util.to_dev(sc), util.to_dev(ids), out, None, M, None, H, vocab)
+    torch.cuda.synchronize()
+    got = util.to_np(out)
+    assert np.isnan(got[M * H:]).all()
+    rows = np.where((ids >= 0) & (ids < vocab), ids, 0)
+    assert np.array_equal(got[:M * H].reshape(M, H).view(np.uint16), table[rows].view(np.uint16))
+    # token taken from the control block when no id array is given
+    control = ops.make_sample_control(0.0, 0, 0, token_id=int(ids[0]))
+    ops.launch_embed_lookup_w4a16(util.to_dev(qw), util.to_dev(sc), None, out, control, 1, None, H, vocab)
+    torch.cuda.synchronize()
+    assert np.array_equal(util.to_np(out)[:H].view(np.uint16), table[ids[0]].view(np.uint16))

@@ -72,3 +72,68 @@ def test_two_rank_gloo_split_equals_unsplit(n_rows):
             p.join(timeout=120)
             assert p.exitcode == 0
         assert dict(ret) == {0: True, 1: True}
+
+
+# ---- token selection over a row-split lm_head: candidates per rank, 8 bytes each, instead of the logits ----
+
+def _oracle_candidates(qw, sc, q8, xs, s8, val, idx, control, offset, rows, K):
+    """Plays the GEMV with the sampling epilogue: `slots` contiguous row chunks, one candidate each."""
+    _, y16 = oracle.gemv_q8(qw.numpy().view(np.uint32), sc.numpy(), q8.numpy(), xs.numpy(), threads=1)
+    slots = val.numel()
+    chunk = -(-rows // slots)
+    for j in range(slots):
+        lo, hi = j * chunk, min((j + 1) * chunk, rows)
+        if lo >= hi:
+            val[j], idx[j] = float("-inf"), 0
+            continue
+        tok, best, _ = oracle.sample(y16[lo:hi], control["temperature"], control["rng_seed"], control["seq_pos"],
+                                     index_offset=offset + lo)
+        val[j], idx[j] = best, tok
+
+
+def _oracle_finish(allv, alli, count, control, token):
+    v, i = allv.numpy()[:count], alli.numpy()[:count]
+    order = np.lexsort((i, -v.astype(np.float64)))     # larger score first, then smaller index
+    token[0] = int(i[order[0]])
+    control["seq_pos"] += 1
+
+
+def _sampler_worker(rank, world, port, n_rows, K, temperature, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        qw = synth.packed_weights(6, "nss", n_rows, K)
+        sc = synth.scales(6, "nss", n_rows, K)
+        qw[n_rows - 2] = qw[1]          # equal logits in different slabs: the lower index has to win
+        sc[n_rows - 2] = sc[1]
+        q8, xs, s8 = oracle.quantize_q8_1(synth.activations(6, "nss.x", K))
+        slab = nsplit.slab_bounds(n_rows, world, rank)
+        w_slab = torch.from_numpy(qw[slab.first:slab.first + slab.rows].view(np.int32).copy())
+        s_slab = torch.from_numpy(sc[slab.first:slab.first + slab.rows].copy())
+        control = {"temperature": temperature, "rng_seed": 77, "seq_pos": 3}
+        op = nsplit.NSplitSampler(w_slab, s_slab, n_rows, K, 5, _oracle_candidates, _oracle_finish)
+        tok = int(op.forward(torch.from_numpy(q8), torch.from_numpy(xs), torch.from_numpy(s8), control)[0])
+        _, full = oracle.gemv_q8(qw, sc, q8, xs, threads=1)
+        expect, _, _ = oracle.sample(full, temperature, 77, 3)
+        ret[rank] = (tok, expect, control["seq_pos"])
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n_rows,temperature", [(512, 0.0), (515, 0.9), (3, 0.0)])
+def test_two_rank_gloo_split_sampler_picks_the_unsplit_token(n_rows, temperature):
+    world, K = 2, 256
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = _free_port()
+        procs = [ctx.Process(target=_sampler_worker, args=(r, world, port, n_rows, K, temperature, ret))
+                 for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+        got = dict(ret)
+        assert got[0] == got[1]                      # every rank ends with the same token
+        assert got[0][0] == got[0][1] and got[0][2] == 4
