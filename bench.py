@@ -233,7 +233,7 @@ def kernel_roofline(torch, ops, layers_dev, stream, peaks, reps=20):
     peak = peak or 6650.0
     # dram__bytes_read.sum + dram__bytes_write.sum of this kernel per launch, from the ncu capture summarised
     # in profiles/gemv_gate_up_swiglu_17920x1536.md
-    traffic = 14225408
+    traffic = 14228480
     res = {"bound": "hbm", "kernel": "gemv_w4_kernel<SwiGLU> (gate_up 17920x1536)", "achieved": achieved, "peak": peak,
            "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "peak_source": f"of {src} (burst copy)",
            "bytes_per_launch": nbytes, "us_per_launch": per_launch_s * 1e6,
@@ -427,6 +427,27 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
         same = int(tok_a.item()) == int(tok_f.item())
         us_a, how_a = time_rounds(unfused_round)
         us_b, how_b = time_rounds(fused_round)
+        peer_result = None
+        if world > 1:
+            try:
+                pc = lambda w, s, a, b, c, v, i, pv, pi, ctl, off, r, k: ops.gemv_w4a8_sample_candidates_peers(
+                    w, s, a, b, c, v, i, pv, pi, ctl, off, r, k)
+                ctl_c = ops.make_sample_control(temperature, 1234, 0)
+                psamplers = [nsplit.NSplitSampler(w, s, N, K, slots, cand, ops.launch_sample_finish, peer_candidates=pc)
+                             for w, s in slabs]
+                cc = ops.make_sample_control(temperature, 99, 5)
+                with torch.cuda.stream(stream):
+                    tok_p = psamplers[0].forward(q8, xs, s8, cc).clone()
+                stream.synchronize()
+
+                def peer_round():
+                    for sm in psamplers:
+                        sm.forward(q8, xs, s8, ctl_c)
+                us_c, how_c = time_rounds(peer_round)
+                peer_result = {"us_per_step": us_c, "timed_as": how_c, "exchange_bytes_per_gpu": slots * 8 * (world - 1),
+                               "same_token": bool(int(tok_p.item()) == int(tok_a.item()))}
+            except Exception as e:
+                peer_result = {"unavailable": str(e)[:200]}
         out["token_selection"] = {
             "temperature": temperature, "candidates_per_gpu": slots,
             "logits_gather_then_sampler": {"us_per_step": us_a, "timed_as": how_a,
@@ -434,6 +455,8 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
             "sampling_epilogue": {"us_per_step": us_b, "timed_as": how_b,
                                   "exchange_bytes_per_gpu": slots * 8 if world > 1 else 0},
             "same_token": bool(same)}
+        if peer_result is not None:
+            out["token_selection"]["sampling_epilogue_peer_store"] = peer_result
     except Exception as e:
         out["token_selection"] = {"unavailable": str(e)[:200]}
     return out

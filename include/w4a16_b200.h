@@ -173,6 +173,16 @@ W4A16_API int w4a16_gemv_w4a8_sample_candidates(const uint32_t* qweight, const v
                                                 void* output_logits, float* candidate_val, int32_t* candidate_idx,
                                                 const void* d_control, int index_offset, int out_features,
                                                 int in_features, w4a16_stream_t stream);
+/* The same, with the candidates also stored at the given addresses: this rank's place in the gathered candidate
+ * arrays of up to 7 PEER GPUs (memory mapped into this process; plain stores over NVLink).  With every rank
+ * doing so, a barrier over the ranks replaces the exchange and w4a16_sample_finish runs on the gathered arrays. */
+W4A16_API int w4a16_gemv_w4a8_sample_candidates_peers(const uint32_t* qweight, const void* scales,
+                                                      const int8_t* input_q8, const float* input_scale,
+                                                      const int32_t* input_sum8, float* candidate_val,
+                                                      int32_t* candidate_idx, float* const* peer_candidate_val,
+                                                      int32_t* const* peer_candidate_idx, int num_peers,
+                                                      const void* d_control, int index_offset, int out_features,
+                                                      int in_features, w4a16_stream_t stream);
 W4A16_API int w4a16_sample_finish(const float* candidate_val, const int32_t* candidate_idx, int count,
                                   void* d_control, int32_t* d_token_out, w4a16_stream_t stream);
 /* Both steps on one GPU; the scratch arrays hold w4a16_sample_slots(out_features) entries. */

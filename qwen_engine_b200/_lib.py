@@ -51,6 +51,9 @@ SIGNATURES = {
     "w4a16_sample_slots": [c_int],
     "w4a16_gemv_w4a8_sample_candidates": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                           c_void_p, c_int, c_int, c_int, c_void_p],
+    "w4a16_gemv_w4a8_sample_candidates_peers": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                POINTER(c_void_p), POINTER(c_void_p), c_int, c_void_p, c_int, c_int,
+                                                c_int, c_void_p],
     "w4a16_sample_finish": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
     "w4a16_gemv_w4a8_sample_and_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],

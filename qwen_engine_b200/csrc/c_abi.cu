@@ -184,13 +184,15 @@ int w4a16_sample_slots(int out_features) {
     return gemv_sample_slots(out_features);
 }
 
-int w4a16_gemv_w4a8_sample_candidates(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
-                                      const float* input_scale, const int32_t* input_sum8, void* output_logits,
-                                      float* candidate_val, int32_t* candidate_idx, const void* d_control,
-                                      int index_offset, int out_features, int in_features, w4a16_stream_t stream) {
+static int sample_candidates(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                             const float* input_scale, const int32_t* input_sum8, void* output_logits,
+                             float* candidate_val, int32_t* candidate_idx, float* const* peer_val,
+                             int32_t* const* peer_idx, int num_peers, const void* d_control, int index_offset,
+                             int out_features, int in_features, w4a16_stream_t stream) {
     if (!qweight || !scales || !input_q8 || !input_scale || !input_sum8 || !candidate_val || !candidate_idx ||
         out_features <= 0 || index_offset < 0)
         return W4A16_ERR_INVALID_ARG;
+    if (num_peers < 0 || num_peers > 7 || (num_peers > 0 && (!peer_val || !peer_idx))) return W4A16_ERR_INVALID_ARG;
     if (int st = check_k(in_features)) return st;
     if (misaligned(qweight, 16) || misaligned(scales, 2) || misaligned(output_logits, 2) || misaligned(input_scale, 4) ||
         misaligned(input_sum8, 4) || misaligned(candidate_val, 4) || misaligned(candidate_idx, 4) ||
@@ -202,7 +204,34 @@ int w4a16_gemv_w4a8_sample_candidates(const uint32_t* qweight, const void* scale
     a.K = in_features; a.units = out_features;
     a.sample_val = candidate_val; a.sample_idx = candidate_idx; a.sample_control = d_control;
     a.sample_index_offset = index_offset;
+    for (int p = 0; p < num_peers; ++p) {
+        if (!peer_val[p] || !peer_idx[p]) return W4A16_ERR_INVALID_ARG;
+        if (misaligned(peer_val[p], 4) || misaligned(peer_idx[p], 4)) return W4A16_ERR_ALIGNMENT;
+        a.sample_peer_val[p] = peer_val[p];
+        a.sample_peer_idx[p] = peer_idx[p];
+    }
+    a.sample_num_peers = num_peers;
     return gemv_launch(kPlain, a, S(stream));
+}
+
+int w4a16_gemv_w4a8_sample_candidates(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                                      const float* input_scale, const int32_t* input_sum8, void* output_logits,
+                                      float* candidate_val, int32_t* candidate_idx, const void* d_control,
+                                      int index_offset, int out_features, int in_features, w4a16_stream_t stream) {
+    return sample_candidates(qweight, scales, input_q8, input_scale, input_sum8, output_logits, candidate_val,
+                             candidate_idx, nullptr, nullptr, 0, d_control, index_offset, out_features, in_features,
+                             stream);
+}
+
+int w4a16_gemv_w4a8_sample_candidates_peers(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                                            const float* input_scale, const int32_t* input_sum8,
+                                            float* candidate_val, int32_t* candidate_idx,
+                                            float* const* peer_candidate_val, int32_t* const* peer_candidate_idx,
+                                            int num_peers, const void* d_control, int index_offset, int out_features,
+                                            int in_features, w4a16_stream_t stream) {
+    return sample_candidates(qweight, scales, input_q8, input_scale, input_sum8, nullptr, candidate_val, candidate_idx,
+                             peer_candidate_val, peer_candidate_idx, num_peers, d_control, index_offset, out_features,
+                             in_features, stream);
 }
 
 int w4a16_sample_finish(const float* candidate_val, const int32_t* candidate_idx, int count, void* d_control,

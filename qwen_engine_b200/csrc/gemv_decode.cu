@@ -446,6 +446,10 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const Ge
         if (tid == 0) {
             a.sample_val[blockIdx.x] = best;
             a.sample_idx[blockIdx.x] = best_idx;
+            for (int p = 0; p < a.sample_num_peers; ++p) {   // plain stores over NVLink
+                a.sample_peer_val[p][blockIdx.x] = best;
+                a.sample_peer_idx[p][blockIdx.x] = best_idx;
+            }
         }
     }
 }

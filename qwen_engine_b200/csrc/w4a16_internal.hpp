@@ -92,6 +92,11 @@ struct GemvArgs {
     int32_t* sample_idx;
     const void* sample_control;   // SampleControl (temperature, seed, position) in device memory, may be null
     int sample_index_offset;      // added to the row number: vocabulary index of row 0 (row-split lm_head)
+    // the same candidates are also stored at these addresses (the rank's place in every peer GPU's gathered
+    // candidate arrays, mapped into this process)
+    float* sample_peer_val[7];
+    int32_t* sample_peer_idx[7];
+    int sample_num_peers;
     int K;
     int units;  // outputs produced: rows (PLAIN, QKV total) or row pairs (SWIGLU)
     // filled in by the planner

@@ -110,7 +110,11 @@ class NSplitSampler:
     """
 
     def __init__(self, qweight_slab: torch.Tensor, scales_slab: torch.Tensor, n_rows: int, in_features: int,
-                 slots: int, candidates, finish, group=None):
+                 slots: int, candidates, finish, group=None, peer_candidates=None):
+        """peer_candidates (optional, GPUs with peer access only): launch(qw, sc, q8, xs, s8, val, idx,
+        peer_val_ptrs, peer_idx_ptrs, control, index_offset, rows, K) whose epilogue also stores the candidates
+        into every peer's gathered array; the arrays then live in symmetric memory and the all-gather becomes a
+        barrier."""
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
@@ -120,23 +124,44 @@ class NSplitSampler:
             raise ValueError(f"rank {self.rank} expects a slab of {self.slab.rows} rows")
         self.qweight, self.scales = qweight_slab, scales_slab
         self.candidates, self.finish = candidates, finish
+        self.peer_candidates = peer_candidates if self.world > 1 else None
         dev = qweight_slab.device
         # [world][2][slots] 32-bit words: scores (as bits) then indices, so that one all-gather moves both
-        self.gathered = torch.zeros((self.world, 2, slots), dtype=torch.int32, device=dev)
+        self.symm = None
+        if self.peer_candidates is not None:
+            import torch.distributed._symmetric_memory as symm_mem
+            flat = symm_mem.empty(self.world * 2 * slots, dtype=torch.int32, device=dev)
+            flat.zero_()
+            self.symm = symm_mem.rendezvous(flat, group=group if group is not None else dist.group.WORLD)
+            self.gathered = flat.view(self.world, 2, slots)
+            off = self.rank * 2 * slots * 4          # this rank's rows, in bytes, inside every buffer
+            peers = [r for r in range(self.world) if r != self.rank]
+            self.peer_val_ptrs = [int(self.symm.buffer_ptrs[r]) + off for r in peers]
+            self.peer_idx_ptrs = [int(self.symm.buffer_ptrs[r]) + off + slots * 4 for r in peers]
+        else:
+            self.gathered = torch.zeros((self.world, 2, slots), dtype=torch.int32, device=dev)
         self.token = torch.zeros(1, dtype=torch.int32, device=dev)
 
     def forward(self, q8, xscale, sum8, control) -> torch.Tensor:
         """Returns the int32 token tensor [1] (the same value on every rank); advances `control`."""
         mine = self.gathered[self.rank]
         val, idx = mine[0].view(torch.float32), mine[1]
-        if self.slab.rows > 0:
-            self.candidates(self.qweight, self.scales, q8, xscale, sum8, val, idx, control, self.slab.first,
-                            self.slab.rows, self.K)
+        if self.peer_candidates is not None:
+            if self.slab.rows == 0:
+                raise ValueError("the peer-store form needs rows on every rank")
+            self.peer_candidates(self.qweight, self.scales, q8, xscale, sum8, val, idx, self.peer_val_ptrs,
+                                 self.peer_idx_ptrs, control, self.slab.first, self.slab.rows, self.K)
+            self.symm.barrier()      # every rank's candidates have landed everywhere
         else:
-            val.fill_(float("-inf"))
-            idx.zero_()
+            if self.slab.rows > 0:
+                self.candidates(self.qweight, self.scales, q8, xscale, sum8, val, idx, control, self.slab.first,
+                                self.slab.rows, self.K)
+            else:
+                val.fill_(float("-inf"))
+                idx.zero_()
+            if self.world > 1:
+                dist.all_gather_into_tensor(self.gathered.view(-1), mine.reshape(-1), group=self.group)
         if self.world > 1:
-            dist.all_gather_into_tensor(self.gathered.view(-1), mine.reshape(-1), group=self.group)
             allv = self.gathered[:, 0, :].contiguous().view(torch.float32).view(-1)
             alli = self.gathered[:, 1, :].contiguous().view(-1)
         else:

@@ -171,3 +171,37 @@ def test_embed_lookup_matches_the_dequantised_rows(ops, H, vocab, M):
     ops.launch_embed_lookup_w4a16(util.to_dev(qw), util.to_dev(sc), None, out, control, 1, None, H, vocab)
     torch.cuda.synchronize()
     assert np.array_equal(util.to_np(out)[:H].view(np.uint16), table[ids[0]].view(np.uint16))
+
+
+def test_peer_store_epilogues_write_the_same_values_everywhere(ops):
+    """The two epilogues that also store into peer GPUs' buffers (logit slice; sampling candidates), with
+    ordinary local allocations standing in for the peers' mapped memory."""
+    from qwen_engine_b200 import synth
+    N, K = 6000, 1536
+    qw, sc = util.to_dev(synth.packed_weights(8, "p", N, K)), util.to_dev(synth.scales(8, "p", N, K))
+    q8, xs, s8 = (util.to_dev(t) for t in oracle.quantize_q8_1(synth.activations(9, "p", K)))
+    ref = torch.empty(N, dtype=torch.float16, device="cuda")
+    ops.launch_gemv_w4a8(qw, sc, q8, xs, s8, None, ref, N, K)
+    # logit slices: the local output and three "peers", each at an offset inside a larger gathered buffer
+    local = torch.zeros(N, dtype=torch.float16, device="cuda")
+    peers = [torch.zeros(3 * N, dtype=torch.float16, device="cuda") for _ in range(3)]
+    ops.gemv_w4a8_peers(qw, sc, q8, xs, s8, local, [p.data_ptr() + 2 * N for p in peers], N, K)
+    torch.cuda.synchronize()
+    assert torch.equal(local, ref)
+    for p in peers:
+        assert torch.equal(p[N:2 * N], ref) and not p[:N].any() and not p[2 * N:].any()
+    # candidates
+    slots = ops.sample_slots(N)
+    control = ops.make_sample_control(0.6, 31337, 2)
+    v0, i0 = _scratch(slots)
+    ops.launch_gemv_w4a8_sample_candidates(qw, sc, q8, xs, s8, None, v0, i0, control, 100, N, K)
+    v1, i1 = _scratch(slots)
+    pv = [torch.zeros(2 * slots, dtype=torch.float32, device="cuda") for _ in range(2)]
+    pi = [torch.zeros(2 * slots, dtype=torch.int32, device="cuda") for _ in range(2)]
+    ops.gemv_w4a8_sample_candidates_peers(qw, sc, q8, xs, s8, v1, i1, [t.data_ptr() + 4 * slots for t in pv],
+                                          [t.data_ptr() + 4 * slots for t in pi], control, 100, N, K)
+    torch.cuda.synchronize()
+    assert torch.equal(v1, v0) and torch.equal(i1, i0)
+    for tv, ti in zip(pv, pi):
+        assert torch.equal(tv[slots:], v0) and torch.equal(ti[slots:], i0)
+        assert not tv[:slots].any() and not ti[:slots].any()
