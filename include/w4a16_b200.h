@@ -370,6 +370,37 @@ W4A16_API int w4a16_sweep_status(w4a16_sweep* sweep, int* out);
 /* Device pointer of a workspace region, for tests: 0 hidden, 1 q, 2 k, 3 v, 4 mlp. */
 W4A16_API void* w4a16_sweep_buffer(const w4a16_sweep* sweep, int which);
 
+/* ---- the reference's `.qwenbin` weight container --------------------------------------- */
+/*
+ * Host-side reader of the file format the reference engine loads (include/config.cuh:75-170,
+ * docs/SPECIFICATION.md, written by tools/export_qwen25.py): versions 1 and 2, W4A16 group 128.  The file's
+ * bytes stay the caller's (mmap or a read buffer); nothing is allocated or copied.  Every offset is checked
+ * against the file size and the 256-byte tensor alignment before an address is formed.
+ */
+typedef struct w4a16_qwenbin_header {
+    uint32_t version, hidden_size, intermediate_size, num_layers, num_q_heads, num_kv_heads, head_dim, vocab_size,
+        max_seq_len, quant_type, tie_word_embeddings;
+    float rms_norm_eps, rope_theta;
+    uint64_t file_bytes;
+} w4a16_qwenbin_header;
+typedef struct w4a16_qwenbin_globals {
+    const void* embed_weight;  const void* embed_scale;      /* [vocab][hidden] packed, fp16 [vocab][hidden/128] */
+    const void* final_norm_gamma;                            /* fp16 [hidden] */
+    const void* lm_head_weight; const void* lm_head_scale;   /* the embedding tensors when tied */
+} w4a16_qwenbin_globals;
+typedef struct w4a16_qwenbin_biases { const void* q_bias; const void* k_bias; const void* v_bias; } w4a16_qwenbin_biases;
+
+W4A16_API int w4a16_qwenbin_parse(const void* file_bytes, uint64_t nbytes, w4a16_qwenbin_header* header);
+/*
+ * Fills layers[0 .. num_layers) (the table w4a16_sweep_create takes), `globals` and `biases[num_layers]` (either
+ * may be NULL) with base + offset, `base` being where the caller put a copy of the whole file, e.g. in device
+ * memory as the reference does (src/engine.cu:85-348); base must be 256-byte aligned.  W4A16_ERR_INVALID_ARG
+ * for a bad magic / version / offset, W4A16_ERR_SHAPE for dimensions or a quantisation the path does not take.
+ */
+W4A16_API int w4a16_qwenbin_tensors(const void* file_bytes, uint64_t nbytes, const void* base,
+                                    w4a16_layer_weights* layers, int max_layers, w4a16_qwenbin_globals* globals,
+                                    w4a16_qwenbin_biases* biases);
+
 /* ---- diagnostics ----------------------------------------------------------------- */
 
 /*

@@ -25,6 +25,25 @@ class LayerWeights(ctypes.Structure):
         "o_weight", "o_scale", "post_norm_gamma", "gate_up_weight", "gate_up_scale", "down_weight", "down_scale")]
 
 
+class QwenBinHeader(ctypes.Structure):
+    """Mirror of w4a16_qwenbin_header."""
+    _fields_ = [(n, ctypes.c_uint32) for n in (
+        "version", "hidden_size", "intermediate_size", "num_layers", "num_q_heads", "num_kv_heads", "head_dim",
+        "vocab_size", "max_seq_len", "quant_type", "tie_word_embeddings")] + [
+        ("rms_norm_eps", ctypes.c_float), ("rope_theta", ctypes.c_float), ("file_bytes", ctypes.c_uint64)]
+
+
+class QwenBinGlobals(ctypes.Structure):
+    """Mirror of w4a16_qwenbin_globals."""
+    _fields_ = [(n, c_void_p) for n in ("embed_weight", "embed_scale", "final_norm_gamma", "lm_head_weight",
+                                        "lm_head_scale")]
+
+
+class QwenBinBiases(ctypes.Structure):
+    """Mirror of w4a16_qwenbin_biases."""
+    _fields_ = [(n, c_void_p) for n in ("q_bias", "k_bias", "v_bias")]
+
+
 class SweepDesc(ctypes.Structure):
     """Mirror of w4a16_sweep_desc."""
     _fields_ = [("num_layers", c_int), ("hidden_size", c_int), ("intermediate_size", c_int),
@@ -46,6 +65,9 @@ SIGNATURES = {
                         c_void_p],
     "w4a16_gemv_w4a8_peers": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(c_void_p), c_int,
                               c_int, c_int, c_void_p],
+    "w4a16_qwenbin_parse": [c_void_p, ctypes.c_uint64, POINTER(QwenBinHeader)],
+    "w4a16_qwenbin_tensors": [c_void_p, ctypes.c_uint64, c_void_p, POINTER(LayerWeights), c_int, POINTER(QwenBinGlobals),
+                              POINTER(QwenBinBiases)],
     "w4a16_embed_lookup_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int],
     "w4a16_sample_and_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int],
     "w4a16_sample_slots": [c_int],

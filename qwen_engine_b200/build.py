@@ -14,7 +14,7 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libw4a16_b200.so"
 SOURCES = ["c_abi.cu", "q8_1_quantize.cu", "gemv_decode.cu", "gemm_prefill.cu", "gemm_tc.cu", "decode_sweep.cu", "sweep_persistent.cu",
-           "gemv_static_scratch.cu", "sampling.cu", "embed_lookup.cu"]
+           "gemv_static_scratch.cu", "sampling.cu", "embed_lookup.cu", "qwenbin.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-lineinfo", "-std=c++20", "--expt-relaxed-constexpr",

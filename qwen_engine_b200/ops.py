@@ -302,7 +302,8 @@ class DecodeSweep:
     """The W4 projections of one batch-1 decode pass as one CUDA graph (C ABI w4a16_sweep_*).
 
     layers: list of dicts with keys input_norm, q, k, v, o, post_norm, gate_up, down; the norm
-    entries are fp16 gamma tensors, the others (qweight, scales) tensor pairs.  The object keeps
+    entries are fp16 gamma tensors, the others (qweight, scales) tensor pairs -- or a ready ctypes array of
+    LayerWeights (e.g. QwenBin.layer_table over an uploaded `.qwenbin` file; the caller keeps that memory alive).  The object keeps
     the tensors alive; the native sweep owns only its graph.
     """
 
@@ -316,8 +317,8 @@ class DecodeSweep:
             check("w4a16_sweep_workspace_bytes", int(nbytes))
         self._ws = torch.zeros(nbytes + 256, dtype=torch.uint8, device="cuda")
         ws_ptr = (self._ws.data_ptr() + 255) // 256 * 256
-        arr = (LayerWeights * len(layers))()
-        for i, L in enumerate(layers):
+        arr = layers if isinstance(layers, ctypes.Array) else (LayerWeights * len(layers))()
+        for i, L in enumerate([] if isinstance(layers, ctypes.Array) else layers):
             arr[i] = LayerWeights(
                 _ptr(L["input_norm"]), _ptr(L["q"][0]), _ptr(L["q"][1]), _ptr(L["k"][0]), _ptr(L["k"][1]),
                 _ptr(L["v"][0]), _ptr(L["v"][1]), _ptr(L["o"][0]), _ptr(L["o"][1]), _ptr(L["post_norm"]),
