@@ -424,10 +424,11 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
             ops.launch_sample_and_advance(lg, val, idx, ca, tok_a, None, N)
             tok_f = samplers[0].forward(q8, xs, s8, cb).clone()
         stream.synchronize()
-        same = int(tok_a.item()) == int(tok_f.item())
+        tok_ref = int(tok_a.item())
+        same = tok_ref == int(tok_f.item())
         us_a, how_a = time_rounds(unfused_round)
         us_b, how_b = time_rounds(fused_round)
-        peer_result = None
+        peer_result = signal_result = None
         if world > 1:
             try:
                 pc = lambda w, s, a, b, c, v, i, pv, pi, ctl, off, r, k: ops.gemv_w4a8_sample_candidates_peers(
@@ -445,9 +446,28 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
                         sm.forward(q8, xs, s8, ctl_c)
                 us_c, how_c = time_rounds(peer_round)
                 peer_result = {"us_per_step": us_c, "timed_as": how_c, "exchange_bytes_per_gpu": slots * 8 * (world - 1),
-                               "same_token": bool(int(tok_p.item()) == int(tok_a.item()))}
+                               "same_token": bool(int(tok_p.item()) == tok_ref)}
             except Exception as e:
                 peer_result = {"unavailable": str(e)[:200]}
+            try:
+                ctl_d = ops.make_sample_control(temperature, 1234, 0)
+                ssamplers = [nsplit.NSplitSignalSampler(w, s, N, K, slots, ops.gemv_w4a8_sample_candidates_signal,
+                                                        ops.sample_finish_after_signals) for w, s in slabs]
+                cd = ops.make_sample_control(temperature, 99, 5)
+                with torch.cuda.stream(stream):
+                    tok_s = ssamplers[0].forward(q8, xs, s8, cd).clone()
+                stream.synchronize()
+
+                def signal_round():
+                    for sm in ssamplers:
+                        sm.forward(q8, xs, s8, ctl_d)
+                us_d, how_d = time_rounds(signal_round)
+                torch.cuda.synchronize()
+                signal_result = {"us_per_step": us_d, "timed_as": how_d, "exchange_bytes_per_gpu": (slots * 8 + 4) * (world - 1),
+                                 "same_token": bool(int(tok_s.item()) == tok_ref),
+                                 "wait_timeouts": int(sum(int(sm.status.item()) != 0 for sm in ssamplers))}
+            except Exception as e:
+                signal_result = {"unavailable": str(e)[:200]}
         out["token_selection"] = {
             "temperature": temperature, "candidates_per_gpu": slots,
             "logits_gather_then_sampler": {"us_per_step": us_a, "timed_as": how_a,
@@ -457,6 +477,8 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
             "same_token": bool(same)}
         if peer_result is not None:
             out["token_selection"]["sampling_epilogue_peer_store"] = peer_result
+        if signal_result is not None:
+            out["token_selection"]["sampling_epilogue_peer_store_signal"] = signal_result
     except Exception as e:
         out["token_selection"] = {"unavailable": str(e)[:200]}
     return out

@@ -183,6 +183,35 @@ W4A16_API int w4a16_gemv_w4a8_sample_candidates_peers(const uint32_t* qweight, c
                                                       int32_t* const* peer_candidate_idx, int num_peers,
                                                       const void* d_control, int index_offset, int out_features,
                                                       int in_features, w4a16_stream_t stream);
+/*
+ * Peer stores plus a completion signal, so that no barrier kernel is needed between the ranks' GEMVs and the
+ * reduction, and nothing about a step comes from the host (the pair can sit in a replayed CUDA graph):
+ * *step_word (device, zero at first) counts this rank's finished launches.  A launch calls its step number
+ * *step_word + 1, stores its candidates into half (step & 1) of every candidate array (each array is
+ * 2 * half_stride entries: a fast rank's next stores must not land in the half a slow rank is still
+ * reducing), and when its last CTA is through writes the step number to *step_word, to *local_flag and --
+ * behind one system-scope fence -- to peer_flags[i], this rank's slot in GPU i's flag array.  *done_counter is a device
+ * word, zero at first, that only this sequence of launches touches.
+ * w4a16_sample_finish_after_signals reads this rank's *step_word, waits until flags[0 .. num_flags) all show that
+ * step (bounded: about a second, then *d_status = 1 + the rank it missed and the reduction runs on what is
+ * there), and reduces half (step & 1) of the gathered arrays like w4a16_sample_finish; `count` entries per half.
+ * All ranks must take part in every step.  Ranks on DIFFERENT GPUs only: launches that wait for one another
+ * must not share a GPU.
+ */
+W4A16_API int w4a16_gemv_w4a8_sample_candidates_signal(const uint32_t* qweight, const void* scales,
+                                                       const int8_t* input_q8, const float* input_scale,
+                                                       const int32_t* input_sum8, float* candidate_val,
+                                                       int32_t* candidate_idx, float* const* peer_candidate_val,
+                                                       int32_t* const* peer_candidate_idx,
+                                                       uint32_t* const* peer_flags, int num_peers,
+                                                       uint32_t* local_flag, uint32_t* done_counter,
+                                                       uint32_t* step_word, int half_stride, const void* d_control,
+                                                       int index_offset, int out_features, int in_features,
+                                                       w4a16_stream_t stream);
+W4A16_API int w4a16_sample_finish_after_signals(const float* candidate_val, const int32_t* candidate_idx, int count,
+                                                int half_stride, const uint32_t* flags, int num_flags,
+                                                const uint32_t* step_word, int* d_status, void* d_control,
+                                                int32_t* d_token_out, w4a16_stream_t stream);
 W4A16_API int w4a16_sample_finish(const float* candidate_val, const int32_t* candidate_idx, int count,
                                   void* d_control, int32_t* d_token_out, w4a16_stream_t stream);
 /* Both steps on one GPU; the scratch arrays hold w4a16_sample_slots(out_features) entries. */

@@ -188,7 +188,9 @@ static int sample_candidates(const uint32_t* qweight, const void* scales, const 
                              const float* input_scale, const int32_t* input_sum8, void* output_logits,
                              float* candidate_val, int32_t* candidate_idx, float* const* peer_val,
                              int32_t* const* peer_idx, int num_peers, const void* d_control, int index_offset,
-                             int out_features, int in_features, w4a16_stream_t stream) {
+                             int out_features, int in_features, w4a16_stream_t stream,
+                             uint32_t* const* peer_flags = nullptr, uint32_t* local_flag = nullptr,
+                             uint32_t* done_counter = nullptr, uint32_t* step_word = nullptr, int half_stride = 0) {
     if (!qweight || !scales || !input_q8 || !input_scale || !input_sum8 || !candidate_val || !candidate_idx ||
         out_features <= 0 || index_offset < 0)
         return W4A16_ERR_INVALID_ARG;
@@ -211,6 +213,19 @@ static int sample_candidates(const uint32_t* qweight, const void* scales, const 
         a.sample_peer_idx[p] = peer_idx[p];
     }
     a.sample_num_peers = num_peers;
+    if (local_flag != nullptr) {
+        if (!done_counter || !step_word || half_stride < 0 || (num_peers > 0 && !peer_flags)) return W4A16_ERR_INVALID_ARG;
+        if (misaligned(local_flag, 4) || misaligned(done_counter, 4) || misaligned(step_word, 4)) return W4A16_ERR_ALIGNMENT;
+        a.sample_flag_local = local_flag;
+        a.sample_done_counter = done_counter;
+        a.sample_step_word = step_word;
+        a.sample_half_stride = half_stride;
+        for (int p = 0; p < num_peers; ++p) {
+            if (!peer_flags[p]) return W4A16_ERR_INVALID_ARG;
+            if (misaligned(peer_flags[p], 4)) return W4A16_ERR_ALIGNMENT;
+            a.sample_peer_flag[p] = peer_flags[p];
+        }
+    }
     return gemv_launch(kPlain, a, S(stream));
 }
 
@@ -232,6 +247,36 @@ int w4a16_gemv_w4a8_sample_candidates_peers(const uint32_t* qweight, const void*
     return sample_candidates(qweight, scales, input_q8, input_scale, input_sum8, nullptr, candidate_val, candidate_idx,
                              peer_candidate_val, peer_candidate_idx, num_peers, d_control, index_offset, out_features,
                              in_features, stream);
+}
+
+int w4a16_gemv_w4a8_sample_candidates_signal(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                                             const float* input_scale, const int32_t* input_sum8,
+                                             float* candidate_val, int32_t* candidate_idx,
+                                             float* const* peer_candidate_val, int32_t* const* peer_candidate_idx,
+                                             uint32_t* const* peer_flags, int num_peers, uint32_t* local_flag,
+                                             uint32_t* done_counter, uint32_t* step_word, int half_stride,
+                                             const void* d_control, int index_offset, int out_features,
+                                             int in_features, w4a16_stream_t stream) {
+    if (!local_flag) return W4A16_ERR_INVALID_ARG;
+    return sample_candidates(qweight, scales, input_q8, input_scale, input_sum8, nullptr, candidate_val, candidate_idx,
+                             peer_candidate_val, peer_candidate_idx, num_peers, d_control, index_offset, out_features,
+                             in_features, stream, peer_flags, local_flag, done_counter, step_word, half_stride);
+}
+
+int w4a16_sample_finish_after_signals(const float* candidate_val, const int32_t* candidate_idx, int count,
+                                      int half_stride, const uint32_t* flags, int num_flags,
+                                      const uint32_t* step_word, int* d_status, void* d_control,
+                                      int32_t* d_token_out, w4a16_stream_t stream) {
+    if (!candidate_val || !candidate_idx || count <= 0 || half_stride < 0 || !flags || num_flags <= 0 || num_flags > 256 ||
+        !step_word)
+        return W4A16_ERR_INVALID_ARG;
+    if (misaligned(candidate_val, 4) || misaligned(candidate_idx, 4) || misaligned(flags, 4) || misaligned(d_status, 4) ||
+        misaligned(step_word, 4) ||
+        misaligned(d_control, 8) || misaligned(d_token_out, 4))
+        return W4A16_ERR_ALIGNMENT;
+    if (int st = ensure_device_ready(nullptr)) return st;
+    return sample_stage2_after_flags(candidate_val, candidate_idx, count, half_stride, flags, num_flags, step_word,
+                                     d_status, d_control, d_token_out, S(stream));
 }
 
 int w4a16_sample_finish(const float* candidate_val, const int32_t* candidate_idx, int count, void* d_control,

@@ -369,7 +369,9 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const Ge
     [[maybe_unused]] uint32_t seq_pos = 0;
     [[maybe_unused]] int32_t best_idx = 0;
     [[maybe_unused]] int it = 0, buf = 0;
+    [[maybe_unused]] uint32_t sample_step = 0;
     if constexpr (SAMPLE) {
+        if (a.sample_step_word != nullptr) sample_step = *reinterpret_cast<volatile uint32_t*>(a.sample_step_word) + 1u;
         if (a.sample_control != nullptr) {
             const SampleControl* c = static_cast<const SampleControl*>(a.sample_control);
             temperature = c->temperature;
@@ -444,11 +446,26 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const Ge
         __shared__ int32_t s_i[32];
         sample_block_reduce(best, best_idx, s_v, s_i);
         if (tid == 0) {
-            a.sample_val[blockIdx.x] = best;
-            a.sample_idx[blockIdx.x] = best_idx;
+            const size_t slot = static_cast<size_t>(sample_step & 1u) * a.sample_half_stride + blockIdx.x;
+            a.sample_val[slot] = best;
+            a.sample_idx[slot] = best_idx;
             for (int p = 0; p < a.sample_num_peers; ++p) {   // plain stores over NVLink
-                a.sample_peer_val[p][blockIdx.x] = best;
-                a.sample_peer_idx[p][blockIdx.x] = best_idx;
+                a.sample_peer_val[p][slot] = best;
+                a.sample_peer_idx[p][slot] = best_idx;
+            }
+            if (a.sample_step_word != nullptr) {
+                // "last block" pattern: stores, fence, count; the CTA that completes the count fences at system
+                // scope (cumulative over what it observed through the counter) and publishes the step number,
+                // which a reader on another GPU then takes with an acquire load
+                __threadfence();
+                if (atomicInc(a.sample_done_counter, gridDim.x - 1u) == gridDim.x - 1u) {
+                    __threadfence_system();   // ONE system-scope fence, then independent flag stores: a release
+                                              // store per peer would wait for the previous peer's round trip
+                    *reinterpret_cast<volatile uint32_t*>(a.sample_step_word) = sample_step;
+                    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(a.sample_flag_local), "r"(sample_step) : "memory");
+                    for (int p = 0; p < a.sample_num_peers; ++p)
+                        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(a.sample_peer_flag[p]), "r"(sample_step) : "memory");
+                }
             }
         }
     }

@@ -66,7 +66,66 @@ __global__ void __launch_bounds__(256) sample_stage2_kernel(const float* __restr
     }
 }
 
+// The same reduction for candidates that other GPUs store into this GPU's memory: first wait (bounded) until
+// every rank's flag shows this rank's own step number (all ranks produce one token per step, in lockstep) --
+// that rank's lm_head launch has stored all its candidates (gemv_decode.cu) --
+// so no separate barrier kernel is needed between the GEMV and the reduction.  A wait that runs out sets
+// *status to 1 + the rank it waited for and the reduction goes ahead on whatever is there.
+__global__ void __launch_bounds__(256) sample_stage2_after_flags_kernel(const float* __restrict__ part_val,
+                                                                        const int32_t* __restrict__ part_idx, int count,
+                                                                        int half_stride, const uint32_t* flags, int num_flags,
+                                                                        const uint32_t* step_word, int* status,
+                                                                        SampleControl* __restrict__ control,
+                                                                        int32_t* __restrict__ token_out) {
+    __shared__ float s_v[32];
+    __shared__ int32_t s_i[32];
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    // the step this rank's own lm_head launch (earlier on the stream) has just finished
+    const uint32_t step = *reinterpret_cast<const volatile uint32_t*>(step_word);
+    part_val += static_cast<size_t>(step & 1u) * half_stride;
+    part_idx += static_cast<size_t>(step & 1u) * half_stride;
+    if (static_cast<int>(threadIdx.x) < num_flags) {
+        const uint32_t* f = flags + threadIdx.x;
+        bool seen = false;
+        for (uint32_t spin = 0; spin < (1u << 22); ++spin) {     // about a second at the longest
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if (static_cast<int32_t>(v - step) >= 0) { seen = true; break; }   // step numbers only grow (wrap-safe)
+            __nanosleep(spin < 64 ? 20 : 200);
+        }
+        if (!seen && status != nullptr) atomicExch(status, 1 + static_cast<int>(threadIdx.x));
+    }
+    __syncthreads();
+    float best = kSampleFloor;
+    int32_t best_idx = 0x7FFFFFFF;
+    for (int i = threadIdx.x; i < count; i += blockDim.x) {
+        // written by other GPUs: read past the (non-coherent) L1
+        const float v = __ldcg(part_val + i);
+        const int32_t ix = __ldcg(part_idx + i);
+        sample_take(best, best_idx, v, ix);
+    }
+    sample_block_reduce(best, best_idx, s_v, s_i);
+    if (threadIdx.x == 0) {
+        if (best_idx == 0x7FFFFFFF) best_idx = 0;
+        if (control != nullptr) {
+            control->token_id = best_idx;
+            control->seq_pos += 1;
+            control->rng_seed += 0x9E3779B97F4A7C15ull;
+        }
+        if (token_out != nullptr) *token_out = best_idx;
+    }
+}
+
 }  // namespace
+
+int sample_stage2_after_flags(const float* part_val, const int32_t* part_idx, int count, int half_stride,
+                              const uint32_t* flags, int num_flags, const uint32_t* step_word, int* status,
+                              void* control, int32_t* token_out, cudaStream_t stream) {
+    return static_cast<int>(launch_kernel(sample_stage2_after_flags_kernel, dim3(1), dim3(256), 0, stream, pdl_enabled(),
+                                          part_val, part_idx, count, half_stride, flags, num_flags, step_word, status,
+                                          static_cast<SampleControl*>(control), token_out));
+}
 
 int sample_stage1_blocks() { return kStage1Blocks; }
 

@@ -97,6 +97,17 @@ struct GemvArgs {
     float* sample_peer_val[7];
     int32_t* sample_peer_idx[7];
     int sample_num_peers;
+    // optional completion signal, safe under CUDA-graph replay (nothing about it comes from the host per step):
+    // *sample_step_word counts this rank's finished launches.  A launch reads it, calls its own step
+    // number word + 1, stores its candidates into half (step & 1) of every array (arrays are
+    // 2 * sample_half_stride long), and when its last CTA is through writes the step number to the step word,
+    // to sample_flag_local and (behind one system-scope fence) to every sample_peer_flag -- this rank's slot in the flag
+    // array of each GPU.  sample_done_counter is a zero-initialised device word that wraps back to zero.
+    uint32_t* sample_step_word;
+    uint32_t* sample_flag_local;
+    uint32_t* sample_peer_flag[7];
+    uint32_t* sample_done_counter;
+    int sample_half_stride;
     int K;
     int units;  // outputs produced: rows (PLAIN, QKV total) or row pairs (SWIGLU)
     // filled in by the planner
@@ -121,6 +132,9 @@ int sample_stage1(const __half* logits, float* part_val, int32_t* part_idx, cons
                   int index_offset, cudaStream_t stream);
 int sample_stage2(const float* part_val, const int32_t* part_idx, int count, void* control, int32_t* token_out,
                   cudaStream_t stream);
+int sample_stage2_after_flags(const float* part_val, const int32_t* part_idx, int count, int half_stride,
+                              const uint32_t* flags, int num_flags, const uint32_t* step_word, int* status,
+                              void* control, int32_t* token_out, cudaStream_t stream);
 
 // ---- M-token contraction (gemm_prefill.cu) ----
 struct GemmArgs {

@@ -129,28 +129,39 @@ class NSplitSampler:
         # [world][2][slots] 32-bit words: scores (as bits) then indices, so that one all-gather moves both
         self.symm = None
         if self.peer_candidates is not None:
+            # Two gathered arrays used in turn: a fast rank's stores of step i+1 must not land in the array a
+            # slow rank is still reducing for step i.  With two, step i+2 reuses step i's array only after the
+            # barrier of step i+1, which no rank passes before every rank has finished reducing step i.
             import torch.distributed._symmetric_memory as symm_mem
-            flat = symm_mem.empty(self.world * 2 * slots, dtype=torch.int32, device=dev)
+            flat = symm_mem.empty(2 * self.world * 2 * slots, dtype=torch.int32, device=dev)
             flat.zero_()
             self.symm = symm_mem.rendezvous(flat, group=group if group is not None else dist.group.WORLD)
-            self.gathered = flat.view(self.world, 2, slots)
-            off = self.rank * 2 * slots * 4          # this rank's rows, in bytes, inside every buffer
+            self._both = flat.view(2, self.world, 2, slots)
+            self._parity = 0
+            self.gathered = self._both[0]
             peers = [r for r in range(self.world) if r != self.rank]
-            self.peer_val_ptrs = [int(self.symm.buffer_ptrs[r]) + off for r in peers]
-            self.peer_idx_ptrs = [int(self.symm.buffer_ptrs[r]) + off + slots * 4 for r in peers]
+            self._peer_ptrs = []
+            for half in range(2):
+                off = (half * self.world + self.rank) * 2 * slots * 4     # this rank's rows, in bytes, in every buffer
+                self._peer_ptrs.append(([int(self.symm.buffer_ptrs[r]) + off for r in peers],
+                                        [int(self.symm.buffer_ptrs[r]) + off + slots * 4 for r in peers]))
         else:
             self.gathered = torch.zeros((self.world, 2, slots), dtype=torch.int32, device=dev)
         self.token = torch.zeros(1, dtype=torch.int32, device=dev)
 
     def forward(self, q8, xscale, sum8, control) -> torch.Tensor:
         """Returns the int32 token tensor [1] (the same value on every rank); advances `control`."""
+        if self.peer_candidates is not None:
+            self.gathered = self._both[self._parity]
+            peer_val_ptrs, peer_idx_ptrs = self._peer_ptrs[self._parity]
+            self._parity ^= 1        # (a captured graph keeps the half it was captured with)
         mine = self.gathered[self.rank]
         val, idx = mine[0].view(torch.float32), mine[1]
         if self.peer_candidates is not None:
             if self.slab.rows == 0:
                 raise ValueError("the peer-store form needs rows on every rank")
-            self.peer_candidates(self.qweight, self.scales, q8, xscale, sum8, val, idx, self.peer_val_ptrs,
-                                 self.peer_idx_ptrs, control, self.slab.first, self.slab.rows, self.K)
+            self.peer_candidates(self.qweight, self.scales, q8, xscale, sum8, val, idx, peer_val_ptrs,
+                                 peer_idx_ptrs, control, self.slab.first, self.slab.rows, self.K)
             self.symm.barrier()      # every rank's candidates have landed everywhere
         else:
             if self.slab.rows > 0:
@@ -167,4 +178,57 @@ class NSplitSampler:
         else:
             allv, alli = val, idx
         self.finish(allv, alli, allv.numel(), control, self.token)
+        return self.token
+
+
+class NSplitSignalSampler:
+    """NSplitSampler without a barrier kernel: the lm_head epilogue stores the candidates into every GPU's
+    gathered arrays AND, when its last CTA is through, a step number into every GPU's flag array; the reduction
+    kernel waits for all flags itself.  Step numbers live in device memory, so the pair of launches can be
+    replayed as a CUDA graph.  GPUs with peer access only; every rank needs rows.
+
+    signal_launch / finish_launch: ops.gemv_w4a8_sample_candidates_signal / ops.sample_finish_after_signals.
+    """
+
+    def __init__(self, qweight_slab: torch.Tensor, scales_slab: torch.Tensor, n_rows: int, in_features: int,
+                 slots: int, signal_launch, finish_launch, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.n_rows, self.K, self.slots = n_rows, in_features, slots
+        self.slab = slab_bounds(n_rows, self.world, self.rank)
+        if self.slab.rows <= 0 or qweight_slab.shape[0] != self.slab.rows or scales_slab.shape[0] != self.slab.rows:
+            raise ValueError(f"rank {self.rank} expects a slab of {self.slab.rows} > 0 rows")
+        self.qweight, self.scales = qweight_slab, scales_slab
+        self.signal_launch, self.finish_launch = signal_launch, finish_launch
+        dev = qweight_slab.device
+        self.half = self.world * slots                       # entries per half of a gathered array
+        words = 4 * self.half + self.world                   # values [2][half], indices [2][half], flags [world]
+        self.buf = symm_mem.empty(words, dtype=torch.int32, device=dev)
+        self.buf.zero_()
+        self.symm = symm_mem.rendezvous(self.buf, group=group if group is not None else dist.group.WORLD)
+        base = lambda r: int(self.symm.buffer_ptrs[r])
+        val_off, idx_off, flag_off = 0, 2 * self.half * 4, 4 * self.half * 4
+        mine = self.rank * slots * 4                         # this rank's slots inside a half, in bytes
+        peers = [r for r in range(self.world) if r != self.rank]
+        self.val_ptr, self.idx_ptr = base(self.rank) + val_off, base(self.rank) + idx_off
+        self.flags_ptr = base(self.rank) + flag_off
+        self.my_val, self.my_idx = self.val_ptr + mine, self.idx_ptr + mine
+        self.my_flag = self.flags_ptr + 4 * self.rank
+        self.peer_val = [base(r) + val_off + mine for r in peers]
+        self.peer_idx = [base(r) + idx_off + mine for r in peers]
+        self.peer_flag = [base(r) + flag_off + 4 * self.rank for r in peers]
+        self.step_word = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.done_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.token = torch.zeros(1, dtype=torch.int32, device=dev)
+        torch.cuda.synchronize()
+        self.symm.barrier()      # everyone's arrays are zeroed before the first remote store
+        torch.cuda.synchronize()
+
+    def forward(self, q8, xscale, sum8, control) -> torch.Tensor:
+        self.signal_launch(self.qweight, self.scales, q8, xscale, sum8, self.my_val, self.my_idx, self.peer_val,
+                           self.peer_idx, self.peer_flag, self.my_flag, self.done_counter, self.step_word, self.half,
+                           control, self.slab.first, self.slab.rows, self.K)
+        self.finish_launch(self.val_ptr, self.idx_ptr, self.half, self.half, self.flags_ptr, self.world, self.step_word,
+                           self.status, control, self.token)
         return self.token

@@ -205,3 +205,47 @@ def test_peer_store_epilogues_write_the_same_values_everywhere(ops):
     for tv, ti in zip(pv, pi):
         assert torch.equal(tv[slots:], v0) and torch.equal(ti[slots:], i0)
         assert not tv[:slots].any() and not ti[:slots].any()
+
+
+def test_completion_signal_protocol_on_one_gpu(ops):
+    """The signalled form with this GPU standing in for its own peers: candidates and the step number go to the
+    local arrays and to two more "peer" arrays; the reduction that waits for the flags finds them set (the
+    producing launch is earlier on the stream, so nothing waits across launches here) and gives the token of
+    the plain fused form, step after step, alternating halves."""
+    from qwen_engine_b200 import synth
+    N, K = 9000, 1536
+    qw, sc = util.to_dev(synth.packed_weights(21, "sig", N, K)), util.to_dev(synth.scales(21, "sig", N, K))
+    slots = ops.sample_slots(N)
+    half = slots
+    mk = lambda: (torch.full((2 * half,), float("nan"), dtype=torch.float32, device="cuda"),
+                  torch.full((2 * half,), -3, dtype=torch.int32, device="cuda"), torch.zeros(3, dtype=torch.int32, device="cuda"))
+    lv, li, lf = mk()
+    peers = [mk() for _ in range(2)]
+    step_word = torch.zeros(1, dtype=torch.int32, device="cuda")
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    c_sig = ops.make_sample_control(0.7, 2024, 0)
+    c_ref = ops.make_sample_control(0.7, 2024, 0)
+    t_sig = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    t_ref = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    rv, ri = _scratch(slots)
+    for step in range(1, 5):
+        q8, xs, s8 = (util.to_dev(t) for t in oracle.quantize_q8_1(synth.activations(30 + step, "sig", K)))
+        ops.gemv_w4a8_sample_candidates_signal(qw, sc, q8, xs, s8, lv.data_ptr(), li.data_ptr(),
+                                               [p[0].data_ptr() for p in peers], [p[1].data_ptr() for p in peers],
+                                               [p[2].data_ptr() + 4 for p in peers], lf.data_ptr() + 4, counter, step_word,
+                                               half, c_sig, 0, N, K)
+        # flags [0] and [2] play ranks whose launches are done as well
+        lf[0] = step; lf[2] = step
+        ops.sample_finish_after_signals(lv.data_ptr(), li.data_ptr(), slots, half, lf.data_ptr(), 3, step_word, status,
+                                        c_sig, t_sig)
+        ops.launch_gemv_w4a8_sample_and_advance(qw, sc, q8, xs, s8, None, rv, ri, c_ref, t_ref, N, K)
+        torch.cuda.synchronize()
+        assert int(step_word.item()) == step and int(counter.item()) == 0 and int(status.item()) == 0
+        assert int(t_sig.item()) == int(t_ref.item())
+        assert ops.read_sample_control(c_sig) == ops.read_sample_control(c_ref)
+        lo = (step & 1) * half
+        assert torch.equal(lv[lo:lo + slots], rv) and torch.equal(li[lo:lo + slots], ri)
+        for pv, pi, pf in peers:
+            assert torch.equal(pv[lo:lo + slots], rv) and torch.equal(pi[lo:lo + slots], ri) and int(pf[1].item()) == step
+        assert int(lf[1].item()) == step
