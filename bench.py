@@ -484,6 +484,57 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
     return out
 
 
+def prefill_big_nsplit(torch, dist, ops, rank, world, stream, steps):
+    """Configuration 4's scaled-up shape: W4A16 prefill GEMM 8192 -> 28672 at 4096 tokens, weight rows split over
+    the ranks, every rank ending with the whole [M][N] output.  Strong scaling; TFLOP/s counts 2*M*N*K once."""
+    from qwen_engine_b200 import nsplit, synth
+    N, K, M = 28672, 8192, int(os.environ.get("W4A16_BENCH_PREFILL_M", "4096"))
+    slab = nsplit.slab_bounds(N, world, rank, 128)
+    qw = torch.from_numpy(synth.packed_weights(13, f"big.r{slab.first}", slab.rows, K).view(np.int32)).cuda()
+    sc = torch.from_numpy(synth.scales(13, f"big.r{slab.first}", slab.rows, K)).cuda()
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.randn((M, K), device="cuda", generator=g).half()
+    launch = lambda w, s_, xx, out, m, rows, k: ops.launch_gemm_prefill_w4a16(w, s_, xx, None, out, m, rows, k)
+    block = lambda w, s_, xx, ptr, ldc, peers, m, rows, k: ops.gemm_prefill_w4a16_block(w, s_, xx, None, ptr, ldc, peers, m, rows, k)
+    flops = 2.0 * M * N * K
+    reps = max(3, min(steps, 10))
+
+    def measure(use_peers):
+        op = nsplit.NSplitGemm(qw, sc, N, K, M, launch, block_launch=block if use_peers else None)
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                y = op.forward(x, M)
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            ms = timed_events(torch, stream, lambda: op.forward(x, M), reps)
+            torch.cuda.synchronize()
+        t = torch.tensor([ms], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t.item()) * 1e3 / reps
+        probe = y[::max(1, M // 7), ::max(1, N // 11)].float().sum().item()
+        return us, probe
+
+    out = {"workload": f"config 4: W4A16 prefill GEMM {K}->{N}, {M} tokens, weight rows split over {world} GPU(s)",
+           "rows_per_gpu": slab.rows, "unit": "TFLOP/s", "scaling": "strong", "timed_as": "eager launches, CUDA events"}
+    us, probe = measure(False)
+    out["nccl_all_gather"] = {"us_per_step": us, "value": flops / (us * 1e-6) / 1e12}
+    best = us
+    if world > 1:
+        try:
+            us_p, probe_p = measure(True)
+            out["peer_store_epilogue"] = {"us_per_step": us_p, "value": flops / (us_p * 1e-6) / 1e12,
+                                          "same_probe_sum": bool(abs(probe_p - probe) <= 1e-3 * max(1.0, abs(probe)))}
+            best = min(best, us_p)
+        except Exception as e:
+            out["peer_store_epilogue"] = {"unavailable": str(e)[:200]}
+    out["us_per_step"] = best
+    out["value"] = flops / (best * 1e-6) / 1e12
+    return out
+
+
 def run_shapes_suite(args):
     """Per-shape table: batch-1 GEMV (Q8_1 in) and the M-token contraction for the four projection shapes
     plus the scaled-up 28672 x 8192 shape.  Each measurement is one CUDA graph that walks `copies`
@@ -733,6 +784,13 @@ def main():
         lm = lm_head_nsplit(torch, dist, ops, rank, world, stream, min(steps, 200), warmup)
         if rank == 0:
             line["lm_head"] = lm
+    if os.environ.get("W4A16_BENCH_PREFILL", "1") == "1":
+        try:
+            pf = prefill_big_nsplit(torch, dist, ops, rank, world, stream, steps)
+        except Exception as e:      # keeps the headline line alive if this extra fails (e.g. memory on a busy GPU)
+            pf = {"unavailable": str(e)[:200]}
+        if rank == 0:
+            line["prefill_big"] = pf
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         ref_cuda = time_reference_cuda(torch, layers_dev, stream, min(steps, 100))
         if ref_cuda:

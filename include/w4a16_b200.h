@@ -307,6 +307,20 @@ W4A16_API int w4a16_gemm_prefill_w4a16(const uint32_t* qweight, const void* scal
                                        const void* residual, void* output_y, int M, int N, int K,
                                        w4a16_stream_t stream, int sm_count);
 
+/*
+ * w4a16_gemm_prefill_w4a16 writing a COLUMN BLOCK of a wider matrix: output_y (and residual) point at the
+ * block's first element inside an [M][ldc] matrix, ldc >= N.  With the weight rows of a large projection
+ * split over the GPUs of a node every rank produces one such block of the full [M][N_total] output; the
+ * block is also stored at up to 7 peer addresses -- its place in every other GPU's matrix, mapped into this
+ * process -- so that the all-gather of the blocks is done by the epilogue's stores over NVLink while other
+ * tiles are still being computed; the caller orders the ranks afterwards.  Peer stores need the tensor-core
+ * form (16-byte aligned weights and activations; W4A16_ERR_SHAPE otherwise).  No reference counterpart.
+ */
+W4A16_API int w4a16_gemm_prefill_w4a16_block(const uint32_t* qweight, const void* scales, const void* input_x,
+                                             const void* residual, void* output_y, int ldc,
+                                             void* const* peer_outputs, int num_peers, int M, int N, int K,
+                                             w4a16_stream_t stream);
+
 /* reference include/kernels.cuh:132-142 launch_gemm_prefill_qkv_w4a16
  * (src/kernels/gemm_prefill.cu:392-489, 642-666). */
 W4A16_API int w4a16_gemm_prefill_qkv_w4a16(const w4a16_qkv_view* view, const void* input_x, int M,

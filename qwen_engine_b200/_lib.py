@@ -96,6 +96,8 @@ SIGNATURES = {
                                                           c_void_p, c_void_p, c_int, c_int, c_void_p],
     "w4a16_gemm_prefill_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
                                  c_int],
+    "w4a16_gemm_prefill_w4a16_block": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, POINTER(c_void_p), c_int,
+                                       c_int, c_int, c_int, c_void_p],
     "w4a16_gemm_prefill_qkv_w4a16": [POINTER(QKVView), c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                      c_int],
     "w4a16_gemm_prefill_dual_gate_up_swiglu_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,

@@ -449,6 +449,28 @@ int w4a16_gemm_prefill_w4a16(const uint32_t* qweight, const void* scales, const 
     return gemm_launch(g, S(stream));
 }
 
+int w4a16_gemm_prefill_w4a16_block(const uint32_t* qweight, const void* scales, const void* input_x,
+                                   const void* residual, void* output_y, int ldc, void* const* peer_outputs,
+                                   int num_peers, int M, int N, int K, w4a16_stream_t stream) {
+    if (!qweight || !scales || !input_x || !output_y || M <= 0 || N <= 0 || ldc < N) return W4A16_ERR_INVALID_ARG;
+    if (num_peers < 0 || num_peers > 7 || (num_peers > 0 && !peer_outputs)) return W4A16_ERR_INVALID_ARG;
+    if (int st = check_k(K)) return st;
+    if (misaligned(qweight, 4) || misaligned(scales, 2) || misaligned(input_x, 16) || misaligned(output_y, 2) ||
+        misaligned(residual, 2))
+        return W4A16_ERR_ALIGNMENT;
+    GemmArgs g = {};
+    g.qweight[0] = qweight; g.scales[0] = H(scales); g.out[0] = H(output_y); g.rows[0] = N;
+    g.x = H(input_x); g.residual = H(residual);
+    g.M = M; g.K = K; g.mode = kPlain; g.ldc = ldc;
+    for (int p = 0; p < num_peers; ++p) {
+        if (!peer_outputs[p]) return W4A16_ERR_INVALID_ARG;
+        if (misaligned(peer_outputs[p], 2)) return W4A16_ERR_ALIGNMENT;
+        g.peer_out[p] = H(peer_outputs[p]);
+    }
+    g.num_peers = num_peers;
+    return gemm_launch(g, S(stream));
+}
+
 int w4a16_gemm_prefill_qkv_w4a16(const w4a16_qkv_view* view, const void* input_x, int M, w4a16_stream_t stream,
                                  int in_features, int num_q_heads, int num_kv_heads, int head_dim, int sm_count) {
     (void)sm_count;

@@ -96,7 +96,8 @@ int gemm_launch(GemmArgs g, cudaStream_t stream) {
     // form stages only two tokens per pass).  The CUDA-core forms also take what TMA cannot address.
     static const int tc_min_m_env = env_int("W4A16_TC_MIN_M", 0);
     const int tc_min_m = tc_min_m_env > 0 ? tc_min_m_env : (g.K > 4096 ? 4 : 5);
-    if (g.M >= tc_min_m && gemm_tc_supported(g)) return gemm_tc_launch(g, dev->sm_count, stream);
+    if ((g.M >= tc_min_m || g.num_peers > 0) && gemm_tc_supported(g)) return gemm_tc_launch(g, dev->sm_count, stream);
+    if (g.num_peers > 0) return W4A16_ERR_SHAPE;   // peer stores exist in the tensor-core form only
 
     SmallMArgs a;
     a.g = g;
@@ -105,7 +106,7 @@ int gemm_launch(GemmArgs g, cudaStream_t stream) {
     if (g.mode == kQkv) {
         a.out_ld[0] = g.rows[0]; a.out_ld[1] = g.rows[1]; a.out_ld[2] = g.rows[2];
     } else {
-        a.out_ld[0] = a.units; a.out_ld[1] = a.out_ld[2] = 0;
+        a.out_ld[0] = (g.mode == kPlain && g.ldc > 0) ? g.ldc : a.units; a.out_ld[1] = a.out_ld[2] = 0;
     }
     // few tokens, 16-byte aligned tensors: the form that streams like the decode GEMV
     static const int v2_on = env_int("W4A16_SMALLM_V2", 1);

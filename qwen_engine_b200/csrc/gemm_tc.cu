@@ -69,6 +69,8 @@ struct TcArgs {
     const __half* residual;
     int M, K, T, stages, tmem_cols;
     int ksplit;              // CTAs (one cluster along grid z) that share the K range of one output tile
+    __half* peer_out[7];     // PLAIN: the output block's place in other GPUs' matrices
+    int num_peers;
 };
 
 // ---- PTX wrappers ------------------------------------------------------------------------
@@ -414,6 +416,9 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
                                 if (a.residual != nullptr) y = __hadd(y, a.residual[static_cast<size_t>(m) * ld + n]);
                             }
                             out[static_cast<size_t>(m) * ld + n] = y;
+                            if constexpr (MODE == kPlain) {
+                                for (int p = 0; p < a.num_peers; ++p) a.peer_out[p][static_cast<size_t>(m) * ld + n] = y;
+                            }
                         }
                     }
                 }
@@ -625,10 +630,13 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
         a.tiles[t] = (a.rows[t] + kTileRows - 1) / kTileRows;
         total_tiles += a.tiles[t];
         a.out_ld[t] = g.mode == kSwiglu ? g.rows[0] / 2 : a.rows[t];
+        if (g.mode == kPlain && t == 0 && g.ldc > 0) a.out_ld[0] = g.ldc;
     }
     a.residual = g.residual;
     a.M = g.M;
     a.K = g.K;
+    a.num_peers = g.mode == kPlain ? g.num_peers : 0;
+    for (int p = 0; p < 7; ++p) a.peer_out[p] = p < a.num_peers ? g.peer_out[p] : nullptr;
     // tokens per tile: the smallest power of two >= M (16..256); halve it while the grid is thin
     int T = 16;
     while (T < g.M && T < 256) T *= 2;

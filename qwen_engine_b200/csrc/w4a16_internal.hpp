@@ -147,6 +147,13 @@ struct GemmArgs {
     int M;
     int K;
     int mode;  // GemvMode values
+    // PLAIN only: row stride of out[0] / residual in elements (0 = rows[0]): a column block of a wider [M][ldc]
+    // matrix, e.g. one rank's slice of an output split by weight rows over several GPUs
+    int ldc;
+    // PLAIN only, tensor-core form: the same block is also stored at these addresses (its place in every peer
+    // GPU's [M][ldc] matrix, mapped into this process; plain stores over NVLink)
+    __half* peer_out[7];
+    int num_peers;
 };
 int gemm_launch(GemmArgs args, cudaStream_t stream);
 int gemm_set_attributes();

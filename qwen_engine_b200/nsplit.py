@@ -232,3 +232,69 @@ class NSplitSignalSampler:
         self.finish_launch(self.val_ptr, self.idx_ptr, self.half, self.half, self.flags_ptr, self.world, self.step_word,
                            self.status, control, self.token)
         return self.token
+
+
+class NSplitGemm:
+    """Y[M][N] = X[M][K] . W^T for M tokens, the weight rows (output columns) split over the ranks; every rank
+    ends with the whole Y.  Slabs are aligned to the tensor-core tile (128 rows).
+
+    launch(qweight_slab, scales_slab, x, out, M, rows, K): the local contraction into a contiguous [M][rows]
+    block (launch_gemm_prefill_w4a16 of this package); the blocks are all-gathered (NCCL) and put side by side.
+    block_launch (optional, GPUs with peer access): launch(qw, sc, x, out_ptr, ldc, peer_ptrs, M, rows, K) writing the
+    block into its columns of an [M][ldc] matrix here AND in every peer's copy of it (symmetric memory); the
+    gather is then done by the epilogue's stores while other tiles are still being computed, and a barrier
+    follows.
+    """
+
+    def __init__(self, qweight_slab: torch.Tensor, scales_slab: torch.Tensor, n_rows: int, in_features: int,
+                 max_tokens: int, launch, group=None, block_launch=None, align: int = 128):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.n_rows, self.K, self.max_tokens = n_rows, in_features, max_tokens
+        self.slab = slab_bounds(n_rows, self.world, self.rank, align)
+        if qweight_slab.shape[0] != self.slab.rows or scales_slab.shape[0] != self.slab.rows:
+            raise ValueError(f"rank {self.rank} expects a slab of {self.slab.rows} rows")
+        self.qweight, self.scales, self.launch = qweight_slab, scales_slab, launch
+        self.block_launch = block_launch if self.world > 1 else None
+        dev = qweight_slab.device
+        self.ld = self.world * self.slab.stride              # columns of the gathered matrix (padded)
+        self.symm = None
+        if self.block_launch is not None:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.full = symm_mem.empty(max_tokens * self.ld, dtype=torch.float16, device=dev)
+            self.symm = symm_mem.rendezvous(self.full, group=group if group is not None else dist.group.WORLD)
+            off = self.slab.first * 2
+            self.my_ptr = int(self.symm.buffer_ptrs[self.rank]) + off
+            self.peer_ptrs = [int(self.symm.buffer_ptrs[r]) + off for r in range(self.world) if r != self.rank]
+        else:
+            self.local = torch.empty(max_tokens * self.slab.stride, dtype=torch.float16, device=dev)
+            self.gathered = torch.empty(self.world * max_tokens * self.slab.stride, dtype=torch.float16, device=dev)
+
+    def forward(self, x: torch.Tensor, M: int) -> torch.Tensor:
+        """x: fp16 [M][K]; returns fp16 [M][n_rows]."""
+        if M > self.max_tokens:
+            raise ValueError("more tokens than the buffers were sized for")
+        s = self.slab
+        if self.block_launch is not None:
+            if s.rows == 0:
+                raise ValueError("the peer-store form needs rows on every rank")
+            self.block_launch(self.qweight, self.scales, x, self.my_ptr, self.ld, self.peer_ptrs, M, s.rows, self.K)
+            self.symm.barrier()
+            return self.full[:M * self.ld].view(M, self.ld)[:, :self.n_rows]
+        mine = self.local[:M * s.stride].view(M, s.stride)
+        if s.rows > 0:
+            block = mine if s.rows == s.stride else self.local[:M * s.rows].view(M, s.rows)
+            self.launch(self.qweight, self.scales, x, block, M, s.rows, self.K)
+            if s.rows != s.stride:        # ragged last slab: widen to the common stride
+                widened = torch.zeros((M, s.stride), dtype=torch.float16, device=x.device)
+                widened[:, :s.rows] = block
+                mine = widened
+        else:
+            mine = torch.zeros((M, s.stride), dtype=torch.float16, device=x.device)
+        if self.world == 1:
+            return mine[:, :self.n_rows]
+        gathered = self.gathered[:self.world * M * s.stride]
+        dist.all_gather_into_tensor(gathered, mine.contiguous().view(-1), group=self.group)
+        # [rank][M][stride] -> [M][rank * stride]
+        return gathered.view(self.world, M, s.stride).permute(1, 0, 2).reshape(M, self.ld)[:, :self.n_rows]

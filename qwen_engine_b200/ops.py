@@ -23,7 +23,7 @@ __all__ = [
     "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
     "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots", "DecodeSweep",
     "launch_gemv_rmsnorm_w4a16", "launch_gemv_qkv_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1",
-    "gemv_w4a8_peers", "make_sample_control", "launch_embed_lookup_w4a16", "read_sample_control", "launch_sample_and_advance", "sample_slots", "launch_gemv_w4a8_sample_candidates", "launch_sample_finish", "gemv_w4a8_sample_candidates_peers", "gemv_w4a8_sample_candidates_signal", "sample_finish_after_signals", "launch_gemv_w4a8_sample_and_advance", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_QUANT_IN_GATE_UP", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
+    "gemv_w4a8_peers", "gemm_prefill_w4a16_block", "make_sample_control", "launch_embed_lookup_w4a16", "read_sample_control", "launch_sample_and_advance", "sample_slots", "launch_gemv_w4a8_sample_candidates", "launch_sample_finish", "gemv_w4a8_sample_candidates_peers", "gemv_w4a8_sample_candidates_signal", "sample_finish_after_signals", "launch_gemv_w4a8_sample_and_advance", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_QUANT_IN_GATE_UP", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
 ]
 
 # Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
@@ -282,6 +282,15 @@ def launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1(gate_up_qweight, gate_up_
               _ptr(gate_up_qweight), _ptr(gate_up_scales), _ptr(input_x), _ptr(gamma), _ptr(output_mlp),
               _ptr(output_q8), _ptr(output_scale), _ptr(output_sum8), hidden_size, intermediate_size,
               _stream(stream)))
+
+
+def gemm_prefill_w4a16_block(qweight, scales, input_x, residual_ptr, output_ptr, ldc, peer_ptrs, M, N, K, stream=None):
+    """launch_gemm_prefill_w4a16 into a column block of an [M][ldc] matrix (addresses as integers), also stored
+    at `peer_ptrs` (the block's place in peer GPUs' matrices)."""
+    arr = (ctypes.c_void_p * max(1, len(peer_ptrs)))(*peer_ptrs)
+    check("w4a16_gemm_prefill_w4a16_block", load().w4a16_gemm_prefill_w4a16_block(
+        _ptr(qweight), _ptr(scales), _ptr(input_x), residual_ptr, output_ptr, ldc, arr, len(peer_ptrs), M, N, K,
+        _stream(stream)))
 
 
 def launch_gemm_prefill_w4a16(qweight, scales, input_x, residual, output_y, M, N, K, stream=None, sm_count=0):

@@ -117,3 +117,31 @@ def test_tensor_core_kernel_never_gave_up_waiting(ops):
     """Every wait in the tcgen05 kernel is bounded; a wait that ran out is counted on the device.
     Collected after the GEMM cases above: the count must still be zero."""
     assert ops.debug_counter(0) == 0
+
+
+@pytest.mark.parametrize("M,N,K,ldc,col", [(40, 256, 512, 1024, 384), (200, 384, 1536, 384, 0), (3, 128, 256, 512, 128)])
+def test_gemm_into_a_column_block_with_peer_copies(ops, M, N, K, ldc, col):
+    """The contraction written as a column block of a wider [M][ldc] matrix (one rank's share of an output split
+    by weight rows), and the same block stored into two more matrices standing in for peer GPUs' memory."""
+    qw, sc, x = _inputs(M + N + K, M, N, K)
+    d_qw, d_sc, d_x = util.to_dev(qw), util.to_dev(sc), util.to_dev(x)
+    ref = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    ops.launch_gemm_prefill_w4a16(d_qw, d_sc, d_x, None, ref, M, N, K)
+    full = torch.full((M, ldc), 7.0, dtype=torch.float16, device="cuda")
+    peers = [torch.full((M, ldc), 7.0, dtype=torch.float16, device="cuda") for _ in range(2)]
+    ops.gemm_prefill_w4a16_block(d_qw, d_sc, d_x, None, full.data_ptr() + 2 * col, ldc,
+                                 [p.data_ptr() + 2 * col for p in peers], M, N, K)
+    torch.cuda.synchronize()
+    for t in [full] + peers:
+        if M >= 5:      # same kernel as the reference launch: same bits
+            assert torch.equal(t[:, col:col + N], ref)
+        else:           # peer stores force the tensor-core form where the plain launch takes the few-token form
+            util.assert_fp16_close(util.to_np(t[:, col:col + N].contiguous()), util.to_np(ref).astype(np.float64), what="block")
+        untouched = torch.ones(ldc, dtype=torch.bool, device="cuda")
+        untouched[col:col + N] = False
+        assert bool((t[:, untouched] == 7.0).all())
+    # without peers a few tokens go through the CUDA-core form, which honours the row stride as well
+    alone = torch.full((M, ldc), 7.0, dtype=torch.float16, device="cuda")
+    ops.gemm_prefill_w4a16_block(d_qw, d_sc, d_x, None, alone.data_ptr() + 2 * col, ldc, [], M, N, K)
+    torch.cuda.synchronize()
+    assert torch.equal(alone[:, col:col + N], ref)

@@ -137,3 +137,45 @@ def test_two_rank_gloo_split_sampler_picks_the_unsplit_token(n_rows, temperature
         got = dict(ret)
         assert got[0] == got[1]                      # every rank ends with the same token
         assert got[0][0] == got[0][1] and got[0][2] == 4
+
+
+# ---- M-token contraction split by weight rows: column blocks gathered side by side ----
+
+def _oracle_gemm_launch(qw, sc, x, out, M, rows, K):
+    _, y16 = oracle.gemm_prefill(qw.numpy().view(np.uint32), sc.numpy(), x.numpy(), np.arange(M, dtype=np.int32),
+                                 np.arange(rows, dtype=np.int32))
+    out.copy_(torch.from_numpy(y16))
+
+
+def _gemm_worker(rank, world, port, n_rows, K, M, ret):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        qw = synth.packed_weights(7, "nsg", n_rows, K)
+        sc = synth.scales(7, "nsg", n_rows, K)
+        x = synth.activations(7, "nsg.x", M, K)
+        slab = nsplit.slab_bounds(n_rows, world, rank, 128)
+        w_slab = torch.from_numpy(qw[slab.first:slab.first + slab.rows].view(np.int32).copy())
+        s_slab = torch.from_numpy(sc[slab.first:slab.first + slab.rows].copy())
+        op = nsplit.NSplitGemm(w_slab, s_slab, n_rows, K, 8, _oracle_gemm_launch)
+        y = op.forward(torch.from_numpy(x), M)
+        _, full = oracle.gemm_prefill(qw, sc, x, np.arange(M, dtype=np.int32), np.arange(n_rows, dtype=np.int32))
+        ret[rank] = bool(y.shape == (M, n_rows) and np.array_equal(y.contiguous().numpy().view(np.uint16), full.view(np.uint16)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n_rows", [512, 300])     # two full slabs; a ragged second slab (256 + 44)
+def test_two_rank_gloo_split_gemm_equals_unsplit(n_rows):
+    world, K, M = 2, 256, 5
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = _free_port()
+        procs = [ctx.Process(target=_gemm_worker, args=(r, world, port, n_rows, K, M, ret)) for r in range(world)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(timeout=120)
+            assert p.exitcode == 0
+        assert dict(ret) == {0: True, 1: True}
