@@ -56,6 +56,8 @@ constexpr int kRawStages = 3;
 constexpr int kRawBytes = kTileRows * 128;   // 128 rows x 128 bytes of packed nibbles = 256 k
 constexpr int kABytes = kTileRows * 128;     // 128 rows x 64 fp16
 constexpr int kMaxStages = 8;
+constexpr int kMaxIssuers = 2;          // warps that may issue tensor-core instructions (k-blocks dealt round robin;
+                                        // measured: a third and fourth bring nothing)
 constexpr unsigned kWaitLimit = 1u << 22;
 
 struct TcArgs {
@@ -69,6 +71,7 @@ struct TcArgs {
     const __half* residual;
     int M, K, T, stages, tmem_cols;
     int ksplit;              // CTAs (one cluster along grid z) that share the K range of one output tile
+    int issuers;             // 1 or 2 warps issuing the tensor-core instructions (even / odd k-blocks, own accumulators)
     __half* peer_out[7];     // PLAIN: the output block's place in other GPUs' matrices
     int num_peers;
 };
@@ -179,6 +182,14 @@ __device__ __forceinline__ void st_shared_cluster_u32(uint32_t addr, uint32_t v)
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// v += the 16 columns at taddr (another issuing warp's accumulator).
+__device__ __forceinline__ void add_second_accumulator(uint32_t taddr, uint32_t (&v)[16]) {
+    uint32_t u[16];
+    tmem_ld16(taddr, u);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + __uint_as_float(u[j]));
+}
 
 // Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 B apart, 8-row groups
 // 1024 B apart (stride byte offset), descriptor version 1 (sm_100).  `addr` may be advanced by
@@ -207,7 +218,7 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 }
 
 template <int MODE, int NG>
-__global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(const __grid_constant__ TcArgs a) {
+__global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16_tc_kernel(const __grid_constant__ TcArgs a) {
     constexpr int kDqWarps = 4 * NG;             // dequantising warps: NG groups of 4
     constexpr int kDqThreads = kDqWarps * 32;
     extern __shared__ uint8_t smem_raw_base[];
@@ -259,7 +270,7 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
     if (tid == 0) {
         for (int i = 0; i < kRawStages; ++i) { mbar_init(raw_full(i), 1); mbar_init(raw_empty(i), kDqWarps); }
         for (int i = 0; i < S; ++i) { mbar_init(full(i), 4 + 1); mbar_init(ab_empty(i), 1); }   // 4 warps + the TMA thread
-        mbar_init(accum_full, 1);
+        mbar_init(accum_full, a.issuers);   // every issuing warp commits once at its end (a K range holds >= 4 k-blocks)
         *s_abort = 0;
         fence_barrier_init();
         tma_prefetch_desc(&a.tmap_x);
@@ -369,6 +380,7 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
                     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
                     tmem_ld16(lane_base + static_cast<uint32_t>(c0), v);
                     tmem_ld_wait();
+                    for (int w = 1; w < a.issuers; ++w) add_second_accumulator(lane_base + static_cast<uint32_t>(w * T + c0), v);
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         st_shared_cluster_u32(remote0 + 4u * static_cast<uint32_t>(((krank - 1) * T + c0 + j) * kTileRows + r), v[j]);
@@ -388,6 +400,7 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
                 const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
                 tmem_ld16(lane_base + static_cast<uint32_t>(c0), v);
                 tmem_ld_wait();
+                for (int w = 1; w < a.issuers; ++w) add_second_accumulator(lane_base + static_cast<uint32_t>(w * T + c0), v);
 
                 TC_TL(28);
                 // the other CTAs' partial sums, slice after slice (16 independent loads in flight each)
@@ -424,59 +437,59 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
                 }
             }
         }
-    } else if (warp == kDqWarps) {
+    } else if (warp >= kDqWarps && warp < kDqWarps + kMaxIssuers) {
         // ---------------- MMA issue ----------------
-        // The whole warp walks the loop with warp-uniform values (so descriptors and ring positions can
-        // live in uniform registers); one elected lane issues the tensor-core instructions.  The
-        // instruction stream of this warp is the critical path of a k-block, hence: descriptors are
-        // advanced by plain adds on their low word (the start-address field counts 16-byte units and
-        // cannot carry out of its 14 bits for shared-memory addresses), ring positions by
-        // compare-and-reset, and the barrier of the NEXT k-block is tested before this k-block's MMAs
-        // are issued so that the test's latency overlaps the issue.
-        {
+        // Issuing a tensor-core instruction costs its thread a fixed time however small the instruction, and
+        // with few tokens that time, not the tensor pipe, bounds a k-block.  Two warps can therefore
+        // issue: warp w takes the k-blocks w, w + n, ..., each into its OWN accumulator (TMEM columns
+        // [w T, (w + 1) T)) so that no order between the instruction streams is needed; the epilogue adds them.  The whole warp walks the loop with warp-uniform values; one lane issues.  The barrier
+        // of the warp's NEXT k-block is tested before this k-block's MMAs are issued so that the test's
+        // latency overlaps the issue.
+        const int w = warp - kDqWarps, nw = a.issuers;
+        if (w < nw) {
             const uint32_t idesc = make_idesc(T);
             const uint64_t a_desc0 = make_smem_desc(smem_u32(s_a));
             const uint64_t b_desc0 = make_smem_desc(smem_u32(s_b));
             const uint32_t a_step = kABytes >> 4, b_step = static_cast<uint32_t>(b_bytes) >> 4;
-            uint64_t a_desc = a_desc0, b_desc = b_desc0;
-            int s = 0;
-            uint32_t ph = 0;
+            const uint32_t tmem_acc = tmem_base + static_cast<uint32_t>(w * T);
+            int s = w % S;
+            uint32_t ph = static_cast<uint32_t>(w / S) & 1u;
             bool ok = true;
             TC_PROF_DECL(p_wait); TC_PROF_DECL(p_mma); TC_PROF_DECL(p_commit); TC_PROF_DECL(p_test);
-            bool ready = mbar_test_wait(full(0), 0);
+            bool ready = false;
+            uint64_t a_desc = a_desc0 + static_cast<uint32_t>(s) * a_step, b_desc = b_desc0 + static_cast<uint32_t>(s) * b_step;
             [[maybe_unused]] long long loop_t0 = TC_PROF_T();
-            for (int kb = 0; kb < num_kb; ++kb) {
+            for (int kb = w; kb < num_kb; kb += nw) {
                 [[maybe_unused]] long long c0 = TC_PROF_T();
                 if (!ready) ok = warp_wait(full(s), ph, s_abort, lane);
                 TC_PROF_ADD(p_wait, c0);
                 if (!ok) break;
-                // position of the next k-block, and an early look at its barrier
-                int sn = s + 1;
+                // position of this warp's next k-block, and an early look at its barrier
+                int sn = s + nw;
                 uint32_t phn = ph;
-                if (sn == S) { sn = 0; phn ^= 1; }
+                while (sn >= S) { sn -= S; phn ^= 1; }
                 [[maybe_unused]] long long c1 = TC_PROF_T();
                 if (lane == 0) {
 #pragma unroll
                     for (int ks = 0; ks < kBK / 16; ++ks)
-                        tc_mma_f16(tmem_base, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
+                        tc_mma_f16(tmem_acc, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb >= nw || ks != 0) ? 1u : 0u);
                     TC_PROF_ADD(p_mma, c1);
                     [[maybe_unused]] long long c2 = TC_PROF_T();
                     tc_commit(ab_empty(s));    // frees the stage when these MMAs have read it
                     TC_PROF_ADD(p_commit, c2);
                 }
                 [[maybe_unused]] long long c3 = TC_PROF_T();
-                ready = (kb + 1 < num_kb) ? mbar_test_wait(full(sn), phn) : true;
+                ready = (kb + nw < num_kb) ? mbar_test_wait(full(sn), phn) : true;
                 ready = __all_sync(0xFFFFFFFFu, ready);
                 TC_PROF_ADD(p_test, c3);
-                a_desc += a_step;
-                b_desc += b_step;
-                if (sn == 0) { a_desc = a_desc0; b_desc = b_desc0; }
                 s = sn;
                 ph = phn;
+                a_desc = a_desc0 + static_cast<uint32_t>(s) * a_step;   // off the critical path: after the issue
+                b_desc = b_desc0 + static_cast<uint32_t>(s) * b_step;
             }
             if (ok && lane == 0) tc_commit(accum_full);
 #ifdef W4A16_TC_PROFILE
-            if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) {
+            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && w == 0) {
                 g_tc_prof[0] = p_wait; g_tc_prof[1] = p_mma; g_tc_prof[2] = p_commit; g_tc_prof[3] = num_kb;
                 g_tc_prof[16] = clock64() - loop_t0; g_tc_prof[19] = p_test;
             }
@@ -484,7 +497,7 @@ __global__ void __launch_bounds__((4 * NG + 3) * 32, 1) gemm_w4a16_tc_kernel(con
         }
         __syncwarp();
         if (ksplit > 1) { cluster_sync_all(); cluster_sync_all(); }
-    } else if (warp == kDqWarps + 1) {
+    } else if (warp == kDqWarps + kMaxIssuers) {
         // ---------------- TMA: token tiles ----------------
         if (lane == 0) {
             int s = 0;
@@ -583,7 +596,7 @@ cudaError_t raise_tc_smem_modes() {
 }
 template <int NG>
 cudaError_t launch_tc(int mode, dim3 grid, size_t smem, cudaStream_t stream, const TcArgs& a) {
-    const dim3 block((4 * NG + 3) * 32);
+    const dim3 block((4 * NG + kMaxIssuers + 2) * 32);
     const dim3 cluster(1, 1, static_cast<unsigned>(a.ksplit));   // the K slices of one output tile
     switch (mode) {
         case kPlain:
@@ -638,8 +651,9 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     a.num_peers = g.mode == kPlain ? g.num_peers : 0;
     for (int p = 0; p < 7; ++p) a.peer_out[p] = p < a.num_peers ? g.peer_out[p] : nullptr;
     // tokens per tile: the smallest power of two >= M (16..256); halve it while the grid is thin
+    static const int max_t = std::max(16, std::min(256, env_int("W4A16_TC_MAX_T", 256)));
     int T = 16;
-    while (T < g.M && T < 256) T *= 2;
+    while (T < g.M && T < max_t) T *= 2;
     while (T > 64 && total_tiles * ((g.M + T - 1) / T) < sm_count) T /= 2;
     static const int stages_env = env_int("W4A16_TC_STAGES", 0);
     int S = stages_env > 0 ? std::min(stages_env, kMaxStages) : kMaxStages;
@@ -647,7 +661,15 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     if (tc_smem_bytes(T, S, g.K) > 227 * 1024) return W4A16_ERR_TOO_LARGE;
     a.T = T;
     a.stages = S;
-    a.tmem_cols = T < 32 ? 32 : T;
+    // two issuing warps for token tiles of at most 128 (measured: gate_up at 16 tokens 18.3 -> 14.3 us, down at 128
+    // tokens 39.0 -> 30.5 us; at 256 tokens the tensor pipe, not the issue, paces the loop and one warp is as fast);
+    // each has its own accumulator, so the column count doubles
+    static const int issuers_env = env_int("W4A16_TC_ISSUERS", 0);
+    a.issuers = issuers_env >= 1 && issuers_env <= kMaxIssuers ? issuers_env : (T <= 128 ? 2 : 1);
+    while (a.issuers > 1 && a.issuers * T > 512) --a.issuers;
+    int cols = 32;
+    while (cols < a.issuers * T) cols *= 2;
+    a.tmem_cols = cols;
     // Split K over a cluster when the output tiles alone leave most SMs idle (decode batches on the per-layer
     // shapes): each tensor-core instruction costs its issuing thread a fixed time however few tokens it
     // carries, so a thin grid is bound by K / 16 instructions in a row per CTA.  Up to 8 CTAs (the portable
