@@ -217,10 +217,13 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
     return __shfl_sync(0xFFFFFFFFu, ok, 0) != 0;
 }
 
-template <int MODE, int NG>
+// EXTRAS = false is the plain form (one issuing warp, no K split, no peer stores): those options cost the
+// prefill shapes 5-18 % when they are runtime branches in the epilogue, so they are compiled out there.
+template <int MODE, int NG, bool EXTRAS>
 __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16_tc_kernel(const __grid_constant__ TcArgs a) {
     constexpr int kDqWarps = 4 * NG;             // dequantising warps: NG groups of 4
     constexpr int kDqThreads = kDqWarps * 32;
+    constexpr int kIssuerWarps = EXTRAS ? kMaxIssuers : 1;   // then one warp for the token TMA, one for the weight TMA
     extern __shared__ uint8_t smem_raw_base[];
     // 1024-byte alignment for the swizzled tiles
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_base) + 1023) & ~uintptr_t(1023));
@@ -261,7 +264,8 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
     const int m0 = blockIdx.y * T;           // first token
     const int rows_t = a.rows[t];
     // K range of this CTA: whole 256-element super-blocks, spread over the cluster as evenly as they go
-    const int ksplit = a.ksplit, krank = blockIdx.z;
+    const int ksplit = EXTRAS ? a.ksplit : 1, krank = EXTRAS ? static_cast<int>(blockIdx.z) : 0;
+    const int issuers = EXTRAS ? a.issuers : 1, num_peers = EXTRAS ? a.num_peers : 0;
     const int total_sb = K / 256;
     const int sb_begin = krank * (total_sb / ksplit) + min(krank, total_sb % ksplit);
     const int num_sb = total_sb / ksplit + (krank < total_sb % ksplit ? 1 : 0);
@@ -270,7 +274,7 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
     if (tid == 0) {
         for (int i = 0; i < kRawStages; ++i) { mbar_init(raw_full(i), 1); mbar_init(raw_empty(i), kDqWarps); }
         for (int i = 0; i < S; ++i) { mbar_init(full(i), 4 + 1); mbar_init(ab_empty(i), 1); }   // 4 warps + the TMA thread
-        mbar_init(accum_full, a.issuers);   // every issuing warp commits once at its end (a K range holds >= 4 k-blocks)
+        mbar_init(accum_full, issuers);   // every issuing warp commits once at its end (a K range holds >= 4 k-blocks)
         *s_abort = 0;
         fence_barrier_init();
         tma_prefetch_desc(&a.tmap_x);
@@ -380,7 +384,7 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
                     const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
                     tmem_ld16(lane_base + static_cast<uint32_t>(c0), v);
                     tmem_ld_wait();
-                    for (int w = 1; w < a.issuers; ++w) add_second_accumulator(lane_base + static_cast<uint32_t>(w * T + c0), v);
+                    for (int w = 1; w < issuers; ++w) add_second_accumulator(lane_base + static_cast<uint32_t>(w * T + c0), v);
 #pragma unroll
                     for (int j = 0; j < 16; ++j)
                         st_shared_cluster_u32(remote0 + 4u * static_cast<uint32_t>(((krank - 1) * T + c0 + j) * kTileRows + r), v[j]);
@@ -400,7 +404,7 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
                 const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
                 tmem_ld16(lane_base + static_cast<uint32_t>(c0), v);
                 tmem_ld_wait();
-                for (int w = 1; w < a.issuers; ++w) add_second_accumulator(lane_base + static_cast<uint32_t>(w * T + c0), v);
+                for (int w = 1; w < issuers; ++w) add_second_accumulator(lane_base + static_cast<uint32_t>(w * T + c0), v);
 
                 TC_TL(28);
                 // the other CTAs' partial sums, slice after slice (16 independent loads in flight each)
@@ -430,14 +434,14 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
                             }
                             out[static_cast<size_t>(m) * ld + n] = y;
                             if constexpr (MODE == kPlain) {
-                                for (int p = 0; p < a.num_peers; ++p) a.peer_out[p][static_cast<size_t>(m) * ld + n] = y;
+                                for (int p = 0; p < num_peers; ++p) a.peer_out[p][static_cast<size_t>(m) * ld + n] = y;
                             }
                         }
                     }
                 }
             }
         }
-    } else if (warp >= kDqWarps && warp < kDqWarps + kMaxIssuers) {
+    } else if (warp >= kDqWarps && warp < kDqWarps + kIssuerWarps) {
         // ---------------- MMA issue ----------------
         // Issuing a tensor-core instruction costs its thread a fixed time however small the instruction, and
         // with few tokens that time, not the tensor pipe, bounds a k-block.  Two warps can therefore
@@ -445,8 +449,59 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
         // [w T, (w + 1) T)) so that no order between the instruction streams is needed; the epilogue adds them.  The whole warp walks the loop with warp-uniform values; one lane issues.  The barrier
         // of the warp's NEXT k-block is tested before this k-block's MMAs are issued so that the test's
         // latency overlaps the issue.
-        const int w = warp - kDqWarps, nw = a.issuers;
-        if (w < nw) {
+        const int w = warp - kDqWarps, nw = issuers;
+        if constexpr (!EXTRAS) {
+            // one issuing warp, the whole K range: ring positions by compare-and-reset, descriptors by plain adds
+        {
+            const uint32_t idesc = make_idesc(T);
+            const uint64_t a_desc0 = make_smem_desc(smem_u32(s_a));
+            const uint64_t b_desc0 = make_smem_desc(smem_u32(s_b));
+            const uint32_t a_step = kABytes >> 4, b_step = static_cast<uint32_t>(b_bytes) >> 4;
+            uint64_t a_desc = a_desc0, b_desc = b_desc0;
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            TC_PROF_DECL(p_wait); TC_PROF_DECL(p_mma); TC_PROF_DECL(p_commit); TC_PROF_DECL(p_test);
+            bool ready = mbar_test_wait(full(0), 0);
+            [[maybe_unused]] long long loop_t0 = TC_PROF_T();
+            for (int kb = 0; kb < num_kb; ++kb) {
+                [[maybe_unused]] long long c0 = TC_PROF_T();
+                if (!ready) ok = warp_wait(full(s), ph, s_abort, lane);
+                TC_PROF_ADD(p_wait, c0);
+                if (!ok) break;
+                // position of the next k-block, and an early look at its barrier
+                int sn = s + 1;
+                uint32_t phn = ph;
+                if (sn == S) { sn = 0; phn ^= 1; }
+                [[maybe_unused]] long long c1 = TC_PROF_T();
+                if (lane == 0) {
+#pragma unroll
+                    for (int ks = 0; ks < kBK / 16; ++ks)
+                        tc_mma_f16(tmem_base, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
+                    TC_PROF_ADD(p_mma, c1);
+                    [[maybe_unused]] long long c2 = TC_PROF_T();
+                    tc_commit(ab_empty(s));    // frees the stage when these MMAs have read it
+                    TC_PROF_ADD(p_commit, c2);
+                }
+                [[maybe_unused]] long long c3 = TC_PROF_T();
+                ready = (kb + 1 < num_kb) ? mbar_test_wait(full(sn), phn) : true;
+                ready = __all_sync(0xFFFFFFFFu, ready);
+                TC_PROF_ADD(p_test, c3);
+                a_desc += a_step;
+                b_desc += b_step;
+                if (sn == 0) { a_desc = a_desc0; b_desc = b_desc0; }
+                s = sn;
+                ph = phn;
+            }
+            if (ok && lane == 0) tc_commit(accum_full);
+#ifdef W4A16_TC_PROFILE
+            if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) {
+                g_tc_prof[0] = p_wait; g_tc_prof[1] = p_mma; g_tc_prof[2] = p_commit; g_tc_prof[3] = num_kb;
+                g_tc_prof[16] = clock64() - loop_t0; g_tc_prof[19] = p_test;
+            }
+#endif
+        }
+        } else if (w < nw) {
             const uint32_t idesc = make_idesc(T);
             const uint64_t a_desc0 = make_smem_desc(smem_u32(s_a));
             const uint64_t b_desc0 = make_smem_desc(smem_u32(s_b));
@@ -456,7 +511,7 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
             uint32_t ph = static_cast<uint32_t>(w / S) & 1u;
             bool ok = true;
             TC_PROF_DECL(p_wait); TC_PROF_DECL(p_mma); TC_PROF_DECL(p_commit); TC_PROF_DECL(p_test);
-            bool ready = false;
+            bool ready = __all_sync(0xFFFFFFFFu, mbar_test_wait(full(s), ph));
             uint64_t a_desc = a_desc0 + static_cast<uint32_t>(s) * a_step, b_desc = b_desc0 + static_cast<uint32_t>(s) * b_step;
             [[maybe_unused]] long long loop_t0 = TC_PROF_T();
             for (int kb = w; kb < num_kb; kb += nw) {
@@ -482,10 +537,12 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
                 ready = (kb + nw < num_kb) ? mbar_test_wait(full(sn), phn) : true;
                 ready = __all_sync(0xFFFFFFFFu, ready);
                 TC_PROF_ADD(p_test, c3);
+                // descriptors by plain adds on their low word (the start-address field counts 16-byte units and
+                // cannot carry out of its 14 bits for shared-memory addresses), recomputed when the ring wraps
+                if (sn > s) { a_desc += static_cast<uint32_t>(nw) * a_step; b_desc += static_cast<uint32_t>(nw) * b_step; }
+                else { a_desc = a_desc0 + static_cast<uint32_t>(sn) * a_step; b_desc = b_desc0 + static_cast<uint32_t>(sn) * b_step; }
                 s = sn;
                 ph = phn;
-                a_desc = a_desc0 + static_cast<uint32_t>(s) * a_step;   // off the critical path: after the issue
-                b_desc = b_desc0 + static_cast<uint32_t>(s) * b_step;
             }
             if (ok && lane == 0) tc_commit(accum_full);
 #ifdef W4A16_TC_PROFILE
@@ -497,7 +554,7 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
         }
         __syncwarp();
         if (ksplit > 1) { cluster_sync_all(); cluster_sync_all(); }
-    } else if (warp == kDqWarps + kMaxIssuers) {
+    } else if (warp == kDqWarps + kIssuerWarps) {
         // ---------------- TMA: token tiles ----------------
         if (lane == 0) {
             int s = 0;
@@ -585,7 +642,10 @@ size_t tc_smem_bytes(int T, int S, int K) {
 namespace {
 template <int MODE, int NG>
 cudaError_t raise_tc_smem() {
-    return cudaFuncSetAttribute(gemm_w4a16_tc_kernel<MODE, NG>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_tc_kernel<MODE, NG, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_w4a16_tc_kernel<MODE, NG, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    return e;
 }
 template <int NG>
 cudaError_t raise_tc_smem_modes() {
@@ -596,19 +656,17 @@ cudaError_t raise_tc_smem_modes() {
 }
 template <int NG>
 cudaError_t launch_tc(int mode, dim3 grid, size_t smem, cudaStream_t stream, const TcArgs& a) {
-    const dim3 block((4 * NG + kMaxIssuers + 2) * 32);
     const dim3 cluster(1, 1, static_cast<unsigned>(a.ksplit));   // the K slices of one output tile
+    const bool extras = a.ksplit > 1 || a.issuers > 1 || a.num_peers > 0;
+    const dim3 block((4 * NG + (extras ? kMaxIssuers : 1) + 2) * 32);
+    const bool pdl = pdl_enabled();
+#define W4_TC_LAUNCH(M_, X_) launch_kernel_cluster(gemm_w4a16_tc_kernel<M_, NG, X_>, grid, block, smem, stream, pdl, cluster, a)
     switch (mode) {
-        case kPlain:
-            return launch_kernel_cluster(gemm_w4a16_tc_kernel<kPlain, NG>, grid, block, smem, stream, pdl_enabled(),
-                                         cluster, a);
-        case kQkv:
-            return launch_kernel_cluster(gemm_w4a16_tc_kernel<kQkv, NG>, grid, block, smem, stream, pdl_enabled(),
-                                         cluster, a);
-        default:
-            return launch_kernel_cluster(gemm_w4a16_tc_kernel<kSwiglu, NG>, grid, block, smem, stream, pdl_enabled(),
-                                         cluster, a);
+        case kPlain: return extras ? W4_TC_LAUNCH(kPlain, true) : W4_TC_LAUNCH(kPlain, false);
+        case kQkv: return extras ? W4_TC_LAUNCH(kQkv, true) : W4_TC_LAUNCH(kQkv, false);
+        default: return extras ? W4_TC_LAUNCH(kSwiglu, true) : W4_TC_LAUNCH(kSwiglu, false);
     }
+#undef W4_TC_LAUNCH
 }
 }  // namespace
 
