@@ -713,6 +713,8 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     int T = 16;
     while (T < g.M && T < max_t) T *= 2;
     while (T > 64 && total_tiles * ((g.M + T - 1) / T) < sm_count) T /= 2;
+    static const int force_t = env_int("W4A16_TC_T", 0);   // experiments: any multiple of 16 up to 256
+    if (force_t >= 16 && force_t <= 256 && force_t % 16 == 0) T = force_t;
     static const int stages_env = env_int("W4A16_TC_STAGES", 0);
     int S = stages_env > 0 ? std::min(stages_env, kMaxStages) : kMaxStages;
     while (S > 2 && tc_smem_bytes(T, S, g.K) > 227 * 1024) --S;
