@@ -428,6 +428,24 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
         same = tok_ref == int(tok_f.item())
         us_a, how_a = time_rounds(unfused_round)
         us_b, how_b = time_rounds(fused_round)
+        one_launch = None
+        if world == 1:
+            ctl_e = ops.make_sample_control(temperature, 1234, 0)
+            cnt = torch.zeros(1, dtype=torch.int32, device="cuda")
+            cv = torch.empty(slots, dtype=torch.float32, device="cuda")
+            ci = torch.empty(slots, dtype=torch.int32, device="cuda")
+            tok_e = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+            def one_launch_round():
+                for w, s in slabs:
+                    ops.launch_gemv_w4a8_sample_one_launch(w, s, q8, xs, s8, None, cv, ci, cnt, ctl_e, tok_e, N, K)
+            ce = ops.make_sample_control(temperature, 99, 5)
+            with torch.cuda.stream(stream):
+                ops.launch_gemv_w4a8_sample_one_launch(slabs[0][0], slabs[0][1], q8, xs, s8, None, cv, ci, cnt, ce, tok_e, N, K)
+            stream.synchronize()
+            same_e = int(tok_e.item()) == tok_ref
+            us_e, how_e = time_rounds(one_launch_round)
+            one_launch = {"us_per_step": us_e, "timed_as": how_e, "same_token": bool(same_e)}
         peer_result = signal_result = None
         if world > 1:
             try:
@@ -475,6 +493,8 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
             "sampling_epilogue": {"us_per_step": us_b, "timed_as": how_b,
                                   "exchange_bytes_per_gpu": slots * 8 if world > 1 else 0},
             "same_token": bool(same)}
+        if one_launch is not None:
+            out["token_selection"]["sampling_epilogue_one_launch"] = one_launch
         if peer_result is not None:
             out["token_selection"]["sampling_epilogue_peer_store"] = peer_result
         if signal_result is not None:

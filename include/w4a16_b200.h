@@ -221,6 +221,16 @@ W4A16_API int w4a16_gemv_w4a8_sample_and_advance(const uint32_t* qweight, const 
                                                  int32_t* sample_scratch_idx, void* d_control, int32_t* d_token_out,
                                                  int out_features, int in_features, w4a16_stream_t stream);
 
+/* The same in ONE launch: the GEMV's CTA that finishes last reduces all candidates, writes the token and advances
+ * the control block.  *d_counter is a device word, zero before the first call, that only this sequence of
+ * launches touches (it wraps back to zero in every launch). */
+W4A16_API int w4a16_gemv_w4a8_sample_one_launch(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                                                const float* input_scale, const int32_t* input_sum8,
+                                                void* output_logits, float* sample_scratch_val,
+                                                int32_t* sample_scratch_idx, uint32_t* d_counter, void* d_control,
+                                                int32_t* d_token_out, int out_features, int in_features,
+                                                w4a16_stream_t stream);
+
 /* reference include/kernels.cuh:84-94 launch_gemv_qkv_w4a8 (src/kernels/gemv_w4a16.cu:123-194,
  * 387-513, 893-926): q, k and v projections in one launch. */
 W4A16_API int w4a16_gemv_qkv_w4a8(const w4a16_qkv_view* view, const int8_t* input_q8,

@@ -81,6 +81,8 @@ SIGNATURES = {
                                                  c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
     "w4a16_sample_finish_after_signals": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                                           c_void_p, c_void_p],
+    "w4a16_gemv_w4a8_sample_one_launch": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "w4a16_sample_finish": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p],
     "w4a16_gemv_w4a8_sample_and_advance": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                            c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],

@@ -229,6 +229,29 @@ static int sample_candidates(const uint32_t* qweight, const void* scales, const 
     return gemv_launch(kPlain, a, S(stream));
 }
 
+int w4a16_gemv_w4a8_sample_one_launch(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                                      const float* input_scale, const int32_t* input_sum8, void* output_logits,
+                                      float* sample_scratch_val, int32_t* sample_scratch_idx, uint32_t* d_counter,
+                                      void* d_control, int32_t* d_token_out, int out_features, int in_features,
+                                      w4a16_stream_t stream) {
+    if (!qweight || !scales || !input_q8 || !input_scale || !input_sum8 || !sample_scratch_val || !sample_scratch_idx ||
+        !d_counter || out_features <= 0)
+        return W4A16_ERR_INVALID_ARG;
+    if (int st = check_k(in_features)) return st;
+    if (misaligned(qweight, 16) || misaligned(scales, 2) || misaligned(output_logits, 2) || misaligned(input_scale, 4) ||
+        misaligned(input_sum8, 4) || misaligned(sample_scratch_val, 4) || misaligned(sample_scratch_idx, 4) ||
+        misaligned(d_counter, 4) || misaligned(d_control, 8) || misaligned(d_token_out, 4))
+        return W4A16_ERR_ALIGNMENT;
+    GemvArgs a = {};
+    a.qweight[0] = qweight; a.scales[0] = H(scales); a.out[0] = H(output_logits); a.rows[0] = out_features;
+    a.q8 = input_q8; a.xscale = input_scale; a.sum8 = input_sum8;
+    a.K = in_features; a.units = out_features;
+    a.sample_val = sample_scratch_val; a.sample_idx = sample_scratch_idx; a.sample_control = d_control;
+    a.sample_done_counter = d_counter;
+    a.sample_finish_inline = 1; a.sample_control_rw = d_control; a.sample_token_out = d_token_out;
+    return gemv_launch(kPlain, a, S(stream));
+}
+
 int w4a16_gemv_w4a8_sample_candidates(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
                                       const float* input_scale, const int32_t* input_sum8, void* output_logits,
                                       float* candidate_val, int32_t* candidate_idx, const void* d_control,

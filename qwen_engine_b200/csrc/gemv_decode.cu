@@ -468,6 +468,35 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const Ge
                 }
             }
         }
+        if (a.sample_finish_inline) {
+            // Single launch: the CTA that arrives last (stores, fence, wrapping counter) reduces the candidates of
+            // all CTAs -- every other CTA is through by then, so the control block may be advanced here too.
+            __shared__ int s_last;
+            if (tid == 0) {
+                __threadfence();
+                s_last = atomicInc(a.sample_done_counter, gridDim.x - 1u) == gridDim.x - 1u ? 1 : 0;
+                __threadfence();
+            }
+            __syncthreads();
+            if (s_last) {
+                best = kSampleFloor;
+                best_idx = 0x7FFFFFFF;
+                for (int i = tid; i < static_cast<int>(gridDim.x); i += blockDim.x)
+                    sample_take(best, best_idx, __ldcg(a.sample_val + i), __ldcg(a.sample_idx + i));
+                __syncthreads();   // s_v / s_i are reused
+                sample_block_reduce(best, best_idx, s_v, s_i);
+                if (tid == 0) {
+                    if (best_idx == 0x7FFFFFFF) best_idx = 0;
+                    SampleControl* c = static_cast<SampleControl*>(a.sample_control_rw);
+                    if (c != nullptr) {
+                        c->token_id = best_idx;
+                        c->seq_pos += 1;
+                        c->rng_seed += 0x9E3779B97F4A7C15ull;
+                    }
+                    if (a.sample_token_out != nullptr) *a.sample_token_out = best_idx;
+                }
+            }
+        }
     }
 }
 

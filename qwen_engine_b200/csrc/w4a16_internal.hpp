@@ -108,6 +108,11 @@ struct GemvArgs {
     uint32_t* sample_peer_flag[7];
     uint32_t* sample_done_counter;
     int sample_half_stride;
+    // optional, single GPU: the launch's last CTA (counted in sample_done_counter, no step word) reduces all
+    // candidates itself, writes the token here / into the control block and advances the block -- no second launch
+    int32_t* sample_token_out;
+    void* sample_control_rw;
+    int sample_finish_inline;
     int K;
     int units;  // outputs produced: rows (PLAIN, QKV total) or row pairs (SWIGLU)
     // filled in by the planner

@@ -23,7 +23,7 @@ __all__ = [
     "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
     "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots", "DecodeSweep",
     "launch_gemv_rmsnorm_w4a16", "launch_gemv_qkv_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1",
-    "gemv_w4a8_peers", "gemm_prefill_w4a16_block", "make_sample_control", "launch_embed_lookup_w4a16", "read_sample_control", "launch_sample_and_advance", "sample_slots", "launch_gemv_w4a8_sample_candidates", "launch_sample_finish", "gemv_w4a8_sample_candidates_peers", "gemv_w4a8_sample_candidates_signal", "sample_finish_after_signals", "launch_gemv_w4a8_sample_and_advance", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_QUANT_IN_GATE_UP", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
+    "gemv_w4a8_peers", "gemm_prefill_w4a16_block", "make_sample_control", "launch_embed_lookup_w4a16", "read_sample_control", "launch_sample_and_advance", "sample_slots", "launch_gemv_w4a8_sample_candidates", "launch_sample_finish", "launch_gemv_w4a8_sample_one_launch", "gemv_w4a8_sample_candidates_peers", "gemv_w4a8_sample_candidates_signal", "sample_finish_after_signals", "launch_gemv_w4a8_sample_and_advance", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_QUANT_IN_GATE_UP", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
 ]
 
 # Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
@@ -208,6 +208,16 @@ def sample_finish_after_signals(candidate_val_ptr, candidate_idx_ptr, count, hal
     check("w4a16_sample_finish_after_signals", load().w4a16_sample_finish_after_signals(
         candidate_val_ptr, candidate_idx_ptr, count, half_stride, flags_ptr, num_flags, _ptr(step_word), _ptr(d_status),
         _ptr(d_control), _ptr(d_token_out), _stream(stream)))
+
+
+def launch_gemv_w4a8_sample_one_launch(qweight, scales, input_q8, input_scale, input_sum8, output_logits, sample_scratch_val,
+                                       sample_scratch_idx, d_counter, d_control, d_token_out, out_features, in_features,
+                                       stream=None):
+    """lm_head + token selection + control-block advance in one launch (d_counter: zero-initialised int32 [1])."""
+    check("w4a16_gemv_w4a8_sample_one_launch", load().w4a16_gemv_w4a8_sample_one_launch(
+        _ptr(qweight), _ptr(scales), _ptr(input_q8), _ptr(input_scale), _ptr(input_sum8), _ptr(output_logits),
+        _ptr(sample_scratch_val), _ptr(sample_scratch_idx), _ptr(d_counter), _ptr(d_control), _ptr(d_token_out),
+        out_features, in_features, _stream(stream)))
 
 
 def launch_sample_finish(candidate_val, candidate_idx, count, d_control, d_token_out, stream=None):

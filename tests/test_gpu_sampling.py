@@ -89,6 +89,22 @@ def test_lm_head_with_sampling_epilogue(ops, N, K, temperature, seed, seq_pos):
         if keep_logits:
             fused_logits = logits2
     assert tokens[0] == tokens[1] and controls[0] == controls[1]
+    # one launch: the GEMV's last CTA reduces the candidates and advances the control block itself
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    c3 = ops.make_sample_control(temperature, seed, seq_pos)
+    for rep in range(2):        # twice: the counter wraps back to zero, the control block moves on
+        fval, fidx = _scratch(slots)
+        t3 = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+        ops.launch_gemv_w4a8_sample_one_launch(d[0], d[1], d[2], d[3], d[4], None, fval, fidx, counter, c3, t3, N, K)
+        torch.cuda.synchronize()
+        assert int(counter.item()) == 0
+        if rep == 0:
+            assert int(t3.item()) == tokens[0] and ops.read_sample_control(c3) == controls[0]
+        else:
+            ref_tok, _, scores = oracle.sample(util.to_np(fused_logits), temperature, controls[0]["rng_seed"], seq_pos + 1)
+            assert ops.read_sample_control(c3)["seq_pos"] == seq_pos + 2
+            if temperature <= 1e-5:
+                assert int(t3.item()) == ref_tok
     # the logits it stores are the plain launch's: bit for bit where both use one K slice per row (lm_head),
     # within the path's tolerance where the plain launch splits K inside the CTA
     if K == 1536 and N >= 100000:
