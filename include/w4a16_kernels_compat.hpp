@@ -159,6 +159,31 @@ inline void launch_gemm_prefill_dual_gate_up_swiglu_w4a16(const uint32_t* gate_u
                         "launch_gemm_prefill_dual_gate_up_swiglu_w4a16");
 }
 
+// ---- the callers either side of the projections (optional: define W4A16_COMPAT_WITH_CONTROL_BLOCK in a
+// translation unit that has the reference's DeviceControlBlock, include/tensor.cuh:28-34, in scope) ----
+#ifdef W4A16_COMPAT_WITH_CONTROL_BLOCK
+static_assert(sizeof(DeviceControlBlock) >= sizeof(w4a16_sample_control), "control block layout");
+
+// reference include/kernels.cuh:11-20 (src/kernels/rmsnorm_rope.cu:15-69)
+inline void launch_embed_lookup_w4a16(const uint32_t* embed_qweight, const half* embed_scales,
+                                      const int32_t* d_token_ids, half* out_hidden,
+                                      const DeviceControlBlock* d_control, int num_tokens, cudaStream_t stream,
+                                      int hidden_size = W4A16_DFLT(HIDDEN_SIZE), int vocab_size = 151936) {
+    w4a16_detail::check(w4a16_embed_lookup_w4a16(embed_qweight, embed_scales, d_token_ids, out_hidden, d_control,
+                                                 num_tokens, stream, hidden_size, vocab_size),
+                        "launch_embed_lookup_w4a16");
+}
+
+// reference include/kernels.cuh:210-219 (src/kernels/sampling.cu:206-230)
+inline void launch_sample_and_advance(const half* logits, float* sample_scratch_val, int32_t* sample_scratch_idx,
+                                      DeviceControlBlock* d_control, int32_t* d_mapped_pinned_token,
+                                      cudaStream_t stream, int vocab_size = 151936) {
+    w4a16_detail::check(w4a16_sample_and_advance(logits, sample_scratch_val, sample_scratch_idx, d_control,
+                                                 d_mapped_pinned_token, stream, vocab_size),
+                        "launch_sample_and_advance");
+}
+#endif
+
 #undef W4A16_DFLT
 
 }  // namespace qwen

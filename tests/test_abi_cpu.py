@@ -67,3 +67,15 @@ def test_compat_header_compiles(tmp_path):
     src.write_text('#include "w4a16_kernels_compat.hpp"\nint main(){ return 0; }\n')
     subprocess.run(["nvcc", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-c", "-I", str(ROOT / "include"), "-o", str(tmp_path / "t.o"), str(src)],
                    check=True)
+    # with a control block of the reference's layout in scope, the embedding and sampling launchers appear too
+    src2 = tmp_path / "t2.cu"
+    src2.write_text(
+        '#include <cstdint>\n'
+        'namespace qwen { struct alignas(256) DeviceControlBlock { int32_t token_id; int32_t seq_pos; float temperature; '
+        'uint32_t reserved; uint64_t rng_seed; }; }\n'
+        '#define W4A16_COMPAT_WITH_CONTROL_BLOCK\n'
+        '#include "w4a16_kernels_compat.hpp"\n'
+        'int main(){ void (*a)(const half*, float*, int32_t*, qwen::DeviceControlBlock*, int32_t*, cudaStream_t, int) = '
+        '&qwen::launch_sample_and_advance; (void)a; return 0; }\n')
+    subprocess.run(["nvcc", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-c", "-I", str(ROOT / "include"), "-o", str(tmp_path / "t2.o"), str(src2)],
+                   check=True)
