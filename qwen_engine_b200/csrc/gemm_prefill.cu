@@ -92,10 +92,11 @@ int gemm_launch(GemmArgs g, cudaStream_t stream) {
     if (int st = ensure_device_ready(&dev)) return st;
 
     // The tcgen05 kernel pads the token count to its smallest tile (16); measured on B200 it overtakes the
-    // CUDA-core few-token form at 5 tokens on the K = 1536 shapes and at 4 on K = 8960 (where the few-token
-    // form stages only two tokens per pass).  The CUDA-core forms also take what TMA cannot address.
+    // CUDA-core few-token form at 5 tokens on the narrow K = 1536 shapes and at 4 on K = 8960 (where the few-token
+    // form stages only two tokens per pass) and on matrices tall enough to give every SM a tile (gate_up).  The CUDA-core forms also take what TMA cannot address.
     static const int tc_min_m_env = env_int("W4A16_TC_MIN_M", 0);
-    const int tc_min_m = tc_min_m_env > 0 ? tc_min_m_env : (g.K > 4096 ? 4 : 5);
+    const int rows_all = g.rows[0] + (g.mode == kQkv ? g.rows[1] + g.rows[2] : 0);
+    const int tc_min_m = tc_min_m_env > 0 ? tc_min_m_env : ((g.K > 4096 || rows_all >= 128 * dev->sm_count) ? 4 : 5);
     if ((g.M >= tc_min_m || g.num_peers > 0) && gemm_tc_supported(g)) return gemm_tc_launch(g, dev->sm_count, stream);
     if (g.num_peers > 0) return W4A16_ERR_SHAPE;   // peer stores exist in the tensor-core form only
 
