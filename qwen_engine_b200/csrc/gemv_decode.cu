@@ -259,8 +259,15 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
         if (a.q8_out != nullptr) {
             __shared__ float s_y[kMaxSubwarps];
             __shared__ float s_cluster_max[4];
+#ifdef W4A16_GEMV_PROFILE
+            long long qt = clock64();
+#define GP_Q(i) if (gp_on) { const long long c_ = clock64(); g_gemv_prof[8100 + (i)] = static_cast<unsigned int>(c_ - qt); qt = c_; }
+#else
+#define GP_Q(i)
+#endif
             if (l == 0) s_y[sub] = y_rounded;
             __syncthreads();
+            GP_Q(0);
             uint32_t rank;
             asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
             float v = 0.0f;
@@ -276,8 +283,10 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
                     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(m) : "memory");
                 }
             }
+            GP_Q(1);
             asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
             asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+            GP_Q(2);
             if (tid < 32) {
                 const float m = fmaxf(fmaxf(s_cluster_max[0], s_cluster_max[1]), fmaxf(s_cluster_max[2], s_cluster_max[3]));
                 const float d = fmaxf(__fdiv_rn(m, 127.0f), 1e-8f);
@@ -293,6 +302,7 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
                 if ((tid & 7) == 0) a.sum8_out[(first + tid) >> 3] = -8 * sum;
                 if (rank == 0 && tid == 0) a.xscale_out[first / kGroup] = d;
             }
+            GP_Q(3);
         }
     }
     GP_MARK(7);
