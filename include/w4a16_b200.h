@@ -71,10 +71,27 @@ W4A16_API const char* w4a16_status_string(int status);
  */
 W4A16_API int w4a16_init(void);
 
-/* Run-time switches. */
+/*
+ * Run-time options: process-wide integers read when a launcher is called (so a launch captured into a CUDA
+ * graph keeps the values of capture time).  With the defaults every launch configuration is a function of
+ * the call's arguments and the device alone.  w4a16_set_option returns W4A16_ERR_INVALID_ARG for an unknown
+ * option or a value outside its range.
+ */
 enum {
-    W4A16_OPT_PDL = 1 /* 1 (default): launch with programmatic dependent launch so the next
-                         kernel's weight prefetch overlaps this kernel's tail; 0: plain launches */
+    W4A16_OPT_PDL = 1,               /* 1 (default): programmatic dependent launch, so that the next kernel's weight
+                                        prefetch overlaps this kernel's tail; 0: plain stream-ordered launches */
+    W4A16_OPT_SIGNAL_WAIT_SPINS = 2, /* polls (about 0.2 us apart) that w4a16_sample_finish_after_signals spends on
+                                        a peer's flag before it gives up and reports the rank in *d_status;
+                                        default 1 << 22, about a second */
+    W4A16_OPT_GEMV_FORM = 3,         /* how the batch-1 GEMV brings its weights on chip: 0 (default) as measured
+                                        best per shape, 1 register-held 16-byte streaming loads issued before the
+                                        wait for the previous kernel, 2 bulk copies (cp.async.bulk) into shared
+                                        memory.  Same output bits in every form. */
+    W4A16_OPT_GEMM_MIN_TOKENS_TENSOR_CORE = 4, /* token count from which the M-token contraction runs on the
+                                        tensor cores; 0 (default): the measured crossover (4 or 5 tokens) */
+    W4A16_OPT_GEMM_FORM = 5,         /* tensor-core form of the M-token contraction: 0 (default) chosen by token
+                                        count, 1 one CTA per tile, 2 CTA pairs (cta_group::2) */
+    W4A16_OPT_COUNT_ = 6
 };
 W4A16_API int w4a16_set_option(int option, int value);
 W4A16_API int w4a16_get_option(int option);
@@ -92,7 +109,33 @@ W4A16_API int w4a16_rmsnorm_q8_1(const void* input, const void* gamma, void* out
                                  int8_t* out_q8, float* out_scale, int32_t* out_sum8,
                                  w4a16_stream_t stream, int hidden_size);
 
+/*
+ * Q8_1 of the attention output as the reference's flash-decode combine step produces it for the O projection
+ * (src/kernels/attention_gqa.cu:258-310, the out_q8 / out_scale / out_sum8 arguments of
+ * launch_attention_gqa_flash_decode, include/kernels.cuh:177-193), as an operator of its own so that an
+ * attention kernel which is not part of this library can hand its result to the W4 path with the reference's
+ * bits: one quantisation group per head, taken from the fp32 accumulator before it is rounded to fp16,
+ * d = max(max|acc| / 127, 1e-8), q = clamp(rn(acc / d), -127, 127) -- a division per element, so the bytes can
+ * differ from w4a16_quantize_fp16_to_q8_1 applied to fp16(acc).  attn_acc: fp32 [num_heads][head_dim],
+ * 16-byte aligned; attn_out_fp16_opt (may be NULL): fp16(acc), the reference's attn_out.  head_dim must be
+ * 128 (W4A16_ERR_SHAPE otherwise): a head is a quantisation group.
+ */
+W4A16_API int w4a16_quantize_attn_heads_f32_to_q8_1(const float* attn_acc, void* attn_out_fp16_opt, int8_t* out_q8,
+                                                    float* out_scale, int32_t* out_sum8, int num_heads,
+                                                    int head_dim, w4a16_stream_t stream);
+
 /* ---- batch-1 decode GEMV ------------------------------------------------------- */
+
+/*
+ * The O projection straight from the attention accumulators: the same quantisation as
+ * w4a16_quantize_attn_heads_f32_to_q8_1, done by every CTA of the GEMV in its prologue (in_features / 128
+ * heads of 128), then w4a16_gemv_w4a8 -- same output bits as that pair of calls, one launch less
+ * (src/engine.cu:389-402 issues the attention kernel with the Q8_1 outputs and then launch_gemv_w4a8).
+ * attn_acc: fp32 [in_features], 16-byte aligned.
+ */
+W4A16_API int w4a16_gemv_attn_heads_f32_w4a16(const uint32_t* qweight, const void* scales, const float* attn_acc,
+                                              const void* residual, void* output_y, int out_features,
+                                              int in_features, w4a16_stream_t stream);
 
 /* reference include/kernels.cuh:60-69 launch_gemv_w4a16 (src/kernels/gemv_w4a16.cu:636-746,
  * 960-979): fp16 activations, quantised to Q8_1 inside the kernel.  residual may be NULL. */
@@ -468,10 +511,9 @@ W4A16_API int w4a16_gemv_group_dots(const uint32_t* qweight, const int8_t* input
                                     int in_features, w4a16_stream_t stream);
 
 /*
- * Debug counters kept on the current device.  which = 0: number of bounded waits of the
- * tensor-core kernel that ran out (each one means a launch gave up and its output is invalid;
- * 0 in normal operation); 1..16: cycle sums of that kernel's roles, zero unless the library was
- * built with -DW4A16_TC_PROFILE.  Synchronises the device.
+ * Counters of bounded device-side waits that ran out, kept on the current device; each count means that a
+ * launch gave up waiting and its output is invalid (0 in normal operation).  which = 0: barrier waits of the
+ * tensor-core kernels; 1: waits of the batch-1 GEMV for its bulk copies.  Synchronises the device.
  */
 W4A16_API int w4a16_debug_counter(int which, unsigned int* out);
 

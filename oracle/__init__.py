@@ -120,6 +120,18 @@ def quantize_q8_1(x: np.ndarray, round_mode: int = ROUND_HALF_EVEN):
     return q8, scale, sum8
 
 
+def quantize_heads_f32(acc: np.ndarray):
+    """acc: fp32 [heads][head_dim] -> (fp16 attn_out, q8, scale[heads], sum8), the flash-decode epilogue's Q8_1."""
+    acc = np.ascontiguousarray(acc, dtype=np.float32)
+    heads, hd = acc.shape
+    out16 = np.empty((heads, hd), dtype=np.float16)
+    q8 = np.empty(heads * hd, dtype=np.int8)
+    scale = np.empty(heads, dtype=np.float32)
+    sum8 = np.empty(heads * hd // 8, dtype=np.int32)
+    lib().orc_quantize_heads_f32(_p(acc), heads, hd, _p(out16), _p(q8), _p(scale), _p(sum8))
+    return out16, q8, scale, sum8
+
+
 def group_dots(packed: np.ndarray, q8: np.ndarray, threads: int | None = None) -> np.ndarray:
     """int32 [N][K/128]: the per-group integer dots of (q-8) with the Q8_1 bytes."""
     packed = np.ascontiguousarray(packed, dtype=np.uint32)

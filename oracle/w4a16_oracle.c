@@ -162,6 +162,39 @@ ORC_API void orc_quantize_weights(const float* w, int64_t N, int K, uint32_t* pa
 }
 
 /*
+ * Q8_1 of the attention output, as the flash-decode combine step produces it for the O projection.
+ * src/kernels/attention_gqa.cu:263-310: one group per head (head_dim elements, 128 in the model), taken
+ * from the fp32 accumulator BEFORE it is rounded to fp16:
+ *   d = max(max|acc| / 127, 1e-8);  q = clamp(rn(acc / d), -127, 127)   -- a division per element, where
+ * the stand-alone quantiser above multiplies by 1/d, so the bytes can differ from quantising fp16(acc);
+ * sum8 per octet as above; attn_out = fp16(acc) (attention_gqa.cu:260).
+ * acc: [heads][head_dim] fp32.  out_fp16 / scale / sum8 may be NULL.  Round half to even.
+ */
+ORC_API void orc_quantize_heads_f32(const float* acc, int heads, int head_dim, uint16_t* out_fp16, int8_t* q8,
+                                    float* scale, int32_t* sum8) {
+    for (int h = 0; h < heads; ++h) {
+        const float* a = acc + (int64_t)h * head_dim;
+        float max_abs = 0.0f;
+        for (int j = 0; j < head_dim; ++j) max_abs = fmaxf(max_abs, fabsf(a[j]));
+        const float d = fmaxf(max_abs / 127.0f, 1e-8f);
+        if (scale) scale[h] = d;
+        for (int o = 0; o < head_dim / 8; ++o) {
+            int32_t s = 0;
+            for (int j = 0; j < 8; ++j) {
+                const float v = a[o * 8 + j];
+                int q = (int)nearbyintf(v / d);
+                if (q < -127) q = -127;
+                if (q > 127) q = 127;
+                q8[(int64_t)h * head_dim + o * 8 + j] = (int8_t)q;
+                s += q;
+                if (out_fp16) out_fp16[(int64_t)h * head_dim + o * 8 + j] = f2h(v);
+            }
+            if (sum8) sum8[(int64_t)h * (head_dim / 8) + o] = -8 * s;
+        }
+    }
+}
+
+/*
  * Q8_1 activation quantiser, the reference's own flavour: int8 q8[n], fp32
  * scale[n/128], int32 sum8[n/8] with sum8[i] = -8 * sum of the octet's q8.
  * include/quant_primitives.cuh:37-89 (sum8: :13-17):

@@ -60,6 +60,8 @@ SIGNATURES = {
     "w4a16_quantize_fp16_to_q8_1": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "w4a16_rmsnorm_q8_1": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int],
     "w4a16_gemv_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "w4a16_quantize_attn_heads_f32_to_q8_1": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+    "w4a16_gemv_attn_heads_f32_w4a16": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "w4a16_gemv_w4a16_static_scratch": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
     "w4a16_gemv_w4a8": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                         c_void_p],

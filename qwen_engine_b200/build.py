@@ -45,21 +45,36 @@ def up_to_date() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
+    """One nvcc -c per source file, in parallel, then one link step."""
     if not force and up_to_date():
         return LIB
-    cmd = [nvcc(), *NVCC_FLAGS]
-    if os.environ.get("W4A16_TC_PROFILE"):
-        cmd += ["-DW4A16_TC_PROFILE"]
-    if os.environ.get("W4A16_GEMV_PROFILE"):
-        cmd += ["-DW4A16_GEMV_PROFILE"]
+    from concurrent.futures import ThreadPoolExecutor
+    objdir = PKG / "build"
+    objdir.mkdir(exist_ok=True)
+    flags = [f for f in NVCC_FLAGS if f != "-shared"]
     if verbose:
-        cmd += ["-Xptxas", "-v"]
-    cmd += ["-o", str(LIB), *[str(CSRC / s) for s in SOURCES]]
-    res = subprocess.run(cmd, cwd=str(CSRC), capture_output=True, text=True)
-    if verbose or res.returncode != 0:
-        sys.stderr.write(res.stdout + res.stderr)
-    if res.returncode != 0:
+        flags += ["-Xptxas", "-v"]
+
+    def compile_one(src: str):
+        obj = objdir / (Path(src).stem + ".o")
+        res = subprocess.run([nvcc(), *flags, "-c", str(CSRC / src), "-o", str(obj)], cwd=str(CSRC),
+                             capture_output=True, text=True)
+        return src, obj, res
+
+    with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 4)) as pool:
+        results = list(pool.map(compile_one, SOURCES))
+    failed = False
+    for src, _, res in results:
+        if verbose or res.returncode != 0:
+            sys.stderr.write(f"---- {src}\n" + res.stdout + res.stderr)
+        failed = failed or res.returncode != 0
+    if failed:
         raise RuntimeError("nvcc failed building libw4a16_b200.so")
+    link = subprocess.run([nvcc(), *NVCC_FLAGS, "-o", str(LIB), *[str(o) for _, o, _ in results]],
+                          capture_output=True, text=True)
+    if link.returncode != 0:
+        sys.stderr.write(link.stdout + link.stderr)
+        raise RuntimeError("linking libw4a16_b200.so failed")
     return LIB
 
 

@@ -13,24 +13,24 @@ constexpr int kMaxDevices = 64;
 DeviceInfo g_dev[kMaxDevices];
 std::mutex g_dev_mutex;
 std::atomic<bool> g_dev_ready[kMaxDevices];
-std::atomic<int> g_pdl{-1};
+// run-time options (w4a16_set_option): plain process-wide integers, read at launch time
+std::atomic<int> g_options[W4A16_OPT_COUNT_];
+const int kOptionDefaults[W4A16_OPT_COUNT_] = {0, /*PDL*/ 1, /*SIGNAL_WAIT_SPINS*/ 1 << 22, /*GEMV_FORM*/ 0,
+                                                /*GEMM_MIN_TOKENS_TENSOR_CORE*/ 0, /*GEMM_FORM*/ 0};
+std::once_flag g_options_once;
+void init_options() {
+    std::call_once(g_options_once, [] {
+        for (int i = 0; i < W4A16_OPT_COUNT_; ++i) g_options[i].store(kOptionDefaults[i], std::memory_order_relaxed);
+    });
+}
 
 }  // namespace
 
-int env_int(const char* name, int fallback) {
-    const char* v = std::getenv(name);
-    return (v && *v) ? std::atoi(v) : fallback;
+int option(int which) {
+    init_options();
+    return (which > 0 && which < W4A16_OPT_COUNT_) ? g_options[which].load(std::memory_order_relaxed) : 0;
 }
-
-bool pdl_enabled() {
-    int v = g_pdl.load(std::memory_order_relaxed);
-    if (v < 0) {
-        v = env_int("W4A16_PDL", 1) ? 1 : 0;
-        g_pdl.store(v, std::memory_order_relaxed);
-    }
-    return v != 0;
-}
-void set_pdl_enabled(bool on) { g_pdl.store(on ? 1 : 0, std::memory_order_relaxed); }
+bool pdl_enabled() { return option(W4A16_OPT_PDL) != 0; }
 
 int ensure_device_ready(const DeviceInfo** out) {
     int dev = -1;
@@ -93,16 +93,23 @@ const char* w4a16_status_string(int status) {
 
 int w4a16_init(void) { return ensure_device_ready(nullptr); }
 
-int w4a16_set_option(int option, int value) {
-    if (option == W4A16_OPT_PDL) {
-        set_pdl_enabled(value != 0);
-        return 0;
+int w4a16_set_option(int which, int value) {
+    if (which <= 0 || which >= W4A16_OPT_COUNT_) return W4A16_ERR_INVALID_ARG;
+    switch (which) {
+        case W4A16_OPT_PDL: value = value != 0; break;
+        case W4A16_OPT_SIGNAL_WAIT_SPINS: if (value < 1) return W4A16_ERR_INVALID_ARG; break;
+        case W4A16_OPT_GEMV_FORM: if (value < 0 || value > 2) return W4A16_ERR_INVALID_ARG; break;
+        case W4A16_OPT_GEMM_MIN_TOKENS_TENSOR_CORE: if (value < 0) return W4A16_ERR_INVALID_ARG; break;
+        case W4A16_OPT_GEMM_FORM: if (value < 0 || value > 2) return W4A16_ERR_INVALID_ARG; break;
+        default: break;
     }
-    return W4A16_ERR_INVALID_ARG;
+    init_options();
+    g_options[which].store(value, std::memory_order_relaxed);
+    return 0;
 }
-int w4a16_get_option(int option) {
-    if (option == W4A16_OPT_PDL) return pdl_enabled() ? 1 : 0;
-    return W4A16_ERR_INVALID_ARG;
+int w4a16_get_option(int which) {
+    if (which <= 0 || which >= W4A16_OPT_COUNT_) return W4A16_ERR_INVALID_ARG;
+    return option(which);
 }
 
 int w4a16_quantize_fp16_to_q8_1(const void* input_x, int8_t* out_q8, float* out_scale, int32_t* out_sum8,
@@ -130,8 +137,9 @@ int w4a16_rmsnorm_q8_1(const void* input, const void* gamma, void* output_fp16_o
 static int gemv_plain(const uint32_t* qweight, const void* scales, const void* x_fp16, const int8_t* q8,
                       const float* xscale, const int32_t* sum8, const void* residual, void* y, int N, int K,
                       w4a16_stream_t stream, const void* gamma = nullptr, void* const* peers = nullptr,
-                      int num_peers = 0) {
+                      int num_peers = 0, const float* x_f32 = nullptr) {
     if (!qweight || !scales || !y || N <= 0) return W4A16_ERR_INVALID_ARG;
+    if (misaligned(x_f32, 16)) return W4A16_ERR_ALIGNMENT;
     if (int st = check_k(K)) return st;
     if (misaligned(qweight, 4) || misaligned(scales, 2) || misaligned(y, 2) || misaligned(residual, 2) ||
         misaligned(x_fp16, 8) || misaligned(xscale, 4) || misaligned(sum8, 4))
@@ -139,6 +147,7 @@ static int gemv_plain(const uint32_t* qweight, const void* scales, const void* x
     GemvArgs a = {};
     a.qweight[0] = qweight; a.scales[0] = H(scales); a.out[0] = H(y); a.rows[0] = N;
     a.q8 = q8; a.xscale = xscale; a.sum8 = sum8; a.x_fp16 = H(x_fp16); a.gamma = H(gamma);
+    a.x_f32 = x_f32;
     a.residual = H(residual);
     a.K = K; a.units = N;
     if (misaligned(gamma, 8)) return W4A16_ERR_ALIGNMENT;
@@ -330,6 +339,26 @@ int w4a16_gemv_w4a16(const uint32_t* qweight, const void* scales, const void* in
     if (!input_x) return W4A16_ERR_INVALID_ARG;
     return gemv_plain(qweight, scales, input_x, nullptr, nullptr, nullptr, residual, output_y, out_features,
                       in_features, stream);
+}
+
+int w4a16_quantize_attn_heads_f32_to_q8_1(const float* attn_acc, void* attn_out_fp16_opt, int8_t* out_q8,
+                                          float* out_scale, int32_t* out_sum8, int num_heads, int head_dim,
+                                          w4a16_stream_t stream) {
+    if (!attn_acc || !out_q8 || !out_scale || !out_sum8 || num_heads <= 0) return W4A16_ERR_INVALID_ARG;
+    if (head_dim != 128) return W4A16_ERR_SHAPE;   // one head = one quantisation group of the W4 path
+    if (misaligned(attn_acc, 16) || misaligned(attn_out_fp16_opt, 16) || misaligned(out_q8, 8) ||
+        misaligned(out_scale, 4) || misaligned(out_sum8, 4))
+        return W4A16_ERR_ALIGNMENT;
+    if (int st = ensure_device_ready(nullptr)) return st;
+    return quantize_heads_f32_to_q8_1(attn_acc, H(attn_out_fp16_opt), out_q8, out_scale, out_sum8, num_heads, S(stream));
+}
+
+int w4a16_gemv_attn_heads_f32_w4a16(const uint32_t* qweight, const void* scales, const float* attn_acc,
+                                    const void* residual, void* output_y, int out_features, int in_features,
+                                    w4a16_stream_t stream) {
+    if (!attn_acc) return W4A16_ERR_INVALID_ARG;
+    return gemv_plain(qweight, scales, nullptr, nullptr, nullptr, nullptr, residual, output_y, out_features,
+                      in_features, stream, nullptr, nullptr, 0, attn_acc);
 }
 
 int w4a16_gemv_w4a8(const uint32_t* qweight, const void* scales, const int8_t* input_q8, const float* input_scale,
@@ -533,26 +562,11 @@ int w4a16_gemv_group_dots(const uint32_t* qweight, const int8_t* input_q8, const
 }
 
 int w4a16_debug_counter(int which, unsigned int* out) {
-    if (!out || which < 0) return W4A16_ERR_INVALID_ARG;
+    if (!out) return W4A16_ERR_INVALID_ARG;
     if (int st = ensure_device_ready(nullptr)) return st;
-    // 50: reset, 51: count, 1000 + i: word i of the decode-GEMV timeline (-DW4A16_GEMV_PROFILE builds)
-    if (which == 50) return gemv_prof(-1, out);
-    if (which == 51) return gemv_prof(-2, out);
-    if (which >= 1000) return gemv_prof(which - 1000, out);
-    if (which > 49) return W4A16_ERR_INVALID_ARG;
     if (which == 0) return gemm_tc_timeouts(out);
-    if (which >= 33) {   // 33..48: persistent sweep, CTA 0: kind*4 + phase, in kilo-cycles; 49: reset them
-        unsigned long long ps[16];
-        if (int st = psweep_prof(ps, which == 49)) return st;
-        *out = which == 49 ? 0u : static_cast<unsigned int>(ps[which - 33] / 1000);
-        return 0;
-    }
-    // 1..32: per-role cycle sums of the tensor-core kernel's CTA (0,0); zero unless the library was
-    // built with -DW4A16_TC_PROFILE
-    unsigned long long prof[32];
-    if (int st = gemm_tc_prof(prof)) return st;
-    *out = static_cast<unsigned int>(prof[which - 1]);
-    return 0;
+    if (which == 1) return gemv_copy_timeouts(out);
+    return W4A16_ERR_INVALID_ARG;
 }
 
 }  // extern "C"

@@ -94,9 +94,9 @@ int gemm_launch(GemmArgs g, cudaStream_t stream) {
     // The tcgen05 kernel pads the token count to its smallest tile (16); measured on B200 it overtakes the
     // CUDA-core few-token form at 5 tokens on the narrow K = 1536 shapes and at 4 on K = 8960 (where the few-token
     // form stages only two tokens per pass) and on matrices tall enough to give every SM a tile (gate_up).  The CUDA-core forms also take what TMA cannot address.
-    static const int tc_min_m_env = env_int("W4A16_TC_MIN_M", 0);
+    const int tc_min_m_opt = option(W4A16_OPT_GEMM_MIN_TOKENS_TENSOR_CORE);
     const int rows_all = g.rows[0] + (g.mode == kQkv ? g.rows[1] + g.rows[2] : 0);
-    const int tc_min_m = tc_min_m_env > 0 ? tc_min_m_env : ((g.K > 4096 || rows_all >= 128 * dev->sm_count) ? 4 : 5);
+    const int tc_min_m = tc_min_m_opt > 0 ? tc_min_m_opt : ((g.K > 4096 || rows_all >= 128 * dev->sm_count) ? 4 : 5);
     if ((g.M >= tc_min_m || g.num_peers > 0) && gemm_tc_supported(g)) return gemm_tc_launch(g, dev->sm_count, stream);
     if (g.num_peers > 0) return W4A16_ERR_SHAPE;   // peer stores exist in the tensor-core form only
 
@@ -110,12 +110,11 @@ int gemm_launch(GemmArgs g, cudaStream_t stream) {
         a.out_ld[0] = (g.mode == kPlain && g.ldc > 0) ? g.ldc : a.units; a.out_ld[1] = a.out_ld[2] = 0;
     }
     // few tokens, 16-byte aligned tensors: the form that streams like the decode GEMV
-    static const int v2_on = env_int("W4A16_SMALLM_V2", 1);
     bool aligned = reinterpret_cast<uintptr_t>(g.x) % 16 == 0;
     for (int t = 0; t < (g.mode == kQkv ? 3 : 1); ++t) aligned = aligned && reinterpret_cast<uintptr_t>(g.qweight[t]) % 16 == 0;
     SmallMPlan plan;
     int U = 8;
-    if (v2_on && aligned && plan_v2(g, a.units, dev->sm_count, &plan, &U)) {
+    if (aligned && plan_v2(g, a.units, dev->sm_count, &plan, &U)) {
         const int R = g.mode == kSwiglu ? 2 : 1;
         // tokens per pass: as many as the shared-memory budget of a CTA (about a third of an SM) allows
         int mt = g.M >= 4 ? 4 : (g.M >= 2 ? 2 : 1);

@@ -36,17 +36,6 @@
 namespace w4 {
 
 __device__ unsigned int g_tc_wait_timeouts = 0;
-#ifdef W4A16_TC_PROFILE
-// Cycle counts of CTA (0,0), per role, summed over its k-blocks (build with -DW4A16_TC_PROFILE).
-__device__ unsigned long long g_tc_prof[32];
-#define TC_PROF_DECL(name) long long name = 0
-#define TC_PROF_T() clock64()
-#define TC_PROF_ADD(acc, t0) acc += clock64() - (t0)
-#else
-#define TC_PROF_DECL(name)
-#define TC_PROF_T() 0
-#define TC_PROF_ADD(acc, t0)
-#endif
 
 namespace {
 
@@ -246,13 +235,6 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-#ifdef W4A16_TC_PROFILE
-    const long long t_entry = clock64();
-    const bool tl_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && tid == 0;
-#define TC_TL(i) if (tl_on) g_tc_prof[i] = clock64() - t_entry;
-#else
-#define TC_TL(i)
-#endif
 
     // which weight tensor / which rows
     int t = 0, tile = blockIdx.x;
@@ -290,7 +272,6 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
-    TC_TL(20);
 
     if (warp < kDqWarps) {
         // ---------------- dequantise: group = warp / 4, thread = weight row inside the group ----------------
@@ -308,7 +289,6 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
             }
             asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");
         }
-        TC_TL(21);
         const int sw = r & 7;
         bool ok = true;
         int rs = 0;
@@ -317,22 +297,16 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
         int s = part;
         uint32_t ph = 0;
         while (s >= S) { s -= S; ph ^= 1; }
-        TC_PROF_DECL(q_raw); TC_PROF_DECL(q_empty); TC_PROF_DECL(q_work); TC_PROF_DECL(q_sync);
         for (int sb = 0; sb < num_sb && ok; ++sb) {
-            [[maybe_unused]] long long d0 = TC_PROF_T();
             ok = warp_wait(raw_full(rs), rph, s_abort, lane);
-            TC_PROF_ADD(q_raw, d0);
             if (!ok) break;
             const uint8_t* raw_row = s_raw + rs * kRawBytes + r * 128;
             const __half2 sc0 = __half2half2(s_scale[(2 * sb) * kTileRows + r]);
             const __half2 sc1 = __half2half2(s_scale[(2 * sb + 1) * kTileRows + r]);
 #pragma unroll
             for (int j = part; j < 4; j += NG) {     // this group's k-blocks of the 256-element super-block
-                [[maybe_unused]] long long d1 = TC_PROF_T();
                 ok = warp_wait(ab_empty(s), ph ^ 1, s_abort, lane);
-                TC_PROF_ADD(q_empty, d1);
                 if (!ok) break;
-                [[maybe_unused]] long long d2 = TC_PROF_T();
                 const uint4 w0 = *reinterpret_cast<const uint4*>(raw_row + (((2 * j) ^ sw) << 4));
                 const uint4 w1 = *reinterpret_cast<const uint4*>(raw_row + (((2 * j + 1) ^ sw) << 4));
                 const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
@@ -344,12 +318,9 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
                     dequant_word_fp16(words[w], sc2, h);
                     *reinterpret_cast<uint4*>(a_row + ((w ^ sw) << 4)) = *reinterpret_cast<const uint4*>(h);
                 }
-                TC_PROF_ADD(q_work, d2);
-                [[maybe_unused]] long long d3 = TC_PROF_T();
                 fence_proxy_async_smem();   // generic-proxy writes -> visible to the tensor core's async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(full(s));
-                TC_PROF_ADD(q_sync, d3);
                 s += NG;
                 while (s >= S) { s -= S; ph ^= 1; }
             }
@@ -357,17 +328,9 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
             if (lane == 0 && ok) mbar_arrive(raw_empty(rs));
             if (++rs == kRawStages) { rs = 0; rph ^= 1; }
         }
-#ifdef W4A16_TC_PROFILE
-        if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (warp & 3) == 0) {
-            const int gq = 4 + 3 * part;
-            if (gq + 2 < 16) { g_tc_prof[gq] = q_raw + q_empty; g_tc_prof[gq + 1] = q_work; g_tc_prof[gq + 2] = q_sync; }
-        }
-#endif
         // ---------------- epilogue: thread = weight row, registers = tokens ----------------
-        TC_TL(22);
         if (ok) ok = warp_wait(accum_full, 0, s_abort, lane);
         tc_fence_after();
-        TC_TL(23);
         // Split K: the CTAs of the cluster hold partial sums of the same output tile.  After a first cluster
         // barrier (everyone's main loop is over, so the leader's pipeline buffers are free) the others store
         // their fp32 partials into the leader's shared memory, [rank-1][token][row] (conflict-free for row-per-thread); after a second barrier the
@@ -376,7 +339,6 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
         float* s_part = reinterpret_cast<float*>(smem);
         if (ksplit > 1) {
             cluster_sync_all();
-            TC_TL(24);
             if (krank != 0 && ok) {
                 const uint32_t remote0 = cluster_map_shared(smem_u32(s_part), 0);
                 for (int c0 = part * 16; c0 < T; c0 += 16 * NG) {
@@ -391,7 +353,6 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
                 }
             }
             cluster_sync_all();
-            TC_TL(25);
         }
         if (ok && krank == 0) {
             const int n = n0 + r;
@@ -406,7 +367,6 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
                 tmem_ld_wait();
                 for (int w = 1; w < issuers; ++w) add_second_accumulator(lane_base + static_cast<uint32_t>(w * T + c0), v);
 
-                TC_TL(28);
                 // the other CTAs' partial sums, slice after slice (16 independent loads in flight each)
                 for (int k = 1; k < ksplit; ++k) {
                     float p[16];
@@ -415,7 +375,6 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
 #pragma unroll
                     for (int j = 0; j < 16; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) + p[j]);
                 }
-                TC_TL(29);
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int m = m0 + c0 + j;
@@ -461,32 +420,22 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
             int s = 0;
             uint32_t ph = 0;
             bool ok = true;
-            TC_PROF_DECL(p_wait); TC_PROF_DECL(p_mma); TC_PROF_DECL(p_commit); TC_PROF_DECL(p_test);
             bool ready = mbar_test_wait(full(0), 0);
-            [[maybe_unused]] long long loop_t0 = TC_PROF_T();
             for (int kb = 0; kb < num_kb; ++kb) {
-                [[maybe_unused]] long long c0 = TC_PROF_T();
                 if (!ready) ok = warp_wait(full(s), ph, s_abort, lane);
-                TC_PROF_ADD(p_wait, c0);
                 if (!ok) break;
                 // position of the next k-block, and an early look at its barrier
                 int sn = s + 1;
                 uint32_t phn = ph;
                 if (sn == S) { sn = 0; phn ^= 1; }
-                [[maybe_unused]] long long c1 = TC_PROF_T();
                 if (lane == 0) {
 #pragma unroll
                     for (int ks = 0; ks < kBK / 16; ++ks)
                         tc_mma_f16(tmem_base, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
-                    TC_PROF_ADD(p_mma, c1);
-                    [[maybe_unused]] long long c2 = TC_PROF_T();
                     tc_commit(ab_empty(s));    // frees the stage when these MMAs have read it
-                    TC_PROF_ADD(p_commit, c2);
                 }
-                [[maybe_unused]] long long c3 = TC_PROF_T();
                 ready = (kb + 1 < num_kb) ? mbar_test_wait(full(sn), phn) : true;
                 ready = __all_sync(0xFFFFFFFFu, ready);
-                TC_PROF_ADD(p_test, c3);
                 a_desc += a_step;
                 b_desc += b_step;
                 if (sn == 0) { a_desc = a_desc0; b_desc = b_desc0; }
@@ -494,12 +443,6 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
                 ph = phn;
             }
             if (ok && lane == 0) tc_commit(accum_full);
-#ifdef W4A16_TC_PROFILE
-            if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0) {
-                g_tc_prof[0] = p_wait; g_tc_prof[1] = p_mma; g_tc_prof[2] = p_commit; g_tc_prof[3] = num_kb;
-                g_tc_prof[16] = clock64() - loop_t0; g_tc_prof[19] = p_test;
-            }
-#endif
         }
         } else if (w < nw) {
             const uint32_t idesc = make_idesc(T);
@@ -510,33 +453,23 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
             int s = w % S;
             uint32_t ph = static_cast<uint32_t>(w / S) & 1u;
             bool ok = true;
-            TC_PROF_DECL(p_wait); TC_PROF_DECL(p_mma); TC_PROF_DECL(p_commit); TC_PROF_DECL(p_test);
             bool ready = __all_sync(0xFFFFFFFFu, mbar_test_wait(full(s), ph));
             uint64_t a_desc = a_desc0 + static_cast<uint32_t>(s) * a_step, b_desc = b_desc0 + static_cast<uint32_t>(s) * b_step;
-            [[maybe_unused]] long long loop_t0 = TC_PROF_T();
             for (int kb = w; kb < num_kb; kb += nw) {
-                [[maybe_unused]] long long c0 = TC_PROF_T();
                 if (!ready) ok = warp_wait(full(s), ph, s_abort, lane);
-                TC_PROF_ADD(p_wait, c0);
                 if (!ok) break;
                 // position of this warp's next k-block, and an early look at its barrier
                 int sn = s + nw;
                 uint32_t phn = ph;
                 while (sn >= S) { sn -= S; phn ^= 1; }
-                [[maybe_unused]] long long c1 = TC_PROF_T();
                 if (lane == 0) {
 #pragma unroll
                     for (int ks = 0; ks < kBK / 16; ++ks)
                         tc_mma_f16(tmem_acc, a_desc + 2 * ks, b_desc + 2 * ks, idesc, (kb >= nw || ks != 0) ? 1u : 0u);
-                    TC_PROF_ADD(p_mma, c1);
-                    [[maybe_unused]] long long c2 = TC_PROF_T();
                     tc_commit(ab_empty(s));    // frees the stage when these MMAs have read it
-                    TC_PROF_ADD(p_commit, c2);
                 }
-                [[maybe_unused]] long long c3 = TC_PROF_T();
                 ready = (kb + nw < num_kb) ? mbar_test_wait(full(sn), phn) : true;
                 ready = __all_sync(0xFFFFFFFFu, ready);
-                TC_PROF_ADD(p_test, c3);
                 // descriptors by plain adds on their low word (the start-address field counts 16-byte units and
                 // cannot carry out of its 14 bits for shared-memory addresses), recomputed when the ring wraps
                 if (sn > s) { a_desc += static_cast<uint32_t>(nw) * a_step; b_desc += static_cast<uint32_t>(nw) * b_step; }
@@ -545,12 +478,6 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
                 ph = phn;
             }
             if (ok && lane == 0) tc_commit(accum_full);
-#ifdef W4A16_TC_PROFILE
-            if (blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && w == 0) {
-                g_tc_prof[0] = p_wait; g_tc_prof[1] = p_mma; g_tc_prof[2] = p_commit; g_tc_prof[3] = num_kb;
-                g_tc_prof[16] = clock64() - loop_t0; g_tc_prof[19] = p_test;
-            }
-#endif
         }
         __syncwarp();
         if (ksplit > 1) { cluster_sync_all(); cluster_sync_all(); }
@@ -559,20 +486,13 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
-            TC_PROF_DECL(x_wait);
-            [[maybe_unused]] long long x_t0 = TC_PROF_T();
             for (int kb = 0; kb < num_kb; ++kb) {
-                [[maybe_unused]] long long w0 = TC_PROF_T();
                 const bool okx = mbar_wait(ab_empty(s), ph ^ 1, s_abort);
-                TC_PROF_ADD(x_wait, w0);
                 if (!okx) break;
                 mbar_arrive_expect_tx(full(s), static_cast<uint32_t>(b_bytes));
                 tma_load_2d(smem_u32(s_b + s * b_bytes), &a.tmap_x, (kb_begin + kb) * kBK, m0, full(s));
                 if (++s == S) { s = 0; ph ^= 1; }
             }
-#ifdef W4A16_TC_PROFILE
-            if (blockIdx.x == 0 && blockIdx.y == 0) { g_tc_prof[17] = x_wait; g_tc_prof[18] = clock64() - x_t0; }
-#endif
         }
         __syncwarp();
         if (ksplit > 1) { cluster_sync_all(); cluster_sync_all(); }
@@ -592,10 +512,8 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
         if (ksplit > 1) { cluster_sync_all(); cluster_sync_all(); }
     }
 
-    TC_TL(26);
     tc_fence_before();
     __syncthreads();
-    TC_TL(27);
     if (warp == kDqWarps) tmem_dealloc(tmem_base, static_cast<uint32_t>(a.tmem_cols));
 }
 
@@ -671,8 +589,7 @@ cudaError_t launch_tc(int mode, dim3 grid, size_t smem, cudaStream_t stream, con
 }  // namespace
 
 int gemm_tc_set_attributes() {
-    cudaError_t e = raise_tc_smem_modes<1>();
-    if (e == cudaSuccess) e = raise_tc_smem_modes<2>();
+    cudaError_t e = raise_tc_smem_modes<2>();
     if (e == cudaSuccess) e = raise_tc_smem_modes<4>();
     return static_cast<int>(e);
 }
@@ -709,14 +626,10 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     a.num_peers = g.mode == kPlain ? g.num_peers : 0;
     for (int p = 0; p < 7; ++p) a.peer_out[p] = p < a.num_peers ? g.peer_out[p] : nullptr;
     // tokens per tile: the smallest power of two >= M (16..256); halve it while the grid is thin
-    static const int max_t = std::max(16, std::min(256, env_int("W4A16_TC_MAX_T", 256)));
     int T = 16;
-    while (T < g.M && T < max_t) T *= 2;
+    while (T < g.M && T < 256) T *= 2;
     while (T > 64 && total_tiles * ((g.M + T - 1) / T) < sm_count) T /= 2;
-    static const int force_t = env_int("W4A16_TC_T", 0);   // experiments: any multiple of 16 up to 256
-    if (force_t >= 16 && force_t <= 256 && force_t % 16 == 0) T = force_t;
-    static const int stages_env = env_int("W4A16_TC_STAGES", 0);
-    int S = stages_env > 0 ? std::min(stages_env, kMaxStages) : kMaxStages;
+    int S = kMaxStages;
     while (S > 2 && tc_smem_bytes(T, S, g.K) > 227 * 1024) --S;
     if (tc_smem_bytes(T, S, g.K) > 227 * 1024) return W4A16_ERR_TOO_LARGE;
     a.T = T;
@@ -724,8 +637,7 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     // two issuing warps for token tiles of at most 128 (measured: gate_up at 16 tokens 18.3 -> 14.3 us, down at 128
     // tokens 39.0 -> 30.5 us; at 256 tokens the tensor pipe, not the issue, paces the loop and one warp is as fast);
     // each has its own accumulator, so the column count doubles
-    static const int issuers_env = env_int("W4A16_TC_ISSUERS", 0);
-    a.issuers = issuers_env >= 1 && issuers_env <= kMaxIssuers ? issuers_env : (T <= 128 ? 2 : 1);
+    a.issuers = T <= 128 ? 2 : 1;
     while (a.issuers > 1 && a.issuers * T > 512) --a.issuers;
     int cols = 32;
     while (cols < a.issuers * T) cols *= 2;
@@ -734,11 +646,9 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     // shapes): each tensor-core instruction costs its issuing thread a fixed time however few tokens it
     // carries, so a thin grid is bound by K / 16 instructions in a row per CTA.  Up to 8 CTAs (the portable
     // cluster size) share a tile; their fp32 partials must fit the leader's pipeline buffers.
-    static const int ksplit_env = env_int("W4A16_TC_KSPLIT", 0);
     const int ctas = total_tiles * ((g.M + T - 1) / T);
     int ksplit = 1;
     if (ctas * 2 <= sm_count) ksplit = std::min(8, sm_count / ctas);
-    if (ksplit_env > 0) ksplit = std::min(ksplit_env, 8);
     ksplit = std::min(ksplit, g.K / 256);
     const size_t ring_bytes = static_cast<size_t>(kRawStages) * kRawBytes + static_cast<size_t>(S) * (kABytes + T * 128);
     while (ksplit > 1 && static_cast<size_t>(ksplit - 1) * T * kTileRows * sizeof(float) > ring_bytes) --ksplit;
@@ -759,22 +669,9 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     const size_t smem = tc_smem_bytes(T, S, g.K);
     // A dequantising group revisits a ring slot every NG k-blocks and waits on a parity: it must never
     // be two uses of a slot ahead of the tensor core, which holds exactly when NG <= stages.
-    static const int groups_env = env_int("W4A16_TC_GROUPS", 4);
-    const int groups = S >= 4 ? std::min(groups_env, 4) : std::min(groups_env, 2);
-    cudaError_t e;
-    if (groups == 1) e = launch_tc<1>(g.mode, grid, smem, stream, a);
-    else if (groups == 2) e = launch_tc<2>(g.mode, grid, smem, stream, a);
-    else e = launch_tc<4>(g.mode, grid, smem, stream, a);
+    const int groups = S >= 4 ? 4 : 2;
+    const cudaError_t e = groups == 2 ? launch_tc<2>(g.mode, grid, smem, stream, a) : launch_tc<4>(g.mode, grid, smem, stream, a);
     return static_cast<int>(e);
-}
-
-int gemm_tc_prof(unsigned long long* out) {
-#ifdef W4A16_TC_PROFILE
-    return static_cast<int>(cudaMemcpyFromSymbol(out, g_tc_prof, sizeof(unsigned long long) * 32));
-#else
-    for (int i = 0; i < 32; ++i) out[i] = 0;
-    return 0;
-#endif
 }
 
 int gemm_tc_timeouts(unsigned int* out) {

@@ -18,7 +18,6 @@
 // fp32 accumulate per lane; (4) 3-step shuffle reduce over the sub-warp, shared-memory
 // reduce over the K slices; (5) epilogue (residual / QKV scatter / SwiGLU), fp16 store.
 #include <algorithm>
-#include <cstdlib>
 
 #include "sampling.cuh"
 #include "w4a16_common.cuh"
@@ -34,37 +33,8 @@ constexpr float kRmsEps = 1e-6f;                      // reference include/confi
 // XIN: where the activation comes from.
 enum XIn { kXQ8 = 0,        // pre-quantised Q8_1 arrays in global memory
            kXFp16 = 1,      // fp16 vector, quantised in the prologue
-           kXFp16Norm = 2 };  // fp16 vector, RMSNorm then quantised in the prologue
-
-// Optional timeline of the decode GEMV (-DW4A16_GEMV_PROFILE): thread 0 of CTA 0 of every launch appends one
-// record {globaltimer at entry, after the wait for the prior grid, at the end; latest end time of any CTA
-// of the launches before it; cycles spent waiting, staging x, in the dot loop, in the reduction + epilogue}.  Read with w4a16_debug_counter.
-#ifdef W4A16_GEMV_PROFILE
-constexpr int kProfRecords = 1024;
-__device__ unsigned int g_gemv_prof[kProfRecords * 8];
-__device__ unsigned int g_gemv_prof_n;
-__device__ unsigned int g_gemv_last_end;   // latest end time of any CTA of any GEMV so far
-__device__ __forceinline__ unsigned int gtimer() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-    return static_cast<unsigned int>(t);
-}
-#define GP_DECL() const bool gp_on = blockIdx.x == 0 && threadIdx.x == 0; unsigned int gp[8]; long long gp_c = 0; \
-    if (gp_on) { gp[0] = gtimer(); gp_c = clock64(); }
-#define GP_MARK(i) if (gp_on) { const long long c_ = clock64(); gp[i] = static_cast<unsigned int>(c_ - gp_c); gp_c = c_; }
-#define GP_GT(i) if (gp_on) { gp[i] = gtimer(); }
-#define GP_PREV_END(i) if (gp_on) { gp[i] = *reinterpret_cast<volatile unsigned int*>(&g_gemv_last_end); }
-#define GP_END() if (threadIdx.x == 0) { atomicMax(&g_gemv_last_end, gtimer()); }
-#define GP_FLUSH() if (gp_on) { const unsigned int n_ = atomicAdd(&g_gemv_prof_n, 1u); if (n_ < kProfRecords) { \
-    for (int i_ = 0; i_ < 8; ++i_) g_gemv_prof[n_ * 8 + i_] = gp[i_]; } }
-#else
-#define GP_DECL()
-#define GP_MARK(i)
-#define GP_GT(i)
-#define GP_PREV_END(i)
-#define GP_END()
-#define GP_FLUSH()
-#endif
+           kXFp16Norm = 2,  // fp16 vector, RMSNorm then quantised in the prologue
+           kXF32Heads = 3 };  // fp32 attention accumulators, quantised per head with the flash-decode epilogue's rule
 
 // Register caps: two 256-thread CTAs per SM need <= 128; the single-row forms with 8 loads per lane run as
 // 224-thread CTAs (down projection) of which three must fit an SM for the whole grid to be resident at once.
@@ -72,7 +42,6 @@ constexpr int gemv_reg_cap(int mode, int u) { return (mode != kSwiglu && u == 8)
 
 template <int MODE, int U, int XIN, bool ALIGNED16>
 __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs a) {
-    GP_DECL();
     constexpr int R = (MODE == kSwiglu) ? 2 : 1;  // weight rows per sub-warp
     extern __shared__ __align__(16) uint8_t smem[];
     const int K = a.K;
@@ -141,45 +110,32 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
     // residual element is requested first and the activation is staged with one round trip.
     [[maybe_unused]] uint4 gam[kStageRounds];
     [[maybe_unused]] bool regs_form = false;
-    if constexpr (XIN != kXQ8) {
+    if constexpr (XIN == kXFp16 || XIN == kXFp16Norm) {
         regs_form = stage_regs_ok(a.x_fp16, XIN == kXFp16Norm ? static_cast<const void*>(a.gamma) : nullptr, K);
         if constexpr (XIN == kXFp16Norm) {
             if (regs_form) prefetch_gamma(a.gamma, K, gam);
         }
     }
     pdl_release_dependents();
-    GP_MARK(4);
     pdl_wait_prior_grids();
-    GP_MARK(4);
-    GP_GT(1);
-    GP_PREV_END(3);
 
     [[maybe_unused]] __half res_pre = __ushort_as_half(0);
     if constexpr (MODE == kPlain) {
         if (active && ks == 0 && l == 0 && a.residual != nullptr) res_pre = a.residual[unit];
     }
     if constexpr (XIN == kXFp16Norm) {
-#ifdef W4A16_GEMV_PROFILE
-        if (regs_form) stage_x_fp16_regs<true>(a.x_fp16, gam, K, kRmsEps, s_q8, s_seed, s_scale,
-                                               gp_on ? &g_gemv_prof[8000 + 8 * MODE] : nullptr);
-#else
         if (regs_form) stage_x_fp16_regs<true>(a.x_fp16, gam, K, kRmsEps, s_q8, s_seed, s_scale);
-#endif
         else stage_x_from_fp16_rmsnorm(a.x_fp16, a.gamma, K, kRmsEps, s_q8, s_seed, s_scale);
     } else if constexpr (XIN == kXFp16) {
-#ifdef W4A16_GEMV_PROFILE
-        if (regs_form) stage_x_fp16_regs<false>(a.x_fp16, gam, K, kRmsEps, s_q8, s_seed, s_scale,
-                                                gp_on ? &g_gemv_prof[8000 + 8 * 3] : nullptr);
-#else
         if (regs_form) stage_x_fp16_regs<false>(a.x_fp16, gam, K, kRmsEps, s_q8, s_seed, s_scale);
-#endif
         else stage_x_from_fp16(a.x_fp16, K, s_q8, s_seed, s_scale);
+    } else if constexpr (XIN == kXF32Heads) {
+        stage_x_from_f32_heads(a.x_f32, K, s_q8, s_seed, s_scale);
     } else {
         if (!stage_x_from_q8_1_regs<(R * U >= 16)>(a.q8, a.xscale, a.sum8, K, a.vec_ok != 0, s_q8, s_seed, s_scale))
             stage_x_from_q8_1(a.q8, a.xscale, a.sum8, K, a.vec_ok != 0, s_q8, s_seed, s_scale);
     }
     __syncthreads();
-    GP_MARK(5);
 
     float acc[R];
 #pragma unroll
@@ -205,8 +161,6 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
         }
         if (s0 + U < s_end) issue(s0 + U);
     }
-
-    GP_MARK(6);
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 4);
@@ -259,15 +213,8 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
         if (a.q8_out != nullptr) {
             __shared__ float s_y[kMaxSubwarps];
             __shared__ float s_cluster_max[4];
-#ifdef W4A16_GEMV_PROFILE
-            long long qt = clock64();
-#define GP_Q(i) if (gp_on) { const long long c_ = clock64(); g_gemv_prof[8100 + (i)] = static_cast<unsigned int>(c_ - qt); qt = c_; }
-#else
-#define GP_Q(i)
-#endif
             if (l == 0) s_y[sub] = y_rounded;
             __syncthreads();
-            GP_Q(0);
             uint32_t rank;
             asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
             float v = 0.0f;
@@ -283,10 +230,8 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
                     asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(m) : "memory");
                 }
             }
-            GP_Q(1);
             asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
             asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-            GP_Q(2);
             if (tid < 32) {
                 const float m = fmaxf(fmaxf(s_cluster_max[0], s_cluster_max[1]), fmaxf(s_cluster_max[2], s_cluster_max[3]));
                 const float d = fmaxf(__fdiv_rn(m, 127.0f), 1e-8f);
@@ -302,29 +247,281 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
                 if ((tid & 7) == 0) a.sum8_out[(first + tid) >> 3] = -8 * sum;
                 if (rank == 0 && tid == 0) a.xscale_out[first / kGroup] = d;
             }
-            GP_Q(3);
         }
     }
-    GP_MARK(7);
-    GP_GT(2);
-    GP_FLUSH();
-    GP_END();
+}
+
+
+// ---- bulk-copy form -----------------------------------------------------------------------------
+// The same GEMV with the CTA's weight rows brought into SHARED MEMORY by the copy engine (cp.async.bulk,
+// completion on an mbarrier) instead of into registers.  A CTA's rows are adjacent in the row-major matrix,
+// so its whole share of the weights is one contiguous range: one elected thread asks for it before the wait
+// for the previous kernel and the bytes arrive without holding a register.  The kernel then needs about 60
+// registers per thread instead of 96-128, which is what lets the CTAs of the NEXT projection become
+// resident, and start their own copies, while this one still computes: on-chip staging for weights is the
+// shared memory of all SMs (33 MB) in addition to the register file.
+// Work split, arithmetic and summation order are those of gemv_w4_kernel (same plan, same chunk_dot, the K
+// slices added in the same order), so both forms give the same bits.
+//
+// CLUSTERK (PLAIN only): the K slices of a row block are spread over the CTAs of a thread-block cluster
+// instead of over the sub-warps of one CTA.  Each CTA then stages -- and, for an fp16 input, quantises --
+// only ITS slice of the activation (a vector of 8960 costs every CTA six quantiser rounds otherwise), copies
+// 32 rows x its slice of the weights, and the partial sums meet in the leading CTA through distributed shared
+// memory: the others store their fp32 partial into the leader's array, one cluster barrier, the leader adds
+// them in slice order.  This is what lets the down projection take the fp16 MLP activation directly, without
+// a quantiser launch in front of it.
+constexpr unsigned kBulkPollLimit = 1u << 20;     // polls of the copy barrier before a CTA gives up (tens of ms)
+__device__ unsigned int g_gemv_copy_timeouts = 0; // bounded waits that ran out (0 in normal operation)
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+struct BulkLayout {            // byte offsets inside the CTA's dynamic shared memory
+    int part, weights, bar, total;
+};
+__host__ __device__ inline BulkLayout bulk_layout(int klen, int part_floats, int weight_bytes) {
+    BulkLayout L;
+    L.part = static_cast<int>((staged_x_bytes(klen) + 15) & ~size_t(15));
+    L.weights = (L.part + part_floats * 4 + 127) & ~127;
+    L.bar = L.weights + ((weight_bytes + 15) & ~15);
+    L.total = L.bar + 16;
+    return L;
+}
+
+template <int MODE, int XIN, bool CLUSTERK>
+__global__ void __maxnreg__(64) gemv_w4_bulk_kernel(const GemvArgs a) {
+    static_assert(!CLUSTERK || (MODE == kPlain && (XIN == kXQ8 || XIN == kXFp16)), "cluster K split: plain rows, no norm");
+    constexpr int R = (MODE == kSwiglu) ? 2 : 1;
+    constexpr int U = 8;       // scale words a lane keeps per batch of steps
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int K = a.K;
+    const int tid = threadIdx.x;
+    const int sub = tid >> 3, l = tid & 7;
+
+    // Which rows and which part of K this CTA covers.
+    uint32_t krank = 0;
+    int row_block = blockIdx.x;
+    if constexpr (CLUSTERK) {
+        asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(krank));
+        row_block = blockIdx.x / a.ksplit;
+        asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");   // "this CTA has started", see below
+    }
+    const int total_steps = K / kStepElems;
+    const int k_step0 = CLUSTERK ? static_cast<int>(krank) * a.steps_per_split : 0;    // first 256-element step of the CTA
+    const int cta_steps = CLUSTERK ? max(0, min(a.steps_per_split, total_steps - k_step0)) : total_steps;
+    const int klen = cta_steps * kStepElems;
+    const int u_local = CLUSTERK ? sub : sub % a.units_per_cta;
+    const int ks = CLUSTERK ? 0 : sub / a.units_per_cta;
+    const int unit0 = row_block * a.units_per_cta;
+    const int unit = unit0 + u_local;
+    const bool active = unit < a.units && (CLUSTERK ? sub < a.units_per_cta : ks < a.ksplit);
+    const int cta_units = min(a.units_per_cta, a.units - unit0);
+
+    // offsets are taken from the longest K range of any CTA of the cluster, so that they agree in all of them
+    // (the partial sums are addressed in the leader's shared memory by the offset they have here)
+    const int klen_max = CLUSTERK ? a.steps_per_split * kStepElems : K;
+    const BulkLayout L = bulk_layout(klen_max, a.ksplit * a.units_per_cta * R, a.units_per_cta * R * (klen_max / 2));
+    int8_t* s_q8 = reinterpret_cast<int8_t*>(smem);
+    int32_t* s_seed = reinterpret_cast<int32_t*>(smem + klen_max);
+    float* s_scale = reinterpret_cast<float*>(smem + klen_max + (klen_max / kChunk) * 4);
+    float* s_part = reinterpret_cast<float*>(smem + L.part);
+    const uint32_t s_w = smem_addr(smem + L.weights);
+    const uint32_t bar = smem_addr(smem + L.bar);
+
+    // the CTA's weight rows, scales and outputs
+    const int words = K / 8, groups = K / kGroup;
+    const uint32_t* wbase = a.qweight[0];
+    const __half* sbase = a.scales[0];
+    __half* obase = a.out[0];
+    int first = unit0;                       // first unit of the CTA inside its tensor
+    if constexpr (MODE == kQkv) {            // a CTA's rows come from one tensor (the planner sees to it)
+        int t = 0;
+        if (first >= a.rows[0]) { first -= a.rows[0]; t = 1; }
+        if (t == 1 && first >= a.rows[1]) { first -= a.rows[1]; t = 2; }
+        wbase = a.qweight[t]; sbase = a.scales[t]; obase = a.out[t];
+    }
+    const size_t row0 = static_cast<size_t>(first) * R;          // first weight row of the CTA
+    const int row_bytes = klen / 2;                             // bytes of one row inside the CTA's K range
+
+    // (1) one thread starts the copies: a contiguous range when the CTA takes whole rows, else one piece per row
+    if (tid == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        const uint32_t bytes = static_cast<uint32_t>(cta_units * R) * static_cast<uint32_t>(row_bytes);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+        const uint8_t* src = reinterpret_cast<const uint8_t*>(wbase + row0 * words) + static_cast<size_t>(k_step0) * (kStepElems / 2);
+        if constexpr (!CLUSTERK) {
+            constexpr uint32_t kPiece = 16384;   // several requests in flight rather than one long one
+            for (uint32_t off = 0; off < bytes; off += kPiece)
+                bulk_copy_g2s(s_w + off, src + off, min(kPiece, bytes - off), bar);
+        } else {
+            for (int r = 0; r < cta_units; ++r)
+                bulk_copy_g2s(s_w + r * row_bytes, src + static_cast<size_t>(r) * (K / 2), row_bytes, bar);
+        }
+    }
+
+    // (2) the lane's scale words (2 bytes each, not alignable for a bulk copy) and the RMSNorm gain: weights of
+    // the model, so they too are requested before the wait
+    const int s_begin = CLUSTERK ? 0 : ks * a.steps_per_split;
+    const int s_end = active ? (CLUSTERK ? cta_steps : min(s_begin + a.steps_per_split, total_steps)) : s_begin;
+    uint16_t sb[R][U];
+    auto load_scales = [&](int s0) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int s = s0 + u;
+            if (s < s_end) {
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+                    sb[r][u] = ld_scale_bits(sbase + (row0 + static_cast<size_t>(u_local) * R + r) * groups + 2 * (k_step0 + s) + (l >> 2));
+            }
+        }
+    };
+    load_scales(s_begin);
+    [[maybe_unused]] uint4 gam[kStageRounds];
+    [[maybe_unused]] bool regs_form = false;
+    const __half* x16 = a.x_fp16 != nullptr ? a.x_fp16 + static_cast<size_t>(k_step0) * kStepElems : nullptr;
+    if constexpr (XIN == kXFp16 || XIN == kXFp16Norm) {
+        regs_form = stage_regs_ok(x16, XIN == kXFp16Norm ? static_cast<const void*>(a.gamma) : nullptr, klen);
+        if constexpr (XIN == kXFp16Norm) {
+            if (regs_form) prefetch_gamma(a.gamma, klen, gam);
+        }
+    }
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+
+    // (3) the activation: everything after the wait is on the critical path between two projections
+    [[maybe_unused]] __half res_pre = __ushort_as_half(0);
+    if constexpr (MODE == kPlain) {
+        if (active && ks == 0 && krank == 0 && l == 0 && a.residual != nullptr) res_pre = a.residual[unit];
+    }
+    if constexpr (XIN == kXFp16Norm) {
+        if (regs_form) stage_x_fp16_regs<true>(x16, gam, klen, kRmsEps, s_q8, s_seed, s_scale);
+        else stage_x_from_fp16_rmsnorm(x16, a.gamma, klen, kRmsEps, s_q8, s_seed, s_scale);
+    } else if constexpr (XIN == kXFp16) {
+        if (regs_form) stage_x_fp16_regs<false>(x16, gam, klen, kRmsEps, s_q8, s_seed, s_scale);
+        else stage_x_from_fp16(x16, klen, s_q8, s_seed, s_scale);
+    } else if constexpr (XIN == kXF32Heads) {
+        stage_x_from_f32_heads(a.x_f32, klen, s_q8, s_seed, s_scale);
+    } else {
+        const int8_t* q8 = a.q8 + static_cast<size_t>(k_step0) * kStepElems;
+        const float* xsc = a.xscale + k_step0 * (kStepElems / kGroup);
+        const int32_t* s8 = a.sum8 + k_step0 * (kStepElems / 8);
+        if (!stage_x_from_q8_1_regs<false>(q8, xsc, s8, klen, a.vec_ok != 0, s_q8, s_seed, s_scale))
+            stage_x_from_q8_1(q8, xsc, s8, klen, a.vec_ok != 0, s_q8, s_seed, s_scale);
+    }
+    __syncthreads();
+
+    // (4) the weights must have landed (bounded wait; phase 0 of a barrier used once)
+    {
+        bool landed = false;
+        for (unsigned it = 0; it < kBulkPollLimit; ++it) {
+            uint32_t ok;
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(ok) : "r"(bar), "r"(0u) : "memory");
+            if (ok) { landed = true; break; }
+            if (it > 64) __nanosleep(32);
+        }
+        if (!landed && tid == 0) atomicAdd(&g_gemv_copy_timeouts, 1u);   // the output of this launch is invalid
+    }
+
+    float acc[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) acc[r] = 0.0f;
+    const uint32_t w_lane = s_w + static_cast<uint32_t>(u_local * R) * row_bytes + l * 16;
+    for (int s0 = s_begin; s0 < s_end; s0 += U) {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int s = s0 + u;
+            if (s < s_end) {
+                const int c = s * kSubwarp + l;   // 32-element chunk index inside the CTA's K range
+                const uint4 xa = reinterpret_cast<const uint4*>(s_q8)[2 * c];
+                const uint4 xb = reinterpret_cast<const uint4*>(s_q8)[2 * c + 1];
+                const int32_t seed = s_seed[c];
+                const float xs = s_scale[c >> 2];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const uint4 w = lds128(w_lane + r * row_bytes + s * (kSubwarp * 16));
+                    const int32_t d = chunk_dot(w, xa, xb, seed);
+                    const float ws = __half2float(__ushort_as_half(sb[r][u]));
+                    acc[r] = fmaf(static_cast<float>(d), ws * xs, acc[r]);
+                }
+            }
+        }
+        if (s0 + U < s_end) load_scales(s0 + U);
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 4);
+        acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 2);
+        acc[r] += __shfl_xor_sync(0xFFFFFFFFu, acc[r], 1);
+    }
+
+    bool finisher = active && ks == 0 && l == 0;
+    if constexpr (CLUSTERK) {
+        // Every CTA of the cluster has started (the arrive at entry) before anyone writes into the leader's
+        // shared memory; the second barrier orders those stores before the leader's reads.
+        asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+        if (active && l == 0) {
+            if (krank == 0) {
+                s_part[sub] = acc[0];
+            } else {
+                uint32_t remote;
+                asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_addr(&s_part[krank * a.units_per_cta + sub])), "r"(0u));
+                asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(acc[0]) : "memory");
+            }
+        }
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+        finisher = finisher && krank == 0;
+        if (finisher) {
+            float t = 0.0f;
+            for (int k = 0; k < a.ksplit; ++k) t += s_part[k * a.units_per_cta + sub];
+            acc[0] = t;
+        }
+    } else if (a.ksplit > 1) {
+        if (l == 0 && ks < a.ksplit) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) s_part[(ks * a.units_per_cta + u_local) * R + r] = acc[r];
+        }
+        __syncthreads();
+        if (ks == 0 && l == 0) {
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                float t = 0.0f;
+                for (int k = 0; k < a.ksplit; ++k) t += s_part[(k * a.units_per_cta + u_local) * R + r];
+                acc[r] = t;
+            }
+        }
+    }
+
+    if (finisher) {
+        float y;
+        if constexpr (MODE == kSwiglu) {
+            const float gate = acc[0];
+            y = (gate / (1.0f + expf(-gate))) * acc[R - 1];
+        } else {
+            y = acc[0];
+            if constexpr (MODE == kPlain) {
+                if (a.residual != nullptr) y += __half2float(res_pre);
+            }
+        }
+        const __half yh = __float2half_rn(y);
+        obase[first + u_local] = yh;
+        if constexpr (MODE == kPlain) {
+            for (int p = 0; p < a.num_peers; ++p) a.peer_out[p][unit] = yh;
+        }
+    }
 }
 
 }  // namespace
-
-// Timeline records of the decode GEMV (zeros unless built with -DW4A16_GEMV_PROFILE).  which: -1 resets the
-// record count, -2 returns it, otherwise word `which` of the record table.
-int gemv_prof(int which, unsigned int* out) {
-#ifdef W4A16_GEMV_PROFILE
-    if (which == -1) { const unsigned int z = 0; *out = 0; return static_cast<int>(cudaMemcpyToSymbol(g_gemv_prof_n, &z, sizeof(z))); }
-    if (which == -2) return static_cast<int>(cudaMemcpyFromSymbol(out, g_gemv_prof_n, sizeof(unsigned int)));
-    if (which >= kProfRecords * 8) return W4A16_ERR_INVALID_ARG;
-    return static_cast<int>(cudaMemcpyFromSymbol(out, g_gemv_prof, sizeof(unsigned int), sizeof(unsigned int) * which));
-#else
-    (void)which; *out = 0; return 0;
-#endif
-}
 
 namespace {
 
@@ -575,32 +772,22 @@ int resident_warps_per_sm(GemvMode mode, int U) {
 // per batch so one batch covers a lane's whole K slice for the model's shapes; and the whole grid
 // resident at once (a second wave of CTAs would start its weight loads only after the wait).
 Plan make_plan(GemvMode mode, int units, int K, int sm_count) {
-    static const int force_units = env_int("W4A16_GEMV_UNITS", 0);
-    static const int force_ksplit = env_int("W4A16_GEMV_KSPLIT", 0);
-    static const int force_u = env_int("W4A16_GEMV_U", 0);
     const int steps = K / kStepElems;
     const int target_ctas = (sm_count * 13 + 9) / 10;
     int upc = 32;
     while (upc > 4 && (units + upc - 1) / upc < target_ctas) upc /= 2;
-    if (force_units > 0) upc = std::min(32, std::max(1, force_units));
     int cap = std::max(1, kMaxSubwarps / upc);   // most K slices the CTA can hold
     cap = std::min(cap, steps);
     int per = (steps + cap - 1) / cap;           // steps per slice if all slices were used
     int ksplit = (steps + per - 1) / per;        // fewest slices that reach that depth
-    auto pick_u = [&](int depth) { return force_u == 4 || force_u == 8 ? force_u : (depth <= 4 ? 4 : 8); };
-    if (force_ksplit > 0) {
-        ksplit = std::min(std::min(force_ksplit, steps), kMaxSubwarps / upc);
-        ksplit = std::max(1, ksplit);
-        per = (steps + ksplit - 1) / ksplit;
-    } else {
-        const int grid = (units + upc - 1) / upc;
-        while (ksplit > 1) {
-            const int warps = (upc * ksplit * kSubwarp + 31) / 32;
-            const int ctas_per_sm = resident_warps_per_sm(mode, pick_u(per)) / warps;
-            if (grid <= ctas_per_sm * sm_count || per >= 8) break;
-            per = (steps + (ksplit - 1) - 1) / (ksplit - 1);   // one slice fewer, deeper slices
-            ksplit = (steps + per - 1) / per;
-        }
+    auto pick_u = [&](int depth) { return depth <= 4 ? 4 : 8; };
+    const int grid = (units + upc - 1) / upc;
+    while (ksplit > 1) {
+        const int warps = (upc * ksplit * kSubwarp + 31) / 32;
+        const int ctas_per_sm = resident_warps_per_sm(mode, pick_u(per)) / warps;
+        if (grid <= ctas_per_sm * sm_count || per >= 8) break;
+        per = (steps + (ksplit - 1) - 1) / (ksplit - 1);   // one slice fewer, deeper slices
+        ksplit = (steps + per - 1) / per;
     }
     Plan p;
     p.units_per_cta = upc;
@@ -622,6 +809,9 @@ cudaError_t launch_aligned(const GemvArgs& a, bool aligned16, dim3 grid, dim3 bl
 }
 template <int MODE, int U>
 cudaError_t launch_input(const GemvArgs& a, bool aligned16, dim3 grid, dim3 block, size_t smem, cudaStream_t stream) {
+    if constexpr (MODE == kPlain) {
+        if (a.x_f32 != nullptr) return launch_aligned<MODE, U, kXF32Heads>(a, aligned16, grid, block, smem, stream);
+    }
     if (a.x_fp16 != nullptr) {
         if (a.gamma != nullptr) return launch_aligned<MODE, U, kXFp16Norm>(a, aligned16, grid, block, smem, stream);
         return launch_aligned<MODE, U, kXFp16>(a, aligned16, grid, block, smem, stream);
@@ -633,6 +823,46 @@ cudaError_t launch_mode(const GemvArgs& a, int U, bool aligned16, dim3 grid, dim
                         cudaStream_t stream) {
     if (U == 4) return launch_input<MODE, 4>(a, aligned16, grid, block, smem, stream);
     return launch_input<MODE, 8>(a, aligned16, grid, block, smem, stream);
+}
+
+// ---- bulk-copy form: instantiations, attributes, launch ----
+template <typename F>
+cudaError_t prepare_bulk(F* f) {
+    cudaError_t e = cudaFuncSetAttribute(f, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    // the largest shared-memory carve-out, the same for every kernel of a decode pass: CTAs of two kernels
+    // share an SM only if they agree on it
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(f, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    return e;
+}
+template <int MODE>
+cudaError_t prepare_bulk_mode() {
+    cudaError_t e = prepare_bulk(gemv_w4_bulk_kernel<MODE, kXQ8, false>);
+    if (e == cudaSuccess) e = prepare_bulk(gemv_w4_bulk_kernel<MODE, kXFp16, false>);
+    if (e == cudaSuccess) e = prepare_bulk(gemv_w4_bulk_kernel<MODE, kXFp16Norm, false>);
+    if constexpr (MODE == kPlain) {
+        if (e == cudaSuccess) e = prepare_bulk(gemv_w4_bulk_kernel<kPlain, kXF32Heads, false>);
+        if (e == cudaSuccess) e = prepare_bulk(gemv_w4_bulk_kernel<kPlain, kXQ8, true>);
+        if (e == cudaSuccess) e = prepare_bulk(gemv_w4_bulk_kernel<kPlain, kXFp16, true>);
+    }
+    return e;
+}
+template <int MODE>
+cudaError_t launch_bulk(const GemvArgs& a, bool cluster_k, dim3 grid, dim3 block, size_t smem, cudaStream_t stream) {
+    const bool pdl = pdl_enabled();
+    if constexpr (MODE == kPlain) {
+        if (cluster_k) {
+            const dim3 cl(static_cast<unsigned>(a.ksplit), 1, 1);
+            if (a.x_fp16 != nullptr)
+                return launch_kernel_cluster(gemv_w4_bulk_kernel<kPlain, kXFp16, true>, grid, block, smem, stream, pdl, cl, a);
+            return launch_kernel_cluster(gemv_w4_bulk_kernel<kPlain, kXQ8, true>, grid, block, smem, stream, pdl, cl, a);
+        }
+        if (a.x_f32 != nullptr) return launch_kernel(gemv_w4_bulk_kernel<kPlain, kXF32Heads, false>, grid, block, smem, stream, pdl, a);
+    }
+    if (a.x_fp16 != nullptr) {
+        if (a.gamma != nullptr) return launch_kernel(gemv_w4_bulk_kernel<MODE, kXFp16Norm, false>, grid, block, smem, stream, pdl, a);
+        return launch_kernel(gemv_w4_bulk_kernel<MODE, kXFp16, false>, grid, block, smem, stream, pdl, a);
+    }
+    return launch_kernel(gemv_w4_bulk_kernel<MODE, kXQ8, false>, grid, block, smem, stream, pdl, a);
 }
 
 template <typename F>
@@ -647,6 +877,10 @@ cudaError_t raise_smem_mode() {
     if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, kXFp16, false>);
     if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, kXFp16Norm, true>);
     if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, kXFp16Norm, false>);
+    if constexpr (MODE == kPlain) {
+        if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, kXF32Heads, true>);
+        if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, kXF32Heads, false>);
+    }
     return e;
 }
 
@@ -660,7 +894,14 @@ int gemv_set_attributes() {
     if (e == cudaSuccess) e = raise_smem_mode<kSwiglu, 4>();
     if (e == cudaSuccess) e = raise_smem_mode<kSwiglu, 8>();
     if (e == cudaSuccess) e = raise_smem(gemv_group_dots_kernel);
+    if (e == cudaSuccess) e = prepare_bulk_mode<kPlain>();
+    if (e == cudaSuccess) e = prepare_bulk_mode<kQkv>();
+    if (e == cudaSuccess) e = prepare_bulk_mode<kSwiglu>();
     return static_cast<int>(e);
+}
+
+int gemv_copy_timeouts(unsigned int* out) {
+    return static_cast<int>(cudaMemcpyFromSymbol(out, g_gemv_copy_timeouts, sizeof(unsigned int)));
 }
 
 int gemv_sample_slots(int out_features) {
@@ -696,7 +937,7 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
     bool aligned16 = true;
     const int ntens = (mode == kQkv) ? 3 : 1;
     for (int t = 0; t < ntens; ++t) aligned16 = aligned16 && (reinterpret_cast<uintptr_t>(a.qweight[t]) % 16 == 0);
-    a.vec_ok = (a.x_fp16 == nullptr) && (reinterpret_cast<uintptr_t>(a.q8) % 16 == 0) &&
+    a.vec_ok = (a.x_fp16 == nullptr) && (a.x_f32 == nullptr) && (reinterpret_cast<uintptr_t>(a.q8) % 16 == 0) &&
                (reinterpret_cast<uintptr_t>(a.sum8) % 16 == 0);
 
     const int R = (mode == kSwiglu) ? 2 : 1;
@@ -709,17 +950,15 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
 
     cudaError_t e;
     // very tall PLAIN matrices: persistent streaming kernel (two CTAs per SM, >= 8 row blocks each)
-    static const int stream_on = env_int("W4A16_GEMV_STREAM", 1);
     const int steps = a.K / kStepElems;
     const int weight_rows = mode == kSwiglu ? 2 * a.units : a.units;
     const int num_blocks = (weight_rows + kMaxSubwarps - 1) / kMaxSubwarps;
-    static const int stream_min_blocks = env_int("W4A16_GEMV_STREAM_MIN", 16);   // row blocks per SM from which it pays
-    static const int stream_swiglu = env_int("W4A16_GEMV_STREAM_SWIGLU", 0);
-    const bool tall = num_blocks >= stream_min_blocks * dev->sm_count;
+    constexpr int kStreamMinBlocksPerSm = 16;   // row blocks per SM from which the persistent streaming form pays
+    const bool tall = num_blocks >= kStreamMinBlocksPerSm * dev->sm_count;
     const bool sampling = a.sample_val != nullptr || a.sample_idx != nullptr;
     if (sampling && (mode != kPlain || !a.sample_val || !a.sample_idx || !aligned16 || steps > 8)) return W4A16_ERR_SHAPE;
-    if ((sampling || stream_on) && !q8_epilogue && aligned16 && steps <= 8 &&
-        ((mode == kPlain && (tall || sampling)) || (mode == kSwiglu && (tall || (stream_swiglu && num_blocks >= 3 * dev->sm_count))))) {
+    if (!q8_epilogue && aligned16 && steps <= 8 && a.x_f32 == nullptr &&
+        ((mode == kPlain && (tall || sampling)) || (mode == kSwiglu && tall))) {
         const dim3 sgrid(std::min(num_blocks, 2 * dev->sm_count)), sblock(kMaxThreads);
         const size_t ssmem = staged_x_bytes(a.K);
         const bool pdl = pdl_enabled();
@@ -733,6 +972,38 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
 #undef W4_STREAM
 #undef W4_STREAM3
         return static_cast<int>(e);
+    }
+    // Bulk-copy form (weights through shared memory): needs 16-byte aligned weights and a CTA share that leaves
+    // room for a second CTA on the SM.
+    const int form = option(W4A16_OPT_GEMV_FORM);
+    if (form != 1 && aligned16 && !q8_epilogue) {
+        // K slices over a cluster when one CTA would otherwise quantise / stage a long vector many times over
+        const bool cluster_k = mode == kPlain && a.gamma == nullptr && a.x_f32 == nullptr && a.ksplit >= 2 &&
+                               a.ksplit <= 8 && a.K / kGroup > 16;
+        GemvArgs b = a;
+        size_t bsmem;
+        dim3 bgrid, bblock;
+        if (cluster_k) {
+            b.units_per_cta = kMaxSubwarps;
+            const int klen = b.steps_per_split * kStepElems;
+            bsmem = bulk_layout(klen, b.ksplit * b.units_per_cta, b.units_per_cta * (klen / 2)).total;
+            bgrid = dim3(static_cast<unsigned>((b.units + b.units_per_cta - 1) / b.units_per_cta) * b.ksplit);
+            bblock = dim3(kMaxThreads);
+            b.vec_ok = (b.x_fp16 == nullptr) && (reinterpret_cast<uintptr_t>(b.q8) % 16 == 0) &&
+                       (reinterpret_cast<uintptr_t>(b.sum8) % 16 == 0);
+        } else {
+            bsmem = bulk_layout(b.K, b.ksplit * b.units_per_cta * R, b.units_per_cta * R * (b.K / 2)).total;
+            bgrid = dim3(grid);
+            bblock = dim3(block);
+        }
+        if (bsmem <= 110 * 1024) {
+            switch (mode) {
+                case kPlain: e = launch_bulk<kPlain>(b, cluster_k, bgrid, bblock, bsmem, stream); break;
+                case kQkv: e = launch_bulk<kQkv>(b, false, bgrid, bblock, bsmem, stream); break;
+                default: e = launch_bulk<kSwiglu>(b, false, bgrid, bblock, bsmem, stream); break;
+            }
+            return static_cast<int>(e);
+        }
     }
     switch (mode) {
         case kPlain: e = launch_mode<kPlain>(a, p.U, aligned16, dim3(grid), dim3(block), smem, stream); break;

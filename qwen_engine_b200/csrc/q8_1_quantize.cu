@@ -91,7 +91,51 @@ __global__ void __launch_bounds__(kNormThreads) rmsnorm_q8_1_kernel(const __half
     }
 }
 
+// Q8_1 of attention heads from their fp32 accumulators (the epilogue of the reference's flash-decode combine
+// kernel, src/kernels/attention_gqa.cu:258-310, as a kernel of its own): one half-warp per head of 128.
+// Also writes fp16(acc) -- the reference's attn_out -- when out_fp16_opt is given.
+__global__ void __launch_bounds__(kQuantThreads) quantize_heads_f32_q8_1_kernel(const float* __restrict__ acc,
+                                                                                 __half* __restrict__ out_fp16_opt,
+                                                                                 int8_t* __restrict__ q8,
+                                                                                 float* __restrict__ scale,
+                                                                                 int32_t* __restrict__ sum8, int heads) {
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    const int hl = threadIdx.x & 15;
+    const int h = blockIdx.x * (kQuantThreads / 16) + (threadIdx.x >> 4);
+    const bool on = h < heads;
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+    if (on) {
+        const float4 a = reinterpret_cast<const float4*>(acc + h * kGroup + hl * 8)[0];
+        const float4 b = reinterpret_cast<const float4*>(acc + h * kGroup + hl * 8)[1];
+        v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+    }
+    int32_t sum;
+    float d;
+    const uint2 packed = quantize_group_f32_div_halfwarp(v, &sum, &d);   // whole warps call it (shuffles)
+    if (!on) return;
+    reinterpret_cast<uint2*>(q8)[h * (kGroup / 8) + hl] = packed;
+    sum8[h * (kGroup / 8) + hl] = -8 * sum;
+    if (hl == 0) scale[h] = d;
+    if (out_fp16_opt != nullptr) {
+        __half2 o[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) o[k] = __floats2half2_rn(v[2 * k], v[2 * k + 1]);
+        reinterpret_cast<uint4*>(out_fp16_opt + h * kGroup + hl * 8)[0] = *reinterpret_cast<const uint4*>(o);
+    }
+}
+
 }  // namespace
+
+int quantize_heads_f32_to_q8_1(const float* acc, __half* out_fp16_opt, int8_t* q8, float* scale, int32_t* sum8,
+                               int heads, cudaStream_t stream) {
+    const int per_cta = kQuantThreads / 16;
+    cudaError_t e = launch_kernel(quantize_heads_f32_q8_1_kernel, dim3((heads + per_cta - 1) / per_cta),
+                                  dim3(kQuantThreads), 0, stream, pdl_enabled(), acc, out_fp16_opt, q8, scale, sum8, heads);
+    return static_cast<int>(e);
+}
 
 int quantize_set_attributes() {
     cudaError_t e = cudaFuncSetAttribute(rmsnorm_q8_1_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);

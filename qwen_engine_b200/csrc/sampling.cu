@@ -76,7 +76,7 @@ __global__ void __launch_bounds__(256) sample_stage2_after_flags_kernel(const fl
                                                                         int half_stride, const uint32_t* flags, int num_flags,
                                                                         const uint32_t* step_word, int* status,
                                                                         SampleControl* __restrict__ control,
-                                                                        int32_t* __restrict__ token_out) {
+                                                                        int32_t* __restrict__ token_out, uint32_t spin_limit) {
     __shared__ float s_v[32];
     __shared__ int32_t s_i[32];
     pdl_release_dependents();
@@ -88,7 +88,7 @@ __global__ void __launch_bounds__(256) sample_stage2_after_flags_kernel(const fl
     if (static_cast<int>(threadIdx.x) < num_flags) {
         const uint32_t* f = flags + threadIdx.x;
         bool seen = false;
-        for (uint32_t spin = 0; spin < (1u << 22); ++spin) {     // about a second at the longest
+        for (uint32_t spin = 0; spin < spin_limit; ++spin) {     // W4A16_OPT_SIGNAL_WAIT_SPINS: about a second by default
             uint32_t v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
             if (static_cast<int32_t>(v - step) >= 0) { seen = true; break; }   // step numbers only grow (wrap-safe)
@@ -124,7 +124,8 @@ int sample_stage2_after_flags(const float* part_val, const int32_t* part_idx, in
                               void* control, int32_t* token_out, cudaStream_t stream) {
     return static_cast<int>(launch_kernel(sample_stage2_after_flags_kernel, dim3(1), dim3(256), 0, stream, pdl_enabled(),
                                           part_val, part_idx, count, half_stride, flags, num_flags, step_word, status,
-                                          static_cast<SampleControl*>(control), token_out));
+                                          static_cast<SampleControl*>(control), token_out,
+                                          static_cast<uint32_t>(option(W4A16_OPT_SIGNAL_WAIT_SPINS))));
 }
 
 int sample_stage1_blocks() { return kStage1Blocks; }

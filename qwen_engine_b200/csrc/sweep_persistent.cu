@@ -32,15 +32,6 @@
 #include "w4a16_internal.hpp"
 
 namespace w4 {
-#ifdef W4A16_TC_PROFILE
-// cycles of CTA 0 thread 0, per stage kind (4) x phase (input, ring wait, compute, publish)
-__device__ unsigned long long g_ps_prof[16];
-#define PS_T() clock64()
-#define PS_ADD(kind, phase, t0) { const long long d_ = clock64() - (t0); ps_all##phase += d_; if ((kind) == 2) ps_gu##phase += d_; if ((kind) == 3) ps_dn##phase += d_; }
-#else
-#define PS_T() 0
-#define PS_ADD(kind, phase, t0)
-#endif
 namespace {
 
 constexpr int kConsumerWarps = 15;   // + 1 producer warp = 512 threads, which leaves 128 registers per thread
@@ -445,17 +436,12 @@ __device__ void consumer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
     uint32_t phase = 0;
     int chunk_parity = 0;
     const int num_stages = a.num_layers * 4;
-#ifdef W4A16_TC_PROFILE
-    long long ps_ctr = 0; long long ps_all0 = 0, ps_all1 = 0, ps_all2 = 0, ps_all3 = 0, ps_gu0 = 0, ps_gu1 = 0, ps_gu2 = 0, ps_gu3 = 0,
-              ps_dn0 = 0, ps_dn1 = 0, ps_dn2 = 0, ps_dn3 = 0;
-#endif
     for (int st = 0; st < num_stages; ++st) {
         const StagePlan p = make_plan(a, st, cta, nctas);
         const LayerDev& L = static_cast<const LayerDev*>(a.layers)[st >> 2];
         const uint32_t in_tag = a.epoch + static_cast<uint32_t>(st);        // tag of the previous stage
         const uint32_t out_tag = a.epoch + static_cast<uint32_t>(st) + 1;
         // ---- 1. the activation vector of this projection ----
-        [[maybe_unused]] long long t_in = PS_T();
         // RMSNorm gains of this thread's groups: constant data, fetched before the wait
         uint4 gamma_regs[2] = {};
         int ngam = 0;
@@ -486,9 +472,6 @@ __device__ void consumer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
             consumer_sync();
             if (*s_abort) return;
         }
-#ifdef W4A16_TC_PROFILE
-        ps_ctr += clock64() - t_in;
-#endif
         bool ok;
         switch (p.kind) {
             case 0: ok = stage_input_norm(a, a.ll_h_down, st == 0 ? a.h_in : nullptr, in_tag, gamma_regs, ngam, s, s_abort, tid); break;
@@ -498,7 +481,6 @@ __device__ void consumer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
         }
         if (!ok) return;
         consumer_sync();
-        PS_ADD(p.kind, 0, t_in);
         // ---- 2. this CTA's rows, one ring slot at a time ----
         const int cpr = p.row_bytes / 16;          // 16-byte chunks per weight row
         // Fast path: a row is spread over `flpr` lanes, at most 3 chunks per lane, and the lane's share of
@@ -528,11 +510,8 @@ __device__ void consumer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
         for (int r = 0; r < p.num_rows; r += p.chunk_rows) {
             const int rows = min(p.chunk_rows, p.num_rows - r);
             int wait_ok = 1;
-            [[maybe_unused]] long long t_w = PS_T();
             if (lane == 0) wait_ok = bar_wait(full0 + 8u * slot, phase, s_abort) ? 1 : 0;
             wait_ok = __shfl_sync(0xFFFFFFFFu, wait_ok, 0);
-            PS_ADD(p.kind, 1, t_w);
-            [[maybe_unused]] long long t_c = PS_T();
             if (!wait_ok) {
                 if (tid == 0) atomicExch(a.status, 1);
                 return;
@@ -616,9 +595,7 @@ __device__ void consumer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
             }
             chunk_parity ^= 1;
             if (++slot == kSlots) { slot = 0; phase ^= 1; }
-            PS_ADD(p.kind, 2, t_c);
         }
-        [[maybe_unused]] long long t_p = PS_T();
         consumer_sync();   // s.out complete
         // ---- 3. publish this CTA's output pairs ----
         if (tid < p.num_pairs) {
@@ -643,18 +620,9 @@ __device__ void consumer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
         // announce: issued after this thread's own stores; the words carry their own tags, so the count
         // may overtake stores of other threads without harm
         if (tid == 0) add_counter(a.counters + 8 * st);
-        PS_ADD(p.kind, 3, t_p);
         // s.out and the staged activation are rewritten only after the next stage's first
         // consumer_sync, which every thread reaches after this point.
     }
-#ifdef W4A16_TC_PROFILE
-    if (blockIdx.x == 0 && tid == 0) {
-        g_ps_prof[0] += ps_all0; g_ps_prof[1] += ps_all1; g_ps_prof[2] += ps_all2; g_ps_prof[3] += ps_all3;
-        g_ps_prof[4] += ps_gu0; g_ps_prof[5] += ps_gu1; g_ps_prof[6] += ps_gu2; g_ps_prof[7] += ps_gu3;
-        g_ps_prof[12] += ps_ctr;
-        g_ps_prof[8] += ps_dn0; g_ps_prof[9] += ps_dn1; g_ps_prof[10] += ps_dn2; g_ps_prof[11] += ps_dn3;
-    }
-#endif
 }
 
 __global__ void __launch_bounds__(kBlockThreads, 1) decode_sweep_persistent_kernel(const PSweepArgs a) {
@@ -696,21 +664,6 @@ constexpr size_t kSmemBytes = static_cast<size_t>(kSlots) * kSlotStride + kMaxK 
                               kMaxHidden * 2 + 512 * 2 + 2 * kPartFloats * 4 + kConsumerWarps * 8 + 16 + 2 * kSlots * 8 + 16;
 
 }  // namespace
-
-int psweep_prof(unsigned long long* out, bool reset) {
-#ifdef W4A16_TC_PROFILE
-    cudaError_t e = cudaMemcpyFromSymbol(out, g_ps_prof, sizeof(unsigned long long) * 16);
-    if (e == cudaSuccess && reset) {
-        unsigned long long z[16] = {};
-        e = cudaMemcpyToSymbol(g_ps_prof, z, sizeof(z));
-    }
-    return static_cast<int>(e);
-#else
-    (void)reset;
-    for (int i = 0; i < 16; ++i) out[i] = 0;
-    return 0;
-#endif
-}
 
 // ---- host interface (used by decode_sweep.cu) -------------------------------------------------------
 

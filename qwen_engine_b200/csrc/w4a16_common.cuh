@@ -277,6 +277,62 @@ __device__ __forceinline__ void quantize_group_halfwarp_to_smem(const float v[8]
     }
 }
 
+// Q8_1 of one group of 128 taken straight from fp32 values, as the reference's flash-decode combine step
+// quantises an attention head for the O projection (src/kernels/attention_gqa.cu:263-310):
+//   d = max(max|v| / 127, 1e-8),  q = clamp(rn(v / d), -127, 127)  -- one division per element, where the
+// fp16 quantiser above multiplies by 1 / d; the bytes can therefore differ from quantising fp16(v).
+// Half-warp form: lane hl owns elements 8 hl .. 8 hl + 7, i.e. exactly one sum8 octet.  Both halves of a
+// warp call it together.  Returns the eight bytes; *octet_sum = their plain sum, *d_out the group scale.
+__device__ __forceinline__ uint2 quantize_group_f32_div_halfwarp(const float v[8], int32_t* octet_sum, float* d_out) {
+    float m = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = fmaxf(m, fabsf(v[j]));
+#pragma unroll
+    for (int mask = 8; mask > 0; mask >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, mask));
+    const float d = fmaxf(__fdiv_rn(m, 127.0f), 1e-8f);
+    uint32_t packed[2] = {0, 0};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        int q = __float2int_rn(__fdiv_rn(v[j], d));
+        q = max(-127, min(127, q));
+        packed[j >> 2] |= (static_cast<uint32_t>(q) & 0xFFu) << (8 * (j & 3));
+    }
+    *octet_sum = byte_sum(packed[0]) + byte_sum(packed[1]);
+    *d_out = d;
+    return make_uint2(packed[0], packed[1]);
+}
+
+// fp32 vector of whole groups (attention heads of 128) -> staged Q8_1 in shared memory, every CTA for itself.
+// x must be 16-byte aligned; blockDim.x a multiple of 32.
+__device__ __forceinline__ void stage_x_from_f32_heads(const float* __restrict__ g_x, int K, int8_t* s_q8,
+                                                       int32_t* s_seed, float* s_scale) {
+    const int hw = threadIdx.x >> 4, hl = threadIdx.x & 15, nhw = blockDim.x >> 4;
+    const int groups = K / kGroup;
+    for (int g0 = 0; g0 < groups; g0 += nhw) {   // uniform trip count: both halves of a warp shuffle together
+        const int g = g0 + hw;
+        const bool on = g < groups;
+        float v[8];
+        if (on) {
+            const float4 a = reinterpret_cast<const float4*>(g_x + g * kGroup + hl * 8)[0];
+            const float4 b = reinterpret_cast<const float4*>(g_x + g * kGroup + hl * 8)[1];
+            v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+        }
+        int32_t sum;
+        float d;
+        const uint2 packed = quantize_group_f32_div_halfwarp(v, &sum, &d);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);   // four lanes = one 32-element chunk
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+        if (on) {
+            reinterpret_cast<uint2*>(s_q8)[g * (kGroup / 8) + hl] = packed;
+            if ((hl & 3) == 0) s_seed[g * 4 + (hl >> 2)] = -8 * sum;
+            if (hl == 0) s_scale[g] = d;
+        }
+    }
+}
+
 // True when the register form applies: few enough groups for kStageRounds rounds and 16-byte aligned vectors.
 __device__ __forceinline__ bool stage_regs_ok(const void* x, const void* gamma, int K) {
     const int nhw = blockDim.x >> 4;
@@ -297,11 +353,7 @@ __device__ __forceinline__ void prefetch_gamma(const __half* __restrict__ g_gamm
 // fp16 activation (optionally RMSNorm'ed with the prefetched gain) -> staged Q8_1.  One global round trip.
 template <bool NORM>
 __device__ __forceinline__ void stage_x_fp16_regs(const __half* g_x, const uint4 (&gam)[kStageRounds], int K, float eps,
-                                                  int8_t* s_q8, int32_t* s_seed, float* s_scale,
-                                                  unsigned int* marks = nullptr) {
-    // marks (profiling builds): cycle stamps of thread 0 after the load arrived / the reduction / the inverse / the end
-    long long mk_t = marks ? clock64() : 0;
-    auto mark = [&](int i) { if (marks) { const long long c = clock64(); marks[i] = static_cast<unsigned int>(c - mk_t); mk_t = c; } };
+                                                  int8_t* s_q8, int32_t* s_seed, float* s_scale) {
     __shared__ double s_red[8];
     const int hw = threadIdx.x >> 4, hl = threadIdx.x & 15, nhw = blockDim.x >> 4;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -313,8 +365,6 @@ __device__ __forceinline__ void stage_x_fp16_regs(const __half* g_x, const uint4
         xr[r] = g < groups ? *reinterpret_cast<const uint4*>(g_x + g * kGroup + hl * 8) : make_uint4(0, 0, 0, 0);
     }
     __half2 inv2 = __float2half2_rn(1.0f);
-    if (marks) { if (xr[0].x == 0xFFFFFFFFu) marks[7] = 1; }   // consume the load so the stamp sees its arrival
-    mark(0);
     if constexpr (NORM) {
         double ss = 0.0;
 #pragma unroll
@@ -331,12 +381,9 @@ __device__ __forceinline__ void stage_x_fp16_regs(const __half* g_x, const uint4
         for (int m = 16; m > 0; m >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, m);
         if (lane == 0) s_red[warp] = ss;
         __syncthreads();
-        mark(1);
         double t = 0.0;
         for (int w = 0; w < nwarps; ++w) t += s_red[w];   // every thread, same order: no second barrier
         inv2 = __float2half2_rn(inv_rms_from_sumsq(t, K, eps));
-        if (marks) { if (__low2float(inv2) == 12345.0f) marks[7] = 2; }
-        mark(2);
     }
     const int rounds = (groups + nhw - 1) / nhw;
 #pragma unroll
@@ -357,7 +404,6 @@ __device__ __forceinline__ void stage_x_fp16_regs(const __half* g_x, const uint4
             quantize_group_halfwarp_to_smem(v, g, hl, g < groups, s_q8, s_seed, s_scale);
         }
     }
-    mark(3);
 }
 
 // Pre-quantised Q8_1 -> shared memory with every global load of the thread in flight at once.

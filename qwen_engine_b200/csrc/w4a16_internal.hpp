@@ -19,8 +19,7 @@ struct DeviceInfo {
 };
 int ensure_device_ready(const DeviceInfo** out);  // lazy per-device set-up; returns a status
 bool pdl_enabled();
-void set_pdl_enabled(bool on);
-int env_int(const char* name, int fallback);       // read once, cached by the caller
+int option(int which);                             // current value of a W4A16_OPT_* run-time option
 
 // One launch with (optionally) the programmatic-serialisation attribute and thread-block cluster dimensions.
 template <typename... KArgs, typename... Args>
@@ -59,6 +58,8 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
 int quantize_fp16_to_q8_1(const __half* x, int8_t* q8, float* scale, int32_t* sum8, int n, cudaStream_t stream);
 int rmsnorm_q8_1(const __half* in, const __half* gamma, __half* out_opt, int8_t* q8, float* scale, int32_t* sum8,
                  int hidden, cudaStream_t stream);
+int quantize_heads_f32_to_q8_1(const float* acc, __half* out_fp16_opt, int8_t* q8, float* scale, int32_t* sum8,
+                               int heads, cudaStream_t stream);
 int quantize_set_attributes();
 
 // ---- decode GEMV (gemv_decode.cu) ----
@@ -76,6 +77,8 @@ struct GemvArgs {
     const int32_t* sum8;
     const __half* x_fp16;
     const __half* gamma;     // with x_fp16: RMSNorm gain applied before the quantiser (null = no norm)
+    const float* x_f32;      // PLAIN only: fp32 attention accumulators, one group of 128 per head, quantised in the
+                             // prologue as the reference's flash-decode epilogue does (division by the scale)
     const __half* residual;  // PLAIN only, may be null, may alias out[0]
     // PLAIN only: the same output slice is also stored into these buffers (peer GPUs' memory mapped into
     // this process: plain stores travel over NVLink)
@@ -125,6 +128,7 @@ int gemv_launch(GemvMode mode, GemvArgs args, cudaStream_t stream);
 int gemv_group_dots(const uint32_t* qweight, const int8_t* q8, const int32_t* sum8, int32_t* out, int N, int K,
                     cudaStream_t stream);
 int gemv_set_attributes();
+int gemv_copy_timeouts(unsigned int* out);   // bounded waits of the bulk-copy GEMV that ran out, on the current device
 int gemv_sample_slots(int out_features);   // candidates the sampling epilogue writes for a matrix of that height
 
 // ---- embedding lookup (embed_lookup.cu) ----
@@ -167,8 +171,6 @@ bool gemm_tc_supported(const GemmArgs& g);
 int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream);
 int gemm_tc_set_attributes();
 int gemm_tc_timeouts(unsigned int* out);
-int gemm_tc_prof(unsigned long long* out);   // zeros unless built with -DW4A16_TC_PROFILE
-int gemv_prof(int which, unsigned int* out);  // decode GEMV timeline (gemv_decode.cu); zeros unless -DW4A16_GEMV_PROFILE
 
 // ---- persistent one-kernel decode sweep (sweep_persistent.cu) ----
 struct PSweepArgs {
@@ -192,6 +194,5 @@ bool psweep_supported(int H, int I, int qdim, int kvdim);
 int psweep_set_attributes();
 void psweep_fill_layer(void* dst, const w4a16_layer_weights& L);
 int psweep_launch(const PSweepArgs& args, int sm_count, cudaStream_t stream);
-int psweep_prof(unsigned long long* out, bool reset);   // zeros unless built with -DW4A16_TC_PROFILE
 
 }  // namespace w4

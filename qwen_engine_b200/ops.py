@@ -16,7 +16,9 @@ import torch
 from ._lib import LayerWeights, QKVView, SweepDesc, W4A16Error, check, load  # noqa: F401
 
 __all__ = [
-    "QKVProjectionView", "W4A16Error", "init", "set_pdl", "load",
+    "QKVProjectionView", "W4A16Error", "init", "set_pdl", "load", "set_option", "get_option", "OPT_PDL",
+    "OPT_SIGNAL_WAIT_SPINS", "OPT_GEMV_FORM", "OPT_GEMM_MIN_TOKENS_TENSOR_CORE", "OPT_GEMM_FORM", "GEMV_FORM_AUTO",
+    "GEMV_FORM_REGISTERS", "GEMV_FORM_BULK", "quantize_attn_heads_f32_to_q8_1", "gemv_attn_heads_f32_w4a16",
     "launch_quantize_fp16_to_q8_1", "launch_rmsnorm_q8_1",
     "launch_gemv_w4a16", "launch_gemv_w4a8", "launch_gemv_qkv_w4a8",
     "launch_gemv_dual_gate_up_swiglu_w4a16", "launch_gemv_dual_gate_up_swiglu_w4a8",
@@ -73,9 +75,22 @@ def init() -> None:
     check("w4a16_init", load().w4a16_init())
 
 
+# run-time options of the library (include/w4a16_b200.h, W4A16_OPT_*)
+OPT_PDL, OPT_SIGNAL_WAIT_SPINS, OPT_GEMV_FORM, OPT_GEMM_MIN_TOKENS_TENSOR_CORE, OPT_GEMM_FORM = 1, 2, 3, 4, 5
+GEMV_FORM_AUTO, GEMV_FORM_REGISTERS, GEMV_FORM_BULK = 0, 1, 2
+
+
+def set_option(which: int, value: int) -> None:
+    check("w4a16_set_option", load().w4a16_set_option(which, int(value)))
+
+
+def get_option(which: int) -> int:
+    return int(load().w4a16_get_option(which))
+
+
 def set_pdl(enabled: bool) -> None:
     """Programmatic dependent launch on (default) or off for all launchers."""
-    check("w4a16_set_option", load().w4a16_set_option(1, int(bool(enabled))))
+    set_option(OPT_PDL, int(bool(enabled)))
 
 
 def launch_quantize_fp16_to_q8_1(input_x, out_q8, out_scale, out_sum8, num_elements, stream=None):
@@ -88,6 +103,22 @@ def launch_rmsnorm_q8_1(input, gamma, output_fp16_opt, out_q8, out_scale, out_su
     check("w4a16_rmsnorm_q8_1", load().w4a16_rmsnorm_q8_1(
         _ptr(input), _ptr(gamma), _ptr(output_fp16_opt), _ptr(out_q8), _ptr(out_scale), _ptr(out_sum8),
         _stream(stream), hidden_size))
+
+
+def quantize_attn_heads_f32_to_q8_1(attn_acc, attn_out_fp16_opt, out_q8, out_scale, out_sum8, num_heads, head_dim=128,
+                                    stream=None):
+    """Q8_1 of attention heads from their fp32 accumulators, with the rule of the reference's flash-decode
+    combine step (src/kernels/attention_gqa.cu:258-310): per head, q = rn(acc / d)."""
+    check("w4a16_quantize_attn_heads_f32_to_q8_1", load().w4a16_quantize_attn_heads_f32_to_q8_1(
+        _ptr(attn_acc), _ptr(attn_out_fp16_opt), _ptr(out_q8), _ptr(out_scale), _ptr(out_sum8), num_heads, head_dim,
+        _stream(stream)))
+
+
+def gemv_attn_heads_f32_w4a16(qweight, scales, attn_acc, residual, output_y, out_features, in_features, stream=None):
+    """O projection straight from the fp32 attention accumulators (quantised per head in the GEMV's prologue)."""
+    check("w4a16_gemv_attn_heads_f32_w4a16", load().w4a16_gemv_attn_heads_f32_w4a16(
+        _ptr(qweight), _ptr(scales), _ptr(attn_acc), _ptr(residual), _ptr(output_y), out_features, in_features,
+        _stream(stream)))
 
 
 def launch_gemv_w4a16(qweight, scales, input_x, residual, output_y, out_features, in_features, stream=None):

@@ -14,7 +14,9 @@ from pathlib import Path
 
 import numpy as np
 
-ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+if len(sys.argv) < 2:
+    sys.exit("usage: make_packer_vectors.py <reference checkout>")
+ref_root = Path(sys.argv[1])
 spec = importlib.util.spec_from_file_location("ref_gguf_conv", ref_root / "tools" / "convert_gguf_to_qwenbin.py")
 mod = importlib.util.module_from_spec(spec)
 spec.loader.exec_module(mod)

@@ -175,3 +175,99 @@ def test_full_size_prefill_row_split_agrees_with_the_unsplit_launch(ops):
     util.assert_fp16_close(a[np.ix_(m_idx, n_idx)], ref64, what="full-size prefill")
     util.assert_fp16_close(b[np.ix_(m_idx, n_idx)], ref64, what="full-size prefill, row-split")
     assert ops.debug_counter(0) == 0
+
+
+# ---- the benchmark's own sizes ----------------------------------------------------------------------------
+# Configuration 3: M in {1, 2, 4, 8, 16, 32, 64} over the four projection shapes (both sides of every dispatch
+# threshold between the few-token CUDA-core forms and the tensor-core kernel).  Configuration 4:
+# M in {128, 512, 1024, 4096} over the same shapes plus 8192 -> 28672.  Outputs are compared on sampled rows and
+# columns (the oracle dequantises only the sampled weight rows), which keeps the CPU side to seconds.
+
+_QWEN = {"qkv": (2048, 1536), "o": (1536, 1536), "gate_up": (17920, 1536), "down": (1536, 8960)}
+_cache = {}
+
+
+def _shape_weights(name):
+    """(packed, scales) on host and device, made once per shape."""
+    if name not in _cache:
+        from qwen_engine_b200 import synth
+        if name == "qkv":
+            parts = [(synth.packed_weights(31, f"q{i}", n, 1536), synth.scales(31, f"q{i}", n, 1536))
+                     for i, n in enumerate((1536, 256, 256))]
+            _cache[name] = (parts, [(util.to_dev(w), util.to_dev(s)) for w, s in parts])
+        elif name == "big":
+            rng = np.random.default_rng(99)
+            w = rng.integers(0, 2 ** 32, size=(28672, 8192 // 8), dtype=np.uint32)
+            s = rng.uniform(0.002, 0.02, size=(28672, 8192 // 128)).astype(np.float16)
+            _cache[name] = ((w, s), (util.to_dev(w), util.to_dev(s)))
+        else:
+            N, K = _QWEN[name]
+            w, s = synth.packed_weights(31, name, N, K), synth.scales(31, name, N, K)
+            _cache[name] = ((w, s), (util.to_dev(w), util.to_dev(s)))
+    return _cache[name]
+
+
+def _check_shape_at(ops, name, M, n_rows=6, n_cols=40):
+    rng = np.random.default_rng(M * 13 + len(name))
+    host, dev = _shape_weights(name)
+    K = 8192 if name == "big" else _QWEN[name][1]
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    d_x = util.to_dev(x)
+    m_idx = _sample(rng, M, n_rows)
+    if name == "qkv":
+        dims = (1536, 256, 256)
+        outs = [torch.full((M * n + 8,), float("nan"), dtype=torch.float16, device="cuda") for n in dims]
+        view = ops.QKVProjectionView(dev[0][0], dev[0][1], outs[0], dev[1][0], dev[1][1], outs[1], dev[2][0], dev[2][1], outs[2])
+        ops.launch_gemm_prefill_qkv_w4a16(view, d_x, M, None, K, 12, 2, 128)
+        torch.cuda.synchronize()
+        for (w, s), o, n in zip(host, outs, dims):
+            got = util.to_np(o)
+            assert np.isnan(got[M * n:]).all()
+            n_idx = _sample(rng, n, n_cols)
+            ref64, _ = oracle.gemm_prefill(w, s, x, m_idx, n_idx)
+            util.assert_fp16_close(got[:M * n].reshape(M, n)[np.ix_(m_idx, n_idx)], ref64, what=f"qkv M={M}")
+    elif name == "gate_up":
+        I = 8960
+        y = torch.full((M * I + 8,), float("nan"), dtype=torch.float16, device="cuda")
+        ops.launch_gemm_prefill_dual_gate_up_swiglu_w4a16(dev[0], dev[1], d_x, y, M, None, K, I)
+        torch.cuda.synchronize()
+        got = util.to_np(y)
+        assert np.isnan(got[M * I:]).all()
+        n_idx = _sample(rng, I, n_cols)
+        ref64, _ = oracle.gemm_prefill(host[0], host[1], x, m_idx, n_idx, swiglu=True)
+        util.assert_fp16_close(got[:M * I].reshape(M, I)[np.ix_(m_idx, n_idx)], ref64, what=f"gate_up M={M}")
+    else:
+        N = 28672 if name == "big" else _QWEN[name][0]
+        use_res = name != "big"
+        res = rng.standard_normal((M, N)).astype(np.float16) if use_res else None
+        y = torch.full((M * N + 8,), float("nan"), dtype=torch.float16, device="cuda")
+        if use_res:
+            y[:M * N] = util.to_dev(res).reshape(-1)      # in place, as the engine calls O and down
+        ops.launch_gemm_prefill_w4a16(dev[0], dev[1], d_x, y if use_res else None, y, M, N, K)
+        torch.cuda.synchronize()
+        got = util.to_np(y)
+        assert np.isnan(got[M * N:]).all()
+        n_idx = _sample(rng, N, n_cols)
+        ref64, _ = oracle.gemm_prefill(host[0], host[1], x, m_idx, n_idx, residual=res)
+        acc = ref64 - res[np.ix_(m_idx, n_idx)].astype(np.float64) if use_res else None
+        rep = util.assert_fp16_close(got[:M * N].reshape(M, N)[np.ix_(m_idx, n_idx)], ref64,
+                                     what=f"{name} M={M}", magnitude=acc)
+        assert rep["max_ulp"] <= 2.5, rep
+
+
+@pytest.mark.parametrize("name", ["qkv", "o", "gate_up", "down"])
+@pytest.mark.parametrize("M", [1, 2, 4, 5, 8, 16, 32, 64])
+def test_decode_batch_grid_matches_oracle(ops, name, M):
+    _check_shape_at(ops, name, M, n_rows=8, n_cols=48)
+
+
+@pytest.mark.parametrize("name,M", [(n, m) for n in ("qkv", "o", "gate_up", "down") for m in (128, 512, 1024, 4096)]
+                         + [("big", 128), ("big", 1024), ("big", 4096)])
+def test_prefill_sizes_of_the_benchmark_match_oracle(ops, name, M):
+    _check_shape_at(ops, name, M)
+    assert ops.debug_counter(0) == 0
+
+
+def test_release_cached_benchmark_weights():
+    _cache.clear()
+    torch.cuda.empty_cache()

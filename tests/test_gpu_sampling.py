@@ -265,3 +265,57 @@ def test_completion_signal_protocol_on_one_gpu(ops):
         for pv, pi, pf in peers:
             assert torch.equal(pv[lo:lo + slots], rv) and torch.equal(pi[lo:lo + slots], ri) and int(pf[1].item()) == step
         assert int(lf[1].item()) == step
+
+
+def test_a_flag_that_nothing_sets_makes_the_bounded_wait_run_out(ops):
+    """Failure detection without a fault: the reduction waits for three ranks' flags, one of which is never set
+    (a rank that did not take part in the step).  With the poll budget cut to about a millisecond
+    (W4A16_OPT_SIGNAL_WAIT_SPINS) the kernel must give up, report 1 + the rank it missed in *d_status, still
+    reduce the candidates that are there and return -- the context stays usable and the next, complete step
+    is served normally."""
+    from qwen_engine_b200 import synth
+    N, K = 6000, 1536
+    qw, sc = util.to_dev(synth.packed_weights(23, "exp", N, K)), util.to_dev(synth.scales(23, "exp", N, K))
+    slots = ops.sample_slots(N)
+    half = slots
+    lv = torch.full((2 * half,), float("nan"), dtype=torch.float32, device="cuda")
+    li = torch.full((2 * half,), -3, dtype=torch.int32, device="cuda")
+    lf = torch.zeros(3, dtype=torch.int32, device="cuda")
+    step_word = torch.zeros(1, dtype=torch.int32, device="cuda")
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    c_sig, c_ref = ops.make_sample_control(0.0, 7, 0), ops.make_sample_control(0.0, 7, 0)
+    t_sig = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    t_ref = torch.full((1,), -1, dtype=torch.int32, device="cuda")
+    rv, ri = _scratch(slots)
+    old = ops.get_option(ops.OPT_SIGNAL_WAIT_SPINS)
+    assert old == 1 << 22
+    try:
+        ops.set_option(ops.OPT_SIGNAL_WAIT_SPINS, 4000)     # 4000 polls of about 0.2 us
+        for step, missing in ((1, 2), (2, None)):
+            q8, xs, s8 = (util.to_dev(t) for t in oracle.quantize_q8_1(synth.activations(40 + step, "exp", K)))
+            ops.gemv_w4a8_sample_candidates_signal(qw, sc, q8, xs, s8, lv.data_ptr(), li.data_ptr(), [], [], [],
+                                                   lf.data_ptr() + 4, counter, step_word, half, c_sig, 0, N, K)
+            lf[0] = step
+            if missing is None:
+                lf[2] = step            # the late rank has caught up
+            status.zero_()
+            t0 = torch.cuda.Event(enable_timing=True); t1 = torch.cuda.Event(enable_timing=True)
+            t0.record()
+            ops.sample_finish_after_signals(lv.data_ptr(), li.data_ptr(), slots, half, lf.data_ptr(), 3, step_word,
+                                            status, c_sig, t_sig)
+            t1.record()
+            ops.launch_gemv_w4a8_sample_and_advance(qw, sc, q8, xs, s8, None, rv, ri, c_ref, t_ref, N, K)
+            torch.cuda.synchronize()
+            if missing is None:
+                assert int(status.item()) == 0
+            else:
+                assert int(status.item()) == 1 + missing          # which rank never signalled
+                assert t0.elapsed_time(t1) < 100.0                # gave up after milliseconds, not the default second
+            # this rank's own candidates were all there, so the token is still the right one
+            assert int(t_sig.item()) == int(t_ref.item())
+            assert ops.read_sample_control(c_sig) == ops.read_sample_control(c_ref)
+    finally:
+        ops.set_option(ops.OPT_SIGNAL_WAIT_SPINS, old)
+    with pytest.raises(ops.W4A16Error):
+        ops.set_option(ops.OPT_SIGNAL_WAIT_SPINS, 0)

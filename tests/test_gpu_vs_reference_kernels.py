@@ -120,3 +120,58 @@ def test_gemm_prefill_equals_reference_kernel(ops, ref, M):
     acc_size = np.abs(b.astype(np.float64) - util.to_np(r).astype(np.float64))
     step = util.fp16_ulp(np.maximum(np.maximum(np.abs(b.astype(np.float64)), acc_size), 1e-3))
     assert (np.abs(a.astype(np.float64) - b.astype(np.float64)) <= 2.01 * step).all()  # one step in fp16(acc), one in the add
+
+
+@pytest.mark.parametrize("name", ["o", "down", "qkv", "gate_up"])
+def test_prefill_at_1024_tokens_equals_reference_kernels(ops, ref, name):
+    """Configuration 4 at a benchmarked token count: this library's tensor-core kernel (256-token tiles) against
+    the reference's 64x64 wmma kernels (src/kernels/gemm_prefill.cu:319-610) on the same inputs."""
+    from qwen_engine_b200 import synth
+    sp = util.stream_ptr()
+    M, H, I = 1024, 1536, 8960
+    x = util.to_dev(synth.activations(41, "pf1k", M, 8960 if name == "down" else H))
+
+    def close(a, b, extra=None, steps=2.01, same=0.95):
+        a, b = util.to_np(a), util.to_np(b)
+        assert np.mean(a.view(np.uint16) == b.view(np.uint16)) >= same
+        size = np.abs(b.astype(np.float64))
+        if extra is not None:
+            size = np.maximum(size, np.abs(b.astype(np.float64) - util.to_np(extra).astype(np.float64)))
+        step = util.fp16_ulp(np.maximum(size, 1e-3))
+        assert (np.abs(a.astype(np.float64) - b.astype(np.float64)) <= steps * step).all()
+
+    if name in ("o", "down"):
+        N, K = (H, H) if name == "o" else (H, I)
+        qw, sc = util.to_dev(synth.packed_weights(42, name, N, K)), util.to_dev(synth.scales(42, name, N, K))
+        r = util.to_dev(synth.activations(43, "pfr", M, N))
+        y_a = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        y_b = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        ops.launch_gemm_prefill_w4a16(qw, sc, x, r, y_a, M, N, K)
+        ref.call("ref_gemm_prefill_w4a16", qw, sc, x, r, y_b, M, N, K, sp, 148)
+        torch.cuda.synchronize()
+        close(y_a, y_b, extra=r)
+    elif name == "qkv":
+        dims = [1536, 256, 256]
+        ws = [(util.to_dev(synth.packed_weights(44, f"t{i}", n, H)), util.to_dev(synth.scales(44, f"t{i}", n, H)))
+              for i, n in enumerate(dims)]
+        oa = [torch.empty((M, n), dtype=torch.float16, device="cuda") for n in dims]
+        ob = [torch.empty((M, n), dtype=torch.float16, device="cuda") for n in dims]
+        ops.launch_gemm_prefill_qkv_w4a16(ops.QKVProjectionView(ws[0][0], ws[0][1], oa[0], ws[1][0], ws[1][1], oa[1],
+                                                                ws[2][0], ws[2][1], oa[2]), x, M)
+        pod = RefKernels.QKVPod(ws[0][0].data_ptr(), ws[0][1].data_ptr(), ob[0].data_ptr(), ws[1][0].data_ptr(),
+                                ws[1][1].data_ptr(), ob[1].data_ptr(), ws[2][0].data_ptr(), ws[2][1].data_ptr(),
+                                ob[2].data_ptr())
+        ref.call("ref_gemm_prefill_qkv_w4a16", pod, x, M, sp, H, 12, 2, 128, 148)
+        torch.cuda.synchronize()
+        for ta, tb in zip(oa, ob):
+            close(ta, tb, steps=1.01)
+    else:
+        qw, sc = util.to_dev(synth.packed_weights(45, "gu", 2 * I, H)), util.to_dev(synth.scales(45, "gu", 2 * I, H))
+        y_a = torch.empty((M, I), dtype=torch.float16, device="cuda")
+        y_b = torch.empty((M, I), dtype=torch.float16, device="cuda")
+        ops.launch_gemm_prefill_dual_gate_up_swiglu_w4a16(qw, sc, x, y_a, M, None, H, I)
+        ref.call("ref_gemm_prefill_dual_gate_up_swiglu_w4a16", qw, sc, x, y_b, M, sp, H, I)
+        torch.cuda.synchronize()
+        # SwiGLU on fp32 accumulators whose sums were taken in different orders, expf against the fast-math
+        # __expf in one flavour: a couple of fp16 steps at most
+        close(y_a, y_b, steps=3.01, same=0.85)

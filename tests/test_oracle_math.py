@@ -116,3 +116,19 @@ def test_philox_known_answer_and_sampler_rules():
     assert not np.array_equal(s1, oracle.sample(logits, 0.8, seed=99, seq_pos=5)[2])
     u = np.exp(-np.exp(-(s1 - logits.astype(np.float32) / np.float32(0.8))))   # invert the Gumbel transform
     assert np.all((u > 0) & (u < 1))
+
+
+def test_attention_head_quantiser_follows_the_division_rule():
+    """orc_quantize_heads_f32 (reference src/kernels/attention_gqa.cu:263-310) against the same rule written
+    with numpy float32 operations: d = max(max|acc| / 127, 1e-8), q = clip(rint(acc / d)), sum8 = -8 * octet sums."""
+    rng = np.random.default_rng(3)
+    acc = (rng.standard_normal((6, 128)) * rng.uniform(0.01, 50, size=(6, 1))).astype(np.float32)
+    acc[4] = 0.0
+    out16, q8, scale, sum8 = oracle.quantize_heads_f32(acc)
+    d = np.maximum(np.abs(acc).max(axis=1) / np.float32(127.0), np.float32(1e-8)).astype(np.float32)
+    want = np.clip(np.rint(acc / d[:, None]), -127, 127).astype(np.int8)
+    assert np.array_equal(scale, d)
+    assert np.array_equal(q8.reshape(6, 128), want)
+    assert np.array_equal(sum8.reshape(6, 16), -8 * want.reshape(6, 16, 8).astype(np.int32).sum(axis=2))
+    assert np.array_equal(out16, acc.astype(np.float16))
+    assert np.all(q8.reshape(6, 128)[4] == 0) and scale[4] == np.float32(1e-8)

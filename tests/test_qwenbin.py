@@ -170,3 +170,28 @@ def test_decode_sweep_runs_on_an_uploaded_container(version):
     ref = oracle.decode_sweep(layers_np, h0)
     util.assert_fp16_close(util.to_np(h_out), ref.astype(np.float64), what=f"sweep over .qwenbin v{version}")
     sweep.close()
+
+
+def test_random_container_writer_is_read_back_by_the_library(tmp_path):
+    """tests/qwenbin_synth.py writes the random model file the drop-in test starts the reference's engine on;
+    its descriptor slots must be the ones the library's reader maps to the same tensors."""
+    from qwen_engine_b200.qwenbin import QwenBin
+    from tests import qwenbin_synth
+    path = tmp_path / "tiny_random.qwenbin"
+    info = qwenbin_synth.write_random_v2(str(path), hidden=256, inter=512, layers=2, nq=2, nkv=1, hd=128, vocab=384)
+    qb = QwenBin(str(path))
+    assert qb.dims()["version"] == 2 and qb.dims()["file_bytes"] == info["bytes"]
+    base = qb.host_base()
+    layers, glob, biases = qb.tensors(base)
+    off = info["offsets"]
+    short = {"q_weight": "q.weight", "q_scale": "q.scale", "k_weight": "k.weight", "k_scale": "k.scale",
+             "v_weight": "v.weight", "v_scale": "v.scale", "o_weight": "o.weight", "o_scale": "o.scale",
+             "gate_up_weight": "gate_up.weight", "gate_up_scale": "gate_up.scale", "down_weight": "down.weight",
+             "down_scale": "down.scale", "input_norm_gamma": "norm1", "post_norm_gamma": "norm2"}
+    for l, L in enumerate(layers):
+        for field, name in short.items():
+            assert L[field] - base == off[f"l{l}.{name}"], (l, field)
+        for field in ("q_bias", "k_bias", "v_bias"):
+            assert biases[l][field] - base == off[f"l{l}.{field[0]}.bias"]
+    assert glob["embed_weight"] - base == off["embed.weight"] and glob["lm_head_scale"] - base == off["embed.scale"]
+    assert glob["final_norm_gamma"] - base == off["final_norm"]

@@ -62,3 +62,33 @@ def test_static_scratch_gemv_refuses_vectors_beyond_the_array():
     ops.gemv_w4a16_static_scratch(w[:8 * K // 8], s[:8 * K // 128], x[:K], None, y, 8, K)
     torch.cuda.synchronize()
     assert (y == 0.0).all()
+
+
+def test_static_scratch_gemv_allocates_no_device_memory():
+    """The claim in the entry point's name: once the first call on the device has looked up the array's address,
+    further calls leave the device's free memory and torch's allocator untouched -- measured around the calls
+    themselves, with every tensor made beforehand -- and the in-place form (residual == output) that the
+    ordinary GEMV allows works here too."""
+    import ctypes
+    import qwen_engine_b200 as ops
+    from qwen_engine_b200 import synth
+    ops.init()
+    N, K = 1536, 8960
+    qw = util.to_dev(synth.packed_weights(104, "na", N, K))
+    sc = util.to_dev(synth.scales(104, "na", N, K))
+    x = util.to_dev(synth.activations(104, "na.x", K))
+    res = util.to_dev(synth.activations(104, "na.r", N))
+    want, got = res.clone(), res.clone()
+    ops.launch_gemv_w4a16(qw, sc, x, want, want, N, K)
+    ops.gemv_w4a16_static_scratch(qw, sc, x, None, torch.empty_like(got), N, K)     # warm-up: first call set-up
+    torch.cuda.synchronize()
+    free0, _ = torch.cuda.mem_get_info()
+    alloc0, reserved0 = torch.cuda.memory_allocated(), torch.cuda.memory_reserved()
+    for _ in range(5):
+        got.copy_(res)
+        ops.gemv_w4a16_static_scratch(qw, sc, x, got, got, N, K)                    # in place
+    torch.cuda.synchronize()
+    free1, _ = torch.cuda.mem_get_info()
+    assert free1 == free0, (free0, free1)
+    assert torch.cuda.memory_allocated() == alloc0 and torch.cuda.memory_reserved() == reserved0
+    assert torch.equal(got, want)
