@@ -78,6 +78,12 @@ class NSplitGemv:
         """Returns the full fp16 output [n_rows] (a view of the gathered buffer when no padding exists)."""
         mine = self.local_slice()
         if self.peer_launch is not None:
+            # One gathered buffer is reused step after step: a rank that is already past the barrier below must
+            # not store its next slice into the buffer of a rank whose consumers of this step are still reading.
+            # The leading barrier holds every rank's stores until all ranks have launched their next step, which
+            # on each of them is stream-ordered after the consumers of the previous one.  (NSplitSignalGemv keeps
+            # two halves and needs neither barrier.)
+            self.symm.barrier()
             if self.slab.rows > 0:
                 self.peer_launch(self.qweight, self.scales, q8, xscale, sum8, mine, self.peer_ptrs, self.slab.rows,
                                  self.K)
@@ -279,6 +285,9 @@ class NSplitGemm:
         if self.block_launch is not None:
             if s.rows == 0:
                 raise ValueError("the peer-store form needs rows on every rank")
+            # the matrix is reused call after call: no rank may store into a peer's copy before that peer has
+            # launched this call too, i.e. is past the readers of the previous result on its stream
+            self.symm.barrier()
             self.block_launch(self.qweight, self.scales, x, self.my_ptr, self.ld, self.peer_ptrs, M, s.rows, self.K)
             self.symm.barrier()
             return self.full[:M * self.ld].view(M, self.ld)[:, :self.n_rows]

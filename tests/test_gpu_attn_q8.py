@@ -69,6 +69,7 @@ def test_o_projection_from_attention_accumulators_equals_quantiser_plus_gemv(ops
     from qwen_engine_b200 import synth
     N, K = 1536, 1536
     acc = _heads(77, K // 128)
+    acc[2] = np.clip(acc[2], -40.0, 40.0)     # keep the projection's fp16 output finite
     qw, sc = util.to_dev(synth.packed_weights(7, "attn.o", N, K)), util.to_dev(synth.scales(7, "attn.o", N, K))
     res = util.to_dev(synth.activations(7, "attn.res", N))
     q8, xs, s8, _ = _run_lib(ops, acc, want_fp16=False)

@@ -149,7 +149,9 @@ def test_prefill_at_1024_tokens_equals_reference_kernels(ops, ref, name):
         ops.launch_gemm_prefill_w4a16(qw, sc, x, r, y_a, M, N, K)
         ref.call("ref_gemm_prefill_w4a16", qw, sc, x, r, y_b, M, N, K, sp, 148)
         torch.cuda.synchronize()
-        close(y_a, y_b, extra=r)
+        # fp16(acc) one step apart at most (two when the accumulators straddle a power of two and the step is
+        # measured at the smaller), then one rounding in the fp16 residual add
+        close(y_a, y_b, extra=r, steps=3.01)
     elif name == "qkv":
         dims = [1536, 256, 256]
         ws = [(util.to_dev(synth.packed_weights(44, f"t{i}", n, H)), util.to_dev(synth.scales(44, f"t{i}", n, H)))
@@ -164,7 +166,7 @@ def test_prefill_at_1024_tokens_equals_reference_kernels(ops, ref, name):
         ref.call("ref_gemm_prefill_qkv_w4a16", pod, x, M, sp, H, 12, 2, 128, 148)
         torch.cuda.synchronize()
         for ta, tb in zip(oa, ob):
-            close(ta, tb, steps=1.01)
+            close(ta, tb, steps=2.01)
     else:
         qw, sc = util.to_dev(synth.packed_weights(45, "gu", 2 * I, H)), util.to_dev(synth.scales(45, "gu", 2 * I, H))
         y_a = torch.empty((M, I), dtype=torch.float16, device="cuda")
