@@ -83,10 +83,11 @@ enum {
     W4A16_OPT_SIGNAL_WAIT_SPINS = 2, /* polls (about 0.2 us apart) that w4a16_sample_finish_after_signals spends on
                                         a peer's flag before it gives up and reports the rank in *d_status;
                                         default 1 << 22, about a second */
-    W4A16_OPT_GEMV_FORM = 3,         /* how the batch-1 GEMV brings its weights on chip: 0 (default) as measured
-                                        best per shape, 1 register-held 16-byte streaming loads issued before the
+    W4A16_OPT_GEMV_FORM = 3,         /* how the batch-1 GEMV brings its weights on chip: 0 (default) the measured
+                                        best, which is 1; 1 register-held 16-byte streaming loads issued before the
                                         wait for the previous kernel, 2 bulk copies (cp.async.bulk) into shared
-                                        memory.  Same output bits in every form. */
+                                        memory (K slices of long plain projections on the CTAs of a cluster).
+                                        Same output bits in every form. */
     W4A16_OPT_GEMM_MIN_TOKENS_TENSOR_CORE = 4, /* token count from which the M-token contraction runs on the
                                         tensor cores; 0 (default): the measured crossover (4 or 5 tokens) */
     W4A16_OPT_GEMM_FORM = 5,         /* tensor-core form of the M-token contraction: 0 (default) chosen by token

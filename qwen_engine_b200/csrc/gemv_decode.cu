@@ -362,8 +362,14 @@ __global__ void __maxnreg__(64) gemv_w4_bulk_kernel(const GemvArgs a) {
             constexpr uint32_t kPiece = 16384;   // several requests in flight rather than one long one
             for (uint32_t off = 0; off < bytes; off += kPiece)
                 bulk_copy_g2s(s_w + off, src + off, min(kPiece, bytes - off), bar);
-        } else {
-            for (int r = 0; r < cta_units; ++r)
+        }
+    }
+    if constexpr (CLUSTERK) {
+        // one piece per row (the rows' slices are not adjacent in memory), issued by the lanes of warp 0 side by side
+        if (tid < 32) {
+            __syncwarp();      // after lane 0 has set up the barrier
+            const uint8_t* src = reinterpret_cast<const uint8_t*>(wbase + row0 * words) + static_cast<size_t>(k_step0) * (kStepElems / 2);
+            for (int r = tid; r < cta_units; r += 32)
                 bulk_copy_g2s(s_w + r * row_bytes, src + static_cast<size_t>(r) * (K / 2), row_bytes, bar);
         }
     }
@@ -975,11 +981,14 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
     }
     // Bulk-copy form (weights through shared memory): needs 16-byte aligned weights and a CTA share that leaves
     // room for a second CTA on the SM.
-    // Measured on B200 (per-shape and in the 28-layer chain) the register form is the faster one for every
-    // shape of the model, so the bulk-copy form runs only on request (W4A16_OPT_GEMV_FORM = 2).
+    // Forms.  Measured on B200, per shape and in the 28-layer chain, register-held weight loads beat bulk copies
+    // into shared memory for every shape of the model (the copies complete as a whole, so no dot product
+    // overlaps their arrival, and the weights cross shared memory once more), and spreading the K slices of the
+    // down projection over a cluster costs more in cluster scheduling than the smaller activation staging saves.
+    // The bulk-copy form therefore runs only on request (W4A16_OPT_GEMV_FORM = 2); it splits K over a cluster
+    // where one CTA would otherwise stage or quantise more than 16 groups.
     const int form = option(W4A16_OPT_GEMV_FORM);
     if (form == 2 && aligned16 && !q8_epilogue) {
-        // K slices over a cluster when one CTA would otherwise quantise / stage a long vector many times over
         const bool cluster_k = mode == kPlain && a.gamma == nullptr && a.x_f32 == nullptr && a.ksplit >= 2 &&
                                a.ksplit <= 8 && a.K / kGroup > 16;
         GemvArgs b = a;

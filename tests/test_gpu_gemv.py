@@ -306,16 +306,20 @@ FORM_SHAPES = [
 
 
 def _both_forms(ops, fn):
-    """Runs fn() once with register-held weight loads and once with bulk copies into shared memory."""
+    """Runs fn() with register-held weight loads and with bulk copies into shared memory (where the K slices of a
+    long vector go to the CTAs of a cluster); returns (register form, bulk form) after checking that the default
+    choice gives those bits too."""
     outs = []
     try:
-        for form in (ops.GEMV_FORM_REGISTERS, ops.GEMV_FORM_BULK):
+        for form in (ops.GEMV_FORM_REGISTERS, ops.GEMV_FORM_BULK, ops.GEMV_FORM_AUTO):
             ops.set_option(ops.OPT_GEMV_FORM, form)
             outs.append(fn())
             torch.cuda.synchronize()
     finally:
         ops.set_option(ops.OPT_GEMV_FORM, ops.GEMV_FORM_AUTO)
-    return outs
+    for o in outs[2:]:
+        assert torch.equal(o.view(torch.int16), outs[1].view(torch.int16))
+    return outs[0], outs[1]
 
 
 @pytest.mark.parametrize("N,K", FORM_SHAPES)
