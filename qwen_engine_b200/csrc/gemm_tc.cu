@@ -517,6 +517,321 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
     if (warp == kDqWarps) tmem_dealloc(tmem_base, static_cast<uint32_t>(a.tmem_cols));
 }
 
+
+// ---- CTA pairs (cta_group::2) ---------------------------------------------------------------------------------
+// Prefill-sized token tiles on the single-CTA kernel above are bound by shared memory: one 128 x 256 x 16
+// instruction reads 12 KB of operands per 128 tensor-core cycles and every CTA fetches the whole 256-token
+// tile from L2 (measured: 0.57 of the bf16 peak, 0.74 even with dequantisation and token loads switched off).
+// Here two CTAs of a cluster -- two SMs -- share one 256-row x 256-token output tile: each dequantises ITS 128
+// weight rows (the A operand, M = 256 split over the pair) and loads ITS 128 tokens (half of the B operand,
+// N = 256 split over the pair); one thread of the leading CTA issues tcgen05.mma.cta_group::2, which reads
+// both CTAs' shared memory and accumulates into both CTAs' tensor memory.  Per CTA and k-block that is 16 KB of
+// tokens from L2 instead of 32 KB and 8 KB of operand reads per instruction instead of 12 KB.  The dequantised
+// weights do not pass through shared memory at all: a dequantising thread owns a weight row, which is a lane of
+// tensor memory, and writes its 64 fp16 values of a k-block there with tcgen05.st; the MMA takes A from tensor
+// memory (columns 256.. next to the 256 accumulator columns, eight k-block stages) and only B from shared
+// memory.  That removes the A tile's shared-memory writes and reads -- the kernel is bound by shared-memory
+// bandwidth otherwise -- and leaves room for eight token stages.
+//
+// Synchronisation.  Every stage has ONE "full" barrier, in the leader: the dequantising warps of both CTAs
+// arrive on it (the peer's through the cluster shared-memory window, after a proxy fence and with release at
+// cluster scope) and both CTAs' token loads complete their bytes on it (cp.async.bulk.tensor ... cta_group::2,
+// no multicast).  The leader's tcgen05.commit.cta_group::2 multicasts to the "empty" barrier of the stage in
+// BOTH CTAs, and at the end to both "accumulator ready" barriers.  Raw weight rings are private to each CTA.
+// All mbarrier waits are bounded as above; both cluster barriers are reached by every thread of both CTAs
+// whatever happened before, and tensor memory is allocated and freed by the same warp of each CTA.
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_remote_release(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(leader_bar)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(static_cast<uint16_t>(3)) : "memory");
+}
+// Instruction descriptor of the pair: D fp32, A/B fp16, both K-major, M = 256 (128 rows per CTA), N = n.
+__device__ __forceinline__ uint32_t make_idesc_pair(int n) {
+    return (1u << 4) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(256 >> 4) << 24);
+}
+
+constexpr int kPairGroups = 4;
+constexpr int kPairDqWarps = 4 * kPairGroups;
+constexpr int kPairThreads = (kPairDqWarps + 3) * 32;   // + MMA warp, token TMA warp, weight TMA warp
+
+// 16 consecutive 32-bit columns of this thread's tensor-memory lane, from registers.
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem]^T over the CTA pair: A (this pair's 256 weight rows, 128 per CTA, 16 k as 8 packed
+// columns) comes from tensor memory, B from both CTAs' shared memory.
+__device__ __forceinline__ void tc_mma_f16_pair_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                                   uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+constexpr int kPairAccumCols = 256;          // accumulator: 256 tokens
+constexpr int kPairACols = kBK / 2;          // one k-block of dequantised weights: 64 fp16 = 32 packed columns
+
+template <int MODE>
+__global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(const __grid_constant__ TcArgs a) {
+    constexpr int NG = kPairGroups;
+    constexpr int kDqWarps = kPairDqWarps;
+    constexpr int kDqThreads = kDqWarps * 32;
+    extern __shared__ uint8_t smem_raw_base[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_base) + 1023) & ~uintptr_t(1023));
+    const int T = a.T, S = a.stages, K = a.K;      // T: tokens of the pair's tile (both CTAs' halves)
+    const int Th = T / 2;                          // tokens this CTA loads
+    const int G = K / kGroup;
+    const int b_bytes = Th * 128;
+    uint8_t* s_raw = smem;
+    uint8_t* s_b = s_raw + kRawStages * kRawBytes;
+    __half* s_scale = reinterpret_cast<__half*>(s_b + S * b_bytes);
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_scale) + ((G * kTileRows * 2 + 15) & ~15));
+    const uint32_t bar0 = smem_u32(s_bar);
+    auto raw_full = [&](int i) { return bar0 + 8u * i; };
+    auto raw_empty = [&](int i) { return bar0 + 8u * (kRawStages + i); };
+    auto full = [&](int i) { return bar0 + 8u * (2 * kRawStages + i); };
+    auto ab_empty = [&](int i) { return bar0 + 8u * (2 * kRawStages + 2 * kMaxStages + i); };
+    const uint32_t accum_full = bar0 + 8u * (2 * kRawStages + 3 * kMaxStages);
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + (2 * kRawStages + 3 * kMaxStages + 1));
+    volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const uint32_t rank = cluster_cta_rank();
+    const bool leader = rank == 0;
+
+    int t = 0, tile = blockIdx.x;     // consecutive 128-row tiles form a pair; tensors hold an even number of tiles
+    if constexpr (MODE == kQkv) {
+        if (tile >= a.tiles[0]) { tile -= a.tiles[0]; t = 1; }
+        if (t == 1 && tile >= a.tiles[1]) { tile -= a.tiles[1]; t = 2; }
+    }
+    const int n0 = tile * kTileRows;
+    const int m0 = blockIdx.y * T;
+    const int rows_t = a.rows[t];
+    const int num_sb = K / 256, num_kb = K / kBK;
+
+    if (tid == 0) {
+        for (int i = 0; i < kRawStages; ++i) { mbar_init(raw_full(i), 1); mbar_init(raw_empty(i), kDqWarps); }
+        // full: 4 warps of each CTA's dequantising group + the leader's expect_tx arrival
+        for (int i = 0; i < S; ++i) { mbar_init(full(i), 2 * 4 + 1); mbar_init(ab_empty(i), 1); }
+        mbar_init(accum_full, 1);
+        *s_abort = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&a.tmap_x);
+        tma_prefetch_desc(&a.tmap_w[t]);
+    }
+    if (warp == kDqWarps) {          // the same warp in both CTAs, the same shared-memory offset for the result
+        tmem_alloc_pair(smem_u32(s_tmem), static_cast<uint32_t>(a.tmem_cols));
+        tmem_relinquish_pair();
+    }
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();              // the peer's barriers exist before anything arrives on them from here
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+
+    if (warp < kDqWarps) {
+        const int r = (warp & 3) * 32 + lane;
+        const int part = warp >> 2;
+        {
+            const __half* sc = a.scales[t];
+            for (int idx = tid; idx < kTileRows * G; idx += kDqThreads) {
+                const int rr = idx / G, g = idx - rr * G;
+                const int row = n0 + rr;
+                s_scale[g * kTileRows + rr] = row < rows_t ? sc[static_cast<size_t>(row) * G + g] : __float2half(0.0f);
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");
+        }
+        const int sw = r & 7;
+        bool ok = true;
+        int rs = 0;
+        uint32_t rph = 0;
+        int s = part;
+        uint32_t ph = 0;
+        while (s >= S) { s -= S; ph ^= 1; }
+        for (int sb = 0; sb < num_sb && ok; ++sb) {
+            ok = warp_wait(raw_full(rs), rph, s_abort, lane);
+            if (!ok) break;
+            const uint8_t* raw_row = s_raw + rs * kRawBytes + r * 128;
+            const __half2 sc0 = __half2half2(s_scale[(2 * sb) * kTileRows + r]);
+            const __half2 sc1 = __half2half2(s_scale[(2 * sb + 1) * kTileRows + r]);
+#pragma unroll
+            for (int j = part; j < 4; j += NG) {
+                ok = warp_wait(ab_empty(s), ph ^ 1, s_abort, lane);
+                if (!ok) break;
+                const uint4 w0 = *reinterpret_cast<const uint4*>(raw_row + (((2 * j) ^ sw) << 4));
+                const uint4 w1 = *reinterpret_cast<const uint4*>(raw_row + (((2 * j + 1) ^ sw) << 4));
+                const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                const __half2 sc2 = (j < 2) ? sc0 : sc1;
+                // the row's 64 dequantised weights, two per 32-bit column, straight into this thread's lane of
+                // tensor memory: the A operand never passes through shared memory
+                const uint32_t a_lane = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
+                                        static_cast<uint32_t>(kPairAccumCols + s * kPairACols);
+#pragma unroll
+                for (int hw = 0; hw < 2; ++hw) {
+                    uint32_t cols[16];
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        __half2 h[4];
+                        dequant_word_fp16(words[4 * hw + w], sc2, h);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) cols[4 * w + q] = *reinterpret_cast<const uint32_t*>(&h[q]);
+                    }
+                    tmem_st16(a_lane + 16u * hw, cols);
+                }
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) {
+                    if (leader) mbar_arrive(full(s));
+                    else mbar_arrive_remote_release(cluster_map_shared(full(s), 0));
+                }
+                s += NG;
+                while (s >= S) { s -= S; ph ^= 1; }
+            }
+            __syncwarp();
+            if (lane == 0 && ok) mbar_arrive(raw_empty(rs));
+            if (++rs == kRawStages) { rs = 0; rph ^= 1; }
+        }
+        // ---- epilogue: this CTA's 128 weight rows x all T tokens of the pair's tile ----
+        if (ok) ok = warp_wait(accum_full, 0, s_abort, lane);
+        tc_fence_after();
+        if (ok) {
+            const int n = n0 + r;
+            const bool row_ok = n < rows_t;
+            __half* out = a.out[t];
+            const int ld = a.out_ld[t];
+            for (int c0 = part * 16; c0 < T; c0 += 16 * NG) {
+                uint32_t v[16];
+                const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+                tmem_ld16(lane_base + static_cast<uint32_t>(c0), v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int m = m0 + c0 + j;
+                    const float acc = __uint_as_float(v[j]);
+                    if constexpr (MODE == kSwiglu) {
+                        const float up = __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
+                        if ((lane & 1) == 0 && row_ok && m < a.M) {
+                            const float y = (acc / (1.0f + expf(-acc))) * up;
+                            out[static_cast<size_t>(m) * ld + (n >> 1)] = __float2half_rn(y);
+                        }
+                    } else {
+                        if (row_ok && m < a.M) {
+                            __half y = __float2half_rn(acc);
+                            if constexpr (MODE == kPlain) {
+                                if (a.residual != nullptr) y = __hadd(y, a.residual[static_cast<size_t>(m) * ld + n]);
+                            }
+                            out[static_cast<size_t>(m) * ld + n] = y;
+                        }
+                    }
+                }
+            }
+        }
+    } else if (warp == kDqWarps) {
+        // ---- MMA issue: the leading CTA only ----
+        if (leader) {
+            const uint32_t idesc = make_idesc_pair(T);
+            const uint64_t b_desc0 = make_smem_desc(smem_u32(s_b));
+            const uint32_t b_step = static_cast<uint32_t>(b_bytes) >> 4;
+            const uint32_t a_tmem0 = tmem_base + kPairAccumCols;
+            uint64_t b_desc = b_desc0;
+            uint32_t a_tmem = a_tmem0;
+            int s = 0;
+            uint32_t ph = 0;
+            bool ok = true;
+            bool ready = mbar_test_wait(full(0), 0);
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!ready) ok = warp_wait(full(s), ph, s_abort, lane);
+                if (!ok) break;
+                tc_fence_after();
+                int sn = s + 1;
+                uint32_t phn = ph;
+                if (sn == S) { sn = 0; phn ^= 1; }
+                if (lane == 0) {
+#pragma unroll
+                    for (int ks = 0; ks < kBK / 16; ++ks)
+                        tc_mma_f16_pair_ts(tmem_base, a_tmem + 8u * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
+                    tc_commit_pair(ab_empty(s));
+                }
+                ready = (kb + 1 < num_kb) ? mbar_test_wait(full(sn), phn) : true;
+                ready = __all_sync(0xFFFFFFFFu, ready);
+                a_tmem += kPairACols;
+                b_desc += b_step;
+                if (sn == 0) { a_tmem = a_tmem0; b_desc = b_desc0; }
+                s = sn;
+                ph = phn;
+            }
+            if (ok && lane == 0) tc_commit_pair(accum_full);
+        }
+        __syncwarp();
+    } else if (warp == kDqWarps + 1) {
+        // ---- TMA: this CTA's half of the token tile; the bytes are counted on the LEADER's barrier ----
+        if (lane == 0) {
+            int s = 0;
+            uint32_t ph = 0;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!mbar_wait(ab_empty(s), ph ^ 1, s_abort)) break;
+                if (leader) mbar_arrive_expect_tx(full(s), static_cast<uint32_t>(2 * b_bytes));
+                tma_load_2d_pair(smem_u32(s_b + s * b_bytes), &a.tmap_x, kb * kBK, m0 + static_cast<int>(rank) * Th,
+                                 cluster_map_shared(full(s), 0));
+                if (++s == S) { s = 0; ph ^= 1; }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---- TMA: raw packed weights of this CTA's 128 rows (private ring) ----
+        if (lane == 0) {
+            int rs = 0;
+            uint32_t rph = 0;
+            for (int sb = 0; sb < num_sb; ++sb) {
+                if (!mbar_wait(raw_empty(rs), rph ^ 1, s_abort)) break;
+                mbar_arrive_expect_tx(raw_full(rs), kRawBytes);
+                tma_load_2d(smem_u32(s_raw + rs * kRawBytes), &a.tmap_w[t], sb * 128, n0, raw_full(rs));
+                if (++rs == kRawStages) { rs = 0; rph ^= 1; }
+            }
+        }
+        __syncwarp();
+    }
+
+    // Neither CTA may leave (or free its tensor memory) while the other's instructions can still touch its
+    // shared memory, barriers or accumulators.
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == kDqWarps) tmem_dealloc_pair(tmem_base, static_cast<uint32_t>(a.tmem_cols));
+}
+
 // ---- host side ----------------------------------------------------------------------------
 
 using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -555,6 +870,12 @@ size_t tc_smem_bytes(int T, int S, int K) {
            ((G * kTileRows * 2 + 15) & ~size_t(15)) + (2 * kRawStages + 3 * kMaxStages + 1) * 8 + 16;
 }
 
+size_t tc_pair_smem_bytes(int T, int S, int K) {     // per CTA: half of the token tile per stage
+    const size_t G = K / kGroup;
+    return 1024 + static_cast<size_t>(kRawStages) * kRawBytes + static_cast<size_t>(S) * ((T / 2) * 128) +
+           ((G * kTileRows * 2 + 15) & ~size_t(15)) + (2 * kRawStages + 3 * kMaxStages + 1) * 8 + 16;
+}
+
 }  // namespace
 
 namespace {
@@ -589,7 +910,12 @@ cudaError_t launch_tc(int mode, dim3 grid, size_t smem, cudaStream_t stream, con
 }  // namespace
 
 int gemm_tc_set_attributes() {
-    cudaError_t e = raise_tc_smem_modes<2>();
+    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_tc_pair_kernel<kPlain>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_w4a16_tc_pair_kernel<kQkv>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(gemm_w4a16_tc_pair_kernel<kSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    if (e == cudaSuccess) e = raise_tc_smem_modes<2>();
     if (e == cudaSuccess) e = raise_tc_smem_modes<4>();
     return static_cast<int>(e);
 }
@@ -661,6 +987,35 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
             return W4A16_ERR_INVALID_ARG;
     }
     for (int t = nt; t < 3; ++t) a.tmap_w[t] = a.tmap_w[0];
+
+    // CTA pairs (cta_group::2) for prefill-sized token tiles: 256 tokens per tile, no K split, no peer stores,
+    // and an even number of 128-row tiles in every weight tensor (a pair never straddles two tensors).
+    const int gemm_form = option(W4A16_OPT_GEMM_FORM);
+    bool pairs = gemm_form != 1 && T == 256 && a.ksplit == 1 && a.num_peers == 0;
+    for (int t = 0; t < nt; ++t) pairs = pairs && a.tiles[t] % 2 == 0;
+    if (pairs) {
+        int SP = kMaxStages;
+        while (SP > 2 && tc_pair_smem_bytes(T, SP, g.K) > 227 * 1024) --SP;
+        pairs = tc_pair_smem_bytes(T, SP, g.K) <= 227 * 1024;
+        if (pairs) {
+            a.stages = SP;
+            a.issuers = 1;
+            a.tmem_cols = 512;      // 256 accumulator columns + up to 8 stages x 32 columns of dequantised weights
+            if (!encode_2d(&a.tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.x, static_cast<uint64_t>(g.K),
+                           static_cast<uint64_t>(g.M), static_cast<uint64_t>(g.K) * 2, kBK, static_cast<uint32_t>(T / 2)))
+                return W4A16_ERR_INVALID_ARG;
+            const dim3 pgrid(total_tiles, (g.M + T - 1) / T, 1), pblock(kPairThreads), pcluster(2, 1, 1);
+            const size_t psmem = tc_pair_smem_bytes(T, SP, g.K);
+            const bool pdl = pdl_enabled();
+            cudaError_t pe;
+            switch (g.mode) {
+                case kPlain: pe = launch_kernel_cluster(gemm_w4a16_tc_pair_kernel<kPlain>, pgrid, pblock, psmem, stream, pdl, pcluster, a); break;
+                case kQkv: pe = launch_kernel_cluster(gemm_w4a16_tc_pair_kernel<kQkv>, pgrid, pblock, psmem, stream, pdl, pcluster, a); break;
+                default: pe = launch_kernel_cluster(gemm_w4a16_tc_pair_kernel<kSwiglu>, pgrid, pblock, psmem, stream, pdl, pcluster, a); break;
+            }
+            return static_cast<int>(pe);
+        }
+    }
     if (!encode_2d(&a.tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.x, static_cast<uint64_t>(g.K),
                    static_cast<uint64_t>(g.M), static_cast<uint64_t>(g.K) * 2, kBK, static_cast<uint32_t>(T)))
         return W4A16_ERR_INVALID_ARG;
