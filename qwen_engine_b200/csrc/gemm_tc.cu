@@ -600,42 +600,67 @@ __device__ __forceinline__ void tc_mma_f16_pair_ts(uint32_t tmem_d, uint32_t tme
 constexpr int kPairAccumCols = 256;          // accumulator: 256 tokens
 constexpr int kPairACols = kBK / 2;          // one k-block of dequantised weights: 64 fp16 = 32 packed columns
 
+constexpr int kPairTokens = 256;             // tokens of a pair's tile (128 loaded by each CTA)
+constexpr int kPairStageTokens = 128;        // tokens per epilogue pass through the staging buffer
+constexpr int kPairStagePitch = kTileRows * 2 + 16;   // bytes per token row of the staging buffer (+16: bank spread)
+constexpr int kPairStageBytes = kPairStageTokens * kPairStagePitch;
+
+// Which 128-row tile of which tensor, and which tokens, a pair tile index stands for (this CTA's half).
+struct PairTile {
+    int t, n0, m0;
+};
+__device__ __forceinline__ PairTile pair_tile(const TcArgs& a, int pt, int n_pairs, int rank, bool qkv) {
+    PairTile r;
+    const int m_idx = pt / n_pairs;
+    int tile = 2 * (pt - m_idx * n_pairs) + rank;      // consecutive 128-row tiles form a pair
+    r.t = 0;
+    if (qkv) {
+        if (tile >= a.tiles[0]) { tile -= a.tiles[0]; r.t = 1; }
+        if (r.t == 1 && tile >= a.tiles[1]) { tile -= a.tiles[1]; r.t = 2; }
+    }
+    r.n0 = tile * kTileRows;
+    r.m0 = m_idx * kPairTokens;
+    return r;
+}
+
+// Persistent: every pair walks the pair tiles p, p + P, ... (neighbouring indices share their tokens, so the token
+// slab stays in L2 while the weights stream).  The rings of raw weights, dequantised weights (tensor memory)
+// and tokens run on across tile boundaries, so the loaders fill them for the next tile while this tile's
+// accumulators are drained.  The group scales are not staged: a dequantising thread reads the two scales of
+// its row per 256-element super-block straight from global memory, one super-block ahead.
+// Epilogue: fp32 accumulators -> fp16 -> a [token][row] staging tile in shared memory -> 16-byte row-contiguous
+// stores (a warp writes 256 consecutive bytes of two token rows), residual added from 16-byte loads.
 template <int MODE>
 __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(const __grid_constant__ TcArgs a) {
     constexpr int NG = kPairGroups;
     constexpr int kDqWarps = kPairDqWarps;
     constexpr int kDqThreads = kDqWarps * 32;
+    constexpr int T = kPairTokens, Th = T / 2;
+    constexpr int b_bytes = Th * 128;
     extern __shared__ uint8_t smem_raw_base[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_base) + 1023) & ~uintptr_t(1023));
-    const int T = a.T, S = a.stages, K = a.K;      // T: tokens of the pair's tile (both CTAs' halves)
-    const int Th = T / 2;                          // tokens this CTA loads
+    const int S = a.stages, K = a.K;
     const int G = K / kGroup;
-    const int b_bytes = Th * 128;
     uint8_t* s_raw = smem;
     uint8_t* s_b = s_raw + kRawStages * kRawBytes;
-    __half* s_scale = reinterpret_cast<__half*>(s_b + S * b_bytes);
-    uint64_t* s_bar = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(s_scale) + ((G * kTileRows * 2 + 15) & ~15));
+    uint8_t* s_stage = s_b + S * b_bytes;
+    uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_stage + kPairStageBytes);
     const uint32_t bar0 = smem_u32(s_bar);
     auto raw_full = [&](int i) { return bar0 + 8u * i; };
     auto raw_empty = [&](int i) { return bar0 + 8u * (kRawStages + i); };
     auto full = [&](int i) { return bar0 + 8u * (2 * kRawStages + i); };
     auto ab_empty = [&](int i) { return bar0 + 8u * (2 * kRawStages + 2 * kMaxStages + i); };
     const uint32_t accum_full = bar0 + 8u * (2 * kRawStages + 3 * kMaxStages);
-    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + (2 * kRawStages + 3 * kMaxStages + 1));
+    const uint32_t accum_empty = accum_full + 8u;
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + (2 * kRawStages + 3 * kMaxStages + 2));
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t rank = cluster_cta_rank();
+    const int rank = static_cast<int>(cluster_cta_rank());
     const bool leader = rank == 0;
-
-    int t = 0, tile = blockIdx.x;     // consecutive 128-row tiles form a pair; tensors hold an even number of tiles
-    if constexpr (MODE == kQkv) {
-        if (tile >= a.tiles[0]) { tile -= a.tiles[0]; t = 1; }
-        if (t == 1 && tile >= a.tiles[1]) { tile -= a.tiles[1]; t = 2; }
-    }
-    const int n0 = tile * kTileRows;
-    const int m0 = blockIdx.y * T;
-    const int rows_t = a.rows[t];
+    const int pair_id = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int n_pairs = (a.tiles[0] + a.tiles[1] + a.tiles[2]) / 2;
+    const int total_pt = n_pairs * ((a.M + T - 1) / T);
     const int num_sb = K / 256, num_kb = K / kBK;
 
     if (tid == 0) {
@@ -643,10 +668,11 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
         // full: 4 warps of each CTA's dequantising group + the leader's expect_tx arrival
         for (int i = 0; i < S; ++i) { mbar_init(full(i), 2 * 4 + 1); mbar_init(ab_empty(i), 1); }
         mbar_init(accum_full, 1);
+        mbar_init(accum_empty, 2 * kDqWarps);     // every draining warp of both CTAs
         *s_abort = 0;
         fence_barrier_init();
         tma_prefetch_desc(&a.tmap_x);
-        tma_prefetch_desc(&a.tmap_w[t]);
+        tma_prefetch_desc(&a.tmap_w[0]);
     }
     if (warp == kDqWarps) {          // the same warp in both CTAs, the same shared-memory offset for the result
         tmem_alloc_pair(smem_u32(s_tmem), static_cast<uint32_t>(a.tmem_cols));
@@ -661,42 +687,50 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
     const uint32_t tmem_base = *s_tmem;
 
     if (warp < kDqWarps) {
+        // ================= dequantise (thread = weight row = tensor-memory lane), then drain =================
         const int r = (warp & 3) * 32 + lane;
-        const int part = warp >> 2;
-        {
-            const __half* sc = a.scales[t];
-            for (int idx = tid; idx < kTileRows * G; idx += kDqThreads) {
-                const int rr = idx / G, g = idx - rr * G;
-                const int row = n0 + rr;
-                s_scale[g * kTileRows + rr] = row < rows_t ? sc[static_cast<size_t>(row) * G + g] : __float2half(0.0f);
-            }
-            asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");
-        }
+        const int part = warp >> 2;              // this group's k-block of every super-block, its token share when draining
         const int sw = r & 7;
+        const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
         bool ok = true;
         int rs = 0;
         uint32_t rph = 0;
-        int s = part;
+        int s = part;                            // ring position of this group's next k-block
         uint32_t ph = 0;
         while (s >= S) { s -= S; ph ^= 1; }
-        for (int sb = 0; sb < num_sb && ok; ++sb) {
-            ok = warp_wait(raw_full(rs), rph, s_abort, lane);
-            if (!ok) break;
-            const uint8_t* raw_row = s_raw + rs * kRawBytes + r * 128;
-            const __half2 sc0 = __half2half2(s_scale[(2 * sb) * kTileRows + r]);
-            const __half2 sc1 = __half2half2(s_scale[(2 * sb + 1) * kTileRows + r]);
-#pragma unroll
-            for (int j = part; j < 4; j += NG) {
+        uint32_t acc_ph = 0;
+        // scales of the first super-block of the first tile
+        uint32_t sc_next = 0;
+        auto load_scales = [&](const PairTile& pt, int sb) -> uint32_t {
+            const int row = pt.n0 + r;
+            if (row >= a.rows[pt.t]) return 0u;   // rows past the tensor dequantise to zero
+            return __ldg(reinterpret_cast<const uint32_t*>(a.scales[pt.t] + static_cast<size_t>(row) * G + 2 * sb));
+        };
+        if (pair_id < total_pt) sc_next = load_scales(pair_tile(a, pair_id, n_pairs, rank, MODE == kQkv), 0);
+        // Every one of the 16 warps reaches every bar.sync of this loop, whatever its waits returned: a warp
+        // whose bounded wait ran out has raised the abort flag, and all warps leave together right after the
+        // first barrier of the tile.
+        for (int pt_i = pair_id; pt_i < total_pt; pt_i += num_pairs) {
+            const PairTile pt = pair_tile(a, pt_i, n_pairs, rank, MODE == kQkv);
+            const int rows_t = a.rows[pt.t];
+            for (int sb = 0; sb < num_sb && ok; ++sb) {
+                const uint32_t sc_pair = sc_next;
+                // one super-block ahead (the next tile's first when this tile is through)
+                if (sb + 1 < num_sb) sc_next = load_scales(pt, sb + 1);
+                else if (pt_i + num_pairs < total_pt) sc_next = load_scales(pair_tile(a, pt_i + num_pairs, n_pairs, rank, MODE == kQkv), 0);
+                ok = warp_wait(raw_full(rs), rph, s_abort, lane);
+                if (!ok) break;
+                const uint8_t* raw_row = s_raw + rs * kRawBytes + r * 128;
+                const int j = part;              // NG == 4: one k-block of the super-block per group
                 ok = warp_wait(ab_empty(s), ph ^ 1, s_abort, lane);
                 if (!ok) break;
+                tc_fence_after();
                 const uint4 w0 = *reinterpret_cast<const uint4*>(raw_row + (((2 * j) ^ sw) << 4));
                 const uint4 w1 = *reinterpret_cast<const uint4*>(raw_row + (((2 * j + 1) ^ sw) << 4));
                 const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-                const __half2 sc2 = (j < 2) ? sc0 : sc1;
-                // the row's 64 dequantised weights, two per 32-bit column, straight into this thread's lane of
-                // tensor memory: the A operand never passes through shared memory
-                const uint32_t a_lane = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16) +
-                                        static_cast<uint32_t>(kPairAccumCols + s * kPairACols);
+                const uint16_t sbits = static_cast<uint16_t>(j < 2 ? (sc_pair & 0xFFFFu) : (sc_pair >> 16));
+                const __half2 sc2 = __half2half2(__ushort_as_half(sbits));
+                const uint32_t a_lane = lane_base + static_cast<uint32_t>(kPairAccumCols + s * kPairACols);
 #pragma unroll
                 for (int hw = 0; hw < 2; ++hw) {
                     uint32_t cols[16];
@@ -715,110 +749,168 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
                 if (lane == 0) {
                     if (leader) mbar_arrive(full(s));
                     else mbar_arrive_remote_release(cluster_map_shared(full(s), 0));
+                    mbar_arrive(raw_empty(rs));
                 }
                 s += NG;
                 while (s >= S) { s -= S; ph ^= 1; }
+                if (++rs == kRawStages) { rs = 0; rph ^= 1; }
             }
-            __syncwarp();
-            if (lane == 0 && ok) mbar_arrive(raw_empty(rs));
-            if (++rs == kRawStages) { rs = 0; rph ^= 1; }
-        }
-        // ---- epilogue: this CTA's 128 weight rows x all T tokens of the pair's tile ----
-        if (ok) ok = warp_wait(accum_full, 0, s_abort, lane);
-        tc_fence_after();
-        if (ok) {
-            const int n = n0 + r;
-            const bool row_ok = n < rows_t;
-            __half* out = a.out[t];
-            const int ld = a.out_ld[t];
-            for (int c0 = part * 16; c0 < T; c0 += 16 * NG) {
-                uint32_t v[16];
-                const uint32_t lane_base = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
-                tmem_ld16(lane_base + static_cast<uint32_t>(c0), v);
-                tmem_ld_wait();
+            // ---- drain this tile: 128 weight rows of this CTA x 256 tokens, two passes of 128 tokens ----
+            if (ok) ok = warp_wait(accum_full, acc_ph, s_abort, lane);
+            acc_ph ^= 1;
+            asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");
+            if (*s_abort) break;             // the same answer in all 16 warps
+            tc_fence_after();
+            const int n = pt.n0 + r;
+            __half* out = a.out[pt.t];
+            const int ld = a.out_ld[pt.t];
+            constexpr int kOutPerRow = MODE == kSwiglu ? kTileRows / 2 : kTileRows;    // outputs of a token row in the tile
+            const int n_out0 = MODE == kSwiglu ? pt.n0 / 2 : pt.n0;
+            const int n_valid = MODE == kSwiglu ? max(0, min(kOutPerRow, (rows_t - pt.n0) / 2)) : max(0, min(kOutPerRow, rows_t - pt.n0));
+            const bool vec_ok = (ld % 8 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (n_valid % 8 == 0) &&
+                                (MODE != kPlain || a.residual == nullptr || reinterpret_cast<uintptr_t>(a.residual) % 16 == 0);
+#pragma unroll 1
+            for (int pass = 0; pass < T / kPairStageTokens; ++pass) {
+                // this warp: its 32 rows x 32 tokens (part) of the pass
 #pragma unroll
-                for (int j = 0; j < 16; ++j) {
-                    const int m = m0 + c0 + j;
-                    const float acc = __uint_as_float(v[j]);
-                    if constexpr (MODE == kSwiglu) {
-                        const float up = __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
-                        if ((lane & 1) == 0 && row_ok && m < a.M) {
-                            const float y = (acc / (1.0f + expf(-acc))) * up;
-                            out[static_cast<size_t>(m) * ld + (n >> 1)] = __float2half_rn(y);
-                        }
-                    } else {
-                        if (row_ok && m < a.M) {
-                            __half y = __float2half_rn(acc);
-                            if constexpr (MODE == kPlain) {
-                                if (a.residual != nullptr) y = __hadd(y, a.residual[static_cast<size_t>(m) * ld + n]);
-                            }
-                            out[static_cast<size_t>(m) * ld + n] = y;
+                for (int q = 0; q < 2; ++q) {
+                    const int tok0 = part * 32 + q * 16;          // token inside the pass
+                    uint32_t v[16];
+                    tmem_ld16(lane_base + static_cast<uint32_t>(pass * kPairStageTokens + tok0), v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int jj = 0; jj < 16; ++jj) {
+                        const float acc = __uint_as_float(v[jj]);
+                        uint8_t* row_ptr = s_stage + (tok0 + jj) * kPairStagePitch;
+                        if constexpr (MODE == kSwiglu) {
+                            const float up = __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
+                            if ((lane & 1) == 0)
+                                reinterpret_cast<__half*>(row_ptr)[r >> 1] = __float2half_rn((acc / (1.0f + expf(-acc))) * up);
+                        } else {
+                            reinterpret_cast<__half*>(row_ptr)[r] = __float2half_rn(acc);
                         }
                     }
                 }
+                if (pass == T / kPairStageTokens - 1) {
+                    // the accumulators have been read: the next tile's first MMA may overwrite them
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) {
+                        if (leader) mbar_arrive(accum_empty);
+                        else mbar_arrive_remote_release(cluster_map_shared(accum_empty, 0));
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");
+                // staging -> global, row-contiguous
+                constexpr int kSegs = kOutPerRow / 8;            // 16-byte segments per token row
+                const int m_base = pt.m0 + pass * kPairStageTokens;
+                if (vec_ok) {
+                    for (int idx = tid; idx < kPairStageTokens * kSegs; idx += kDqThreads) {
+                        const int tok = idx / kSegs, seg = idx - tok * kSegs;
+                        const int m = m_base + tok;
+                        if (m < a.M && seg * 8 < n_valid) {
+                            uint4 val = *reinterpret_cast<const uint4*>(s_stage + tok * kPairStagePitch + seg * 16);
+                            const size_t off = static_cast<size_t>(m) * ld + n_out0 + seg * 8;
+                            if constexpr (MODE == kPlain) {
+                                if (a.residual != nullptr) {
+                                    const uint4 res = *reinterpret_cast<const uint4*>(a.residual + off);
+                                    __half2* vh = reinterpret_cast<__half2*>(&val);
+                                    const __half2* rh = reinterpret_cast<const __half2*>(&res);
+#pragma unroll
+                                    for (int e = 0; e < 4; ++e) vh[e] = __hadd2(vh[e], rh[e]);
+                                }
+                            }
+                            *reinterpret_cast<uint4*>(out + off) = val;
+                        }
+                    }
+                } else {
+                    for (int idx = tid; idx < kPairStageTokens * kOutPerRow; idx += kDqThreads) {
+                        const int tok = idx / kOutPerRow, c = idx - tok * kOutPerRow;
+                        const int m = m_base + tok;
+                        if (m < a.M && c < n_valid) {
+                            __half y = reinterpret_cast<const __half*>(s_stage + tok * kPairStagePitch)[c];
+                            const size_t off = static_cast<size_t>(m) * ld + n_out0 + c;
+                            if constexpr (MODE == kPlain) {
+                                if (a.residual != nullptr) y = __hadd(y, a.residual[off]);
+                            }
+                            out[off] = y;
+                        }
+                    }
+                }
+                asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");   // the staging tile is free again
             }
+            (void)n;
         }
     } else if (warp == kDqWarps) {
-        // ---- MMA issue: the leading CTA only ----
+        // ================= MMA issue: the leading CTA only =================
         if (leader) {
             const uint32_t idesc = make_idesc_pair(T);
             const uint64_t b_desc0 = make_smem_desc(smem_u32(s_b));
-            const uint32_t b_step = static_cast<uint32_t>(b_bytes) >> 4;
+            constexpr uint32_t b_step = static_cast<uint32_t>(b_bytes) >> 4;
             const uint32_t a_tmem0 = tmem_base + kPairAccumCols;
             uint64_t b_desc = b_desc0;
             uint32_t a_tmem = a_tmem0;
             int s = 0;
-            uint32_t ph = 0;
+            uint32_t ph = 0, empty_ph = 0;
             bool ok = true;
-            bool ready = mbar_test_wait(full(0), 0);
-            for (int kb = 0; kb < num_kb; ++kb) {
-                if (!ready) ok = warp_wait(full(s), ph, s_abort, lane);
-                if (!ok) break;
-                tc_fence_after();
-                int sn = s + 1;
-                uint32_t phn = ph;
-                if (sn == S) { sn = 0; phn ^= 1; }
-                if (lane == 0) {
-#pragma unroll
-                    for (int ks = 0; ks < kBK / 16; ++ks)
-                        tc_mma_f16_pair_ts(tmem_base, a_tmem + 8u * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
-                    tc_commit_pair(ab_empty(s));
+            for (int pt_i = pair_id, it = 0; pt_i < total_pt && ok; pt_i += num_pairs, ++it) {
+                if (it > 0) {            // both CTAs have drained the previous tile's accumulators
+                    ok = warp_wait(accum_empty, empty_ph, s_abort, lane);
+                    empty_ph ^= 1;
+                    if (!ok) break;
                 }
-                ready = (kb + 1 < num_kb) ? mbar_test_wait(full(sn), phn) : true;
-                ready = __all_sync(0xFFFFFFFFu, ready);
-                a_tmem += kPairACols;
-                b_desc += b_step;
-                if (sn == 0) { a_tmem = a_tmem0; b_desc = b_desc0; }
-                s = sn;
-                ph = phn;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_test_wait(full(s), ph)) ok = warp_wait(full(s), ph, s_abort, lane);
+                    if (!ok) break;
+                    tc_fence_after();
+                    if (lane == 0) {
+#pragma unroll
+                        for (int ks = 0; ks < kBK / 16; ++ks)
+                            tc_mma_f16_pair_ts(tmem_base, a_tmem + 8u * ks, b_desc + 2 * ks, idesc, (kb | ks) != 0 ? 1u : 0u);
+                        tc_commit_pair(ab_empty(s));
+                    }
+                    __syncwarp();
+                    a_tmem += kPairACols;
+                    b_desc += b_step;
+                    if (++s == S) { s = 0; ph ^= 1; a_tmem = a_tmem0; b_desc = b_desc0; }
+                }
+                if (ok && lane == 0) tc_commit_pair(accum_full);
+                __syncwarp();
             }
-            if (ok && lane == 0) tc_commit_pair(accum_full);
         }
         __syncwarp();
     } else if (warp == kDqWarps + 1) {
-        // ---- TMA: this CTA's half of the token tile; the bytes are counted on the LEADER's barrier ----
+        // ================= TMA: this CTA's half of the token tile; bytes counted on the LEADER's barrier =================
         if (lane == 0) {
             int s = 0;
             uint32_t ph = 0;
-            for (int kb = 0; kb < num_kb; ++kb) {
-                if (!mbar_wait(ab_empty(s), ph ^ 1, s_abort)) break;
-                if (leader) mbar_arrive_expect_tx(full(s), static_cast<uint32_t>(2 * b_bytes));
-                tma_load_2d_pair(smem_u32(s_b + s * b_bytes), &a.tmap_x, kb * kBK, m0 + static_cast<int>(rank) * Th,
-                                 cluster_map_shared(full(s), 0));
-                if (++s == S) { s = 0; ph ^= 1; }
+            bool ok = true;
+            for (int pt_i = pair_id; pt_i < total_pt && ok; pt_i += num_pairs) {
+                const PairTile pt = pair_tile(a, pt_i, n_pairs, rank, MODE == kQkv);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!mbar_wait(ab_empty(s), ph ^ 1, s_abort)) { ok = false; break; }
+                    if (leader) mbar_arrive_expect_tx(full(s), static_cast<uint32_t>(2 * b_bytes));
+                    tma_load_2d_pair(smem_u32(s_b + s * b_bytes), &a.tmap_x, kb * kBK, pt.m0 + rank * Th,
+                                     cluster_map_shared(full(s), 0));
+                    if (++s == S) { s = 0; ph ^= 1; }
+                }
             }
         }
         __syncwarp();
     } else {
-        // ---- TMA: raw packed weights of this CTA's 128 rows (private ring) ----
+        // ================= TMA: raw packed weights of this CTA's 128 rows (private ring) =================
         if (lane == 0) {
             int rs = 0;
             uint32_t rph = 0;
-            for (int sb = 0; sb < num_sb; ++sb) {
-                if (!mbar_wait(raw_empty(rs), rph ^ 1, s_abort)) break;
-                mbar_arrive_expect_tx(raw_full(rs), kRawBytes);
-                tma_load_2d(smem_u32(s_raw + rs * kRawBytes), &a.tmap_w[t], sb * 128, n0, raw_full(rs));
-                if (++rs == kRawStages) { rs = 0; rph ^= 1; }
+            bool ok = true;
+            for (int pt_i = pair_id; pt_i < total_pt && ok; pt_i += num_pairs) {
+                const PairTile pt = pair_tile(a, pt_i, n_pairs, rank, MODE == kQkv);
+                for (int sb = 0; sb < num_sb; ++sb) {
+                    if (!mbar_wait(raw_empty(rs), rph ^ 1, s_abort)) { ok = false; break; }
+                    mbar_arrive_expect_tx(raw_full(rs), kRawBytes);
+                    tma_load_2d(smem_u32(s_raw + rs * kRawBytes), &a.tmap_w[pt.t], sb * 128, pt.n0, raw_full(rs));
+                    if (++rs == kRawStages) { rs = 0; rph ^= 1; }
+                }
             }
         }
         __syncwarp();
@@ -870,10 +962,9 @@ size_t tc_smem_bytes(int T, int S, int K) {
            ((G * kTileRows * 2 + 15) & ~size_t(15)) + (2 * kRawStages + 3 * kMaxStages + 1) * 8 + 16;
 }
 
-size_t tc_pair_smem_bytes(int T, int S, int K) {     // per CTA: half of the token tile per stage
-    const size_t G = K / kGroup;
-    return 1024 + static_cast<size_t>(kRawStages) * kRawBytes + static_cast<size_t>(S) * ((T / 2) * 128) +
-           ((G * kTileRows * 2 + 15) & ~size_t(15)) + (2 * kRawStages + 3 * kMaxStages + 1) * 8 + 16;
+size_t tc_pair_smem_bytes(int S) {     // per CTA: raw weight ring, token halves, epilogue staging, barriers
+    return 1024 + static_cast<size_t>(kRawStages) * kRawBytes + static_cast<size_t>(S) * ((kPairTokens / 2) * 128) +
+           kPairStageBytes + (2 * kRawStages + 3 * kMaxStages + 2) * 8 + 16;
 }
 
 }  // namespace
@@ -992,29 +1083,30 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     // and an even number of 128-row tiles in every weight tensor (a pair never straddles two tensors).
     const int gemm_form = option(W4A16_OPT_GEMM_FORM);
     bool pairs = gemm_form != 1 && T == 256 && a.ksplit == 1 && a.num_peers == 0;
-    for (int t = 0; t < nt; ++t) pairs = pairs && a.tiles[t] % 2 == 0;
+    for (int t = 0; t < nt; ++t)     // (scales are read as pairs of fp16: 4-byte alignment)
+        pairs = pairs && a.tiles[t] % 2 == 0 && reinterpret_cast<uintptr_t>(g.scales[t]) % 4 == 0;
     if (pairs) {
         int SP = kMaxStages;
-        while (SP > 2 && tc_pair_smem_bytes(T, SP, g.K) > 227 * 1024) --SP;
-        pairs = tc_pair_smem_bytes(T, SP, g.K) <= 227 * 1024;
-        if (pairs) {
-            a.stages = SP;
-            a.issuers = 1;
-            a.tmem_cols = 512;      // 256 accumulator columns + up to 8 stages x 32 columns of dequantised weights
-            if (!encode_2d(&a.tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.x, static_cast<uint64_t>(g.K),
-                           static_cast<uint64_t>(g.M), static_cast<uint64_t>(g.K) * 2, kBK, static_cast<uint32_t>(T / 2)))
-                return W4A16_ERR_INVALID_ARG;
-            const dim3 pgrid(total_tiles, (g.M + T - 1) / T, 1), pblock(kPairThreads), pcluster(2, 1, 1);
-            const size_t psmem = tc_pair_smem_bytes(T, SP, g.K);
-            const bool pdl = pdl_enabled();
-            cudaError_t pe;
-            switch (g.mode) {
-                case kPlain: pe = launch_kernel_cluster(gemm_w4a16_tc_pair_kernel<kPlain>, pgrid, pblock, psmem, stream, pdl, pcluster, a); break;
-                case kQkv: pe = launch_kernel_cluster(gemm_w4a16_tc_pair_kernel<kQkv>, pgrid, pblock, psmem, stream, pdl, pcluster, a); break;
-                default: pe = launch_kernel_cluster(gemm_w4a16_tc_pair_kernel<kSwiglu>, pgrid, pblock, psmem, stream, pdl, pcluster, a); break;
-            }
-            return static_cast<int>(pe);
+        while (SP > 2 && tc_pair_smem_bytes(SP) > 227 * 1024) --SP;
+        a.stages = SP;
+        a.issuers = 1;
+        a.tmem_cols = 512;      // 256 accumulator columns + up to 8 stages x 32 columns of dequantised weights
+        if (!encode_2d(&a.tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.x, static_cast<uint64_t>(g.K),
+                       static_cast<uint64_t>(g.M), static_cast<uint64_t>(g.K) * 2, kBK, static_cast<uint32_t>(T / 2)))
+            return W4A16_ERR_INVALID_ARG;
+        // persistent: one pair per two SMs, each walking the pair tiles p, p + P, ...
+        const int pair_tiles = (total_tiles / 2) * ((g.M + T - 1) / T);
+        const int num_pairs = std::max(1, std::min(sm_count / 2, pair_tiles));
+        const dim3 pgrid(2 * num_pairs, 1, 1), pblock(kPairThreads), pcluster(2, 1, 1);
+        const size_t psmem = tc_pair_smem_bytes(SP);
+        const bool pdl = pdl_enabled();
+        cudaError_t pe;
+        switch (g.mode) {
+            case kPlain: pe = launch_kernel_cluster(gemm_w4a16_tc_pair_kernel<kPlain>, pgrid, pblock, psmem, stream, pdl, pcluster, a); break;
+            case kQkv: pe = launch_kernel_cluster(gemm_w4a16_tc_pair_kernel<kQkv>, pgrid, pblock, psmem, stream, pdl, pcluster, a); break;
+            default: pe = launch_kernel_cluster(gemm_w4a16_tc_pair_kernel<kSwiglu>, pgrid, pblock, psmem, stream, pdl, pcluster, a); break;
         }
+        return static_cast<int>(pe);
     }
     if (!encode_2d(&a.tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.x, static_cast<uint64_t>(g.K),
                    static_cast<uint64_t>(g.M), static_cast<uint64_t>(g.K) * 2, kBK, static_cast<uint32_t>(T)))
