@@ -601,7 +601,7 @@ constexpr int kPairAccumCols = 256;          // accumulator: 256 tokens
 constexpr int kPairACols = kBK / 2;          // one k-block of dequantised weights: 64 fp16 = 32 packed columns
 
 constexpr int kPairTokens = 256;             // tokens of a pair's tile (128 loaded by each CTA)
-constexpr int kPairStageTokens = 128;        // tokens per epilogue pass through the staging buffer
+constexpr int kPairStageTokens = kPairTokens;   // the staging buffer holds the whole tile's outputs of this CTA
 constexpr int kPairStagePitch = kTileRows * 2 + 16;   // bytes per token row of the staging buffer (+16: bank spread)
 constexpr int kPairStageBytes = kPairStageTokens * kPairStagePitch;
 
@@ -699,69 +699,78 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
         uint32_t ph = 0;
         while (s >= S) { s -= S; ph ^= 1; }
         uint32_t acc_ph = 0;
-        // scales of the first super-block of the first tile
-        uint32_t sc_next = 0;
+        const int my_tiles = pair_id < total_pt ? (total_pt - pair_id + num_pairs - 1) / num_pairs : 0;
         auto load_scales = [&](const PairTile& pt, int sb) -> uint32_t {
             const int row = pt.n0 + r;
             if (row >= a.rows[pt.t]) return 0u;   // rows past the tensor dequantise to zero
             return __ldg(reinterpret_cast<const uint32_t*>(a.scales[pt.t] + static_cast<size_t>(row) * G + 2 * sb));
         };
-        if (pair_id < total_pt) sc_next = load_scales(pair_tile(a, pair_id, n_pairs, rank, MODE == kQkv), 0);
+        // The dequantising cursor: (tile iteration, super-block) of the next k-block this group produces.  It runs
+        // ahead of the draining below by one super-block, so that the tensor core has work while a tile's outputs
+        // are still on their way to global memory.
+        int cur_it = 0, cur_sb = 0;
+        PairTile cur_pt = my_tiles > 0 ? pair_tile(a, pair_id, n_pairs, rank, MODE == kQkv) : PairTile{0, 0, 0};
+        uint32_t sc_next = my_tiles > 0 ? load_scales(cur_pt, 0) : 0u;
+        auto advance = [&]() {      // dequantises the cursor's k-block; false when a bounded wait ran out
+            const uint32_t sc_pair = sc_next;
+            const int sb = cur_sb;
+            // move the cursor and fetch its scales one step ahead
+            if (++cur_sb == num_sb) {
+                cur_sb = 0;
+                ++cur_it;
+                if (cur_it < my_tiles) cur_pt = pair_tile(a, pair_id + cur_it * num_pairs, n_pairs, rank, MODE == kQkv);
+            }
+            if (cur_it < my_tiles) sc_next = load_scales(cur_pt, cur_sb);
+            (void)sb;
+            if (!warp_wait(raw_full(rs), rph, s_abort, lane)) return false;
+            const uint8_t* raw_row = s_raw + rs * kRawBytes + r * 128;
+            const int j = part;              // NG == 4: one k-block of the super-block per group
+            if (!warp_wait(ab_empty(s), ph ^ 1, s_abort, lane)) return false;
+            tc_fence_after();
+            const uint4 w0 = *reinterpret_cast<const uint4*>(raw_row + (((2 * j) ^ sw) << 4));
+            const uint4 w1 = *reinterpret_cast<const uint4*>(raw_row + (((2 * j + 1) ^ sw) << 4));
+            const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+            const uint16_t sbits = static_cast<uint16_t>(j < 2 ? (sc_pair & 0xFFFFu) : (sc_pair >> 16));
+            const __half2 sc2 = __half2half2(__ushort_as_half(sbits));
+            const uint32_t a_lane = lane_base + static_cast<uint32_t>(kPairAccumCols + s * kPairACols);
+#pragma unroll
+            for (int hw = 0; hw < 2; ++hw) {
+                uint32_t cols[16];
+#pragma unroll
+                for (int w = 0; w < 4; ++w) {
+                    __half2 h[4];
+                    dequant_word_fp16(words[4 * hw + w], sc2, h);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) cols[4 * w + q] = *reinterpret_cast<const uint32_t*>(&h[q]);
+                }
+                tmem_st16(a_lane + 16u * hw, cols);
+            }
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (leader) mbar_arrive(full(s));
+                else mbar_arrive_remote_release(cluster_map_shared(full(s), 0));
+                mbar_arrive(raw_empty(rs));
+            }
+            s += NG;
+            while (s >= S) { s -= S; ph ^= 1; }
+            if (++rs == kRawStages) { rs = 0; rph ^= 1; }
+            return true;
+        };
         // Every one of the 16 warps reaches every bar.sync of this loop, whatever its waits returned: a warp
         // whose bounded wait ran out has raised the abort flag, and all warps leave together right after the
         // first barrier of the tile.
-        for (int pt_i = pair_id; pt_i < total_pt; pt_i += num_pairs) {
-            const PairTile pt = pair_tile(a, pt_i, n_pairs, rank, MODE == kQkv);
+        for (int it = 0; it < my_tiles; ++it) {
+            const PairTile pt = pair_tile(a, pair_id + it * num_pairs, n_pairs, rank, MODE == kQkv);
             const int rows_t = a.rows[pt.t];
-            for (int sb = 0; sb < num_sb && ok; ++sb) {
-                const uint32_t sc_pair = sc_next;
-                // one super-block ahead (the next tile's first when this tile is through)
-                if (sb + 1 < num_sb) sc_next = load_scales(pt, sb + 1);
-                else if (pt_i + num_pairs < total_pt) sc_next = load_scales(pair_tile(a, pt_i + num_pairs, n_pairs, rank, MODE == kQkv), 0);
-                ok = warp_wait(raw_full(rs), rph, s_abort, lane);
-                if (!ok) break;
-                const uint8_t* raw_row = s_raw + rs * kRawBytes + r * 128;
-                const int j = part;              // NG == 4: one k-block of the super-block per group
-                ok = warp_wait(ab_empty(s), ph ^ 1, s_abort, lane);
-                if (!ok) break;
-                tc_fence_after();
-                const uint4 w0 = *reinterpret_cast<const uint4*>(raw_row + (((2 * j) ^ sw) << 4));
-                const uint4 w1 = *reinterpret_cast<const uint4*>(raw_row + (((2 * j + 1) ^ sw) << 4));
-                const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-                const uint16_t sbits = static_cast<uint16_t>(j < 2 ? (sc_pair & 0xFFFFu) : (sc_pair >> 16));
-                const __half2 sc2 = __half2half2(__ushort_as_half(sbits));
-                const uint32_t a_lane = lane_base + static_cast<uint32_t>(kPairAccumCols + s * kPairACols);
-#pragma unroll
-                for (int hw = 0; hw < 2; ++hw) {
-                    uint32_t cols[16];
-#pragma unroll
-                    for (int w = 0; w < 4; ++w) {
-                        __half2 h[4];
-                        dequant_word_fp16(words[4 * hw + w], sc2, h);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) cols[4 * w + q] = *reinterpret_cast<const uint32_t*>(&h[q]);
-                    }
-                    tmem_st16(a_lane + 16u * hw, cols);
-                }
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) {
-                    if (leader) mbar_arrive(full(s));
-                    else mbar_arrive_remote_release(cluster_map_shared(full(s), 0));
-                    mbar_arrive(raw_empty(rs));
-                }
-                s += NG;
-                while (s >= S) { s -= S; ph ^= 1; }
-                if (++rs == kRawStages) { rs = 0; rph ^= 1; }
-            }
-            // ---- drain this tile: 128 weight rows of this CTA x 256 tokens, two passes of 128 tokens ----
+            while (ok && cur_it == it) ok = advance();          // the rest of this tile's k-blocks
+            // ---- drain this tile: 128 weight rows of this CTA x 256 tokens ----
             if (ok) ok = warp_wait(accum_full, acc_ph, s_abort, lane);
             acc_ph ^= 1;
             asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");
             if (*s_abort) break;             // the same answer in all 16 warps
             tc_fence_after();
-            const int n = pt.n0 + r;
             __half* out = a.out[pt.t];
             const int ld = a.out_ld[pt.t];
             constexpr int kOutPerRow = MODE == kSwiglu ? kTileRows / 2 : kTileRows;    // outputs of a token row in the tile
@@ -769,77 +778,72 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
             const int n_valid = MODE == kSwiglu ? max(0, min(kOutPerRow, (rows_t - pt.n0) / 2)) : max(0, min(kOutPerRow, rows_t - pt.n0));
             const bool vec_ok = (ld % 8 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (n_valid % 8 == 0) &&
                                 (MODE != kPlain || a.residual == nullptr || reinterpret_cast<uintptr_t>(a.residual) % 16 == 0);
-#pragma unroll 1
-            for (int pass = 0; pass < T / kPairStageTokens; ++pass) {
-                // this warp: its 32 rows x 32 tokens (part) of the pass
+            // (1) accumulators -> fp16 -> staging tile [token][row]: this warp's 32 rows x 64 tokens
 #pragma unroll
-                for (int q = 0; q < 2; ++q) {
-                    const int tok0 = part * 32 + q * 16;          // token inside the pass
-                    uint32_t v[16];
-                    tmem_ld16(lane_base + static_cast<uint32_t>(pass * kPairStageTokens + tok0), v);
-                    tmem_ld_wait();
+            for (int q = 0; q < 4; ++q) {
+                const int tok0 = part * 64 + q * 16;
+                uint32_t v[16];
+                tmem_ld16(lane_base + static_cast<uint32_t>(tok0), v);
+                tmem_ld_wait();
 #pragma unroll
-                    for (int jj = 0; jj < 16; ++jj) {
-                        const float acc = __uint_as_float(v[jj]);
-                        uint8_t* row_ptr = s_stage + (tok0 + jj) * kPairStagePitch;
-                        if constexpr (MODE == kSwiglu) {
-                            const float up = __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
-                            if ((lane & 1) == 0)
-                                reinterpret_cast<__half*>(row_ptr)[r >> 1] = __float2half_rn((acc / (1.0f + expf(-acc))) * up);
-                        } else {
-                            reinterpret_cast<__half*>(row_ptr)[r] = __float2half_rn(acc);
-                        }
+                for (int jj = 0; jj < 16; ++jj) {
+                    const float acc = __uint_as_float(v[jj]);
+                    uint8_t* row_ptr = s_stage + (tok0 + jj) * kPairStagePitch;
+                    if constexpr (MODE == kSwiglu) {
+                        const float up = __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
+                        if ((lane & 1) == 0)
+                            reinterpret_cast<__half*>(row_ptr)[r >> 1] = __float2half_rn((acc / (1.0f + expf(-acc))) * up);
+                    } else {
+                        reinterpret_cast<__half*>(row_ptr)[r] = __float2half_rn(acc);
                     }
                 }
-                if (pass == T / kPairStageTokens - 1) {
-                    // the accumulators have been read: the next tile's first MMA may overwrite them
-                    tc_fence_before();
-                    __syncwarp();
-                    if (lane == 0) {
-                        if (leader) mbar_arrive(accum_empty);
-                        else mbar_arrive_remote_release(cluster_map_shared(accum_empty, 0));
-                    }
-                }
-                asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");
-                // staging -> global, row-contiguous
-                constexpr int kSegs = kOutPerRow / 8;            // 16-byte segments per token row
-                const int m_base = pt.m0 + pass * kPairStageTokens;
-                if (vec_ok) {
-                    for (int idx = tid; idx < kPairStageTokens * kSegs; idx += kDqThreads) {
-                        const int tok = idx / kSegs, seg = idx - tok * kSegs;
-                        const int m = m_base + tok;
-                        if (m < a.M && seg * 8 < n_valid) {
-                            uint4 val = *reinterpret_cast<const uint4*>(s_stage + tok * kPairStagePitch + seg * 16);
-                            const size_t off = static_cast<size_t>(m) * ld + n_out0 + seg * 8;
-                            if constexpr (MODE == kPlain) {
-                                if (a.residual != nullptr) {
-                                    const uint4 res = *reinterpret_cast<const uint4*>(a.residual + off);
-                                    __half2* vh = reinterpret_cast<__half2*>(&val);
-                                    const __half2* rh = reinterpret_cast<const __half2*>(&res);
-#pragma unroll
-                                    for (int e = 0; e < 4; ++e) vh[e] = __hadd2(vh[e], rh[e]);
-                                }
-                            }
-                            *reinterpret_cast<uint4*>(out + off) = val;
-                        }
-                    }
-                } else {
-                    for (int idx = tid; idx < kPairStageTokens * kOutPerRow; idx += kDqThreads) {
-                        const int tok = idx / kOutPerRow, c = idx - tok * kOutPerRow;
-                        const int m = m_base + tok;
-                        if (m < a.M && c < n_valid) {
-                            __half y = reinterpret_cast<const __half*>(s_stage + tok * kPairStagePitch)[c];
-                            const size_t off = static_cast<size_t>(m) * ld + n_out0 + c;
-                            if constexpr (MODE == kPlain) {
-                                if (a.residual != nullptr) y = __hadd(y, a.residual[off]);
-                            }
-                            out[off] = y;
-                        }
-                    }
-                }
-                asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");   // the staging tile is free again
             }
-            (void)n;
+            // (2) the accumulators have been read: the next tile's first MMA may overwrite them
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (leader) mbar_arrive(accum_empty);
+                else mbar_arrive_remote_release(cluster_map_shared(accum_empty, 0));
+            }
+            // (3) feed the tensor core before the slow part: one super-block of the next tile
+            if (ok && cur_it == it + 1 && cur_it < my_tiles) ok = advance();
+            asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");       // the staging tile is complete
+            // (4) staging -> global, row-contiguous
+            constexpr int kSegs = kOutPerRow / 8;            // 16-byte segments per token row
+            if (vec_ok) {
+                for (int idx = tid; idx < T * kSegs; idx += kDqThreads) {
+                    const int tok = idx / kSegs, seg = idx - tok * kSegs;
+                    const int m = pt.m0 + tok;
+                    if (m < a.M && seg * 8 < n_valid) {
+                        uint4 val = *reinterpret_cast<const uint4*>(s_stage + tok * kPairStagePitch + seg * 16);
+                        const size_t off = static_cast<size_t>(m) * ld + n_out0 + seg * 8;
+                        if constexpr (MODE == kPlain) {
+                            if (a.residual != nullptr) {
+                                const uint4 res = *reinterpret_cast<const uint4*>(a.residual + off);
+                                __half2* vh = reinterpret_cast<__half2*>(&val);
+                                const __half2* rh = reinterpret_cast<const __half2*>(&res);
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) vh[e] = __hadd2(vh[e], rh[e]);
+                            }
+                        }
+                        *reinterpret_cast<uint4*>(out + off) = val;
+                    }
+                }
+            } else {
+                for (int idx = tid; idx < T * kOutPerRow; idx += kDqThreads) {
+                    const int tok = idx / kOutPerRow, c = idx - tok * kOutPerRow;
+                    const int m = pt.m0 + tok;
+                    if (m < a.M && c < n_valid) {
+                        __half y = reinterpret_cast<const __half*>(s_stage + tok * kPairStagePitch)[c];
+                        const size_t off = static_cast<size_t>(m) * ld + n_out0 + c;
+                        if constexpr (MODE == kPlain) {
+                            if (a.residual != nullptr) y = __hadd(y, a.residual[off]);
+                        }
+                        out[off] = y;
+                    }
+                }
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");   // the staging tile is free again
         }
     } else if (warp == kDqWarps) {
         // ================= MMA issue: the leading CTA only =================
