@@ -602,7 +602,8 @@ constexpr int kPairACols = kBK / 2;          // one k-block of dequantised weigh
 
 constexpr int kPairTokens = 256;             // tokens of a pair's tile (128 loaded by each CTA)
 constexpr int kPairStageTokens = kPairTokens;   // the staging buffer holds the whole tile's outputs of this CTA
-constexpr int kPairStagePitch = kTileRows * 2 + 16;   // bytes per token row of the staging buffer (+16: bank spread)
+constexpr int kPairStagePitch = kTileRows * 2;         // bytes per token row of the staging buffer
+constexpr int kPairRawStages = 2;            // raw weight ring: 2 x 256 k ahead is ample; the room goes to token stages
 constexpr int kPairStageBytes = kPairStageTokens * kPairStagePitch;
 
 // Which 128-row tile of which tensor, and which tokens, a pair tile index stands for (this CTA's half).
@@ -642,17 +643,17 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
     const int S = a.stages, K = a.K;
     const int G = K / kGroup;
     uint8_t* s_raw = smem;
-    uint8_t* s_b = s_raw + kRawStages * kRawBytes;
+    uint8_t* s_b = s_raw + kPairRawStages * kRawBytes;
     uint8_t* s_stage = s_b + S * b_bytes;
     uint64_t* s_bar = reinterpret_cast<uint64_t*>(s_stage + kPairStageBytes);
     const uint32_t bar0 = smem_u32(s_bar);
     auto raw_full = [&](int i) { return bar0 + 8u * i; };
-    auto raw_empty = [&](int i) { return bar0 + 8u * (kRawStages + i); };
-    auto full = [&](int i) { return bar0 + 8u * (2 * kRawStages + i); };
-    auto ab_empty = [&](int i) { return bar0 + 8u * (2 * kRawStages + 2 * kMaxStages + i); };
-    const uint32_t accum_full = bar0 + 8u * (2 * kRawStages + 3 * kMaxStages);
+    auto raw_empty = [&](int i) { return bar0 + 8u * (kPairRawStages + i); };
+    auto full = [&](int i) { return bar0 + 8u * (2 * kPairRawStages + i); };
+    auto ab_empty = [&](int i) { return bar0 + 8u * (2 * kPairRawStages + 2 * kMaxStages + i); };
+    const uint32_t accum_full = bar0 + 8u * (2 * kPairRawStages + 3 * kMaxStages);
     const uint32_t accum_empty = accum_full + 8u;
-    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + (2 * kRawStages + 3 * kMaxStages + 2));
+    uint32_t* s_tmem = reinterpret_cast<uint32_t*>(s_bar + (2 * kPairRawStages + 3 * kMaxStages + 2));
     volatile int* s_abort = reinterpret_cast<volatile int*>(s_tmem + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -664,7 +665,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
     const int num_sb = K / 256, num_kb = K / kBK;
 
     if (tid == 0) {
-        for (int i = 0; i < kRawStages; ++i) { mbar_init(raw_full(i), 1); mbar_init(raw_empty(i), kDqWarps); }
+        for (int i = 0; i < kPairRawStages; ++i) { mbar_init(raw_full(i), 1); mbar_init(raw_empty(i), kDqWarps); }
         // full: 4 warps of each CTA's dequantising group + the leader's expect_tx arrival
         for (int i = 0; i < S; ++i) { mbar_init(full(i), 2 * 4 + 1); mbar_init(ab_empty(i), 1); }
         mbar_init(accum_full, 1);
@@ -755,7 +756,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
             }
             s += NG;
             while (s >= S) { s -= S; ph ^= 1; }
-            if (++rs == kRawStages) { rs = 0; rph ^= 1; }
+            if (++rs == kPairRawStages) { rs = 0; rph ^= 1; }
             return true;
         };
         // Every one of the 16 warps reaches every bar.sync of this loop, whatever its waits returned: a warp
@@ -765,6 +766,11 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
             const PairTile pt = pair_tile(a, pair_id + it * num_pairs, n_pairs, rank, MODE == kQkv);
             const int rows_t = a.rows[pt.t];
             while (ok && cur_it == it) ok = advance();          // the rest of this tile's k-blocks
+            // Look-ahead: while the tensor core works off the tail of this tile, fill the ring with the first
+            // k-blocks of the next one (S / NG per group, i.e. every stage once: those stages are freed by MMAs of
+            // THIS tile, so the wait cannot depend on the draining below), so that the next tile starts the
+            // moment its accumulators are free and keeps running while the outputs go to global memory.
+            for (int la = 0; la < S / NG && ok && cur_it == it + 1 && cur_it < my_tiles; ++la) ok = advance();
             // ---- drain this tile: 128 weight rows of this CTA x 256 tokens ----
             if (ok) ok = warp_wait(accum_full, acc_ph, s_abort, lane);
             acc_ph ^= 1;
@@ -778,16 +784,25 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
             const int n_valid = MODE == kSwiglu ? max(0, min(kOutPerRow, (rows_t - pt.n0) / 2)) : max(0, min(kOutPerRow, rows_t - pt.n0));
             const bool vec_ok = (ld % 8 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (n_valid % 8 == 0) &&
                                 (MODE != kPlain || a.residual == nullptr || reinterpret_cast<uintptr_t>(a.residual) % 16 == 0);
-            // (1) accumulators -> fp16 -> staging tile [token][row]: this warp's 32 rows x 64 tokens
+            // (1) this warp's 32 rows x 64 tokens of the accumulators into registers; with that the tensor memory is
+            // free, and the next tile's first MMA may overwrite it while the values are still being stored
+            uint32_t v[4][16];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) tmem_ld16(lane_base + static_cast<uint32_t>(part * 64 + q * 16), v[q]);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (leader) mbar_arrive(accum_empty);
+                else mbar_arrive_remote_release(cluster_map_shared(accum_empty, 0));
+            }
+            // (2) fp32 -> fp16 -> staging tile [token][row]
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const int tok0 = part * 64 + q * 16;
-                uint32_t v[16];
-                tmem_ld16(lane_base + static_cast<uint32_t>(tok0), v);
-                tmem_ld_wait();
 #pragma unroll
                 for (int jj = 0; jj < 16; ++jj) {
-                    const float acc = __uint_as_float(v[jj]);
+                    const float acc = __uint_as_float(v[q][jj]);
                     uint8_t* row_ptr = s_stage + (tok0 + jj) * kPairStagePitch;
                     if constexpr (MODE == kSwiglu) {
                         const float up = __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
@@ -798,17 +813,8 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
                     }
                 }
             }
-            // (2) the accumulators have been read: the next tile's first MMA may overwrite them
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) {
-                if (leader) mbar_arrive(accum_empty);
-                else mbar_arrive_remote_release(cluster_map_shared(accum_empty, 0));
-            }
-            // (3) feed the tensor core before the slow part: one super-block of the next tile
-            if (ok && cur_it == it + 1 && cur_it < my_tiles) ok = advance();
             asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");       // the staging tile is complete
-            // (4) staging -> global, row-contiguous
+            // (3) staging -> global, row-contiguous
             constexpr int kSegs = kOutPerRow / 8;            // 16-byte segments per token row
             if (vec_ok) {
                 for (int idx = tid; idx < T * kSegs; idx += kDqThreads) {
@@ -913,7 +919,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
                     if (!mbar_wait(raw_empty(rs), rph ^ 1, s_abort)) { ok = false; break; }
                     mbar_arrive_expect_tx(raw_full(rs), kRawBytes);
                     tma_load_2d(smem_u32(s_raw + rs * kRawBytes), &a.tmap_w[pt.t], sb * 128, pt.n0, raw_full(rs));
-                    if (++rs == kRawStages) { rs = 0; rph ^= 1; }
+                    if (++rs == kPairRawStages) { rs = 0; rph ^= 1; }
                 }
             }
         }
@@ -967,8 +973,8 @@ size_t tc_smem_bytes(int T, int S, int K) {
 }
 
 size_t tc_pair_smem_bytes(int S) {     // per CTA: raw weight ring, token halves, epilogue staging, barriers
-    return 1024 + static_cast<size_t>(kRawStages) * kRawBytes + static_cast<size_t>(S) * ((kPairTokens / 2) * 128) +
-           kPairStageBytes + (2 * kRawStages + 3 * kMaxStages + 2) * 8 + 16;
+    return 1024 + static_cast<size_t>(kPairRawStages) * kRawBytes + static_cast<size_t>(S) * ((kPairTokens / 2) * 128) +
+           kPairStageBytes + (2 * kPairRawStages + 3 * kMaxStages + 2) * 8 + 16;
 }
 
 }  // namespace
