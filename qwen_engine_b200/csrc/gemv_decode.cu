@@ -713,6 +713,100 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const Ge
     }
 }
 
+// Streaming form for tall matrices with a LONG K (more than 2048 elements): the same persistent walk over row
+// blocks of 32, but a row's K range is taken in slices of 2048 (8 steps of 256), the next slice's -- or the next
+// row block's -- weight words already in flight while the current slice is multiplied, and the quantised
+// activation read from shared memory (a lane's share of an 8192-element vector would not fit registers).
+// A row's chunks are accumulated in K order by the same lane as in gemv_w4_kernel without a K split, so the
+// two agree bit for bit.  PLAIN mode, 16-byte aligned weights.
+template <int XIN, bool FULL>     // FULL: K is a multiple of 2048, every slice has all 8 steps (no guards in the loops)
+__global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_longk_kernel(const GemvArgs a, const int num_blocks) {
+    constexpr int STEPS = 8;
+    extern __shared__ __align__(16) uint8_t smem[];
+    const int K = a.K;
+    int8_t* s_q8 = reinterpret_cast<int8_t*>(smem);
+    int32_t* s_seed = reinterpret_cast<int32_t*>(smem + K);
+    float* s_scale = reinterpret_cast<float*>(smem + K + (K / kChunk) * 4);
+    const int tid = threadIdx.x, sub = tid >> 3, l = tid & 7;
+    const int words = K / 8, groups = K / kGroup, steps = K / kStepElems;
+    const int nslices = (steps + STEPS - 1) / STEPS;
+    const int N = a.units;
+
+    // the unit after (blk, sl) in this CTA's walk: the row block's next slice, else the CTA's next row block
+    auto next_unit = [&](int& blk, int& sl) {
+        if (++sl == nslices) { sl = 0; blk += gridDim.x; }
+    };
+    auto issue = [&](uint4 (&w)[STEPS], uint16_t (&sb)[STEPS], int blk, int sl) {
+        const int row = min(blk * kMaxSubwarps + sub, N - 1);      // rows past the end re-read the last row; never stored
+        const uint32_t* wp = a.qweight[0] + static_cast<size_t>(row) * words + (sl * STEPS * kSubwarp + l) * 4;
+        const __half* sp = a.scales[0] + static_cast<size_t>(row) * groups + 2 * sl * STEPS + (l >> 2);
+#pragma unroll
+        for (int i = 0; i < STEPS; ++i) {
+            if (FULL || sl * STEPS + i < steps) {
+                w[i] = ld_weights_16(wp + i * (kSubwarp * 4));
+                sb[i] = ld_scale_bits(sp + 2 * i);
+            } else {
+                w[i] = make_uint4(0, 0, 0, 0);
+                sb[i] = 0;       // a zero scale switches an unused slot off
+            }
+        }
+    };
+    float acc = 0.0f;
+    // one unit: 8 chunks of this lane against the staged activation; at a row's last slice reduce and store
+    auto consume = [&](const uint4 (&w)[STEPS], const uint16_t (&sb)[STEPS], int blk, int sl) {
+        const uint4* xq = reinterpret_cast<const uint4*>(s_q8) + 2 * (sl * STEPS * kSubwarp + l);
+        const int32_t* xseed = s_seed + sl * STEPS * kSubwarp + l;
+        const float* xscale = s_scale + 2 * sl * STEPS + (l >> 2);
+#pragma unroll
+        for (int i = 0; i < STEPS; ++i) {
+            if (FULL || sl * STEPS + i < steps) {
+                const uint4 xa = xq[2 * i * kSubwarp];
+                const uint4 xb = xq[2 * i * kSubwarp + 1];
+                const int32_t d = chunk_dot(w[i], xa, xb, xseed[i * kSubwarp]);
+                acc = fmaf(static_cast<float>(d), __half2float(__ushort_as_half(sb[i])) * xscale[2 * i], acc);
+            }
+        }
+        if (sl == nslices - 1) {
+            acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 4);
+            acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 2);
+            acc += __shfl_xor_sync(0xFFFFFFFFu, acc, 1);
+            const int row = blk * kMaxSubwarps + sub;
+            if (l == 0 && row < N) {
+                float y = acc;
+                if (a.residual != nullptr) y += __half2float(a.residual[row]);
+                const __half yh = __float2half_rn(y);
+                a.out[0][row] = yh;
+                for (int p = 0; p < a.num_peers; ++p) a.peer_out[p][row] = yh;
+            }
+            acc = 0.0f;
+        }
+    };
+
+    uint4 w0[STEPS], w1[STEPS];
+    uint16_t sb0[STEPS], sb1[STEPS];
+    int blk = blockIdx.x, sl = 0;
+    if (blk < num_blocks) issue(w0, sb0, blk, 0);
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    if constexpr (XIN == kXFp16Norm) stage_x_from_fp16_rmsnorm(a.x_fp16, a.gamma, K, kRmsEps, s_q8, s_seed, s_scale);
+    else if constexpr (XIN == kXFp16) stage_x_from_fp16(a.x_fp16, K, s_q8, s_seed, s_scale);
+    else stage_x_from_q8_1(a.q8, a.xscale, a.sum8, K, a.vec_ok != 0, s_q8, s_seed, s_scale);
+    __syncthreads();
+    // two register sets used in turn: the next unit's words are in flight while this one is multiplied
+    while (blk < num_blocks) {
+        int nblk = blk, nsl = sl;
+        next_unit(nblk, nsl);
+        if (nblk < num_blocks) issue(w1, sb1, nblk, nsl);
+        consume(w0, sb0, blk, sl);
+        if (nblk >= num_blocks) break;
+        blk = nblk; sl = nsl;
+        next_unit(nblk, nsl);
+        if (nblk < num_blocks) issue(w0, sb0, nblk, nsl);
+        consume(w1, sb1, blk, sl);
+        blk = nblk; sl = nsl;
+    }
+}
+
 // Diagnostic: the per-group int32 dots, through the same staging and chunk_dot as above.
 __global__ void __launch_bounds__(kMaxThreads) gemv_group_dots_kernel(const uint32_t* __restrict__ qweight,
                                                                        const int8_t* __restrict__ q8,
@@ -900,6 +994,12 @@ int gemv_set_attributes() {
     if (e == cudaSuccess) e = raise_smem_mode<kSwiglu, 4>();
     if (e == cudaSuccess) e = raise_smem_mode<kSwiglu, 8>();
     if (e == cudaSuccess) e = raise_smem(gemv_group_dots_kernel);
+    if (e == cudaSuccess) e = raise_smem(gemv_w4_stream_longk_kernel<kXQ8, true>);
+    if (e == cudaSuccess) e = raise_smem(gemv_w4_stream_longk_kernel<kXQ8, false>);
+    if (e == cudaSuccess) e = raise_smem(gemv_w4_stream_longk_kernel<kXFp16, true>);
+    if (e == cudaSuccess) e = raise_smem(gemv_w4_stream_longk_kernel<kXFp16, false>);
+    if (e == cudaSuccess) e = raise_smem(gemv_w4_stream_longk_kernel<kXFp16Norm, true>);
+    if (e == cudaSuccess) e = raise_smem(gemv_w4_stream_longk_kernel<kXFp16Norm, false>);
     if (e == cudaSuccess) e = prepare_bulk_mode<kPlain>();
     if (e == cudaSuccess) e = prepare_bulk_mode<kQkv>();
     if (e == cudaSuccess) e = prepare_bulk_mode<kSwiglu>();
@@ -963,6 +1063,20 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
     const bool tall = num_blocks >= kStreamMinBlocksPerSm * dev->sm_count;
     const bool sampling = a.sample_val != nullptr || a.sample_idx != nullptr;
     if (sampling && (mode != kPlain || !a.sample_val || !a.sample_idx || !aligned16 || steps > 8)) return W4A16_ERR_SHAPE;
+    // tall plain matrices with a long K: the streaming form that takes K in slices of 2048
+    if (mode == kPlain && !q8_epilogue && !sampling && aligned16 && steps > 8 && a.x_f32 == nullptr &&
+        static_cast<long long>(num_blocks) * ((steps + 7) / 8) >= 8LL * 2 * dev->sm_count &&
+        staged_x_bytes(a.K) <= 160 * 1024 && option(W4A16_OPT_GEMV_FORM) != 2) {
+        const dim3 sgrid(std::min(num_blocks, 2 * dev->sm_count)), sblock(kMaxThreads);
+        const size_t ssmem = staged_x_bytes(a.K);
+        const bool pdl = pdl_enabled();
+#define W4_LONGK(XINV) (steps % 8 == 0 ? launch_kernel(gemv_w4_stream_longk_kernel<XINV, true>, sgrid, sblock, ssmem, stream, pdl, a, num_blocks) \
+                                       : launch_kernel(gemv_w4_stream_longk_kernel<XINV, false>, sgrid, sblock, ssmem, stream, pdl, a, num_blocks))
+        if (a.x_fp16 != nullptr) e = a.gamma != nullptr ? W4_LONGK(kXFp16Norm) : W4_LONGK(kXFp16);
+        else e = W4_LONGK(kXQ8);
+#undef W4_LONGK
+        return static_cast<int>(e);
+    }
     if (!q8_epilogue && aligned16 && steps <= 8 && a.x_f32 == nullptr &&
         ((mode == kPlain && (tall || sampling)) || (mode == kSwiglu && tall))) {
         const dim3 sgrid(std::min(num_blocks, 2 * dev->sm_count)), sblock(kMaxThreads);

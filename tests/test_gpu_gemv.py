@@ -92,6 +92,8 @@ SHAPES = [
     (151936, 1536, False),  # lm_head: tall enough for the persistent streaming kernel
     (80000, 1536, True),    # streaming kernel with an in-place residual and a ragged last row block
     (76001, 1024, False),   # streaming kernel, 4 steps per lane, odd row count
+    (28672, 8192, True),    # tall and K > 2048: the streaming kernel that takes K in slices of 2048 (benchmark shape)
+    (20001, 4352, False),   # the same with a ragged last slice (17 steps) and an odd row count
 ]
 
 
