@@ -44,7 +44,10 @@ def parse():
                     help="sweep: the headline line; shapes: per-shape GEMV and M-token GEMM table (configs 0, 3, 4); "
                          "single: a few launches of one kernel (for ncu captures)")
     ap.add_argument("--shape", default="gate_up", help="single: qkv | o | gate_up | down | lm_head | big")
-    ap.add_argument("--m", type=int, default=0, help="single: 0 = batch-1 GEMV on Q8_1, else M tokens through the GEMM")
+    ap.add_argument("--m", type=int, default=0, help="single: 0 = batch-1 GEMV, else M tokens through the GEMM")
+    ap.add_argument("--input", default="q8", choices=["q8", "fp16", "fp16norm"],
+                    help="single, batch-1: pre-quantised Q8_1 input, fp16 input, or fp16 input with RMSNorm in the prologue")
+    ap.add_argument("--no-shapes", action="store_true", help="skip the per-shape table (configs 0, 3, 4) in the headline line")
     ap.add_argument("--m-list", default="1,2,4,8,16,32,64,128,512,1024,4096")
     ap.add_argument("--layers", type=int, default=28, help=argparse.SUPPRESS)
     ap.add_argument("--no-cpu-baseline", action="store_true", help=argparse.SUPPRESS)
@@ -149,18 +152,29 @@ def time_cpu_sweep(layers_np, h0, budget_s: float = 12.0, max_reps: int = 20):
     return nbytes / dt / 1e9, threads, f"{reps} full {len(layers_np)}-layer sweeps of the oracle port, {dt * 1e3:.1f} ms each", h
 
 
+def bench_config(num_layers, world, nbytes, extra=None):
+    """The `config` object both arms print."""
+    cfg = {"workload": WORKLOAD, "layers": num_layers, "parallelism": f"replicas x{world}",
+           "algorithmic_bytes_per_step": nbytes,
+           "l2": "inputs larger than L2: 675 MB of packed weights are streamed per step"}
+    if extra:
+        cfg.update(extra)
+    return cfg
+
+
 def run_reference_arm(args):
+    """The reference's CPU check of this path (tests/test_kernels.cu:308-363, restated in oracle/) on all host
+    threads: W warm-up sweeps, then exactly K timed sweeps (one 28-layer sweep = one step, about 0.1 s)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from qwen_engine_b200 import synth
     layers_np = make_layers_np(args.layers)
     h0 = synth.activations(7, "h0", synth.HIDDEN)
-    # one "step" = one oracle sweep; W warm-up and K timed steps, bounded so the run ends in minutes
     import oracle
     threads = oracle.default_threads()
     nbytes = synth.layer_algorithmic_bytes() * len(layers_np)
-    steps, warm = max(1, min(args.steps, 20)), max(1, min(args.warmup, 3))
+    steps, warm = max(1, args.steps), max(0, args.warmup)
     for _ in range(warm):
         oracle.decode_sweep(layers_np, h0, threads=threads)
     t0 = time.perf_counter()
@@ -172,11 +186,11 @@ def run_reference_arm(args):
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
         "warmup": warm, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers": len(layers_np),
-                   "note": "reference's CPU check restated in C (tests/test_kernels.cu:308-363), all host threads; "
-                           "the reference has no separately callable CPU implementation of this path"},
+        "config": bench_config(len(layers_np), max(1, args.gpus), nbytes),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"{steps} full {len(layers_np)}-layer sweeps"},
+                         "sample": f"{steps} full {len(layers_np)}-layer sweeps",
+                         "note": "the reference's CPU check restated in C (tests/test_kernels.cu:308-363), all host "
+                                 "threads; the reference has no separately callable CPU implementation of this path"},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -195,57 +209,55 @@ def timed_events(torch, stream, fn, steps):
     return e0.elapsed_time(e1)  # ms
 
 
+def measured_traffic(kernel_key):
+    """DRAM bytes per launch of a kernel as an ncu capture counted them (dram__bytes_read.sum +
+    dram__bytes_write.sum), from the machine-readable companion of the committed summaries; None if absent."""
+    try:
+        table = json.loads((ROOT / "profiles" / "dram_traffic.json").read_text())
+        return table[kernel_key]["dram_bytes_per_launch"]
+    except Exception:
+        return None
+
+
 def kernel_roofline(torch, ops, layers_dev, stream, peaks, reps=20):
-    """Average duration of the dominant kernel (gate_up + SwiGLU GEMV), timed alone: one CUDA graph
-    of 28 launches over the 28 layers' distinct weights (397 MB > L2, so every launch streams from
-    HBM), CUDA events around each replay."""
+    """Average duration of the dominant kernel of the sweep, timed alone and in the form the sweep launches it:
+    the gate_up + SwiGLU GEMV with the RMSNorm + Q8_1 of its fp16 input in the prologue.  One CUDA graph of 28
+    launches over the 28 layers' distinct weights (397 MB > L2, so every launch streams from HBM), CUDA events
+    around each replay."""
     from qwen_engine_b200 import synth
     H, I = synth.HIDDEN, synth.INTER
     x = torch.from_numpy(synth.activations(3, "roof", H)).cuda()
-    q8 = torch.empty(H, dtype=torch.int8, device="cuda")
-    xs = torch.empty(H // 128, dtype=torch.float32, device="cuda")
-    s8 = torch.empty(H // 8, dtype=torch.int32, device="cuda")
     out = torch.empty(I, dtype=torch.float16, device="cuda")
-    res = {}
     with torch.cuda.stream(stream):
-        ops.launch_quantize_fp16_to_q8_1(x, q8, xs, s8, H)
-
-        def all_layers(name):
+        def all_layers():
             for L in layers_dev:
-                if name == "gate_up":
-                    ops.launch_gemv_dual_gate_up_swiglu_w4a8(L[name][0], L[name][1], q8, xs, s8, out, H, I)
-                elif name == "o":
-                    ops.launch_gemv_w4a8(L[name][0], L[name][1], q8, xs, s8, None, out, H, H)
-        all_layers("gate_up")
+                ops.launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16(L["gate_up"][0], L["gate_up"][1], x, L["post_norm"], out, H, I)
+        all_layers()
         stream.synchronize()
         g = torch.cuda.CUDAGraph()
         with torch.cuda.graph(g, stream=stream):
-            all_layers("gate_up")
+            all_layers()
         for _ in range(3):
             g.replay()
         stream.synchronize()
         ms = timed_events(torch, stream, g.replay, reps)
     per_launch_s = ms * 1e-3 / (reps * len(layers_dev))
-    nbytes = synth.gemv_algorithmic_bytes(2 * I, H, n_out=I)
+    nbytes = synth.gemv_algorithmic_bytes(2 * I, H, n_out=I) - H * 49 // 32 + 2 * H + 2 * H   # fp16 x and gain instead of Q8_1 x
     achieved = nbytes / per_launch_s / 1e9
     peak = peaks.get("hbm_gbs")
     src = "measured" if peak else "fallback"
     peak = peak or 6650.0
-    # dram__bytes_read.sum + dram__bytes_write.sum of this kernel per launch, from the ncu capture summarised
-    # in profiles/gemv_gate_up_swiglu_17920x1536.md
-    traffic = 14228480
-    res = {"bound": "hbm", "kernel": "gemv_w4_kernel<SwiGLU> (gate_up 17920x1536)", "achieved": achieved, "peak": peak,
-           "unit": "GB/s", "frac": achieved / peak, "traffic": traffic, "peak_source": f"of {src} (burst copy)",
-           "bytes_per_launch": nbytes, "us_per_launch": per_launch_s * 1e6,
-           "how": f"CUDA graph of {len(layers_dev)} launches over distinct weights, {reps} replays, CUDA events"}
-    return res
+    return {"bound": "hbm", "kernel": "gemv_w4_kernel<SwiGLU, fp16 + RMSNorm input> (gate_up 17920x1536)",
+            "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+            "traffic": measured_traffic("gemv_gate_up_swiglu_rmsnorm"), "peak_source": f"of {src} (burst copy)",
+            "bytes_per_launch": nbytes, "us_per_launch": per_launch_s * 1e6,
+            "how": f"CUDA graph of {len(layers_dev)} launches over distinct weights, {reps} replays, CUDA events"}
 
 
 def time_reference_cuda(torch, layers_dev, stream, steps):
     """Second comparison: the reference's own CUDA kernels rebuilt for sm_100a (oracle/_ref), the same
     chain in one CUDA graph.  Returns None when that library is not present."""
-    sys.path.insert(0, str(ROOT))
-    from tests.util import RefKernels
+    from oracle import RefKernels
     if not RefKernels.available("fastmath"):
         return None
     import ctypes
@@ -534,70 +546,68 @@ def prefill_big_nsplit(torch, dist, ops, rank, world, stream, steps):
         if world > 1:
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         us = float(t.item()) * 1e3 / reps
-        probe = y[::max(1, M // 7), ::max(1, N // 11)].float().sum().item()
-        return us, probe
+        return us, y.clone()        # the whole [M][N] result, compared outside the timed region
 
     out = {"workload": f"config 4: W4A16 prefill GEMM {K}->{N}, {M} tokens, weight rows split over {world} GPU(s)",
            "rows_per_gpu": slab.rows, "unit": "TFLOP/s", "scaling": "strong", "timed_as": "eager launches, CUDA events"}
-    us, probe = measure(False)
+    us, y_ref = measure(False)
     out["nccl_all_gather"] = {"us_per_step": us, "value": flops / (us * 1e-6) / 1e12}
     best = us
     if world > 1:
         try:
-            us_p, probe_p = measure(True)
+            us_p, y_peer = measure(True)
+            # the peer-store form splits K differently on narrow slabs: every entry within one fp16 step, nearly all equal
+            diff = (y_peer.float() - y_ref.float()).abs()
+            tol = torch.maximum(y_ref.float().abs(), torch.tensor(1.0, device=y_ref.device)) * 2.0 ** -10
             out["peer_store_epilogue"] = {"us_per_step": us_p, "value": flops / (us_p * 1e-6) / 1e12,
-                                          "same_probe_sum": bool(abs(probe_p - probe) <= 1e-3 * max(1.0, abs(probe)))}
+                                          "equals_nccl_result": bool(torch.equal(y_peer, y_ref)),
+                                          "all_within_one_fp16_step": bool((diff <= tol).all().item()),
+                                          "identical_fraction": float((y_peer == y_ref).float().mean().item())}
             best = min(best, us_p)
         except Exception as e:
             out["peer_store_epilogue"] = {"unavailable": str(e)[:200]}
     out["us_per_step"] = best
     out["value"] = flops / (best * 1e-6) / 1e12
+    out["gpus"] = world       # strong scaling: efficiency = us_per_step(1 GPU) / (world * us_per_step)
     return out
 
 
-def run_shapes_suite(args):
-    """Per-shape table: batch-1 GEMV (Q8_1 in) and the M-token contraction for the four projection shapes
-    plus the scaled-up 28672 x 8192 shape.  Each measurement is one CUDA graph that walks `copies`
-    distinct weight sets (so small shapes are not served from L2), timed with CUDA events."""
-    import torch
-    import qwen_engine_b200 as ops
+SHAPES_QWEN = {"qkv": (2048, 1536), "o": (1536, 1536), "gate_up": (17920, 1536), "down": (1536, 8960)}
+SHAPE_BIG = (28672, 8192)
+
+
+def shapes_table(torch, ops, stream, peaks, reps=10, m_small=(1, 2, 4, 8, 16, 32, 64), m_prefill=(128, 512, 1024, 4096)):
+    """Configurations 0, 3 and 4 per shape.  Every measurement is one CUDA graph that walks enough distinct weight
+    copies that nothing is served from L2, timed with CUDA events on `stream`.
+      gemv    batch-1 GEMV on pre-quantised input: us, GB/s of algorithmic bytes, fraction of the measured copy peak
+              (config 0 is `down`);
+      small_m M in {1..64}: us of the form the dispatcher picks, of the CUDA-core few-token form and of the
+              tensor-core form, so the crossover can be read off (config 3);
+      prefill M in {128..4096}: us, TFLOP/s and the fraction of the measured bf16 peak (config 4)."""
     from qwen_engine_b200 import synth
-    torch.cuda.set_device(0)
-    ops.init()
-    peaks = {}
-    try:
-        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
-    except Exception:
-        pass
-    stream = torch.cuda.Stream()
-    reps = max(3, min(args.steps, 20))
-    shapes = {"qkv": (2048, 1536), "o": (1536, 1536), "gate_up": (17920, 1536), "down": (1536, 8960),
-              "big": (28672, 8192)}
-    m_list = [int(v) for v in args.m_list.split(",") if v]
-    out = {"suite": "shapes", "gemv": {}, "gemm": {}, "peaks": {k: peaks.get(k) for k in ("hbm_gbs", "bf16_tflops")}}
+    hbm, tf = peaks.get("hbm_gbs") or 6650.0, peaks.get("bf16_tflops") or 1590.0
+    out = {"peaks": {"hbm_gbs": hbm, "bf16_tflops": tf, "source": "measured" if peaks.get("hbm_gbs") else "fallback"},
+           "gemv": {}, "small_m": {}, "prefill": {}}
     g = torch.Generator(device="cuda").manual_seed(1)
 
     def weights(N, K, copies):
-        ws = []
-        for _ in range(copies):
-            w = torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), dtype=torch.int32, device="cuda", generator=g)
-            sc = (torch.rand((N, K // 128), device="cuda", generator=g) * 0.018 + 0.002).half()
-            ws.append((w, sc))
-        return ws
+        return [(torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), dtype=torch.int32, device="cuda", generator=g),
+                 (torch.rand((N, K // 128), device="cuda", generator=g) * 0.018 + 0.002).half()) for _ in range(copies)]
 
-    def timed_graph(fn):
+    def timed_graph(fn, n=reps):
         with torch.cuda.stream(stream):
             fn()
             stream.synchronize()
             gr = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gr, stream=stream):
                 fn()
-            for _ in range(2):
+            for _ in range(3):
                 gr.replay()
             stream.synchronize()
-            ms = timed_events(torch, stream, gr.replay, reps)
-        return ms * 1e3 / reps   # us per graph
+            ms = timed_events(torch, stream, gr.replay, n)
+        return ms * 1e3 / n   # us per graph
 
+    shapes = dict(SHAPES_QWEN, big=SHAPE_BIG)
     for name, (N, K) in shapes.items():
         wbytes = synth.weight_bytes(N, K)
         copies = max(2, min(28, int(np.ceil(3 * 126e6 / wbytes))))
@@ -619,28 +629,66 @@ def run_shapes_suite(args):
                     ops.launch_gemv_w4a8(w, sc, q8, xs, s8, None, y, N, K)
         us = timed_graph(gemv_all) / copies
         nb = synth.gemv_algorithmic_bytes(N, K, n_out=n_out)
-        out["gemv"][name] = {"N": N, "K": K, "us": us, "GB/s": nb / us / 1e3, "copies": copies}
+        out["gemv"][name] = {"N": N, "K": K, "us": round(us, 3), "GB/s": round(nb / us / 1e3, 1),
+                             "frac_of_hbm_peak": round(nb / us / 1e3 / hbm, 3), "weight_copies": copies}
 
-        for M in m_list:
-            if name == "big" and M not in (16, 128, 1024, 4096):
-                continue
+        def gemm_for(M, use):
             xm = torch.randn((M, K), device="cuda", generator=g).half()
             ym = torch.empty((M, n_out), dtype=torch.float16, device="cuda")
-            use = ws[:max(2, min(copies, 8))] if M >= 512 else ws
 
-            def gemm_all():
+            def run():
                 for w, sc in use:
                     if name == "gate_up":
                         ops.launch_gemm_prefill_dual_gate_up_swiglu_w4a16(w, sc, xm, ym, M, None, K, n_out)
                     else:
                         ops.launch_gemm_prefill_w4a16(w, sc, xm, None, ym, M, N, K)
-            us = timed_graph(gemm_all) / len(use)
+            return run
+
+        if name != "big":
+            for M in m_small:
+                row = {}
+                for label, opt in (("dispatch", 0), ("cuda_core", 1 << 20), ("tensor_core", 1)):
+                    ops.set_option(ops.OPT_GEMM_MIN_TOKENS_TENSOR_CORE, opt)
+                    try:
+                        row[label + "_us"] = round(timed_graph(gemm_for(M, ws), n=max(3, reps // 2)) / copies, 3)
+                    finally:
+                        ops.set_option(ops.OPT_GEMM_MIN_TOKENS_TENSOR_CORE, 0)
+                row["GB/s"] = round((wbytes + 2 * M * K + 2 * M * n_out) / row["dispatch_us"] / 1e3, 1)
+                out["small_m"][f"{name}.M{M}"] = row
+        for M in (m_prefill if name != "big" else (m_prefill[0], m_prefill[-1])):
+            use = ws[:2] if M >= 512 else ws
+            us = timed_graph(gemm_for(M, use), n=max(3, reps // 2)) / len(use)
             flops = 2.0 * M * N * K
-            nb = wbytes + 2 * M * K + 2 * M * n_out
-            out["gemm"][f"{name}.M{M}"] = {"us": us, "TFLOP/s": flops / us / 1e6, "GB/s": nb / us / 1e3}
+            out["prefill"][f"{name}.M{M}"] = {"us": round(us, 2), "TFLOP/s": round(flops / us / 1e6, 1),
+                                              "frac_of_bf16_peak": round(flops / us / 1e6 / tf, 3)}
         del ws
         torch.cuda.empty_cache()
+    # the GEMV -> tensor-core crossover per shape: the smallest M at which the tensor-core form is the faster one
+    for name in SHAPES_QWEN:
+        cross = None
+        for M in m_small:
+            r = out["small_m"][f"{name}.M{M}"]
+            if r["tensor_core_us"] < r["cuda_core_us"]:
+                cross = M
+                break
+        out["small_m"][f"{name}.crossover_M"] = cross
     out["tc_wait_timeouts"] = ops.debug_counter(0)
+    return out
+
+
+def run_shapes_suite(args):
+    """`--suite shapes`: the per-shape table alone."""
+    import torch
+    import qwen_engine_b200 as ops
+    torch.cuda.set_device(0)
+    ops.init()
+    peaks = {}
+    try:
+        peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
+    except Exception:
+        pass
+    out = shapes_table(torch, ops, torch.cuda.Stream(), peaks, reps=max(3, min(args.steps, 20)))
+    out["suite"] = "shapes"
     print(json.dumps(out), flush=True)
 
 
@@ -667,12 +715,20 @@ def run_single(args):
         s8 = torch.empty(K // 8, dtype=torch.int32, device="cuda")
         y = torch.empty(n_out, dtype=torch.float16, device="cuda")
         ops.launch_quantize_fp16_to_q8_1(x, q8, xs, s8, K)
+        gamma = torch.full((K,), 0.05, dtype=torch.float16, device="cuda")
         for i in range(reps):
             w, sc = ws[i % copies]
             if args.shape == "gate_up":
-                ops.launch_gemv_dual_gate_up_swiglu_w4a8(w, sc, q8, xs, s8, y, K, n_out)
-            else:
+                if args.input == "q8":
+                    ops.launch_gemv_dual_gate_up_swiglu_w4a8(w, sc, q8, xs, s8, y, K, n_out)
+                elif args.input == "fp16":
+                    ops.launch_gemv_dual_gate_up_swiglu_w4a16(w, sc, x, y, K, n_out)
+                else:
+                    ops.launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16(w, sc, x, gamma, y, K, n_out)
+            elif args.input == "q8":
                 ops.launch_gemv_w4a8(w, sc, q8, xs, s8, None, y, N, K)
+            else:
+                ops.launch_gemv_rmsnorm_w4a16(w, sc, x, gamma if args.input == "fp16norm" else None, None, y, N, K)
     else:
         M = args.m
         xm = torch.randn((M, K), device="cuda", generator=g).half()
@@ -684,7 +740,7 @@ def run_single(args):
             else:
                 ops.launch_gemm_prefill_w4a16(w, sc, xm, None, ym, M, N, K)
     torch.cuda.synchronize()
-    print(json.dumps({"suite": "single", "shape": args.shape, "m": args.m, "launches": reps, "copies": copies,
+    print(json.dumps({"suite": "single", "shape": args.shape, "m": args.m, "input": args.input, "launches": reps, "copies": copies,
                       "tc_wait_timeouts": ops.debug_counter(0)}), flush=True)
 
 
@@ -781,10 +837,8 @@ def main():
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warmup,
         "ms_per_step": ms_per_step, "us_per_sweep": ms_per_step * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers": len(layers_np), "parallelism": f"replicas x{world}",
-                   "algorithmic_bytes_per_step": nbytes,
-                   "l2": "inputs larger than L2: 675 MB of packed weights are streamed per step",
-                   "pdl": bool(ops.load().w4a16_get_option(1)), "sweep_flags": sweep_flags},
+        "config": bench_config(len(layers_np), world, nbytes),
+        "options": {"pdl": bool(ops.get_option(ops.OPT_PDL)), "sweep_flags": sweep_flags},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": synth.HIDDEN * 2,
                 "d2h_bytes_per_step": synth.HIDDEN * 2,
                 "how": "w4a16_sweep_run_host: pinned fp16 hidden state in, sweep graph, hidden state out, "
@@ -811,12 +865,25 @@ def main():
             pf = {"unavailable": str(e)[:200]}
         if rank == 0:
             line["prefill_big"] = pf
+    if rank == 0 and world == 1 and not args.no_shapes:
+        try:
+            line["roofline"]["per_shape"] = shapes_table(torch, ops, stream, peaks)
+        except Exception as e:
+            line["roofline"]["per_shape"] = {"unavailable": str(e)[:200]}
+    if rank == 0:
+        # the driver's record keeps the objects it knows: the extras are also carried inside `roofline`
+        line["roofline"]["sweep"] = line["roofline_sweep"]
+        for key in ("lm_head", "prefill_big"):
+            if key in line:
+                line["roofline"][key] = line[key]
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         ref_cuda = time_reference_cuda(torch, layers_dev, stream, min(steps, 100))
         if ref_cuda:
             line["reference_cuda_sm100a"] = ref_cuda
         gbs, cores, sample, h_cpu = time_cpu_sweep(layers_np, h0_np)
         line["cpu_baseline"] = {"value": gbs, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        if ref_cuda:   # second comparison: the reference's own CUDA kernels rebuilt for sm_100a
+            line["cpu_baseline"]["reference_cuda_sm100a"] = ref_cuda
         # sanity: first layer of the device sweep against the oracle on the same input
         import oracle
         one = ops.DecodeSweep(layers_dev[:1], stream=stream)

@@ -91,12 +91,14 @@ int gemm_launch(GemmArgs g, cudaStream_t stream) {
     const DeviceInfo* dev = nullptr;
     if (int st = ensure_device_ready(&dev)) return st;
 
-    // The tcgen05 kernel pads the token count to its smallest tile (16); measured on B200 it overtakes the
-    // CUDA-core few-token form at 5 tokens on the narrow K = 1536 shapes and at 4 on K = 8960 (where the few-token
-    // form stages only two tokens per pass) and on matrices tall enough to give every SM a tile (gate_up).  The CUDA-core forms also take what TMA cannot address.
+    // The tcgen05 kernel pads the token count to its smallest tile (16), so below a handful of tokens the CUDA-core
+    // few-token form (the decode GEMV's memory behaviour with fp16 arithmetic) is the faster one.  Measured
+    // crossovers on B200: 3 tokens where K > 4096 (down: the few-token form stages only two tokens per pass there),
+    // 4 on matrices tall enough to give every SM a CTA of their own (gate_up), 7 on the narrow K <= 4096 shapes
+    // (QKV, O).  The CUDA-core forms also take what TMA cannot address.
     const int tc_min_m_opt = option(W4A16_OPT_GEMM_MIN_TOKENS_TENSOR_CORE);
     const int rows_all = g.rows[0] + (g.mode == kQkv ? g.rows[1] + g.rows[2] : 0);
-    const int tc_min_m = tc_min_m_opt > 0 ? tc_min_m_opt : ((g.K > 4096 || rows_all >= 128 * dev->sm_count) ? 4 : 5);
+    const int tc_min_m = tc_min_m_opt > 0 ? tc_min_m_opt : (g.K > 4096 ? 3 : (rows_all >= 64 * dev->sm_count ? 4 : 7));
     if ((g.M >= tc_min_m || g.num_peers > 0) && gemm_tc_supported(g)) return gemm_tc_launch(g, dev->sm_count, stream);
     if (g.num_peers > 0) return W4A16_ERR_SHAPE;   // peer stores exist in the tensor-core form only
 

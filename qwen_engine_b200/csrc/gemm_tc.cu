@@ -28,6 +28,8 @@
 
 #include <algorithm>
 #include <mutex>
+#include <utility>
+#include <vector>
 
 #include "gemm_smallm.cuh"
 #include "w4a16_common.cuh"
@@ -1010,6 +1012,43 @@ cudaError_t launch_tc(int mode, dim3 grid, size_t smem, cudaStream_t stream, con
 }
 }  // namespace
 
+
+int groups_for(int S) { return S >= 4 ? 4 : 2; }
+
+// Clusters of `ksplit` CTAs of the K-split kernel that can be resident at once on the current device (cached).
+int max_active_clusters(int mode, int groups, int ksplit, size_t smem) {
+    static std::mutex mu;
+    static std::vector<std::pair<uint64_t, int>> cache;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    const uint64_t key = (static_cast<uint64_t>(dev) << 48) ^ (static_cast<uint64_t>(mode) << 40) ^ (static_cast<uint64_t>(groups) << 36) ^
+                         (static_cast<uint64_t>(ksplit) << 32) ^ static_cast<uint64_t>(smem);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (const auto& kv : cache)
+            if (kv.first == key) return kv.second;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1, 1, static_cast<unsigned>(ksplit));
+    cfg.blockDim = dim3((4 * groups + kMaxIssuers + 2) * 32);
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = static_cast<unsigned>(ksplit);
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    cudaError_t e;
+#define W4_OCC(M_, G_) cudaOccupancyMaxActiveClusters(&n, gemm_w4a16_tc_kernel<M_, G_, true>, &cfg)
+    if (groups == 2) e = mode == kPlain ? W4_OCC(kPlain, 2) : mode == kQkv ? W4_OCC(kQkv, 2) : W4_OCC(kSwiglu, 2);
+    else e = mode == kPlain ? W4_OCC(kPlain, 4) : mode == kQkv ? W4_OCC(kQkv, 4) : W4_OCC(kSwiglu, 4);
+#undef W4_OCC
+    if (e != cudaSuccess) { cudaGetLastError(); n = 1 << 20; }   // unknown: do not restrict
+    std::lock_guard<std::mutex> lock(mu);
+    cache.emplace_back(key, n);
+    return n;
+}
+
 int gemm_tc_set_attributes() {
     cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_tc_pair_kernel<kPlain>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
     if (e == cudaSuccess)
@@ -1052,10 +1091,16 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     a.K = g.K;
     a.num_peers = g.mode == kPlain ? g.num_peers : 0;
     for (int p = 0; p < 7; ++p) a.peer_out[p] = p < a.num_peers ? g.peer_out[p] : nullptr;
+    // CTA pairs (cta_group::2) from 256 tokens on: 256-token tiles, no K split, no peer stores, an even number of
+    // 128-row tiles in every weight tensor (a pair never straddles two tensors) and 4-byte aligned scales (read
+    // in pairs).  Measured faster than the single-CTA form even where the pair tiles do not fill the GPU.
+    bool pairs = option(W4A16_OPT_GEMM_FORM) != 1 && g.M >= 256 && a.num_peers == 0;
+    for (int t = 0; t < nt; ++t)
+        pairs = pairs && a.tiles[t] % 2 == 0 && reinterpret_cast<uintptr_t>(g.scales[t]) % 4 == 0;
     // tokens per tile: the smallest power of two >= M (16..256); halve it while the grid is thin
     int T = 16;
     while (T < g.M && T < 256) T *= 2;
-    while (T > 64 && total_tiles * ((g.M + T - 1) / T) < sm_count) T /= 2;
+    while (!pairs && T > 64 && total_tiles * ((g.M + T - 1) / T) < sm_count) T /= 2;
     int S = kMaxStages;
     while (S > 2 && tc_smem_bytes(T, S, g.K) > 227 * 1024) --S;
     if (tc_smem_bytes(T, S, g.K) > 227 * 1024) return W4A16_ERR_TOO_LARGE;
@@ -1075,11 +1120,14 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     // cluster size) share a tile; their fp32 partials must fit the leader's pipeline buffers.
     const int ctas = total_tiles * ((g.M + T - 1) / T);
     int ksplit = 1;
-    if (ctas * 2 <= sm_count) ksplit = std::min(8, sm_count / ctas);
+    if (!pairs && ctas * 2 <= sm_count) ksplit = std::min(8, sm_count / ctas);
     ksplit = std::min(ksplit, g.K / 256);
     const size_t ring_bytes = static_cast<size_t>(kRawStages) * kRawBytes + static_cast<size_t>(S) * (kABytes + T * 128);
     while (ksplit > 1 && static_cast<size_t>(ksplit - 1) * T * kTileRows * sizeof(float) > ring_bytes) --ksplit;
     a.ksplit = std::max(1, ksplit);
+    // All clusters of a K-split launch should be resident at once (a second wave doubles the time).  How many fit
+    // depends on how the SMs are spread over the GPCs, so the runtime is asked; fewer slices until they do.
+    while (a.ksplit > 1 && max_active_clusters(g.mode, groups_for(S), a.ksplit, tc_smem_bytes(T, S, g.K)) < ctas) --a.ksplit;
 
 
     for (int t = 0; t < nt; ++t) {
@@ -1089,12 +1137,6 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     }
     for (int t = nt; t < 3; ++t) a.tmap_w[t] = a.tmap_w[0];
 
-    // CTA pairs (cta_group::2) for prefill-sized token tiles: 256 tokens per tile, no K split, no peer stores,
-    // and an even number of 128-row tiles in every weight tensor (a pair never straddles two tensors).
-    const int gemm_form = option(W4A16_OPT_GEMM_FORM);
-    bool pairs = gemm_form != 1 && T == 256 && a.ksplit == 1 && a.num_peers == 0;
-    for (int t = 0; t < nt; ++t)     // (scales are read as pairs of fp16: 4-byte alignment)
-        pairs = pairs && a.tiles[t] % 2 == 0 && reinterpret_cast<uintptr_t>(g.scales[t]) % 4 == 0;
     if (pairs) {
         int SP = kMaxStages;
         while (SP > 2 && tc_pair_smem_bytes(SP) > 227 * 1024) --SP;
@@ -1126,7 +1168,7 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     const size_t smem = tc_smem_bytes(T, S, g.K);
     // A dequantising group revisits a ring slot every NG k-blocks and waits on a parity: it must never
     // be two uses of a slot ahead of the tensor core, which holds exactly when NG <= stages.
-    const int groups = S >= 4 ? 4 : 2;
+    const int groups = groups_for(S);
     const cudaError_t e = groups == 2 ? launch_tc<2>(g.mode, grid, smem, stream, a) : launch_tc<4>(g.mode, grid, smem, stream, a);
     return static_cast<int>(e);
 }

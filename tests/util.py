@@ -73,39 +73,7 @@ def assert_fp16_close(y, ref64, max_rel=1e-2, median_ulp=2.0, what="", magnitude
     return rep
 
 
-class RefKernels:
-    """The reference's CUDA kernels rebuilt for sm_100a (oracle/Makefile `ref`), if present."""
-
-    class QKVPod(ctypes.Structure):
-        _fields_ = [(n, ctypes.c_void_p) for n in ("q_weight", "q_scale", "d_q", "k_weight", "k_scale", "d_k",
-                                                   "v_weight", "v_scale", "d_v")]
-
-    def __init__(self, flavour: str):
-        path = REF_DIR / f"libqwen_ref_{flavour}.so"
-        self.lib = ctypes.CDLL(str(path))
-        self.flavour = flavour
-
-    @staticmethod
-    def available(flavour: str = "ieee") -> bool:
-        return (REF_DIR / f"libqwen_ref_{flavour}.so").exists()
-
-    def call(self, name: str, *args):
-        fn = getattr(self.lib, name)
-        fn.restype = ctypes.c_int
-        conv = []
-        for a in args:
-            if a is None:
-                conv.append(ctypes.c_void_p(0))
-            elif isinstance(a, ctypes.c_void_p):
-                conv.append(a)
-            elif isinstance(a, int):
-                conv.append(ctypes.c_int(a))
-            elif isinstance(a, ctypes.Structure):
-                conv.append(ctypes.byref(a))
-            else:  # torch tensor
-                conv.append(ctypes.c_void_p(a.data_ptr()))
-        st = fn(*conv)
-        assert st == 0, f"{name} ({self.flavour}) failed with {st}"
+from oracle import RefKernels  # noqa: E402,F401  (the loader of the rebuilt reference kernels lives with the checkers)
 
 
 def stream_ptr() -> ctypes.c_void_p:
