@@ -271,3 +271,72 @@ def test_prefill_sizes_of_the_benchmark_match_oracle(ops, name, M):
 def test_release_cached_benchmark_weights():
     _cache.clear()
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("M,N,K,mode", [(300, 1536, 1536, "res"), (257, 256, 512, "plain"), (700, 512, 256, "swiglu"),
+                                        (1000, 1536, 8960, "res"), (260, 2048, 1536, "qkv")])
+def test_cta_pair_kernel_on_small_and_ragged_shapes(ops, M, N, K, mode):
+    """The cta_group::2 kernel forced (W4A16_OPT_GEMM_FORM = 2) onto shapes the dispatcher would give to the
+    single-CTA kernel: a ragged last token tile, a single pair tile, SwiGLU, the in-place residual, three tensors.
+    Checked against the oracle on sampled entries and against the single-CTA kernel on all of them."""
+    from qwen_engine_b200 import synth
+    rng = np.random.default_rng(M + N + K)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    d_x = util.to_dev(x)
+
+    def run(form):
+        ops.set_option(ops.OPT_GEMM_FORM, form)
+        try:
+            if mode == "qkv":
+                dims = (1536, 256, 256)
+                ws = [(synth.packed_weights(M, f"p{i}", n, K), synth.scales(M, f"p{i}", n, K)) for i, n in enumerate(dims)]
+                dev = [(util.to_dev(w), util.to_dev(s)) for w, s in ws]
+                outs = [torch.full((M * n + 8,), float("nan"), dtype=torch.float16, device="cuda") for n in dims]
+                view = ops.QKVProjectionView(dev[0][0], dev[0][1], outs[0], dev[1][0], dev[1][1], outs[1], dev[2][0], dev[2][1], outs[2])
+                ops.launch_gemm_prefill_qkv_w4a16(view, d_x, M, None, K, 12, 2, 128)
+                torch.cuda.synchronize()
+                return ws, [util.to_np(o) for o in outs]
+            qw, sc = synth.packed_weights(M, "p", N, K), synth.scales(M, "p", N, K)
+            if mode == "swiglu":
+                y = torch.full((M * (N // 2) + 8,), float("nan"), dtype=torch.float16, device="cuda")
+                ops.launch_gemm_prefill_dual_gate_up_swiglu_w4a16(util.to_dev(qw), util.to_dev(sc), d_x, y, M, None, K, N // 2)
+                torch.cuda.synchronize()
+                return (qw, sc), util.to_np(y)
+            res = np.random.default_rng(7).standard_normal((M, N)).astype(np.float16) if mode == "res" else None
+            y = torch.full((M * N + 8,), float("nan"), dtype=torch.float16, device="cuda")
+            if res is not None:
+                y[:M * N] = util.to_dev(res).reshape(-1)
+            ops.launch_gemm_prefill_w4a16(util.to_dev(qw), util.to_dev(sc), d_x, y if res is not None else None, y, M, N, K)
+            torch.cuda.synchronize()
+            return (qw, sc, res), util.to_np(y)
+        finally:
+            ops.set_option(ops.OPT_GEMM_FORM, 0)
+
+    w, pair = run(2)
+    _, single = run(1)
+    m_idx = _sample(rng, M, 8)
+    if mode == "qkv":
+        for (qw, sc), a, b, n in zip(w, pair, single, (1536, 256, 256)):
+            assert np.isnan(a[M * n:]).all()
+            a, b = a[:M * n].reshape(M, n), b[:M * n].reshape(M, n)
+            util.assert_fp16_close(a, b.astype(np.float64), what="pair vs single")
+            n_idx = _sample(rng, n, 32)
+            util.assert_fp16_close(a[np.ix_(m_idx, n_idx)], oracle.gemm_prefill(qw, sc, x, m_idx, n_idx)[0], what="pair qkv")
+    elif mode == "swiglu":
+        I = N // 2
+        assert np.isnan(pair[M * I:]).all()
+        a, b = pair[:M * I].reshape(M, I), single[:M * I].reshape(M, I)
+        util.assert_fp16_close(a, b.astype(np.float64), what="pair vs single")
+        n_idx = _sample(rng, I, 32)
+        util.assert_fp16_close(a[np.ix_(m_idx, n_idx)], oracle.gemm_prefill(w[0], w[1], x, m_idx, n_idx, swiglu=True)[0], what="pair swiglu")
+    else:
+        assert np.isnan(pair[M * N:]).all()
+        a, b = pair[:M * N].reshape(M, N), single[:M * N].reshape(M, N)
+        res = w[2]
+        acc_all = b.astype(np.float64) - res.astype(np.float64) if res is not None else None
+        util.assert_fp16_close(a, b.astype(np.float64), what="pair vs single", magnitude=acc_all)
+        n_idx = _sample(rng, N, 32)
+        ref64, _ = oracle.gemm_prefill(w[0], w[1], x, m_idx, n_idx, residual=res)
+        acc = ref64 - res[np.ix_(m_idx, n_idx)].astype(np.float64) if res is not None else None
+        util.assert_fp16_close(a[np.ix_(m_idx, n_idx)], ref64, what="pair plain", magnitude=acc)
+    assert ops.debug_counter(0) == 0
