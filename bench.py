@@ -364,6 +364,46 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
         us = float(t.item()) * 1e3 / (rounds * copies)
         return us, how, result
 
+    def measure_signal():
+        """The barrier-free form: slices and completion flags written by the GEMV epilogue, a gathering kernel that
+        waits for the flags (nsplit.NSplitSignalGemv)."""
+        shards = [nsplit.NSplitSignalGemv(w, s, N, K, ops.gemv_w4a8_peers_signal, ops.gather_after_signals) for w, s in slabs]
+        with torch.cuda.stream(stream):
+            def one_round():
+                for sh in shards:
+                    sh.forward(q8, xs, s8)
+            for _ in range(2):
+                one_round()
+            stream.synchronize()
+            result = shards[0].forward(q8, xs, s8).clone()
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            rounds = max(1, (steps + copies - 1) // copies)
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    one_round()
+                run, how = graph.replay, "cuda graph"
+            except Exception:
+                torch.cuda.synchronize()
+                run, how = one_round, "eager"
+            for _ in range(max(1, warmup // copies)):
+                run()
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            ms = timed_events(torch, stream, run, rounds)
+            torch.cuda.synchronize()
+        t = torch.tensor([ms], device="cuda")
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        timeouts = int(sum(int(sh.status.item()) != 0 for sh in shards))
+        if timeouts:
+            raise RuntimeError(f"{timeouts} signal waits ran out")
+        return float(t.item()) * 1e3 / (rounds * copies), how, result
+
     us_nccl, how_nccl, y_nccl = measure(False)
     out = {"workload": f"config 2: lm_head {K}->{N}, rows split over {world} GPU(s)", "rows_per_gpu": rows,
            "unit": UNIT, "scaling": "strong", "weight_copies_rotated": copies,
@@ -377,8 +417,16 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
             best = min(best, us_peer)
         except Exception as e:   # no peer access / symmetric memory on this box
             out["peer_store_epilogue"] = {"unavailable": str(e)[:200]}
+        try:
+            us_sig, how_sig, y_sig = measure_signal()
+            out["peer_store_signal"] = {"us_per_step": us_sig, "value": nbytes / (us_sig * 1e-6) / 1e9,
+                                        "timed_as": how_sig, "equals_nccl_result": bool(torch.equal(y_nccl, y_sig))}
+            best = min(best, us_sig)
+        except Exception as e:
+            out["peer_store_signal"] = {"unavailable": str(e)[:200]}
     out["us_per_step"] = best
     out["value"] = nbytes / (best * 1e-6) / 1e9
+    out["gpus"] = world       # strong scaling: efficiency = us_per_step(1 GPU) / (world * us_per_step)
 
     # ---- token selection after lm_head: logits + stand-alone sampler vs. candidates from the GEMV's epilogue ----
     try:

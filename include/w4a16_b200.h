@@ -165,6 +165,32 @@ W4A16_API int w4a16_gemv_w4a8_peers(const uint32_t* qweight, const void* scales,
                                     void* const* peer_outputs, int num_peers, int out_features,
                                     int in_features, w4a16_stream_t stream);
 
+/*
+ * The row-split GEMV without a barrier between the ranks (no reference counterpart).  Every rank's launch stores
+ * its slice -- with 16-byte stores -- into half (step & 1) of ITS OWN gathered vector and of every peer's
+ * (gathered_slice / peer_slices[i] point at this rank's first element inside half 0 of each buffer; the halves are
+ * half_stride elements apart), and when its last CTA is through it writes the step number to *step_word, to
+ * *local_flag and, behind one system-scope fence, to peer_flags[i] -- this rank's slot in GPU i's flag array.
+ * step = *step_word + 1; *step_word and *done_counter are device words, zero at first, that only this sequence of
+ * launches touches: nothing about a step comes from the host, so the pair of calls replays as a CUDA graph.
+ * Two halves are used in turn because a fast rank's next slice must not land in the vector a slow rank's readers
+ * still use; a rank reaches step s + 2 only after w4a16_gather_after_signals of step s + 1 has seen every
+ * rank's flag, i.e. after every rank has finished reading step s.
+ * w4a16_gather_after_signals waits until flags[0 .. num_flags) all show this rank's step (bounded by
+ * W4A16_OPT_SIGNAL_WAIT_SPINS; on expiry *d_status = 1 + the rank it missed and the copy runs on what is there)
+ * and copies num_elements of half (step & 1) of the gathered vector into `output`.
+ * Needs 16-byte aligned weights and in_features <= 2048.  Ranks on DIFFERENT GPUs only: launches that wait for
+ * one another must not share a GPU.
+ */
+W4A16_API int w4a16_gemv_w4a8_peers_signal(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                                           const float* input_scale, const int32_t* input_sum8, void* gathered_slice,
+                                           void* const* peer_slices, uint32_t* const* peer_flags, int num_peers,
+                                           uint32_t* local_flag, uint32_t* done_counter, uint32_t* step_word,
+                                           int half_stride, int out_features, int in_features, w4a16_stream_t stream);
+W4A16_API int w4a16_gather_after_signals(const void* gathered, int half_stride, const uint32_t* flags, int num_flags,
+                                         const uint32_t* step_word, int* d_status, void* output, int num_elements,
+                                         w4a16_stream_t stream);
+
 /* ---- embedding lookup on the W4 table ---------------------------------------------------- */
 /*
  * reference include/kernels.cuh launch_embed_lookup_w4a16 (src/kernels/rmsnorm_rope.cu:15-69): row `token` of

@@ -67,6 +67,9 @@ SIGNATURES = {
                         c_void_p],
     "w4a16_gemv_w4a8_peers": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(c_void_p), c_int,
                               c_int, c_int, c_void_p],
+    "w4a16_gemv_w4a8_peers_signal": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, POINTER(c_void_p),
+                                     POINTER(c_void_p), c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "w4a16_gather_after_signals": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
     "w4a16_qwenbin_parse": [c_void_p, ctypes.c_uint64, POINTER(QwenBinHeader)],
     "w4a16_qwenbin_tensors": [c_void_p, ctypes.c_uint64, c_void_p, POINTER(LayerWeights), c_int, POINTER(QwenBinGlobals),
                               POINTER(QwenBinBiases)],

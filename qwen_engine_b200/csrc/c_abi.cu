@@ -369,6 +369,51 @@ int w4a16_gemv_w4a8(const uint32_t* qweight, const void* scales, const int8_t* i
                       in_features, stream);
 }
 
+int w4a16_gemv_w4a8_peers_signal(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
+                                 const float* input_scale, const int32_t* input_sum8, void* gathered_slice,
+                                 void* const* peer_slices, uint32_t* const* peer_flags, int num_peers,
+                                 uint32_t* local_flag, uint32_t* done_counter, uint32_t* step_word, int half_stride,
+                                 int out_features, int in_features, w4a16_stream_t stream) {
+    if (!qweight || !scales || !input_q8 || !input_scale || !input_sum8 || !gathered_slice || !local_flag ||
+        !done_counter || !step_word || out_features <= 0 || half_stride < out_features)
+        return W4A16_ERR_INVALID_ARG;
+    if (int st = check_k(in_features)) return st;
+    if (num_peers < 0 || num_peers > 7 || (num_peers > 0 && (!peer_slices || !peer_flags))) return W4A16_ERR_INVALID_ARG;
+    if (misaligned(qweight, 16) || misaligned(scales, 2) || misaligned(gathered_slice, 2) || misaligned(input_scale, 4) ||
+        misaligned(input_sum8, 4) || misaligned(local_flag, 4) || misaligned(done_counter, 4) || misaligned(step_word, 4))
+        return W4A16_ERR_ALIGNMENT;
+    GemvArgs a = {};
+    a.qweight[0] = qweight; a.scales[0] = H(scales); a.out[0] = H(gathered_slice); a.rows[0] = out_features;
+    a.q8 = input_q8; a.xscale = input_scale; a.sum8 = input_sum8;
+    a.K = in_features; a.units = out_features;
+    for (int p = 0; p < num_peers; ++p) {
+        if (!peer_slices[p] || !peer_flags[p]) return W4A16_ERR_INVALID_ARG;
+        if (misaligned(peer_slices[p], 2) || misaligned(peer_flags[p], 4)) return W4A16_ERR_ALIGNMENT;
+        a.peer_out[p] = H(peer_slices[p]);
+        a.sample_peer_flag[p] = peer_flags[p];
+    }
+    a.num_peers = num_peers;
+    a.sample_flag_local = local_flag;
+    a.sample_done_counter = done_counter;
+    a.sample_step_word = step_word;
+    a.sample_half_stride = half_stride;
+    return gemv_launch(kPlain, a, S(stream));
+}
+
+int w4a16_gather_after_signals(const void* gathered, int half_stride, const uint32_t* flags, int num_flags,
+                               const uint32_t* step_word, int* d_status, void* output, int num_elements,
+                               w4a16_stream_t stream) {
+    if (!gathered || !flags || !step_word || !output || num_flags <= 0 || num_flags > 256 || num_elements <= 0 ||
+        half_stride < num_elements)
+        return W4A16_ERR_INVALID_ARG;
+    if (misaligned(gathered, 2) || misaligned(output, 2) || misaligned(flags, 4) || misaligned(step_word, 4) ||
+        misaligned(d_status, 4))
+        return W4A16_ERR_ALIGNMENT;
+    if (int st = ensure_device_ready(nullptr)) return st;
+    return gather_after_flags(H(gathered), half_stride, flags, num_flags, step_word, d_status, H(output), num_elements,
+                              S(stream));
+}
+
 int w4a16_gemv_w4a8_peers(const uint32_t* qweight, const void* scales, const int8_t* input_q8,
                           const float* input_scale, const int32_t* input_sum8, void* output_y,
                           void* const* peer_outputs, int num_peers, int out_features, int in_features,

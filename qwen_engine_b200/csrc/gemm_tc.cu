@@ -21,7 +21,7 @@
 //                 128B-swizzled so that row-per-thread reads are bank-conflict free
 //   epilogue    : tcgen05.ld 32x32b (thread = weight row, registers = tokens), fp16 stores
 //
-// No cluster, no multicast.  Every mbarrier wait is bounded: on expiry the kernel raises an
+// One destination per copy, no cluster.  Every mbarrier wait is bounded: on expiry the kernel raises an
 // abort flag, all roles leave their loops, TMEM is freed and the kernel returns; the host can
 // read the count of such events with w4a16_debug_counter(0).
 #include <cuda.h>
@@ -537,9 +537,10 @@ __global__ void __launch_bounds__((4 * NG + kMaxIssuers + 2) * 32, 1) gemm_w4a16
 //
 // Synchronisation.  Every stage has ONE "full" barrier, in the leader: the dequantising warps of both CTAs
 // arrive on it (the peer's through the cluster shared-memory window, after a proxy fence and with release at
-// cluster scope) and both CTAs' token loads complete their bytes on it (cp.async.bulk.tensor ... cta_group::2,
-// no multicast).  The leader's tcgen05.commit.cta_group::2 multicasts to the "empty" barrier of the stage in
-// BOTH CTAs, and at the end to both "accumulator ready" barriers.  Raw weight rings are private to each CTA.
+// cluster scope) and both CTAs' token loads complete their bytes on it (each CTA loads its own half with the
+// cta_group::2 form of the tensor copy; every load has one destination).  The leader's tcgen05.commit.cta_group::2
+// arrives on the "empty" barrier of the stage in BOTH CTAs (a CTA mask of 3), and at the end on both
+// "accumulator ready" barriers.  Raw weight rings are private to each CTA.
 // All mbarrier waits are bounded as above; both cluster barriers are reached by every thread of both CTAs
 // whatever happened before, and tensor memory is allocated and freed by the same warp of each CTA.
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
@@ -784,8 +785,11 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
             constexpr int kOutPerRow = MODE == kSwiglu ? kTileRows / 2 : kTileRows;    // outputs of a token row in the tile
             const int n_out0 = MODE == kSwiglu ? pt.n0 / 2 : pt.n0;
             const int n_valid = MODE == kSwiglu ? max(0, min(kOutPerRow, (rows_t - pt.n0) / 2)) : max(0, min(kOutPerRow, rows_t - pt.n0));
-            const bool vec_ok = (ld % 8 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (n_valid % 8 == 0) &&
-                                (MODE != kPlain || a.residual == nullptr || reinterpret_cast<uintptr_t>(a.residual) % 16 == 0);
+            bool vec_ok = (ld % 8 == 0) && (reinterpret_cast<uintptr_t>(out) % 16 == 0) && (n_valid % 8 == 0) &&
+                          (MODE != kPlain || a.residual == nullptr || reinterpret_cast<uintptr_t>(a.residual) % 16 == 0);
+            if constexpr (MODE == kPlain) {
+                for (int p = 0; p < a.num_peers; ++p) vec_ok = vec_ok && reinterpret_cast<uintptr_t>(a.peer_out[p]) % 16 == 0;
+            }
             // (1) this warp's 32 rows x 64 tokens of the accumulators into registers; with that the tensor memory is
             // free, and the next tile's first MMA may overwrite it while the values are still being stored
             uint32_t v[4][16];
@@ -835,6 +839,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
                             }
                         }
                         *reinterpret_cast<uint4*>(out + off) = val;
+                        if constexpr (MODE == kPlain) {     // the block's place in the other GPUs' matrices: 16-byte stores over NVLink
+                            for (int p = 0; p < a.num_peers; ++p) *reinterpret_cast<uint4*>(a.peer_out[p] + off) = val;
+                        }
                     }
                 }
             } else {
@@ -848,6 +855,9 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
                             if (a.residual != nullptr) y = __hadd(y, a.residual[off]);
                         }
                         out[off] = y;
+                        if constexpr (MODE == kPlain) {
+                            for (int p = 0; p < a.num_peers; ++p) a.peer_out[p][off] = y;
+                        }
                     }
                 }
             }
@@ -1091,10 +1101,13 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
     a.K = g.K;
     a.num_peers = g.mode == kPlain ? g.num_peers : 0;
     for (int p = 0; p < 7; ++p) a.peer_out[p] = p < a.num_peers ? g.peer_out[p] : nullptr;
-    // CTA pairs (cta_group::2) from 256 tokens on: 256-token tiles, no K split, no peer stores, an even number of
+    // CTA pairs (cta_group::2) from 256 tokens on: 256-token tiles, no K split, an even number of
     // 128-row tiles in every weight tensor (a pair never straddles two tensors) and 4-byte aligned scales (read
-    // in pairs).  Measured faster than the single-CTA form even where the pair tiles do not fill the GPU.
-    bool pairs = option(W4A16_OPT_GEMM_FORM) != 1 && g.M >= 256 && a.num_peers == 0;
+    // in pairs).  Measured faster than the single-CTA form from about 20 pair tiles on (a quarter of the GPU's 74
+    // pairs busy); with fewer, narrower token tiles on more CTAs win.  W4A16_OPT_GEMM_FORM = 2 forces pairs.
+    const int pair_tiles_256 = (total_tiles / 2) * ((g.M + 255) / 256);
+    bool pairs = option(W4A16_OPT_GEMM_FORM) != 1 && g.M >= 256 &&
+                 (pair_tiles_256 >= 20 || option(W4A16_OPT_GEMM_FORM) == 2);
     for (int t = 0; t < nt; ++t)
         pairs = pairs && a.tiles[t] % 2 == 0 && reinterpret_cast<uintptr_t>(g.scales[t]) % 4 == 0;
     // tokens per tile: the smallest power of two >= M (16..256); halve it while the grid is thin

@@ -535,9 +535,13 @@ namespace {
 // the weights of the NEXT block already in flight while the current one is reduced, and the lane's share
 // of the quantised activation lives in registers for the whole launch (a lane always meets the same
 // 16-byte chunks l, l+8, ... of every row).  PLAIN mode, 16-byte aligned weights, K <= 256 * STEPS.
-template <int XIN, int STEPS, bool SWIGLU, bool SAMPLE = false>
+// EPI: 0 plain epilogue; 1 token selection (SAMPLE); 2 signalled row-split output (SIGNAL): the slice goes into
+// half (step & 1) of this GPU's and every peer's gathered vector with 16-byte stores, and the launch's last
+// CTA publishes the step number to every GPU's flag array, so that no barrier kernel has to follow.
+template <int XIN, int STEPS, bool SWIGLU, int EPI = 0>
 __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const GemvArgs a, const int num_blocks) {
-    static_assert(!(SWIGLU && SAMPLE), "token selection follows a plain projection");
+    constexpr bool SAMPLE = EPI == 1, SIGNAL = EPI == 2;
+    static_assert(!(SWIGLU && EPI != 0), "token selection and signalled outputs follow a plain projection");
     extern __shared__ __align__(16) uint8_t smem[];
     const int K = a.K;
     int8_t* s_q8 = reinterpret_cast<int8_t*>(smem);
@@ -583,6 +587,8 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const Ge
     [[maybe_unused]] int32_t best_idx = 0;
     [[maybe_unused]] int it = 0, buf = 0;
     [[maybe_unused]] uint32_t sample_step = 0;
+    [[maybe_unused]] __shared__ __align__(16) __half s_blk[SIGNAL ? 2 : 1][kMaxSubwarps];
+    if constexpr (SIGNAL) sample_step = *reinterpret_cast<volatile uint32_t*>(a.sample_step_word) + 1u;
     if constexpr (SAMPLE) {
         if (a.sample_step_word != nullptr) sample_step = *reinterpret_cast<volatile uint32_t*>(a.sample_step_word) + 1u;
         if (a.sample_control != nullptr) {
@@ -627,7 +633,24 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const Ge
             if (l == 0 && (sub & 1) == 0 && row < N)
                 a.out[0][row >> 1] = __float2half_rn((acc / (1.0f + expf(-acc))) * up);
         } else {
-            if (l == 0 && row < N) {
+            if constexpr (SIGNAL) {
+                // the block's 32 outputs are collected in shared memory and leave as 16-byte stores: lane = (destination,
+                // segment of 8 rows); one barrier per block, the two buffers used in turn
+                if (l == 0) s_blk[it & 1][sub] = __float2half_rn(acc);
+                __syncthreads();
+                if (tid < 4 * (1 + a.num_peers)) {
+                    const int d = tid >> 2, seg = tid & 3;
+                    __half* dst = (d == 0 ? a.out[0] : a.peer_out[d - 1]) +
+                                  static_cast<size_t>(sample_step & 1u) * a.sample_half_stride + blk * kMaxSubwarps + seg * 8;
+                    const int r0 = blk * kMaxSubwarps + seg * 8;
+                    if (r0 + 8 <= N && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                        *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(&s_blk[it & 1][seg * 8]);
+                    } else {
+                        for (int j = 0; j < 8 && r0 + j < N; ++j) dst[j] = s_blk[it & 1][seg * 8 + j];
+                    }
+                }
+                ++it;
+            } else if (l == 0 && row < N) {
                 float y = acc;
                 if (a.residual != nullptr) y += __half2float(a.residual[row]);
                 const __half yh = __float2half_rn(y);
@@ -653,6 +676,20 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const Ge
         }
 #pragma unroll
         for (int i = 0; i < STEPS; ++i) { w0[i] = w1[i]; sb0[i] = sb1[i]; }
+    }
+    if constexpr (SIGNAL) {
+        // "last block" pattern: the storing lanes fence, the CTA counts itself; the CTA that completes the count
+        // fences at system scope (cumulative over what it observed through the counter) and publishes the step
+        // number with independent relaxed stores, which the gathering kernel of every GPU takes with acquire loads
+        if (tid < 32) __threadfence();
+        __syncthreads();
+        if (tid == 0 && atomicInc(a.sample_done_counter, gridDim.x - 1u) == gridDim.x - 1u) {
+            __threadfence_system();
+            *reinterpret_cast<volatile uint32_t*>(a.sample_step_word) = sample_step;
+            asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(a.sample_flag_local), "r"(sample_step) : "memory");
+            for (int p = 0; p < a.num_peers; ++p)
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(a.sample_peer_flag[p]), "r"(sample_step) : "memory");
+        }
     }
     if constexpr (SAMPLE) {
         __shared__ float s_v[32];
@@ -1062,6 +1099,11 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
     constexpr int kStreamMinBlocksPerSm = 16;   // row blocks per SM from which the persistent streaming form pays
     const bool tall = num_blocks >= kStreamMinBlocksPerSm * dev->sm_count;
     const bool sampling = a.sample_val != nullptr || a.sample_idx != nullptr;
+    // signalled row-split output (no sampling): step word + flags given, the streaming kernel whatever the height
+    const bool signalled = !sampling && a.sample_step_word != nullptr;
+    if (signalled && (mode != kPlain || !aligned16 || steps > 8 || a.residual != nullptr || !a.sample_done_counter ||
+                      !a.sample_flag_local || !a.out[0]))
+        return W4A16_ERR_SHAPE;
     if (sampling && (mode != kPlain || !a.sample_val || !a.sample_idx || !aligned16 || steps > 8)) return W4A16_ERR_SHAPE;
     // tall plain matrices with a long K: the streaming form that takes K in slices of 2048
     if (mode == kPlain && !q8_epilogue && !sampling && aligned16 && steps > 8 && a.x_f32 == nullptr &&
@@ -1078,7 +1120,7 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
         return static_cast<int>(e);
     }
     if (!q8_epilogue && aligned16 && steps <= 8 && a.x_f32 == nullptr &&
-        ((mode == kPlain && (tall || sampling)) || (mode == kSwiglu && tall))) {
+        ((mode == kPlain && (tall || sampling || signalled)) || (mode == kSwiglu && tall))) {
         const dim3 sgrid(std::min(num_blocks, 2 * dev->sm_count)), sblock(kMaxThreads);
         const size_t ssmem = staged_x_bytes(a.K);
         const bool pdl = pdl_enabled();
@@ -1086,7 +1128,7 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
     (steps <= 4 ? launch_kernel(gemv_w4_stream_kernel<XINV, 4, SW, SA>, sgrid, sblock, ssmem, stream, pdl, a, num_blocks)     \
      : steps <= 6 ? launch_kernel(gemv_w4_stream_kernel<XINV, 6, SW, SA>, sgrid, sblock, ssmem, stream, pdl, a, num_blocks)  \
                   : launch_kernel(gemv_w4_stream_kernel<XINV, 8, SW, SA>, sgrid, sblock, ssmem, stream, pdl, a, num_blocks))
-#define W4_STREAM(XINV) (mode == kSwiglu ? W4_STREAM3(XINV, true, false) : sampling ? W4_STREAM3(XINV, false, true) : W4_STREAM3(XINV, false, false))
+#define W4_STREAM(XINV) (mode == kSwiglu ? W4_STREAM3(XINV, true, 0) : sampling ? W4_STREAM3(XINV, false, 1) : signalled ? W4_STREAM3(XINV, false, 2) : W4_STREAM3(XINV, false, 0))
         if (a.x_fp16 != nullptr) e = a.gamma != nullptr ? W4_STREAM(kXFp16Norm) : W4_STREAM(kXFp16);
         else e = W4_STREAM(kXQ8);
 #undef W4_STREAM

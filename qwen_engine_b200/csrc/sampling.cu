@@ -2,6 +2,8 @@
 // reference's launch_sample_and_advance, src/kernels/sampling.cu:60-232) and the second stage that also
 // finishes the fused form, where the lm_head GEMV leaves one (score, index) candidate per CTA
 // (gemv_decode.cu) and the fp16 logits never have to be read back.
+#include <algorithm>
+
 #include "sampling.cuh"
 #include "w4a16_common.cuh"
 #include "w4a16_internal.hpp"
@@ -117,7 +119,51 @@ __global__ void __launch_bounds__(256) sample_stage2_after_flags_kernel(const fl
     }
 }
 
+// The consumer side of the signalled row split for whole vectors (logits): waits (bounded) until every rank's flag
+// shows this rank's own step number, then copies half (step & 1) of the gathered vector -- written by all GPUs'
+// GEMV epilogues -- into a plain output vector.  Every CTA polls the flags itself (a handful of words), then
+// copies its share with 16-byte loads that bypass the non-coherent L1.
+__global__ void __launch_bounds__(256) gather_after_flags_kernel(const __half* __restrict__ gathered, int half_stride,
+                                                                 const uint32_t* flags, int num_flags,
+                                                                 const uint32_t* step_word, int* status,
+                                                                 __half* __restrict__ out, int n, uint32_t spin_limit) {
+    pdl_release_dependents();
+    pdl_wait_prior_grids();
+    const uint32_t step = *reinterpret_cast<const volatile uint32_t*>(step_word);
+    if (static_cast<int>(threadIdx.x) < num_flags) {
+        const uint32_t* f = flags + threadIdx.x;
+        bool seen = false;
+        for (uint32_t spin = 0; spin < spin_limit; ++spin) {
+            uint32_t v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            if (static_cast<int32_t>(v - step) >= 0) { seen = true; break; }
+            __nanosleep(spin < 64 ? 20 : 200);
+        }
+        if (!seen && status != nullptr) atomicExch(status, 1 + static_cast<int>(threadIdx.x));
+    }
+    __syncthreads();
+    const __half* src = gathered + static_cast<size_t>(step & 1u) * half_stride;
+    const bool vec = ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(out)) & 15u) == 0;
+    const int stride = gridDim.x * blockDim.x * 8;
+    for (int i = (blockIdx.x * blockDim.x + threadIdx.x) * 8; i < n; i += stride) {
+        if (vec && i + 8 <= n) {
+            *reinterpret_cast<uint4*>(out + i) = __ldcg(reinterpret_cast<const uint4*>(src + i));
+        } else {
+            for (int j = i; j < min(i + 8, n); ++j)
+                out[j] = __ushort_as_half(__ldcg(reinterpret_cast<const unsigned short*>(src + j)));
+        }
+    }
+}
+
 }  // namespace
+
+int gather_after_flags(const __half* gathered, int half_stride, const uint32_t* flags, int num_flags,
+                       const uint32_t* step_word, int* status, __half* out, int n, cudaStream_t stream) {
+    const int grid = std::max(1, std::min(64, (n + 2047) / 2048));
+    return static_cast<int>(launch_kernel(gather_after_flags_kernel, dim3(grid), dim3(256), 0, stream, pdl_enabled(), gathered,
+                                          half_stride, flags, num_flags, step_word, status, out, n,
+                                          static_cast<uint32_t>(option(W4A16_OPT_SIGNAL_WAIT_SPINS))));
+}
 
 int sample_stage2_after_flags(const float* part_val, const int32_t* part_idx, int count, int half_stride,
                               const uint32_t* flags, int num_flags, const uint32_t* step_word, int* status,

@@ -145,6 +145,9 @@ int sample_stage2_after_flags(const float* part_val, const int32_t* part_idx, in
                               const uint32_t* flags, int num_flags, const uint32_t* step_word, int* status,
                               void* control, int32_t* token_out, cudaStream_t stream);
 
+int gather_after_flags(const __half* gathered, int half_stride, const uint32_t* flags, int num_flags,
+                       const uint32_t* step_word, int* status, __half* out, int n, cudaStream_t stream);
+
 // ---- M-token contraction (gemm_prefill.cu) ----
 struct GemmArgs {
     const uint32_t* qweight[3];

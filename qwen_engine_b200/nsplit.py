@@ -103,6 +103,59 @@ class NSplitGemv:
         return torch.cat(parts)
 
 
+class NSplitSignalGemv:
+    """NSplitGemv without any barrier kernel: the GEMV epilogue stores the slice into every GPU's gathered vector
+    (two halves used in turn) and its last CTA writes a step number into every GPU's flag array; a small gathering
+    kernel waits for all flags and copies the vector out.  Step numbers and the choice of half live in device
+    memory, so the pair of launches replays as a CUDA graph, and a fast rank can never overwrite the half a slow
+    rank's readers still use.  GPUs with peer access only; every rank needs rows.
+
+    signal_launch / gather_launch: ops.gemv_w4a8_peers_signal / ops.gather_after_signals.
+    """
+
+    def __init__(self, qweight_slab: torch.Tensor, scales_slab: torch.Tensor, n_rows: int, in_features: int,
+                 signal_launch, gather_launch, group=None, align: int = 8):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        self.n_rows, self.K = n_rows, in_features
+        self.slab = slab_bounds(n_rows, self.world, self.rank, align)      # 8-row alignment keeps 16-byte stores
+        if self.slab.rows <= 0 or qweight_slab.shape[0] != self.slab.rows or scales_slab.shape[0] != self.slab.rows:
+            raise ValueError(f"rank {self.rank} expects a slab of {self.slab.rows} > 0 rows")
+        self.qweight, self.scales = qweight_slab, scales_slab
+        self.signal_launch, self.gather_launch = signal_launch, gather_launch
+        dev = qweight_slab.device
+        self.half = (self.world * self.slab.stride + 7) // 8 * 8          # elements per half of the gathered vector
+        words = self.half + self.world                                    # 2 halves of fp16 = `half` 32-bit words, then flags
+        self.buf = symm_mem.empty(words, dtype=torch.int32, device=dev)
+        self.buf.zero_()
+        self.symm = symm_mem.rendezvous(self.buf, group=group if group is not None else dist.group.WORLD)
+        base = lambda r: int(self.symm.buffer_ptrs[r])
+        flag_off = self.half * 4
+        mine = self.rank * self.slab.stride * 2                           # this rank's slice inside a half, in bytes
+        peers = [r for r in range(self.world) if r != self.rank]
+        self.gathered_ptr = base(self.rank)
+        self.flags_ptr = base(self.rank) + flag_off
+        self.my_slice = base(self.rank) + mine
+        self.my_flag = self.flags_ptr + 4 * self.rank
+        self.peer_slices = [base(r) + mine for r in peers]
+        self.peer_flags = [base(r) + flag_off + 4 * self.rank for r in peers]
+        self.step_word = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.done_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.out = torch.empty(n_rows, dtype=torch.float16, device=dev)
+        torch.cuda.synchronize()
+        self.symm.barrier()      # everyone's buffers are zeroed before the first remote store
+        torch.cuda.synchronize()
+
+    def forward(self, q8, xscale, sum8) -> torch.Tensor:
+        """Returns the full fp16 output [n_rows] (this object's own buffer, rewritten by the next call)."""
+        self.signal_launch(self.qweight, self.scales, q8, xscale, sum8, self.my_slice, self.peer_slices, self.peer_flags,
+                           self.my_flag, self.done_counter, self.step_word, self.half, self.slab.rows, self.K)
+        self.gather_launch(self.gathered_ptr, self.half, self.flags_ptr, self.world, self.step_word, self.status, self.out,
+                           self.n_rows)
+        return self.out
+
+
 class NSplitSampler:
     """Token selection for a row-split lm_head without gathering the logits: every rank scores its own slab
     in the GEMV's epilogue (vocabulary indices offset by the slab's first row), the ranks all-gather their

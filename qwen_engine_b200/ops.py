@@ -25,7 +25,7 @@ __all__ = [
     "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
     "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots", "DecodeSweep",
     "launch_gemv_rmsnorm_w4a16", "launch_gemv_qkv_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1",
-    "gemv_w4a8_peers", "gemm_prefill_w4a16_block", "make_sample_control", "launch_embed_lookup_w4a16", "read_sample_control", "launch_sample_and_advance", "sample_slots", "launch_gemv_w4a8_sample_candidates", "launch_sample_finish", "launch_gemv_w4a8_sample_one_launch", "gemv_w4a8_sample_candidates_peers", "gemv_w4a8_sample_candidates_signal", "sample_finish_after_signals", "launch_gemv_w4a8_sample_and_advance", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_QUANT_IN_GATE_UP", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
+    "gemv_w4a8_peers", "gemm_prefill_w4a16_block", "make_sample_control", "launch_embed_lookup_w4a16", "read_sample_control", "launch_sample_and_advance", "sample_slots", "launch_gemv_w4a8_sample_candidates", "launch_sample_finish", "launch_gemv_w4a8_sample_one_launch", "gemv_w4a8_sample_candidates_peers", "gemv_w4a8_sample_candidates_signal", "sample_finish_after_signals", "gemv_w4a8_peers_signal", "gather_after_signals", "launch_gemv_w4a8_sample_and_advance", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_QUANT_IN_GATE_UP", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
 ]
 
 # Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
@@ -232,6 +232,26 @@ def gemv_w4a8_sample_candidates_signal(qweight, scales, input_q8, input_scale, i
         _ptr(qweight), _ptr(scales), _ptr(input_q8), _ptr(input_scale), _ptr(input_sum8), candidate_val_ptr,
         candidate_idx_ptr, pv, pi, pf, n, local_flag_ptr, _ptr(done_counter), _ptr(step_word), half_stride,
         _ptr(d_control), index_offset, out_features, in_features, _stream(stream)))
+
+
+def gemv_w4a8_peers_signal(qweight, scales, input_q8, input_scale, input_sum8, gathered_slice_ptr, peer_slice_ptrs,
+                           peer_flag_ptrs, local_flag_ptr, done_counter, step_word, half_stride, out_features, in_features,
+                           stream=None):
+    """Row-split GEMV whose epilogue stores the slice into every GPU's gathered vector and signals completion
+    (addresses as integers where they point into symmetric memory)."""
+    n = len(peer_slice_ptrs)
+    ps = (ctypes.c_void_p * max(1, n))(*peer_slice_ptrs)
+    pf = (ctypes.c_void_p * max(1, n))(*peer_flag_ptrs)
+    check("w4a16_gemv_w4a8_peers_signal", load().w4a16_gemv_w4a8_peers_signal(
+        _ptr(qweight), _ptr(scales), _ptr(input_q8), _ptr(input_scale), _ptr(input_sum8), gathered_slice_ptr, ps, pf, n,
+        local_flag_ptr, _ptr(done_counter), _ptr(step_word), half_stride, out_features, in_features, _stream(stream)))
+
+
+def gather_after_signals(gathered_ptr, half_stride, flags_ptr, num_flags, step_word, d_status, output, num_elements,
+                         stream=None):
+    check("w4a16_gather_after_signals", load().w4a16_gather_after_signals(
+        gathered_ptr, half_stride, flags_ptr, num_flags, _ptr(step_word), _ptr(d_status), _ptr(output), num_elements,
+        _stream(stream)))
 
 
 def sample_finish_after_signals(candidate_val_ptr, candidate_idx_ptr, count, half_stride, flags_ptr, num_flags, step_word,

@@ -319,3 +319,57 @@ def test_a_flag_that_nothing_sets_makes_the_bounded_wait_run_out(ops):
         ops.set_option(ops.OPT_SIGNAL_WAIT_SPINS, old)
     with pytest.raises(ops.W4A16Error):
         ops.set_option(ops.OPT_SIGNAL_WAIT_SPINS, 0)
+
+
+def test_signalled_logits_gather_on_one_gpu(ops):
+    """The barrier-free row split of a whole output vector, with this GPU standing in for its own peers: rank 1 of
+    3 stores its slice into its own gathered vector and into two more "peer" vectors (16-byte stores, two halves
+    used in turn) and signals; the gathering kernel waits for the three flags (the other two set by the test) and
+    copies the vector out.  Checked against the plain GEMV, step after step; then with one flag left unset and a
+    short poll budget the gather must report the missing rank and return."""
+    from qwen_engine_b200 import synth
+    # tall enough that the plain launch takes the streaming kernel too (same summation order, so the same bits);
+    # 76008 rows end in a ragged block of 8
+    rows, K, world, rank = 76008, 1536, 3, 1
+    stride = rows
+    half = world * stride
+    qw, sc = util.to_dev(synth.packed_weights(25, "sg", rows, K)), util.to_dev(synth.scales(25, "sg", rows, K))
+    mk = lambda: torch.full((2 * half,), float("nan"), dtype=torch.float16, device="cuda")
+    local, peers = mk(), [mk(), mk()]
+    flags = [torch.zeros(world, dtype=torch.int32, device="cuda") for _ in range(3)]
+    step_word = torch.zeros(1, dtype=torch.int32, device="cuda")
+    counter = torch.zeros(1, dtype=torch.int32, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    out = torch.empty(half, dtype=torch.float16, device="cuda")
+    want = torch.empty(rows, dtype=torch.float16, device="cuda")
+    off = rank * stride * 2
+    for step in range(1, 5):
+        q8, xs, s8 = (util.to_dev(t) for t in oracle.quantize_q8_1(synth.activations(50 + step, "sg", K)))
+        ops.gemv_w4a8_peers_signal(qw, sc, q8, xs, s8, local.data_ptr() + off, [p.data_ptr() + off for p in peers],
+                                   [f.data_ptr() + 4 * rank for f in flags[1:]], flags[0].data_ptr() + 4 * rank, counter,
+                                   step_word, half, rows, K)
+        # the other two ranks' slices and flags, as their launches would have left them
+        lo = (step & 1) * half
+        local[lo:lo + stride] = 1.0
+        local[lo + 2 * stride:lo + 3 * stride] = 2.0
+        flags[0][0] = step
+        flags[0][2] = step
+        ops.gather_after_signals(local.data_ptr(), half, flags[0].data_ptr(), world, step_word, status, out, half)
+        ops.launch_gemv_w4a8(qw, sc, q8, xs, s8, None, want, rows, K)
+        torch.cuda.synchronize()
+        assert int(step_word.item()) == step and int(counter.item()) == 0 and int(status.item()) == 0
+        assert torch.equal(out[stride:2 * stride], want)
+        assert bool((out[:stride] == 1.0).all()) and bool((out[2 * stride:] == 2.0).all())
+        for p, f in zip(peers, flags[1:]):
+            assert torch.equal(p[lo + stride:lo + 2 * stride], want) and int(f[rank].item()) == step
+        assert int(flags[0][rank].item()) == step
+    # a rank that never signals: bounded wait, status = 1 + rank, the call returns
+    old = ops.get_option(ops.OPT_SIGNAL_WAIT_SPINS)
+    try:
+        ops.set_option(ops.OPT_SIGNAL_WAIT_SPINS, 3000)
+        flags[0][2] = 0
+        ops.gather_after_signals(local.data_ptr(), half, flags[0].data_ptr(), world, step_word, status, out, half)
+        torch.cuda.synchronize()
+        assert int(status.item()) == 1 + 2
+    finally:
+        ops.set_option(ops.OPT_SIGNAL_WAIT_SPINS, old)
