@@ -48,6 +48,11 @@ def parse():
     ap.add_argument("--input", default="q8", choices=["q8", "fp16", "fp16norm"],
                     help="single, batch-1: pre-quantised Q8_1 input, fp16 input, or fp16 input with RMSNorm in the prologue")
     ap.add_argument("--no-shapes", action="store_true", help="skip the per-shape table (configs 0, 3, 4) in the headline line")
+    ap.add_argument("--gemv-form", type=int, default=0, choices=[0, 1, 2],
+                    help="W4A16_OPT_GEMV_FORM for the run: 0 default, 1 register-held weight loads, 2 bulk copies into shared memory")
+    ap.add_argument("--sweep-flags", type=int, default=-1, help="W4A16_SWEEP_* flags of the decode sweep (default: the library's)")
+    ap.add_argument("--no-lm-head", action="store_true", help="skip the lm_head / token selection extras (1 GPU only)")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the 8192 -> 28672 prefill extra")
     ap.add_argument("--m-list", default="1,2,4,8,16,32,64,128,512,1024,4096")
     ap.add_argument("--layers", type=int, default=28, help=argparse.SUPPRESS)
     ap.add_argument("--no-cpu-baseline", action="store_true", help=argparse.SUPPRESS)
@@ -211,12 +216,15 @@ def timed_events(torch, stream, fn, steps):
 
 def measured_traffic(kernel_key):
     """DRAM bytes per launch of a kernel as an ncu capture counted them (dram__bytes_read.sum +
-    dram__bytes_write.sum), from the machine-readable companion of the committed summaries; None if absent."""
-    try:
-        table = json.loads((ROOT / "profiles" / "dram_traffic.json").read_text())
-        return table[kernel_key]["dram_bytes_per_launch"]
-    except Exception:
-        return None
+    dram__bytes_write.sum): the `traffic_key <kernel> dram_bytes_per_launch <bytes>` line of the committed
+    summaries under profiles/; None if no summary holds one."""
+    import re
+    pat = re.compile(r"traffic_key\s+" + re.escape(kernel_key) + r"\s+dram_bytes_per_launch\s+(\d+)")
+    for path in sorted((ROOT / "profiles").glob("*.md")):
+        m = pat.search(path.read_text())
+        if m:
+            return int(m.group(1))
+    return None
 
 
 def kernel_roofline(torch, ops, layers_dev, stream, peaks, reps=20):
@@ -431,7 +439,7 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
     # ---- token selection after lm_head: logits + stand-alone sampler vs. candidates from the GEMV's epilogue ----
     try:
         slots = ops.sample_slots(rows)
-        temperature = float(os.environ.get("W4A16_BENCH_TEMPERATURE", "0.8"))
+        temperature = 0.8
         ctl_a = ops.make_sample_control(temperature, 1234, 0)
         ctl_b = ops.make_sample_control(temperature, 1234, 0)
         val = torch.empty(256, dtype=torch.float32, device="cuda")
@@ -568,7 +576,7 @@ def prefill_big_nsplit(torch, dist, ops, rank, world, stream, steps):
     """Configuration 4's scaled-up shape: W4A16 prefill GEMM 8192 -> 28672 at 4096 tokens, weight rows split over
     the ranks, every rank ending with the whole [M][N] output.  Strong scaling; TFLOP/s counts 2*M*N*K once."""
     from qwen_engine_b200 import nsplit, synth
-    N, K, M = 28672, 8192, int(os.environ.get("W4A16_BENCH_PREFILL_M", "4096"))
+    N, K, M = 28672, 8192, 4096
     slab = nsplit.slab_bounds(N, world, rank, 128)
     qw = torch.from_numpy(synth.packed_weights(13, f"big.r{slab.first}", slab.rows, K).view(np.int32)).cuda()
     sc = torch.from_numpy(synth.scales(13, f"big.r{slab.first}", slab.rows, K)).cuda()
@@ -735,8 +743,10 @@ def run_shapes_suite(args):
         peaks = json.loads((ROOT / "MEASURED_PEAKS.json").read_text())
     except Exception:
         pass
+    ops.set_option(ops.OPT_GEMV_FORM, args.gemv_form)
     out = shapes_table(torch, ops, torch.cuda.Stream(), peaks, reps=max(3, min(args.steps, 20)))
     out["suite"] = "shapes"
+    out["gemv_form"] = args.gemv_form
     print(json.dumps(out), flush=True)
 
 
@@ -747,6 +757,7 @@ def run_single(args):
     from qwen_engine_b200 import synth
     torch.cuda.set_device(0)
     ops.init()
+    ops.set_option(ops.OPT_GEMV_FORM, args.gemv_form)
     shapes = {"qkv": (2048, 1536), "o": (1536, 1536), "gate_up": (17920, 1536), "down": (1536, 8960),
               "lm_head": (151936, 1536), "big": (28672, 8192)}
     N, K = shapes[args.shape]
@@ -833,7 +844,8 @@ def main():
     h_out = torch.empty_like(h_in)
     pin_in = torch.from_numpy(h0_np).pin_memory()
     pin_out = torch.empty(synth.HIDDEN, dtype=torch.float16).pin_memory()
-    sweep_flags = int(os.environ.get("W4A16_SWEEP_FLAGS", str(ops.SWEEP_DEFAULT)))
+    sweep_flags = args.sweep_flags if args.sweep_flags >= 0 else ops.SWEEP_DEFAULT
+    ops.set_option(ops.OPT_GEMV_FORM, args.gemv_form)
     with torch.cuda.stream(stream):
         sweep = ops.DecodeSweep(layers_dev, stream=stream, flags=sweep_flags)
     nbytes = synth.layer_algorithmic_bytes() * len(layers_np)
@@ -886,7 +898,7 @@ def main():
         "ms_per_step": ms_per_step, "us_per_sweep": ms_per_step * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "int8", "data": "synthetic",
         "config": bench_config(len(layers_np), world, nbytes),
-        "options": {"pdl": bool(ops.get_option(ops.OPT_PDL)), "sweep_flags": sweep_flags},
+        "options": {"pdl": bool(ops.get_option(ops.OPT_PDL)), "sweep_flags": sweep_flags, "gemv_form": args.gemv_form},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": synth.HIDDEN * 2,
                 "d2h_bytes_per_step": synth.HIDDEN * 2,
                 "how": "w4a16_sweep_run_host: pinned fp16 hidden state in, sweep graph, hidden state out, "
@@ -902,11 +914,11 @@ def main():
         line["roofline_sweep"] = {"achieved": value / world, "peak": peaks.get("hbm_gbs", 6650.0),
                                   "frac": value / world / peaks.get("hbm_gbs", 6650.0), "unit": UNIT,
                                   "note": f"whole sweep ({sweep.launches} dependent launches) per GPU against the copy peak"}
-    if world > 1 or os.environ.get("W4A16_BENCH_LM_HEAD", "1") == "1":
+    if world > 1 or not args.no_lm_head:
         lm = lm_head_nsplit(torch, dist, ops, rank, world, stream, min(steps, 200), warmup)
         if rank == 0:
             line["lm_head"] = lm
-    if os.environ.get("W4A16_BENCH_PREFILL", "1") == "1":
+    if not args.no_prefill:
         try:
             pf = prefill_big_nsplit(torch, dist, ops, rank, world, stream, steps)
         except Exception as e:      # keeps the headline line alive if this extra fails (e.g. memory on a busy GPU)
