@@ -457,6 +457,13 @@ enum {
                                     of four CTAs share one group of 128): no quantiser launch and no
                                     re-quantisation in front of down; needs intermediate % 128 == 0; takes
                                     precedence over FUSE_QUANT_DOWN; same output bits */
+    W4A16_SWEEP_PUBLISH_SUMSQ = 32, /* FUSE_NORM | FUSE_QUANT_O, and the O and down GEMVs add the squares of their
+                                    outputs into partial sums that the next RMSNorm prologue reads instead of
+                                    reducing; same output bits */
+    W4A16_SWEEP_PUBLISH_AMAX = 64,  /* FUSE_NORM | FUSE_QUANT_O, and the gate_up GEMV leaves the |max| of every group of
+                                    128 outputs (atomicMax) so that the down GEMV quantises its fp16 input element by
+                                    element, without a reduction and without a quantiser launch (4 launches per
+                                    layer); same output bits */
     W4A16_SWEEP_PERSISTENT = 8   /* the whole pass as ONE persistent kernel (one CTA per SM): weights of all
                                     layers stream through a shared-memory ring while the CTAs exchange the
                                     small activation vectors through tagged 8-byte words; needs

@@ -23,6 +23,11 @@ struct w4a16_sweep {
     int8_t* mlp_q8 = nullptr; // Q8_1 of the MLP activation when the gate_up launch writes it itself
     float* mlp_scale = nullptr;
     int32_t* mlp_sum8 = nullptr;
+    // reductions published from launch to launch (W4A16_SWEEP_PUBLISH_*): [sumsq_attn: 8 doubles][amax: inter / 128 words]
+    // contiguous (one clear range), then [sumsq_down: 8 doubles]
+    double* sumsq_attn = nullptr;
+    uint32_t* mlp_amax = nullptr;
+    double* sumsq_down = nullptr;
     cudaGraph_t graph = nullptr;
     cudaGraphExec_t exec = nullptr;
     int launches = 0;
@@ -47,6 +52,7 @@ struct Carve {
     // persistent form: exchange buffers (8-byte tagged words), device copy of the layer table, status word
     size_t ll_h_attn, ll_h_down, ll_q, ll_mlp, layer_table, status, counters;
     size_t mlp_q8, mlp_scale, mlp_sum8;
+    size_t pub_attn, pub_down;
 };
 Carve carve(int hidden, int inter, int nq, int nkv, int hd) {
     const size_t kmax = static_cast<size_t>(hidden > inter ? hidden : inter);
@@ -71,6 +77,8 @@ Carve carve(int hidden, int inter, int nq, int nkv, int hd) {
     c.mlp_q8 = off; off += align_up(inter);
     c.mlp_scale = off; off += align_up(inter / 128 * sizeof(float));
     c.mlp_sum8 = off; off += align_up(inter / 8 * sizeof(int32_t));
+    c.pub_attn = off; off += align_up(w4::kSumsqSlots * sizeof(double) + (inter / 128 + 1) * sizeof(uint32_t));
+    c.pub_down = off; off += align_up(w4::kSumsqSlots * sizeof(double));
     c.total = off;
     return c;
 }
@@ -82,6 +90,9 @@ int issue_pass(w4a16_sweep* s, cudaStream_t stream, int* launches) {
     const int qdim = d.num_q_heads * d.head_dim, kvdim = d.num_kv_heads * d.head_dim;
     int n = 0;
     const int flags = d.flags;
+    const bool pub_sums = (flags & W4A16_SWEEP_PUBLISH_SUMSQ) != 0, pub_amax = (flags & W4A16_SWEEP_PUBLISH_AMAX) != 0;
+    const bool publish = pub_sums || pub_amax;
+    bool first = true;
     for (const auto& L : s->layers) {
         GemvArgs a = {};
         a.qweight[0] = static_cast<const uint32_t*>(L.q_weight); a.scales[0] = static_cast<const __half*>(L.q_scale);
@@ -90,7 +101,14 @@ int issue_pass(w4a16_sweep* s, cudaStream_t stream, int* launches) {
         a.out[0] = s->q; a.out[1] = s->k; a.out[2] = s->v;
         a.rows[0] = qdim; a.rows[1] = kvdim; a.rows[2] = kvdim;
         a.K = H; a.units = qdim + 2 * kvdim;
-        if (flags & W4A16_SWEEP_FUSE_NORM) {
+        if (publish) {
+            // takes the sum of squares the previous layer's down launch left (the first layer reduces itself);
+            // clears what the O and gate_up launches of this layer will add to
+            a.x_fp16 = s->h; a.gamma = static_cast<const __half*>(L.input_norm_gamma);
+            a.sumsq_in = (first || !pub_sums) ? nullptr : s->sumsq_down;
+            a.clear_words = reinterpret_cast<uint32_t*>(s->sumsq_attn);
+            a.clear_count = 2 * kSumsqSlots + I / 128;
+        } else if (flags & W4A16_SWEEP_FUSE_NORM) {
             a.x_fp16 = s->h; a.gamma = static_cast<const __half*>(L.input_norm_gamma);
         } else {
             if (int st = rmsnorm_q8_1(s->h, static_cast<const __half*>(L.input_norm_gamma), nullptr, s->act_q8,
@@ -106,7 +124,8 @@ int issue_pass(w4a16_sweep* s, cudaStream_t stream, int* launches) {
         o.qweight[0] = static_cast<const uint32_t*>(L.o_weight); o.scales[0] = static_cast<const __half*>(L.o_scale);
         o.out[0] = s->h; o.rows[0] = H; o.residual = s->h;
         o.K = qdim; o.units = H;
-        if (flags & W4A16_SWEEP_FUSE_QUANT_O) {
+        if (pub_sums) o.sumsq_out = s->sumsq_attn;
+        if (publish || (flags & W4A16_SWEEP_FUSE_QUANT_O)) {
             o.x_fp16 = s->q;
         } else {
             if (int st = quantize_fp16_to_q8_1(s->q, s->act_q8, s->act_scale, s->act_sum8, qdim, stream)) return st;
@@ -120,7 +139,13 @@ int issue_pass(w4a16_sweep* s, cudaStream_t stream, int* launches) {
         g.scales[0] = static_cast<const __half*>(L.gate_up_scale);
         g.out[0] = s->mlp; g.rows[0] = 2 * I;
         g.K = H; g.units = I;
-        if (flags & W4A16_SWEEP_FUSE_NORM) {
+        if (publish) {
+            g.x_fp16 = s->h; g.gamma = static_cast<const __half*>(L.post_norm_gamma);
+            if (pub_sums) g.sumsq_in = s->sumsq_attn;
+            if (pub_amax) g.amax_out = s->mlp_amax;
+            g.clear_words = reinterpret_cast<uint32_t*>(s->sumsq_down);
+            g.clear_count = 2 * kSumsqSlots;
+        } else if (flags & W4A16_SWEEP_FUSE_NORM) {
             g.x_fp16 = s->h; g.gamma = static_cast<const __half*>(L.post_norm_gamma);
         } else {
             if (int st = rmsnorm_q8_1(s->h, static_cast<const __half*>(L.post_norm_gamma), nullptr, s->act_q8,
@@ -129,7 +154,7 @@ int issue_pass(w4a16_sweep* s, cudaStream_t stream, int* launches) {
             ++n;
             g.q8 = s->act_q8; g.xscale = s->act_scale; g.sum8 = s->act_sum8;
         }
-        const bool quant_in_gate_up = (flags & W4A16_SWEEP_QUANT_IN_GATE_UP) != 0;
+        const bool quant_in_gate_up = !publish && (flags & W4A16_SWEEP_QUANT_IN_GATE_UP) != 0;
         if (quant_in_gate_up) { g.q8_out = s->mlp_q8; g.xscale_out = s->mlp_scale; g.sum8_out = s->mlp_sum8; }
         if (int st = gemv_launch(kSwiglu, g, stream)) return st;
         ++n;
@@ -138,7 +163,10 @@ int issue_pass(w4a16_sweep* s, cudaStream_t stream, int* launches) {
         dn.scales[0] = static_cast<const __half*>(L.down_scale);
         dn.out[0] = s->h; dn.rows[0] = H; dn.residual = s->h;
         dn.K = I; dn.units = H;
-        if (quant_in_gate_up) {
+        if (pub_sums) dn.sumsq_out = s->sumsq_down;
+        if (pub_amax) {
+            dn.x_fp16 = s->mlp; dn.amax_in = s->mlp_amax;
+        } else if (quant_in_gate_up) {
             dn.q8 = s->mlp_q8; dn.xscale = s->mlp_scale; dn.sum8 = s->mlp_sum8;
         } else if (flags & W4A16_SWEEP_FUSE_QUANT_DOWN) {
             dn.x_fp16 = s->mlp;
@@ -149,6 +177,7 @@ int issue_pass(w4a16_sweep* s, cudaStream_t stream, int* launches) {
         }
         if (int st = gemv_launch(kPlain, dn, stream)) return st;
         ++n;
+        first = false;
     }
     if (launches) *launches = n;
     return 0;
@@ -209,6 +238,10 @@ int w4a16_sweep_create(const w4a16_sweep_desc* desc, w4a16_stream_t stream_, w4a
     s->mlp_q8 = reinterpret_cast<int8_t*>(base + c.mlp_q8);
     s->mlp_scale = reinterpret_cast<float*>(base + c.mlp_scale);
     s->mlp_sum8 = reinterpret_cast<int32_t*>(base + c.mlp_sum8);
+    s->sumsq_attn = reinterpret_cast<double*>(base + c.pub_attn);
+    s->mlp_amax = reinterpret_cast<uint32_t*>(base + c.pub_attn + w4::kSumsqSlots * sizeof(double));
+    s->sumsq_down = reinterpret_cast<double*>(base + c.pub_down);
+    if ((desc->flags & (W4A16_SWEEP_PUBLISH_SUMSQ | W4A16_SWEEP_PUBLISH_AMAX)) && (I % 128 || 2 * w4::kSumsqSlots + I / 128 > 128)) return W4A16_ERR_SHAPE;
     if ((desc->flags & W4A16_SWEEP_QUANT_IN_GATE_UP) && I % 128) return W4A16_ERR_SHAPE;
 
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);

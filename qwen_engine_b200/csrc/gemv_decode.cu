@@ -34,11 +34,22 @@ constexpr float kRmsEps = 1e-6f;                      // reference include/confi
 enum XIn { kXQ8 = 0,        // pre-quantised Q8_1 arrays in global memory
            kXFp16 = 1,      // fp16 vector, quantised in the prologue
            kXFp16Norm = 2,  // fp16 vector, RMSNorm then quantised in the prologue
-           kXF32Heads = 3 };  // fp32 attention accumulators, quantised per head with the flash-decode epilogue's rule
+           kXF32Heads = 3,  // fp32 attention accumulators, quantised per head with the flash-decode epilogue's rule
+           kXFp16Amax = 4 };  // fp16 vector whose per-group |max| the producing launch published: quantised without a reduction
 
-// Register caps: two 256-thread CTAs per SM need <= 128; the single-row forms with 8 loads per lane run as
-// 224-thread CTAs (down projection) of which three must fit an SM for the whole grid to be resident at once.
-constexpr int gemv_reg_cap(int mode, int u) { return (mode != kSwiglu && u == 8) ? 96 : 128; }
+// Shared memory behind the staged activation and the K-split partial sums, kXFp16Amax only: 1/scale per group,
+// then the raw fp16 vector (16-byte aligned).
+__host__ __device__ inline size_t amax_stage_offset(int K, int part_floats) {
+    return (staged_x_bytes(K) + static_cast<size_t>(part_floats) * 4 + 15) / 16 * 16;
+}
+__host__ __device__ inline size_t amax_stage_bytes(int K) { return (static_cast<size_t>(K / kGroup) * 4 + 15) / 16 * 16 + static_cast<size_t>(K) * 2; }
+
+// Register caps.  What matters in a chain of dependent launches is that the CTAs of the NEXT launch become
+// resident, and issue their weight loads, while this one still runs: 88 registers for the single-row forms with
+// 8 loads per lane (down: three 192-thread CTAs per SM leave room for CTAs of the next QKV launch; measured
+// 1 % of the 28-layer pass against a cap of 96, no spills), 128 for the rest (the SwiGLU row pairs spill below
+// 120; capping the 4-load forms at 64 costs them 0.2 us per launch).
+constexpr int gemv_reg_cap(int mode, int u) { return (mode != kSwiglu && u == 8) ? 88 : 128; }
 
 template <int MODE, int U, int XIN, bool ALIGNED16>
 __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs a) {
@@ -123,9 +134,15 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
     if constexpr (MODE == kPlain) {
         if (active && ks == 0 && l == 0 && a.residual != nullptr) res_pre = a.residual[unit];
     }
+    if (blockIdx.x == 0 && tid < a.clear_count) a.clear_words[tid] = 0u;   // scratch of a later launch
     if constexpr (XIN == kXFp16Norm) {
-        if (regs_form) stage_x_fp16_regs<true>(a.x_fp16, gam, K, kRmsEps, s_q8, s_seed, s_scale);
+        if (regs_form) stage_x_fp16_regs<true>(a.x_fp16, gam, K, kRmsEps, s_q8, s_seed, s_scale, a.sumsq_in);
         else stage_x_from_fp16_rmsnorm(a.x_fp16, a.gamma, K, kRmsEps, s_q8, s_seed, s_scale);
+    } else if constexpr (XIN == kXFp16Amax) {
+        uint8_t* extra = smem + amax_stage_offset(K, a.ksplit * a.units_per_cta * R);
+        float* s_inv = reinterpret_cast<float*>(extra);
+        __half* s_raw = reinterpret_cast<__half*>(extra + (static_cast<size_t>(K / kGroup) * 4 + 15) / 16 * 16);
+        stage_x_fp16_amax(a.x_fp16, a.amax_in, K, s_q8, s_seed, s_scale, s_raw, s_inv);
     } else if constexpr (XIN == kXFp16) {
         if (regs_form) stage_x_fp16_regs<false>(a.x_fp16, gam, K, kRmsEps, s_q8, s_seed, s_scale);
         else stage_x_from_fp16(a.x_fp16, K, s_q8, s_seed, s_scale);
@@ -201,6 +218,24 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
         y_rounded = __half2float(yh);
         if constexpr (MODE == kPlain) {
             for (int p = 0; p < a.num_peers; ++p) a.peer_out[p][unit] = yh;   // slice into every peer's buffer
+        }
+    }
+    if constexpr (MODE == kPlain) {
+        // Squares of this launch's fp16 outputs for the next RMSNorm: the output threads of a warp are its lanes
+        // 0, 8, 16, 24; one double atomic per warp that has any.
+        if (a.sumsq_out != nullptr && (tid >> 5) * 4 < a.units_per_cta) {
+            double sq = static_cast<double>(y_rounded) * static_cast<double>(y_rounded);   // 0 in lanes without an output
+            sq += __shfl_xor_sync(0xFFFFFFFFu, sq, 8);
+            sq += __shfl_xor_sync(0xFFFFFFFFu, sq, 16);
+            if ((tid & 31) == 0) atomicAdd(a.sumsq_out + (blockIdx.x % kSumsqSlots), sq);
+        }
+    }
+    if constexpr (MODE == kSwiglu) {
+        // |max| of every group of 128 outputs for the launch that quantises them: a warp's four outputs are
+        // consecutive and start at a multiple of four, hence in one group.
+        if (a.amax_out != nullptr && ks == 0) {
+            const uint32_t m = __reduce_max_sync(0xFFFFFFFFu, __float_as_uint(fabsf(y_rounded)));
+            if ((tid & 31) == 0 && m != 0u) atomicMax(a.amax_out + (blockIdx.x * a.units_per_cta + u_local) / kGroup, m);
         }
     }
 
@@ -951,6 +986,13 @@ cudaError_t launch_input(const GemvArgs& a, bool aligned16, dim3 grid, dim3 bloc
     }
     if (a.x_fp16 != nullptr) {
         if (a.gamma != nullptr) return launch_aligned<MODE, U, kXFp16Norm>(a, aligned16, grid, block, smem, stream);
+        if constexpr (MODE == kPlain) {
+            if (a.amax_in != nullptr && reinterpret_cast<uintptr_t>(a.x_fp16) % 16 == 0) {
+                const size_t smem_amax = amax_stage_offset(a.K, a.ksplit * a.units_per_cta) + amax_stage_bytes(a.K);
+                if (smem_amax <= 200 * 1024)
+                    return launch_aligned<MODE, U, kXFp16Amax>(a, aligned16, grid, block, smem_amax, stream);
+            }
+        }
         return launch_aligned<MODE, U, kXFp16>(a, aligned16, grid, block, smem, stream);
     }
     return launch_aligned<MODE, U, kXQ8>(a, aligned16, grid, block, smem, stream);
@@ -1017,6 +1059,8 @@ cudaError_t raise_smem_mode() {
     if constexpr (MODE == kPlain) {
         if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, kXF32Heads, true>);
         if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, kXF32Heads, false>);
+        if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, kXFp16Amax, true>);
+        if (e == cudaSuccess) e = raise_smem(gemv_w4_kernel<MODE, U, kXFp16Amax, false>);
     }
     return e;
 }
@@ -1069,6 +1113,11 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
         p.steps_per_split = a.K / kStepElems;
         p.U = 8;
     }
+    // Hand-offs of a decode pass exist in the register form only (the other forms ignore amax_in / sumsq_in, which
+    // merely save work, but would drop what a later launch relies on).
+    const bool handoff = a.sumsq_out != nullptr || a.amax_out != nullptr || a.clear_count > 0;
+    if (a.clear_count < 0 || a.clear_count > 128 || (a.clear_count > 0 && !a.clear_words)) return W4A16_ERR_INVALID_ARG;
+    if ((a.amax_out && (mode != kSwiglu || p.units_per_cta % 4)) || (a.sumsq_out && mode != kPlain)) return W4A16_ERR_SHAPE;
     if (mode == kQkv) {
         // a CTA's rows must come from one tensor
         while (p.units_per_cta > 1 && (a.rows[0] % p.units_per_cta || a.rows[1] % p.units_per_cta)) p.units_per_cta /= 2;
@@ -1106,7 +1155,7 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
         return W4A16_ERR_SHAPE;
     if (sampling && (mode != kPlain || !a.sample_val || !a.sample_idx || !aligned16 || steps > 8)) return W4A16_ERR_SHAPE;
     // tall plain matrices with a long K: the streaming form that takes K in slices of 2048
-    if (mode == kPlain && !q8_epilogue && !sampling && aligned16 && steps > 8 && a.x_f32 == nullptr &&
+    if (mode == kPlain && !q8_epilogue && !sampling && !handoff && aligned16 && steps > 8 && a.x_f32 == nullptr &&
         static_cast<long long>(num_blocks) * ((steps + 7) / 8) >= 8LL * 2 * dev->sm_count &&
         staged_x_bytes(a.K) <= 160 * 1024 && option(W4A16_OPT_GEMV_FORM) != 2) {
         const dim3 sgrid(std::min(num_blocks, 2 * dev->sm_count)), sblock(kMaxThreads);
@@ -1119,7 +1168,7 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
 #undef W4_LONGK
         return static_cast<int>(e);
     }
-    if (!q8_epilogue && aligned16 && steps <= 8 && a.x_f32 == nullptr &&
+    if (!q8_epilogue && !handoff && aligned16 && steps <= 8 && a.x_f32 == nullptr &&
         ((mode == kPlain && (tall || sampling || signalled)) || (mode == kSwiglu && tall))) {
         const dim3 sgrid(std::min(num_blocks, 2 * dev->sm_count)), sblock(kMaxThreads);
         const size_t ssmem = staged_x_bytes(a.K);
@@ -1144,7 +1193,7 @@ int gemv_launch(GemvMode mode, GemvArgs a, cudaStream_t stream) {
     // The bulk-copy form therefore runs only on request (W4A16_OPT_GEMV_FORM = 2); it splits K over a cluster
     // where one CTA would otherwise stage or quantise more than 16 groups.
     const int form = option(W4A16_OPT_GEMV_FORM);
-    if (form == 2 && aligned16 && !q8_epilogue) {
+    if (form == 2 && aligned16 && !q8_epilogue && !handoff) {
         const bool cluster_k = mode == kPlain && a.gamma == nullptr && a.x_f32 == nullptr && a.ksplit >= 2 &&
                                a.ksplit <= 8 && a.K / kGroup > 16;
         GemvArgs b = a;

@@ -351,9 +351,13 @@ __device__ __forceinline__ void prefetch_gamma(const __half* __restrict__ g_gamm
 }
 
 // fp16 activation (optionally RMSNorm'ed with the prefetched gain) -> staged Q8_1.  One global round trip.
+// sumsq_in (NORM only, may be null): the sum of x's squares as the producing launch published it, in 8 partial
+// sums; the CTA then skips its own reduction (conversions to double, two shuffle trees, one barrier).  The value
+// is the same sum of the same exact squares, so the rounded mean does not change.
 template <bool NORM>
 __device__ __forceinline__ void stage_x_fp16_regs(const __half* g_x, const uint4 (&gam)[kStageRounds], int K, float eps,
-                                                  int8_t* s_q8, int32_t* s_seed, float* s_scale) {
+                                                  int8_t* s_q8, int32_t* s_seed, float* s_scale,
+                                                  const double* sumsq_in = nullptr) {
     __shared__ double s_red[8];
     const int hw = threadIdx.x >> 4, hl = threadIdx.x & 15, nhw = blockDim.x >> 4;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
@@ -365,7 +369,19 @@ __device__ __forceinline__ void stage_x_fp16_regs(const __half* g_x, const uint4
         xr[r] = g < groups ? *reinterpret_cast<const uint4*>(g_x + g * kGroup + hl * 8) : make_uint4(0, 0, 0, 0);
     }
     __half2 inv2 = __float2half2_rn(1.0f);
-    if constexpr (NORM) {
+    if (NORM && sumsq_in != nullptr) {
+        // One warp fetches the 8 partial sums (one 64-byte request per CTA: every CTA of the grid reads the same
+        // line, and a request per thread makes that line a hot spot) in the same round trip as the loads above.
+        if (warp == 0) {
+            double s = lane < 8 ? __ldcg(sumsq_in + lane) : 0.0;
+            s += __shfl_xor_sync(0xFFFFFFFFu, s, 4);
+            s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
+            s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
+            if (lane == 0) s_red[0] = s;
+        }
+        __syncthreads();
+        inv2 = __float2half2_rn(inv_rms_from_sumsq(s_red[0], K, eps));
+    } else if constexpr (NORM) {
         double ss = 0.0;
 #pragma unroll
         for (int r = 0; r < kStageRounds; ++r) {
@@ -402,6 +418,58 @@ __device__ __forceinline__ void stage_x_fp16_regs(const __half* g_x, const uint4
                 v[2 * k + 1] = f.y;
             }
             quantize_group_halfwarp_to_smem(v, g, hl, g < groups, s_q8, s_seed, s_scale);
+        }
+    }
+}
+
+// fp16 activation whose per-group |max| the producing launch has published (float bits, one word per group of
+// 128): every CTA quantises it element by element, no reduction.  The raw vector goes through shared memory
+// (cp.async, no registers held), the scales are derived while it is in flight.  Same arithmetic as
+// quantize_group128_lane given the same maximum, so the staged arrays equal the stand-alone quantiser's.
+// s_raw: K halves, 16-byte aligned; s_inv: K / 128 floats.  Needs x 16-byte aligned; all threads call it.
+__device__ __forceinline__ void stage_x_fp16_amax(const __half* g_x, const uint32_t* g_amax, int K, int8_t* s_q8,
+                                                  int32_t* s_seed, float* s_scale, __half* s_raw, float* s_inv) {
+    const int tid = threadIdx.x, nthr = blockDim.x;
+    const int octets = K / 8;
+    for (int i = tid; i < octets; i += nthr) {
+        const uint32_t dst = static_cast<uint32_t>(__cvta_generic_to_shared(s_raw + i * 8));
+        asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(g_x + i * 8) : "memory");
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int g = tid; g < K / kGroup; g += nthr) {
+        const float m = __uint_as_float(__ldcg(g_amax + g));
+        const float d = fmaxf(__fdiv_rn(m, 127.0f), 1e-8f);
+        s_scale[g] = d;
+        s_inv[g] = __fdiv_rn(1.0f, d);
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    const int rounds = (octets + nthr - 1) / nthr;
+    for (int r = 0; r < rounds; ++r) {   // uniform trip count: the four lanes of a chunk shuffle together
+        const int i = tid + r * nthr;
+        const bool on = i < octets;
+        uint4 xr = make_uint4(0, 0, 0, 0);
+        float inv_d = 0.0f;
+        if (on) {
+            xr = *reinterpret_cast<const uint4*>(s_raw + i * 8);
+            inv_d = s_inv[i >> 4];
+        }
+        const uint32_t* xw = reinterpret_cast<const uint32_t*>(&xr);
+        uint32_t packed[2] = {0, 0};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&xw[k]));
+            int q0 = __float2int_rn(__fmul_rn(f.x, inv_d)), q1 = __float2int_rn(__fmul_rn(f.y, inv_d));
+            q0 = max(-127, min(127, q0));
+            q1 = max(-127, min(127, q1));
+            packed[k >> 1] |= ((static_cast<uint32_t>(q0) & 0xFFu) | ((static_cast<uint32_t>(q1) & 0xFFu) << 8)) << (16 * (k & 1));
+        }
+        int32_t sum = byte_sum(packed[0]) + byte_sum(packed[1]);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
+        sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
+        if (on) {
+            reinterpret_cast<uint2*>(s_q8)[i] = make_uint2(packed[0], packed[1]);
+            if ((i & 3) == 0) s_seed[i >> 2] = -8 * sum;
         }
     }
 }

@@ -65,6 +65,8 @@ int quantize_set_attributes();
 // ---- decode GEMV (gemv_decode.cu) ----
 enum GemvMode { kPlain = 0, kQkv = 1, kSwiglu = 2 };
 
+constexpr int kSumsqSlots = 8;   // partial sums a producer spreads its double atomics over
+
 struct GemvArgs {
     // PLAIN / SWIGLU use index 0 only; QKV uses q, k, v in 0, 1, 2.
     const uint32_t* qweight[3];
@@ -116,6 +118,21 @@ struct GemvArgs {
     int32_t* sample_token_out;
     void* sample_control_rw;
     int sample_finish_inline;
+    // Hand-offs between the launches of a decode pass (all optional): a producer publishes the reductions its
+    // consumer would otherwise redo in every CTA, on the critical path between two dependent launches.
+    //   amax_out   SWIGLU: max |output| (the fp16 value, as float bits) of every group of 128 outputs, by atomicMax;
+    //              the words must be zero when the launch starts
+    //   amax_in    PLAIN, x_fp16 without gamma: those maxima for x; the prologue quantises without reducing
+    //   sumsq_out  PLAIN: squares of the fp16 outputs added (double) into kSumsqSlots partial sums, slot = CTA % slots;
+    //              zero when the launch starts
+    //   sumsq_in   x_fp16 with gamma: the partial sums of x's squares; the prologue skips its own reduction
+    //   clear_words / clear_count  words CTA 0 zeroes after its wait for the prior grid (the scratch of a LATER launch)
+    uint32_t* amax_out;
+    const uint32_t* amax_in;
+    double* sumsq_out;
+    const double* sumsq_in;
+    uint32_t* clear_words;
+    int clear_count;
     int K;
     int units;  // outputs produced: rows (PLAIN, QKV total) or row pairs (SWIGLU)
     // filled in by the planner

@@ -25,7 +25,7 @@ __all__ = [
     "launch_gemm_prefill_w4a16", "launch_gemm_prefill_qkv_w4a16",
     "launch_gemm_prefill_dual_gate_up_swiglu_w4a16", "gemv_group_dots", "DecodeSweep",
     "launch_gemv_rmsnorm_w4a16", "launch_gemv_qkv_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16", "launch_gemv_dual_gate_up_swiglu_rmsnorm_w4a16_q8_1",
-    "gemv_w4a8_peers", "gemm_prefill_w4a16_block", "make_sample_control", "launch_embed_lookup_w4a16", "read_sample_control", "launch_sample_and_advance", "sample_slots", "launch_gemv_w4a8_sample_candidates", "launch_sample_finish", "launch_gemv_w4a8_sample_one_launch", "gemv_w4a8_sample_candidates_peers", "gemv_w4a8_sample_candidates_signal", "sample_finish_after_signals", "gemv_w4a8_peers_signal", "gather_after_signals", "launch_gemv_w4a8_sample_and_advance", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_QUANT_IN_GATE_UP", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
+    "gemv_w4a8_peers", "gemm_prefill_w4a16_block", "make_sample_control", "launch_embed_lookup_w4a16", "read_sample_control", "launch_sample_and_advance", "sample_slots", "launch_gemv_w4a8_sample_candidates", "launch_sample_finish", "launch_gemv_w4a8_sample_one_launch", "gemv_w4a8_sample_candidates_peers", "gemv_w4a8_sample_candidates_signal", "sample_finish_after_signals", "gemv_w4a8_peers_signal", "gather_after_signals", "launch_gemv_w4a8_sample_and_advance", "SWEEP_SEPARATE", "SWEEP_FUSE_ALL", "SWEEP_PERSISTENT", "SWEEP_QUANT_IN_GATE_UP", "SWEEP_PUBLISH_SUMSQ", "SWEEP_PUBLISH_AMAX", "SWEEP_DEFAULT", "gemv_w4a16_static_scratch", "debug_counter",
 ]
 
 # Qwen2.5-1.5B defaults of the reference's launchers (include/config.cuh:10-22)
@@ -387,8 +387,10 @@ def gemv_group_dots(qweight, input_q8, input_sum8, out_dots, out_features, in_fe
 SWEEP_SEPARATE, SWEEP_FUSE_NORM, SWEEP_FUSE_QUANT_O, SWEEP_FUSE_QUANT_DOWN, SWEEP_FUSE_ALL = 0, 1, 2, 4, 7
 SWEEP_PERSISTENT = 8
 SWEEP_QUANT_IN_GATE_UP = 16
+SWEEP_PUBLISH_SUMSQ = 32
+SWEEP_PUBLISH_AMAX = 64
 # the fastest measured form on B200: RMSNorm inside QKV / gate_up, Q8_1 inside O, a separate quantiser before down
-SWEEP_DEFAULT = SWEEP_FUSE_NORM | SWEEP_FUSE_QUANT_O
+SWEEP_DEFAULT = SWEEP_FUSE_NORM | SWEEP_FUSE_QUANT_O | SWEEP_PUBLISH_SUMSQ
 
 
 class DecodeSweep:

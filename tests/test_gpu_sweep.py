@@ -114,6 +114,28 @@ def test_fused_sweeps_give_the_bits_of_the_separate_launch_sequence(ops, model, 
     fused.close()
 
 
+@pytest.mark.parametrize("seed,flags", [(7, 32), (8, 64), (9, 96)])
+def test_sweep_with_published_reductions_gives_the_same_bits(ops, model, seed, flags):
+    """Producers publishing what their consumers would reduce again (sum of squares for the next RMSNorm by the O
+    and down launches, |max| per group of 128 by the gate_up launch) removes the quantiser launch and the
+    reductions from the prologues without changing a bit; replays of the graph (which clear and refill the
+    published words every layer) agree with each other."""
+    from qwen_engine_b200 import synth
+    _, layers_dev = model
+    h_in = util.to_dev(synth.activations(seed, "h0", synth.HIDDEN))
+    ref_sweep = ops.DecodeSweep(layers_dev, flags=ops.SWEEP_SEPARATE)
+    fused = ops.DecodeSweep(layers_dev, flags=flags)
+    assert fused.launches == 28 * (4 if flags & ops.SWEEP_PUBLISH_AMAX else 5)
+    a, b = torch.empty_like(h_in), torch.empty_like(h_in)
+    ref_sweep.run_device(h_in, a)
+    for _ in range(4):
+        fused.run_device(h_in, b)
+        torch.cuda.synchronize()
+        assert torch.equal(a, b)
+    ref_sweep.close()
+    fused.close()
+
+
 @pytest.mark.parametrize("flags", [16, 19, 23])
 def test_sweep_with_q8_1_written_by_gate_up_gives_the_same_bits(ops, model, flags):
     """The gate_up launch quantising its own output (clusters of four CTAs per group of 128) replaces the
