@@ -80,9 +80,10 @@ W4A16_API int w4a16_init(void);
 enum {
     W4A16_OPT_PDL = 1,               /* 1 (default): programmatic dependent launch, so that the next kernel's weight
                                         prefetch overlaps this kernel's tail; 0: plain stream-ordered launches */
-    W4A16_OPT_SIGNAL_WAIT_SPINS = 2, /* polls (about 0.2 us apart) that w4a16_sample_finish_after_signals spends on
-                                        a peer's flag before it gives up and reports the rank in *d_status;
-                                        default 1 << 22, about a second */
+    W4A16_OPT_SIGNAL_WAIT_SPINS = 2, /* polls (about 0.2 us apart) that w4a16_sample_finish_after_signals and
+                                        w4a16_gather_after_signals spend on a peer's flag, and a CTA of the persistent
+                                        sweep on another CTA's counter or tagged word, before giving up and reporting
+                                        it (*d_status, w4a16_sweep_status); default 1 << 22, about a second */
     W4A16_OPT_GEMV_FORM = 3,         /* how the batch-1 GEMV brings its weights on chip: 0 (default) the measured
                                         best, which is 1; 1 register-held 16-byte streaming loads issued before the
                                         wait for the previous kernel, 2 bulk copies (cp.async.bulk) into shared
@@ -494,7 +495,9 @@ W4A16_API int w4a16_sweep_run_host(w4a16_sweep* sweep, const void* h_h_in, void*
                                    w4a16_stream_t stream);
 
 /* 0 after a clean pass; nonzero if a bounded wait of the persistent kernel ran out (1 ring, 2 exchange):
- * the pass's output is then invalid.  Synchronises the device.  Always 0 for graph-mode sweeps. */
+ * the pass's output is then invalid, and this call re-bases the exchange (device idle, tags, counters and the
+ * status word cleared, launch count and tags restarted) so that the next pass starts clean -- call it after
+ * every pass whose result matters.  Synchronises the device.  Always 0 for graph-mode sweeps. */
 W4A16_API int w4a16_sweep_status(w4a16_sweep* sweep, int* out);
 
 /* Device pointer of a workspace region, for tests: 0 hidden, 1 q, 2 k, 3 v, 4 mlp. */

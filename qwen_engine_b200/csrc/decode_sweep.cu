@@ -37,6 +37,8 @@ struct w4a16_sweep {
     uint32_t epoch = 0;
     uint32_t launch_count = 0;
     int sm_count = 0;
+    uint8_t* exchange_begin = nullptr;   // tagged exchange buffers, status word and arrival counters: one range
+    size_t exchange_bytes = 0;
 };
 
 namespace {
@@ -272,7 +274,9 @@ int w4a16_sweep_create(const w4a16_sweep_desc* desc, w4a16_stream_t stream_, w4a
         if ((e = cudaMemcpyAsync(d_table, table.data(), table.size(), cudaMemcpyHostToDevice, stream)) != cudaSuccess)
             return static_cast<int>(e);
         // tags start above zero, so zeroed exchange buffers never look published
-        if ((e = cudaMemsetAsync(base + c.ll_h_attn, 0, c.layer_table - c.ll_h_attn, stream)) != cudaSuccess)
+        s->exchange_begin = base + c.ll_h_attn;
+        s->exchange_bytes = c.layer_table - c.ll_h_attn;
+        if ((e = cudaMemsetAsync(s->exchange_begin, 0, s->exchange_bytes, stream)) != cudaSuccess)
             return static_cast<int>(e);
         if ((e = cudaStreamSynchronize(stream)) != cudaSuccess) return static_cast<int>(e);   // `table` is a local
         s->persistent = true;
@@ -358,7 +362,16 @@ int w4a16_sweep_status(w4a16_sweep* s, int* out) {
     if (!s || !out) return W4A16_ERR_INVALID_ARG;
     *out = 0;
     if (!s->persistent) return 0;
-    return static_cast<int>(cudaMemcpy(out, s->pargs.status, sizeof(int), cudaMemcpyDeviceToHost));
+    cudaError_t e = cudaMemcpy(out, s->pargs.status, sizeof(int), cudaMemcpyDeviceToHost);
+    if (e != cudaSuccess || *out == 0) return static_cast<int>(e);
+    // A bounded wait ran out: the CTAs left early, so the arrival counters are short for ever and every later
+    // launch would run into its own bounds.  Start over: nothing of the pass is in flight once the device is
+    // idle; clear tags, counters and status and count launches and tags from zero again.
+    if ((e = cudaDeviceSynchronize()) != cudaSuccess) return static_cast<int>(e);
+    if ((e = cudaMemset(s->exchange_begin, 0, s->exchange_bytes)) != cudaSuccess) return static_cast<int>(e);
+    s->launch_count = 0;
+    s->epoch = 0;
+    return 0;
 }
 
 void* w4a16_sweep_buffer(const w4a16_sweep* s, int which) {

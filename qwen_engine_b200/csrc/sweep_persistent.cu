@@ -184,7 +184,7 @@ __device__ __forceinline__ void locate_row(const PSweepArgs& a, int kind, int vr
 __device__ void producer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0, uint32_t empty0,
                               volatile int* s_abort, int lane) {
     const int cta = blockIdx.x, nctas = gridDim.x;
-    int slot = 0;
+    int slot = 0, issued = 0;
     uint32_t phase = 0;
     const int num_stages = a.num_layers * 4;
     for (int st = 0; st < num_stages; ++st) {
@@ -195,7 +195,21 @@ __device__ void producer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
             int ok = 1;
             if (lane == 0) ok = bar_wait(empty0 + 8u * slot, phase ^ 1, s_abort) ? 1 : 0;
             ok = __shfl_sync(0xFFFFFFFFu, ok, 0);
-            if (!ok) return;
+            if (!ok) {
+                // Leaving early: a CTA must not exit while bulk copies into its shared memory are in flight.  The
+                // latest fill of every slot (at most kSlots of them) is waited for, each wait bounded.
+                asm volatile("cp.async.wait_all;" ::: "memory");
+                if (lane == 0) {
+                    for (int k = 0; k < min(issued, kSlots); ++k) {
+                        const int j = (slot - 1 - k + 2 * kSlots) % kSlots;
+                        const uint32_t ph = j < slot ? phase : phase ^ 1u;
+                        for (unsigned it = 0; it < kPollLimit; ++it)
+                            if (bar_try_wait(full0 + 8u * j, ph)) break;
+                    }
+                }
+                __syncwarp();
+                return;
+            }
             const uint32_t full = full0 + 8u * slot;
             uint8_t* dst_w = ring + slot * kSlotStride;
             uint8_t* dst_s = dst_w + kSlotBytes;
@@ -217,6 +231,7 @@ __device__ void producer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
                 done += seg;
             }
             cp_async_arrive_noinc(full);   // every lane: its scale copies count towards this slot
+            ++issued;
             if (++slot == kSlots) { slot = 0; phase ^= 1; }
         }
     }
@@ -229,7 +244,7 @@ __device__ void producer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
 // read succeeds; a word whose store is still in flight is read again.  False on time-out / abort.
 template <int MAXW, typename IdxFn>
 __device__ __forceinline__ bool poll_words(const uint2* base, IdxFn idx, int count, uint32_t tag, uint32_t (&data)[MAXW],
-                                           volatile int* s_abort, int* status) {
+                                           volatile int* s_abort, int* status, unsigned limit) {
     uint32_t tags[MAXW];
 #pragma unroll
     for (int i = 0; i < MAXW; ++i) {
@@ -242,7 +257,7 @@ __device__ __forceinline__ bool poll_words(const uint2* base, IdxFn idx, int cou
             tags[i] = tag;
         }
     }
-    for (unsigned it = 0; it < kPollLimit; ++it) {
+    for (unsigned it = 0; it < limit; ++it) {
         bool all = true;
 #pragma unroll
         for (int i = 0; i < MAXW; ++i) {
@@ -321,7 +336,7 @@ __device__ bool stage_input_norm(const PSweepArgs& a, const uint2* ll, const __h
         for (int i = 0; i < MAXW; ++i)
             if (i < count) data[i] = reinterpret_cast<const uint32_t*>(plain)[idx(i)];
     } else {
-        if (!poll_words<MAXW>(ll, idx, count, tag, data, s_abort, a.status)) return false;
+        if (!poll_words<MAXW>(ll, idx, count, tag, data, s_abort, a.status, a.poll_limit)) return false;
     }
 #pragma unroll
     for (int i = 0; i < MAXW; ++i) {
@@ -384,7 +399,7 @@ __device__ bool stage_input_plain(const PSweepArgs& a, const uint2* ll, int n, u
 #pragma unroll
     for (int i = 0; i < MAXR; ++i)
         if (grp(i) < groups) count = 4 * i + 4;
-    if (!poll_words<4 * MAXR>(ll, idx, count, tag, data, s_abort, a.status)) return false;
+    if (!poll_words<4 * MAXR>(ll, idx, count, tag, data, s_abort, a.status, a.poll_limit)) return false;
     const int rounds = (groups + 2 * kConsumerWarps - 1) / (2 * kConsumerWarps);
 #pragma unroll
     for (int i = 0; i < MAXR; ++i) {
@@ -461,7 +476,7 @@ __device__ void consumer_loop(const PSweepArgs& a, uint8_t* ring, uint32_t full0
             if (tid == 0) {
                 const uint32_t* ctr = a.counters + 8 * (st - 1);
                 bool seen = false;
-                for (unsigned it = 0; it < kPollLimit; ++it) {
+                for (unsigned it = 0; it < a.poll_limit; ++it) {
                     // counters may have wrapped past the target of a later launch: compare as a distance
                     if (static_cast<int32_t>(ld_counter(ctr) - a.counter_target) >= 0) { seen = true; break; }
                     if (*s_abort) break;
@@ -701,6 +716,8 @@ void psweep_fill_layer(void* dst, const w4a16_layer_weights& L) {
 
 int psweep_launch(const PSweepArgs& args, int sm_count, cudaStream_t stream) {
     PSweepArgs a = args;
+    const int spins = option(W4A16_OPT_SIGNAL_WAIT_SPINS);
+    a.poll_limit = spins > 0 ? static_cast<unsigned>(spins) : kPollLimit;
     void* params[] = {&a};
     const int max_pairs = std::max(std::max(a.H, a.I), a.qdim + 2 * a.kvdim) / 2;
     int grid = sm_count;

@@ -208,6 +208,7 @@ struct PSweepArgs {
     uint32_t* counters;   // [4 * num_layers] at 32-byte spacing: CTAs that have published each stage, ever
     uint32_t counter_target;   // value a stage counter reaches when all CTAs of THIS launch have published
     int* status;          // 0 ok; 1 ring wait ran out; 2 tag poll ran out
+    unsigned poll_limit;  // polls a CTA spends on another CTA's counter or tagged word before it gives up
 };
 size_t psweep_layer_bytes();
 bool psweep_supported(int H, int I, int qdim, int kvdim);

@@ -266,3 +266,35 @@ def test_persistent_sweep_full_depth_is_deterministic_and_close_to_the_launch_se
     assert np.sqrt(np.mean((x - y) ** 2)) <= 0.05 * rms
     graph.close()
     pers.close()
+
+
+def test_persistent_sweep_recovers_after_a_wait_that_ran_out(ops, model):
+    """A bounded wait of the persistent kernel is made to run out on the host side of the protocol only: with a
+    limit of one poll a CTA gives up on the first counter or tagged word that is not there yet.  The kernel must
+    return, report it, and -- because the status call re-bases tags and counters -- the next pass with the usual
+    limit must be clean and give the bits of an undisturbed sweep."""
+    from qwen_engine_b200 import synth
+    _, layers_dev = model
+    h_in = util.to_dev(synth.activations(11, "h0", synth.HIDDEN))
+    ref = ops.DecodeSweep(layers_dev[:4], flags=ops.SWEEP_PERSISTENT)
+    want = torch.empty_like(h_in)
+    ref.run_device(h_in, want)
+    torch.cuda.synchronize()
+    assert ref.status() == 0
+    ref.close()
+    pers = ops.DecodeSweep(layers_dev[:4], flags=ops.SWEEP_PERSISTENT)
+    out = torch.empty_like(h_in)
+    usual = ops.get_option(ops.OPT_SIGNAL_WAIT_SPINS)
+    try:
+        ops.set_option(ops.OPT_SIGNAL_WAIT_SPINS, 1)
+        pers.run_device(h_in, out)
+        torch.cuda.synchronize()
+        assert pers.status() != 0          # reported, and re-based by the same call
+    finally:
+        ops.set_option(ops.OPT_SIGNAL_WAIT_SPINS, usual)
+    for _ in range(2):
+        pers.run_device(h_in, out)
+        torch.cuda.synchronize()
+        assert pers.status() == 0
+        assert torch.equal(out, want)
+    pers.close()
