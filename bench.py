@@ -434,7 +434,35 @@ def lm_head_nsplit(torch, dist, ops, rank, world, stream, steps, warmup):
             out["peer_store_signal"] = {"unavailable": str(e)[:200]}
     out["us_per_step"] = best
     out["value"] = nbytes / (best * 1e-6) / 1e9
-    out["gpus"] = world       # strong scaling: efficiency = us_per_step(1 GPU) / (world * us_per_step)
+    out["gpus"] = world
+    if world > 1:
+        # strong-scaling efficiency against the whole matrix on ONE GPU, timed in this same run (random weights of the
+        # full height: the timing does not depend on their values), = t(1 GPU) / (world * t(world GPUs))
+        try:
+            full = [(torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), dtype=torch.int32, device="cuda"),
+                     (torch.rand((N, K // 128), device="cuda") * 0.018 + 0.002).half()) for _ in range(4)]
+            y_full = torch.empty(N, dtype=torch.float16, device="cuda")
+            with torch.cuda.stream(stream):
+                def full_round():
+                    for w, s in full:
+                        ops.launch_gemv_w4a8(w, s, q8, xs, s8, None, y_full, N, K)
+                full_round()
+                stream.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    full_round()
+                graph.replay()
+                stream.synchronize()
+                rounds = max(1, steps // 4)
+                one_us = timed_events(torch, stream, graph.replay, rounds) * 1e3 / (rounds * 4)
+            out["single_gpu_us_per_step"] = one_us
+            for key in ("nccl_all_gather", "peer_store_epilogue", "peer_store_signal"):
+                if isinstance(out.get(key), dict) and "us_per_step" in out[key]:
+                    out[key]["strong_scaling_efficiency"] = one_us / (world * out[key]["us_per_step"])
+            out["strong_scaling_efficiency"] = one_us / (world * best)
+            del full
+        except Exception as e:
+            out["single_gpu_us_per_step"] = {"unavailable": str(e)[:200]}
 
     # ---- token selection after lm_head: logits + stand-alone sampler vs. candidates from the GEMV's epilogue ----
     try:
@@ -624,7 +652,26 @@ def prefill_big_nsplit(torch, dist, ops, rank, world, stream, steps):
             out["peer_store_epilogue"] = {"unavailable": str(e)[:200]}
     out["us_per_step"] = best
     out["value"] = flops / (best * 1e-6) / 1e12
-    out["gpus"] = world       # strong scaling: efficiency = us_per_step(1 GPU) / (world * us_per_step)
+    out["gpus"] = world
+    if world > 1:
+        # strong-scaling efficiency against the whole contraction on ONE GPU, timed in this same run
+        try:
+            w_full = torch.randint(-2 ** 31, 2 ** 31 - 1, (N, K // 8), dtype=torch.int32, device="cuda")
+            s_full = (torch.rand((N, K // 128), device="cuda") * 0.018 + 0.002).half()
+            y_full = torch.empty((M, N), dtype=torch.float16, device="cuda")
+            with torch.cuda.stream(stream):
+                for _ in range(2):
+                    ops.launch_gemm_prefill_w4a16(w_full, s_full, x, None, y_full, M, N, K)
+                stream.synchronize()
+                one_us = timed_events(torch, stream, lambda: ops.launch_gemm_prefill_w4a16(w_full, s_full, x, None, y_full, M, N, K), reps) * 1e3 / reps
+            out["single_gpu_us_per_step"] = one_us
+            for key in ("nccl_all_gather", "peer_store_epilogue"):
+                if isinstance(out.get(key), dict) and "us_per_step" in out[key]:
+                    out[key]["strong_scaling_efficiency"] = one_us / (world * out[key]["us_per_step"])
+            out["strong_scaling_efficiency"] = one_us / (world * best)
+            del w_full, s_full, y_full
+        except Exception as e:
+            out["single_gpu_us_per_step"] = {"unavailable": str(e)[:200]}
     return out
 
 
