@@ -116,6 +116,11 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
     };
 
     issue(s_begin);
+    if constexpr (MODE == kSwiglu) {
+        // Q8_1 epilogue: its remote shared-memory stores need every CTA of the cluster to have started; each CTA
+        // says so here (the wait sits just before the stores, so it overlaps everything in between).
+        if (a.q8_out != nullptr) asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+    }
     // Everything that does not depend on the prior grid goes before the wait: the weights above and the
     // RMSNorm gain.  After it, every global round trip is on the critical path between two GEMVs, so the
     // residual element is requested first and the activation is staged with one round trip.
@@ -252,6 +257,7 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
             __syncthreads();
             uint32_t rank;
             asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+            asm volatile("barrier.cluster.wait.aligned;" ::: "memory");   // pairs with the arrive at kernel entry
             float v = 0.0f;
             if (tid < 32) {
                 v = s_y[tid];
