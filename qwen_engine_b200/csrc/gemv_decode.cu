@@ -169,8 +169,8 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
             const int s = s0 + u;
             if (s < s_end) {
                 const int c = s * kSubwarp + l;  // 32-element chunk index along K
-                const uint4 xa = reinterpret_cast<const uint4*>(s_q8)[2 * c];
-                const uint4 xb = reinterpret_cast<const uint4*>(s_q8)[2 * c + 1];
+                const uint4 xa = reinterpret_cast<const uint4*>(s_q8)[q8_slot(c, 0)];
+                const uint4 xb = reinterpret_cast<const uint4*>(s_q8)[q8_slot(c, 1)];
                 const int32_t seed = s_seed[c];
                 const float xs = s_scale[c >> 2];
 #pragma unroll
@@ -489,8 +489,8 @@ __global__ void __maxnreg__(64) gemv_w4_bulk_kernel(const GemvArgs a) {
             const int s = s0 + u;
             if (s < s_end) {
                 const int c = s * kSubwarp + l;   // 32-element chunk index inside the CTA's K range
-                const uint4 xa = reinterpret_cast<const uint4*>(s_q8)[2 * c];
-                const uint4 xb = reinterpret_cast<const uint4*>(s_q8)[2 * c + 1];
+                const uint4 xa = reinterpret_cast<const uint4*>(s_q8)[q8_slot(c, 0)];
+                const uint4 xb = reinterpret_cast<const uint4*>(s_q8)[q8_slot(c, 1)];
                 const int32_t seed = s_seed[c];
                 const float xs = s_scale[c >> 2];
 #pragma unroll
@@ -650,8 +650,8 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_kernel(const Ge
 #pragma unroll
     for (int i = 0; i < STEPS; ++i) {
         const int c = (i < steps ? i : 0) * kSubwarp + l;
-        xa[i] = reinterpret_cast<const uint4*>(s_q8)[2 * c];
-        xb[i] = reinterpret_cast<const uint4*>(s_q8)[2 * c + 1];
+        xa[i] = reinterpret_cast<const uint4*>(s_q8)[q8_slot(c, 0)];
+        xb[i] = reinterpret_cast<const uint4*>(s_q8)[q8_slot(c, 1)];
         seed[i] = s_seed[c];
         xs[i] = i < steps ? s_scale[c >> 2] : 0.0f;     // a zero factor switches an unused slot off
     }
@@ -832,14 +832,14 @@ __global__ void __launch_bounds__(kMaxThreads, 2) gemv_w4_stream_longk_kernel(co
     float acc = 0.0f;
     // one unit: 8 chunks of this lane against the staged activation; at a row's last slice reduce and store
     auto consume = [&](const uint4 (&w)[STEPS], const uint16_t (&sb)[STEPS], int blk, int sl) {
-        const uint4* xq = reinterpret_cast<const uint4*>(s_q8) + 2 * (sl * STEPS * kSubwarp + l);
+        const uint4* xq = reinterpret_cast<const uint4*>(s_q8) + q8_slot(sl * STEPS * kSubwarp + l, 0);   // chunk-interleaved
         const int32_t* xseed = s_seed + sl * STEPS * kSubwarp + l;
         const float* xscale = s_scale + 2 * sl * STEPS + (l >> 2);
 #pragma unroll
         for (int i = 0; i < STEPS; ++i) {
             if (FULL || sl * STEPS + i < steps) {
-                const uint4 xa = xq[2 * i * kSubwarp];
-                const uint4 xb = xq[2 * i * kSubwarp + 1];
+                const uint4 xa = xq[16 * i];        // chunk + 8 i: the next block of eight chunks
+                const uint4 xb = xq[16 * i + 8];
                 const int32_t d = chunk_dot(w[i], xa, xb, xseed[i * kSubwarp]);
                 acc = fmaf(static_cast<float>(d), __half2float(__ushort_as_half(sb[i])) * xscale[2 * i], acc);
             }
@@ -899,13 +899,13 @@ __global__ void __launch_bounds__(kMaxThreads) gemv_group_dots_kernel(const uint
         const int tid = threadIdx.x, nthr = blockDim.x;
         if (vec_ok) {
             for (int i = tid; i < K / 16; i += nthr)
-                reinterpret_cast<uint4*>(s_q8)[i] = reinterpret_cast<const uint4*>(q8)[i];
+                reinterpret_cast<uint4*>(s_q8)[q8_slot(i >> 1, i & 1)] = reinterpret_cast<const uint4*>(q8)[i];
             for (int c = tid; c < K / kChunk; c += nthr) {
                 const int4 v = reinterpret_cast<const int4*>(sum8)[c];
                 s_seed[c] = v.x + v.y + v.z + v.w;
             }
         } else {
-            for (int i = tid; i < K; i += nthr) s_q8[i] = q8[i];
+            for (int i = tid; i < K; i += nthr) s_q8[q8_byte(i)] = q8[i];
             for (int c = tid; c < K / kChunk; c += nthr)
                 s_seed[c] = sum8[4 * c] + sum8[4 * c + 1] + sum8[4 * c + 2] + sum8[4 * c + 3];
         }
@@ -921,8 +921,8 @@ __global__ void __launch_bounds__(kMaxThreads) gemv_group_dots_kernel(const uint
         int32_t d = 0;
         if (active) {
             const uint4 w = aligned16 ? ld_weights_16(wrow + c * 4) : ld_weights_4x4(wrow + c * 4);
-            const uint4 xa = reinterpret_cast<const uint4*>(s_q8)[2 * c];
-            const uint4 xb = reinterpret_cast<const uint4*>(s_q8)[2 * c + 1];
+            const uint4 xa = reinterpret_cast<const uint4*>(s_q8)[q8_slot(c, 0)];
+            const uint4 xb = reinterpret_cast<const uint4*>(s_q8)[q8_slot(c, 1)];
             d = chunk_dot(w, xa, xb, s_seed[c]);
         }
         d += __shfl_xor_sync(0xFFFFFFFFu, d, 1);

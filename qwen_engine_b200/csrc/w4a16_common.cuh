@@ -129,7 +129,7 @@ __device__ __forceinline__ void load_half4_as_float(const __half* p, float v[4])
 }
 
 // Layout of the staged activation in shared memory (all 16-byte aligned):
-//   q8[K] int8 | chunk_seed[K/32] int32 | scale[K/128] fp32
+//   q8[K] int8 (chunk-interleaved, see q8_slot) | chunk_seed[K/32] int32 | scale[K/128] fp32
 struct StagedX {
     const int8_t* q8;
     const int32_t* seed;
@@ -138,6 +138,14 @@ struct StagedX {
 __host__ __device__ inline size_t staged_x_bytes(int K) {
     return static_cast<size_t>(K) + static_cast<size_t>(K / kChunk) * 4 + static_cast<size_t>(K / kGroup) * 4;
 }
+
+// Where the staged int8 activation keeps its bytes.  A lane of the GEMV reads the 32 bytes of one chunk as two
+// 16-byte halves, and the 8 lanes of a sub-warp read 8 consecutive chunks: in natural order that is a 32-byte
+// stride, two lanes per bank.  So chunks are interleaved in blocks of eight: the first halves of the eight chunks
+// (128 contiguous bytes), then their second halves.  K is a multiple of 256, i.e. of eight chunks.
+//   q8_slot(c, h): uint4 index of half h of chunk c;  q8_byte(e): byte offset of element e.
+__host__ __device__ __forceinline__ int q8_slot(int c, int h) { return ((c >> 3) << 4) + (h << 3) + (c & 7); }
+__host__ __device__ __forceinline__ int q8_byte(int e) { return q8_slot(e >> 5, (e >> 4) & 1) * 16 + (e & 15); }
 
 // RMSNorm scale from the sum of squares.  The sum is taken in double (squares of fp16 values are exact there
 // and their sum is off by parts in 2^50 at most, so the order of the additions does not reach the fp32 mean
@@ -157,14 +165,14 @@ __device__ __forceinline__ void stage_x_from_q8_1(const int8_t* __restrict__ g_q
     if (vec_ok) {
         const uint4* src = reinterpret_cast<const uint4*>(g_q8);
         uint4* dst = reinterpret_cast<uint4*>(s_q8);
-        for (int i = tid; i < K / 16; i += nthr) dst[i] = src[i];
+        for (int i = tid; i < K / 16; i += nthr) dst[q8_slot(i >> 1, i & 1)] = src[i];
         const int4* s8 = reinterpret_cast<const int4*>(g_sum8);
         for (int c = tid; c < K / kChunk; c += nthr) {
             const int4 v = s8[c];
             s_seed[c] = v.x + v.y + v.z + v.w;
         }
     } else {
-        for (int i = tid; i < K; i += nthr) s_q8[i] = g_q8[i];
+        for (int i = tid; i < K; i += nthr) s_q8[q8_byte(i)] = g_q8[i];
         for (int c = tid; c < K / kChunk; c += nthr)
             s_seed[c] = g_sum8[4 * c] + g_sum8[4 * c + 1] + g_sum8[4 * c + 2] + g_sum8[4 * c + 3];
     }
@@ -182,7 +190,7 @@ __device__ __forceinline__ void stage_x_from_fp16(const __half* __restrict__ g_x
         load_half4_as_float(g_x + g * kGroup + lane * 4, v);
         float d;
         const uint32_t packed = quantize_group128_lane(v, &d);
-        reinterpret_cast<uint32_t*>(s_q8)[g * (kGroup / 4) + lane] = packed;
+        *reinterpret_cast<uint32_t*>(s_q8 + q8_byte(g * kGroup + lane * 4)) = packed;
         int32_t s = byte_sum(packed);
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
@@ -231,7 +239,7 @@ __device__ __forceinline__ void stage_x_from_fp16_rmsnorm(const __half* __restri
         const float v[4] = {f0.x, f0.y, f1.x, f1.y};
         float d;
         const uint32_t packed = quantize_group128_lane(v, &d);
-        reinterpret_cast<uint32_t*>(s_q8)[g * (kGroup / 4) + lane] = packed;
+        *reinterpret_cast<uint32_t*>(s_q8 + q8_byte(g * kGroup + lane * 4)) = packed;
         int32_t s = byte_sum(packed);
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 1);
         s += __shfl_xor_sync(0xFFFFFFFFu, s, 2);
@@ -271,7 +279,7 @@ __device__ __forceinline__ void quantize_group_halfwarp_to_smem(const float v[8]
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
     sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
     if (on) {
-        reinterpret_cast<uint2*>(s_q8)[g * (kGroup / 8) + hl] = make_uint2(packed[0], packed[1]);
+        *reinterpret_cast<uint2*>(s_q8 + q8_byte(g * kGroup + hl * 8)) = make_uint2(packed[0], packed[1]);
         if ((hl & 3) == 0) s_seed[g * 4 + (hl >> 2)] = -8 * sum;
         if (hl == 0) s_scale[g] = d;
     }
@@ -326,7 +334,7 @@ __device__ __forceinline__ void stage_x_from_f32_heads(const float* __restrict__
         sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);   // four lanes = one 32-element chunk
         sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
         if (on) {
-            reinterpret_cast<uint2*>(s_q8)[g * (kGroup / 8) + hl] = packed;
+            *reinterpret_cast<uint2*>(s_q8 + q8_byte(g * kGroup + hl * 8)) = packed;
             if ((hl & 3) == 0) s_seed[g * 4 + (hl >> 2)] = -8 * sum;
             if (hl == 0) s_scale[g] = d;
         }
@@ -468,7 +476,7 @@ __device__ __forceinline__ void stage_x_fp16_amax(const __half* g_x, const uint3
         sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 1);
         sum += __shfl_xor_sync(0xFFFFFFFFu, sum, 2);
         if (on) {
-            reinterpret_cast<uint2*>(s_q8)[i] = make_uint2(packed[0], packed[1]);
+            *reinterpret_cast<uint2*>(s_q8 + q8_byte(i * 8)) = make_uint2(packed[0], packed[1]);
             if ((i & 3) == 0) s_seed[i >> 2] = -8 * sum;
         }
     }
@@ -495,7 +503,7 @@ __device__ __forceinline__ bool stage_x_from_q8_1_regs(const int8_t* g_q8, const
 #pragma unroll
         for (int i = 0; i < MAXQ; ++i) {
             const int idx = tid + i * nthr;
-            if (idx < K / 16) reinterpret_cast<uint4*>(s_q8)[idx] = q[i];
+            if (idx < K / 16) reinterpret_cast<uint4*>(s_q8)[q8_slot(idx >> 1, idx & 1)] = q[i];
         }
     }
 #pragma unroll
@@ -508,7 +516,7 @@ __device__ __forceinline__ bool stage_x_from_q8_1_regs(const int8_t* g_q8, const
 #pragma unroll
         for (int i = 0; i < MAXQ; ++i) {
             const int idx = tid + i * nthr;
-            if (idx < K / 16) reinterpret_cast<uint4*>(s_q8)[idx] = q[i];
+            if (idx < K / 16) reinterpret_cast<uint4*>(s_q8)[q8_slot(idx >> 1, idx & 1)] = q[i];
         }
     }
 #pragma unroll
