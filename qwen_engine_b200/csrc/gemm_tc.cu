@@ -965,17 +965,45 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
+// Encoded maps are kept per (pointer, shape, box): a model's weight matrices and an engine's activation buffers
+// come back launch after launch, and an encode costs the host a microsecond or two.  A map holds nothing but the
+// address and the geometry, so an entry stays valid even if the memory behind it was freed and handed out again.
+struct MapKey {
+    const void* base;
+    uint64_t inner, outer, row_bytes;
+    uint32_t box_inner, box_outer;
+    int dt;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && inner == o.inner && outer == o.outer && row_bytes == o.row_bytes &&
+               box_inner == o.box_inner && box_outer == o.box_outer && dt == o.dt;
+    }
+};
+constexpr size_t kMapCacheEntries = 256;
+
 bool encode_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* base, uint64_t inner, uint64_t outer,
                uint64_t row_bytes, uint32_t box_inner, uint32_t box_outer) {
+    static std::mutex mu;
+    static std::vector<std::pair<MapKey, CUtensorMap>> cache;
+    static size_t next = 0;
+    const MapKey key{base, inner, outer, row_bytes, box_inner, box_outer, static_cast<int>(dt)};
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        for (const auto& kv : cache)
+            if (kv.first == key) { *map = kv.second; return true; }
+    }
     EncodeTiledFn fn = encode_tiled_fn();
     if (!fn) return false;
     const cuuint64_t dims[2] = {inner, outer};
     const cuuint64_t strides[1] = {row_bytes};
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t estr[2] = {1, 1};
-    return fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    if (fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return false;
+    std::lock_guard<std::mutex> lock(mu);
+    if (cache.size() < kMapCacheEntries) cache.emplace_back(key, *map);
+    else { cache[next] = {key, *map}; next = (next + 1) % kMapCacheEntries; }
+    return true;
 }
 
 size_t tc_smem_bytes(int T, int S, int K) {
