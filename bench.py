@@ -750,12 +750,17 @@ def shapes_table(torch, ops, stream, peaks, reps=10, m_small=(1, 2, 4, 8, 16, 32
         if name != "big":
             for M in m_small:
                 row = {}
-                for label, opt in (("dispatch", 0), ("cuda_core", 1 << 20), ("tensor_core", 1)):
+                # dispatch: what the library picks; cuda_core: the few-token CUDA-core form; mma_sync: the weight-streaming
+                # kernel with warp-level MMAs; tensor_core: the tcgen05 kernel
+                for label, opt, mma_max in (("dispatch", 0, 0), ("cuda_core", 1 << 20, 1), ("mma_sync", 1, 1 << 20),
+                                            ("tensor_core", 1, 1)):
                     ops.set_option(ops.OPT_GEMM_MIN_TOKENS_TENSOR_CORE, opt)
+                    ops.set_option(ops.OPT_GEMM_MMA_MAX_TOKENS, mma_max)
                     try:
                         row[label + "_us"] = round(timed_graph(gemm_for(M, ws), n=max(3, reps // 2)) / copies, 3)
                     finally:
                         ops.set_option(ops.OPT_GEMM_MIN_TOKENS_TENSOR_CORE, 0)
+                        ops.set_option(ops.OPT_GEMM_MMA_MAX_TOKENS, 0)
                 row["GB/s"] = round((wbytes + 2 * M * K + 2 * M * n_out) / row["dispatch_us"] / 1e3, 1)
                 out["small_m"][f"{name}.M{M}"] = row
         for M in (m_prefill if name != "big" else (m_prefill[0], m_prefill[-1])):
@@ -771,7 +776,7 @@ def shapes_table(torch, ops, stream, peaks, reps=10, m_small=(1, 2, 4, 8, 16, 32
         cross = None
         for M in m_small:
             r = out["small_m"][f"{name}.M{M}"]
-            if r["tensor_core_us"] < r["cuda_core_us"]:
+            if min(r["tensor_core_us"], r["mma_sync_us"]) < r["cuda_core_us"]:
                 cross = M
                 break
         out["small_m"][f"{name}.crossover_M"] = cross

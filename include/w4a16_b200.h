@@ -93,7 +93,9 @@ enum {
                                         tensor cores; 0 (default): the measured crossover (4 or 5 tokens) */
     W4A16_OPT_GEMM_FORM = 5,         /* tensor-core form of the M-token contraction: 0 (default) chosen by token
                                         count, 1 one CTA per tile, 2 CTA pairs (cta_group::2) */
-    W4A16_OPT_COUNT_ = 6
+    W4A16_OPT_GEMM_MMA_MAX_TOKENS = 6, /* largest token count that takes the weight-streaming mma.sync kernel instead of
+                                        the tcgen05 kernels: 0 (default) the measured crossover, 1 never, n up to n */
+    W4A16_OPT_COUNT_ = 7
 };
 W4A16_API int w4a16_set_option(int option, int value);
 W4A16_API int w4a16_get_option(int option);

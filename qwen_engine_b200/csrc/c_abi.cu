@@ -16,7 +16,7 @@ std::atomic<bool> g_dev_ready[kMaxDevices];
 // run-time options (w4a16_set_option): plain process-wide integers, read at launch time
 std::atomic<int> g_options[W4A16_OPT_COUNT_];
 const int kOptionDefaults[W4A16_OPT_COUNT_] = {0, /*PDL*/ 1, /*SIGNAL_WAIT_SPINS*/ 1 << 22, /*GEMV_FORM*/ 0,
-                                                /*GEMM_MIN_TOKENS_TENSOR_CORE*/ 0, /*GEMM_FORM*/ 0};
+                                                /*GEMM_MIN_TOKENS_TENSOR_CORE*/ 0, /*GEMM_FORM*/ 0, /*GEMM_MMA_MAX_TOKENS*/ 0};
 std::once_flag g_options_once;
 void init_options() {
     std::call_once(g_options_once, [] {
@@ -101,6 +101,7 @@ int w4a16_set_option(int which, int value) {
         case W4A16_OPT_GEMV_FORM: if (value < 0 || value > 2) return W4A16_ERR_INVALID_ARG; break;
         case W4A16_OPT_GEMM_MIN_TOKENS_TENSOR_CORE: if (value < 0) return W4A16_ERR_INVALID_ARG; break;
         case W4A16_OPT_GEMM_FORM: if (value < 0 || value > 2) return W4A16_ERR_INVALID_ARG; break;
+        case W4A16_OPT_GEMM_MMA_MAX_TOKENS: if (value < 0) return W4A16_ERR_INVALID_ARG; break;
         default: break;
     }
     init_options();

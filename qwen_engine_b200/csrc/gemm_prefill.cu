@@ -2,6 +2,7 @@
 #include <algorithm>
 
 #include "gemm_smallm.cuh"
+#include "gemm_smallm_mma.cuh"
 #include "w4a16_internal.hpp"
 
 namespace w4 {
@@ -77,12 +78,75 @@ bool plan_v2(const GemmArgs& g, int units, int sm_count, SmallMPlan* out, int* U
     return true;
 }
 
+// ---- few-token mma.sync form (gemm_smallm_mma_kernel) ----
+template <int MODE, int U>
+cudaError_t launch_mma_nt(const SmallMArgs& a, const SmallMmaPlan& p, int NT, dim3 grid, dim3 block, size_t smem, cudaStream_t stream) {
+    const bool pdl = pdl_enabled();
+    if (NT == 1) return launch_kernel(gemm_smallm_mma_kernel<MODE, U, 1>, grid, block, smem, stream, pdl, a, p);
+    if (NT == 2) return launch_kernel(gemm_smallm_mma_kernel<MODE, U, 2>, grid, block, smem, stream, pdl, a, p);
+    return launch_kernel(gemm_smallm_mma_kernel<MODE, U, 4>, grid, block, smem, stream, pdl, a, p);
+}
+template <int MODE>
+cudaError_t launch_mma(const SmallMArgs& a, const SmallMmaPlan& p, int U, int NT, dim3 grid, dim3 block, size_t smem, cudaStream_t stream) {
+    if (U == 4) return launch_mma_nt<MODE, 4>(a, p, NT, grid, block, smem, stream);
+    return launch_mma_nt<MODE, 8>(a, p, NT, grid, block, smem, stream);
+}
+template <int MODE, int U, int NT>
+cudaError_t raise_mma() {
+    return cudaFuncSetAttribute(gemm_smallm_mma_kernel<MODE, U, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+}
+template <int MODE>
+cudaError_t raise_mma_mode() {
+    cudaError_t e = raise_mma<MODE, 4, 1>();
+    if (e == cudaSuccess) e = raise_mma<MODE, 4, 2>();
+    if (e == cudaSuccess) e = raise_mma<MODE, 4, 4>();
+    if (e == cudaSuccess) e = raise_mma<MODE, 8, 1>();
+    if (e == cudaSuccess) e = raise_mma<MODE, 8, 2>();
+    if (e == cudaSuccess) e = raise_mma<MODE, 8, 4>();
+    return e;
+}
+
+// CTA shape of the mma.sync form.  A warp = 16 MMA rows x one K slice of at most 8 steps of 128; enough slices that
+// about 8 warps per SM exist where the matrix is short, row groups per CTA so that a CTA has up to 8-16 warps while
+// the grid still covers the SMs.  False when the shape does not fit (rows not in whole groups, shared memory).
+bool plan_mma(const GemmArgs& g, int units, int sm_count, SmallMmaPlan* out, int* U, int* NT, size_t* smem) {
+    const int uw = g.mode == kSwiglu ? 8 : 16;
+    if (units % uw) return false;
+    if (g.mode == kQkv && (g.rows[0] % 16 || g.rows[1] % 16 || g.rows[2] % 16)) return false;
+    const int steps = g.K / kGroup;
+    const int groups_total = units / uw;
+    int ksplit = std::max((steps + 7) / 8, (8 * sm_count + groups_total - 1) / groups_total);
+    ksplit = std::min(ksplit, std::min(steps, 16));
+    const int per = (steps + ksplit - 1) / ksplit;
+    ksplit = (steps + per - 1) / per;
+    if (per > 8) return false;
+    int gpc = std::max(1, std::min(8, 8 / ksplit));
+    while (gpc > 1 && groups_total / gpc < sm_count) gpc /= 2;
+    int nt = g.M <= 8 ? 1 : (g.M <= 16 ? 2 : 4);
+    auto bytes = [&](int n) {
+        return static_cast<size_t>(g.K / 4) * (8 * n) * 8 + static_cast<size_t>(ksplit) * gpc * n * 4 * 32 * sizeof(float);
+    };
+    while (nt > 1 && bytes(nt) > 100 * 1024) nt /= 2;
+    if (bytes(nt) > 200 * 1024) return false;
+    out->groups_per_cta = gpc;
+    out->ksplit = ksplit;
+    out->steps_per_split = per;
+    out->passes_tokens = 8 * nt;
+    *U = per <= 4 ? 4 : 8;
+    *NT = nt;
+    *smem = bytes(nt);
+    return true;
+}
+
 }  // namespace
 
 int gemm_set_attributes() {
     cudaError_t e = raise_v2_mode<kPlain>();
     if (e == cudaSuccess) e = raise_v2_mode<kQkv>();
     if (e == cudaSuccess) e = raise_v2_mode<kSwiglu>();
+    if (e == cudaSuccess) e = raise_mma_mode<kPlain>();
+    if (e == cudaSuccess) e = raise_mma_mode<kQkv>();
+    if (e == cudaSuccess) e = raise_mma_mode<kSwiglu>();
     if (e != cudaSuccess) return static_cast<int>(e);
     return gemm_tc_set_attributes();
 }
@@ -99,9 +163,6 @@ int gemm_launch(GemmArgs g, cudaStream_t stream) {
     const int tc_min_m_opt = option(W4A16_OPT_GEMM_MIN_TOKENS_TENSOR_CORE);
     const int rows_all = g.rows[0] + (g.mode == kQkv ? g.rows[1] + g.rows[2] : 0);
     const int tc_min_m = tc_min_m_opt > 0 ? tc_min_m_opt : (g.K > 4096 ? 3 : (rows_all >= 64 * dev->sm_count ? 4 : 7));
-    if ((g.M >= tc_min_m || g.num_peers > 0) && gemm_tc_supported(g)) return gemm_tc_launch(g, dev->sm_count, stream);
-    if (g.num_peers > 0) return W4A16_ERR_SHAPE;   // peer stores exist in the tensor-core form only
-
     SmallMArgs a;
     a.g = g;
     const int total_rows = g.rows[0] + (g.mode == kQkv ? g.rows[1] + g.rows[2] : 0);
@@ -111,9 +172,35 @@ int gemm_launch(GemmArgs g, cudaStream_t stream) {
     } else {
         a.out_ld[0] = (g.mode == kPlain && g.ldc > 0) ? g.ldc : a.units; a.out_ld[1] = a.out_ld[2] = 0;
     }
-    // few tokens, 16-byte aligned tensors: the form that streams like the decode GEMV
     bool aligned = reinterpret_cast<uintptr_t>(g.x) % 16 == 0;
     for (int t = 0; t < (g.mode == kQkv ? 3 : 1); ++t) aligned = aligned && reinterpret_cast<uintptr_t>(g.qweight[t]) % 16 == 0;
+
+    // Two to sixteen tokens: the weight-streaming kernel with the warp-level MMA (no fixed tcgen05 costs).  Measured on
+    // B200 against the other two forms: faster from 2 tokens on every Qwen shape (QKV: equal to the CUDA-core form up
+    // to 4), and up to 16 tokens as long as they are staged in one pass (K = 8960 holds 8 tokens per pass: from 9 the
+    // tcgen05 kernel wins there).  mma.sync runs at about 150 TFLOP/s on this GPU, which is what bounds it from 8 tokens.
+    const int mma_max_opt = option(W4A16_OPT_GEMM_MMA_MAX_TOKENS);
+    const int mma_max_m = mma_max_opt > 0 ? mma_max_opt : 16;
+    if (aligned && g.num_peers == 0 && g.M >= std::max(2, tc_min_m_opt) && g.M <= mma_max_m) {
+        SmallMmaPlan mp;
+        int mU = 8, mNT = 1;
+        size_t msmem = 0;
+        if (plan_mma(g, a.units, dev->sm_count, &mp, &mU, &mNT, &msmem) && (mma_max_opt > 0 || g.M <= mp.passes_tokens)) {
+            const dim3 mgrid((a.units / (g.mode == kSwiglu ? 8 : 16) + mp.groups_per_cta - 1) / mp.groups_per_cta);
+            const dim3 mblock(32 * mp.groups_per_cta * mp.ksplit);
+            cudaError_t me;
+            switch (g.mode) {
+                case kPlain: me = launch_mma<kPlain>(a, mp, mU, mNT, mgrid, mblock, msmem, stream); break;
+                case kQkv: me = launch_mma<kQkv>(a, mp, mU, mNT, mgrid, mblock, msmem, stream); break;
+                default: me = launch_mma<kSwiglu>(a, mp, mU, mNT, mgrid, mblock, msmem, stream); break;
+            }
+            return static_cast<int>(me);
+        }
+    }
+    if ((g.M >= tc_min_m || g.num_peers > 0) && gemm_tc_supported(g)) return gemm_tc_launch(g, dev->sm_count, stream);
+    if (g.num_peers > 0) return W4A16_ERR_SHAPE;   // peer stores exist in the tensor-core form only
+
+    // few tokens, 16-byte aligned tensors: the form that streams like the decode GEMV
     SmallMPlan plan;
     int U = 8;
     if (aligned && plan_v2(g, a.units, dev->sm_count, &plan, &U)) {

@@ -17,7 +17,7 @@ from ._lib import LayerWeights, QKVView, SweepDesc, W4A16Error, check, load  # n
 
 __all__ = [
     "QKVProjectionView", "W4A16Error", "init", "set_pdl", "load", "set_option", "get_option", "OPT_PDL",
-    "OPT_SIGNAL_WAIT_SPINS", "OPT_GEMV_FORM", "OPT_GEMM_MIN_TOKENS_TENSOR_CORE", "OPT_GEMM_FORM", "GEMV_FORM_AUTO",
+    "OPT_SIGNAL_WAIT_SPINS", "OPT_GEMV_FORM", "OPT_GEMM_MIN_TOKENS_TENSOR_CORE", "OPT_GEMM_FORM", "OPT_GEMM_MMA_MAX_TOKENS", "GEMV_FORM_AUTO",
     "GEMV_FORM_REGISTERS", "GEMV_FORM_BULK", "quantize_attn_heads_f32_to_q8_1", "gemv_attn_heads_f32_w4a16",
     "launch_quantize_fp16_to_q8_1", "launch_rmsnorm_q8_1",
     "launch_gemv_w4a16", "launch_gemv_w4a8", "launch_gemv_qkv_w4a8",
@@ -77,6 +77,7 @@ def init() -> None:
 
 # run-time options of the library (include/w4a16_b200.h, W4A16_OPT_*)
 OPT_PDL, OPT_SIGNAL_WAIT_SPINS, OPT_GEMV_FORM, OPT_GEMM_MIN_TOKENS_TENSOR_CORE, OPT_GEMM_FORM = 1, 2, 3, 4, 5
+OPT_GEMM_MMA_MAX_TOKENS = 6
 GEMV_FORM_AUTO, GEMV_FORM_REGISTERS, GEMV_FORM_BULK = 0, 1, 2
 
 

@@ -261,6 +261,19 @@ def test_decode_batch_grid_matches_oracle(ops, name, M):
     _check_shape_at(ops, name, M, n_rows=8, n_cols=48)
 
 
+@pytest.mark.parametrize("name", ["qkv", "o", "gate_up", "down"])
+@pytest.mark.parametrize("M", [2, 3, 7, 9, 13, 16, 24, 40])
+def test_mma_sync_few_token_form_matches_oracle(ops, name, M):
+    """The weight-streaming kernel with warp-level MMAs, forced up to 64 tokens (several token passes for the long K,
+    token tiles that are not full, a last pass with fewer tokens than a tile): against the oracle on sampled
+    entries, including the last token row."""
+    ops.set_option(ops.OPT_GEMM_MMA_MAX_TOKENS, 64)
+    try:
+        _check_shape_at(ops, name, M, n_rows=8, n_cols=48)
+    finally:
+        ops.set_option(ops.OPT_GEMM_MMA_MAX_TOKENS, 0)
+
+
 @pytest.mark.parametrize("name,M", [(n, m) for n in ("qkv", "o", "gate_up", "down") for m in (128, 512, 1024, 4096)]
                          + [("big", 128), ("big", 1024), ("big", 4096)])
 def test_prefill_sizes_of_the_benchmark_match_oracle(ops, name, M):
