@@ -115,13 +115,21 @@ bool plan_mma(const GemmArgs& g, int units, int sm_count, SmallMmaPlan* out, int
     if (g.mode == kQkv && (g.rows[0] % 16 || g.rows[1] % 16 || g.rows[2] % 16)) return false;
     const int steps = g.K / kGroup;
     const int groups_total = units / uw;
-    int ksplit = std::max((steps + 7) / 8, (8 * sm_count + groups_total - 1) / groups_total);
+    // slices of at most 4 steps where 16 warps allow it (the 4-step form has registers to spare for the token loads)
+    int ksplit = std::max((steps + 3) / 4, (8 * sm_count + groups_total - 1) / groups_total);
     ksplit = std::min(ksplit, std::min(steps, 16));
-    const int per = (steps + ksplit - 1) / ksplit;
+    int per = (steps + ksplit - 1) / ksplit;
     ksplit = (steps + per - 1) / per;
-    if (per > 8) return false;
-    int gpc = std::max(1, std::min(8, 8 / ksplit));
-    while (gpc > 1 && groups_total / gpc < sm_count) gpc /= 2;
+    // the whole grid must be resident (16 warps per SM at 128 registers): deeper slices where it would not be
+    while (static_cast<long long>(groups_total) * ksplit > 16LL * sm_count && per < 8) {
+        ++per;
+        ksplit = (steps + per - 1) / per;
+    }
+    if (per > 8 || static_cast<long long>(groups_total) * ksplit > 16LL * sm_count) return false;
+    // every CTA stages all the tokens, so fewer and larger CTAs mean less traffic for them: up to 16 warps per CTA
+    // as long as about one CTA per SM remains
+    int gpc = std::max(1, std::min(8, 16 / ksplit));
+    while (gpc > 1 && groups_total / gpc < (sm_count * 9) / 10) gpc /= 2;
     int nt = g.M <= 8 ? 1 : (g.M <= 16 ? 2 : 4);
     auto bytes = [&](int n) {
         return static_cast<size_t>(g.K / 4) * (8 * n) * 8 + static_cast<size_t>(ksplit) * gpc * n * 4 * 32 * sizeof(float);
@@ -178,7 +186,7 @@ int gemm_launch(GemmArgs g, cudaStream_t stream) {
     // Two to sixteen tokens: the weight-streaming kernel with the warp-level MMA (no fixed tcgen05 costs).  Measured on
     // B200 against the other two forms: faster from 2 tokens on every Qwen shape (QKV: equal to the CUDA-core form up
     // to 4), and up to 16 tokens as long as they are staged in one pass (K = 8960 holds 8 tokens per pass: from 9 the
-    // tcgen05 kernel wins there).  mma.sync runs at about 150 TFLOP/s on this GPU, which is what bounds it from 8 tokens.
+    // tcgen05 kernel wins there).
     const int mma_max_opt = option(W4A16_OPT_GEMM_MMA_MAX_TOKENS);
     const int mma_max_m = mma_max_opt > 0 ? mma_max_opt : 16;
     if (aligned && g.num_peers == 0 && g.M >= std::max(2, tc_min_m_opt) && g.M <= mma_max_m) {

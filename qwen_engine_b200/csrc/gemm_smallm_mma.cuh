@@ -95,10 +95,14 @@ __global__ void __launch_bounds__(512) gemm_smallm_mma_kernel(const SmallMArgs a
     const int s_begin = ks * p.steps_per_split;
     const int s_end = active ? min(s_begin + p.steps_per_split, total_steps) : s_begin;
 
+    // Half of a lane's weight loads go out before the wait for the previous kernel, the other half right behind the
+    // first token loads: the tokens, which everything waits for, then do not queue behind the whole weight stream,
+    // and the MMAs of the early steps run while the late steps' weights arrive.
+    constexpr int kEarlyU = U == 8 ? U : U / 2;   // (the 8-step form has no registers to spare for the token batch)
     uint4 w[2][U];
     uint16_t sb[2][U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
+    for (int u = 0; u < kEarlyU; ++u) {
         const int s = s_begin + u;
         if (s < s_end) {
 #pragma unroll
@@ -114,21 +118,65 @@ __global__ void __launch_bounds__(512) gemm_smallm_mma_kernel(const SmallMArgs a
     for (int m0 = 0; m0 < M; m0 += TOK) {
         if (m0 > 0) __syncthreads();   // the previous pass has finished reading the staged tokens
         // stage TOK tokens in B-fragment order: 16 bytes of a token = two cells (j, j + 1) of the same (step, t)
-        for (int idx = tid; idx < TOK * (K / 8); idx += blockDim.x) {
-            const int tok = idx / (K / 8), e = (idx - tok * (K / 8)) * 8;
-            uint4 xv = make_uint4(0, 0, 0, 0);
-            if (m0 + tok < M) xv = *reinterpret_cast<const uint4*>(a.g.x + static_cast<size_t>(m0 + tok) * K + e);
-            const int step = e >> 7, tt = (e >> 5) & 3, j0 = (e & 31) >> 2;
-            s_x[mma_x_cell(step, j0, tok, tt, TOK)] = make_uint2(xv.x, xv.y);
-            s_x[mma_x_cell(step, j0 + 1, tok, tt, TOK)] = make_uint2(xv.z, xv.w);
+        // (every global round trip here is on the critical path: several loads of a thread are in flight at once)
+        constexpr int kBatch = U == 8 ? 4 : 8;   // what the registers beside the weights allow
+        const int pieces = TOK * (K / 8);
+        auto load_batch = [&](int base, uint4 (&xv)[kBatch]) {
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+                const int idx = base + b * blockDim.x + tid;
+                const int tok = idx / (K / 8), e = (idx - tok * (K / 8)) * 8;
+                xv[b] = make_uint4(0, 0, 0, 0);
+                if (idx < pieces && m0 + tok < M)
+                    xv[b] = *reinterpret_cast<const uint4*>(a.g.x + static_cast<size_t>(m0 + tok) * K + e);
+            }
+        };
+        auto store_batch = [&](int base, const uint4 (&xv)[kBatch]) {
+#pragma unroll
+            for (int b = 0; b < kBatch; ++b) {
+                const int idx = base + b * blockDim.x + tid;
+                if (idx < pieces) {
+                    const int tok = idx / (K / 8), e = (idx - tok * (K / 8)) * 8;
+                    const int step = e >> 7, tt = (e >> 5) & 3, j0 = (e & 31) >> 2;
+                    s_x[mma_x_cell(step, j0, tok, tt, TOK)] = make_uint2(xv[b].x, xv[b].y);
+                    s_x[mma_x_cell(step, j0 + 1, tok, tt, TOK)] = make_uint2(xv[b].z, xv[b].w);
+                }
+            }
+        };
+        {
+            uint4 xv[kBatch];
+            load_batch(0, xv);
+            if (m0 == 0) {     // the rest of the weights, right behind the first token loads
+#pragma unroll
+                for (int u = kEarlyU; u < U; ++u) {
+                    const int s = s_begin + u;
+                    if (s < s_end) {
+#pragma unroll
+                        for (int r = 0; r < 2; ++r) {
+                            w[r][u] = ld_weights_16(wrow[r] + s * 16 + t * 4);
+                            sb[r][u] = ld_scale_bits(srow[r] + s);
+                        }
+                    }
+                }
+            }
+            store_batch(0, xv);
+        }
+        for (int base = kBatch * blockDim.x; base < pieces; base += kBatch * blockDim.x) {
+            uint4 xv[kBatch];
+            load_batch(base, xv);
+            store_batch(base, xv);
         }
         __syncthreads();
 
-        float d[NT][4];
+        // two accumulators per token tile (even / odd MMA of a word): consecutive MMAs of a warp do not wait for each other
+        constexpr int ACC = NT <= 2 ? 2 : 1;
+        float d2[NT][ACC][4];
 #pragma unroll
         for (int n = 0; n < NT; ++n)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) d[n][i] = 0.0f;
+            for (int c = 0; c < ACC; ++c)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) d2[n][c][i] = 0.0f;
 
 #pragma unroll
         for (int u = 0; u < U; ++u) {
@@ -155,13 +203,18 @@ __global__ void __launch_bounds__(512) gemm_smallm_mma_kernel(const SmallMArgs a
 #pragma unroll
                         for (int n = 0; n < NT; ++n) {
                             const uint2 b = s_x[mma_x_cell(s, j, n * 8 + g, t, TOK)];
-                            mma_m16n8k16(d[n], a0, a1, a2, a3, b.x, b.y);
+                            mma_m16n8k16(d2[n][jj % ACC], a0, a1, a2, a3, b.x, b.y);
                         }
                     }
                 }
             }
         }
 
+        float d[NT][4];
+#pragma unroll
+        for (int n = 0; n < NT; ++n)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) d[n][i] = ACC == 2 ? d2[n][0][i] + d2[n][ACC - 1][i] : d2[n][0][i];
         // K slices: the warps of a row group add their accumulators through shared memory, in slice order
         if (p.ksplit > 1) {
             if (ks < p.ksplit) {
