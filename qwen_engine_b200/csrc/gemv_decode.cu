@@ -139,7 +139,8 @@ __global__ void __maxnreg__(gemv_reg_cap(MODE, U)) gemv_w4_kernel(const GemvArgs
     if constexpr (MODE == kPlain) {
         if (active && ks == 0 && l == 0 && a.residual != nullptr) res_pre = a.residual[unit];
     }
-    if (blockIdx.x == 0 && tid < a.clear_count) a.clear_words[tid] = 0u;   // scratch of a later launch
+    if (blockIdx.x == 0)   // scratch of a later launch
+        for (int i = tid; i < a.clear_count; i += blockDim.x) a.clear_words[i] = 0u;
     if constexpr (XIN == kXFp16Norm) {
         if (regs_form) stage_x_fp16_regs<true>(a.x_fp16, gam, K, kRmsEps, s_q8, s_seed, s_scale, a.sumsq_in);
         else stage_x_from_fp16_rmsnorm(a.x_fp16, a.gamma, K, kRmsEps, s_q8, s_seed, s_scale);
