@@ -614,14 +614,14 @@ constexpr int kPairStageBytes = kPairStageTokens * kPairStagePitch;
 struct PairTile {
     int t, n0, m0;
 };
-__device__ __forceinline__ PairTile pair_tile(const TcArgs& a, int pt, int n_pairs, int rank, bool qkv) {
+__device__ __forceinline__ PairTile pair_tile(const TcArgs& a, int pt, int n_pairs, int rank, bool qkv, int tokens) {
     PairTile r;
     // Tile order: panels of a.panel token tiles; inside a panel the token tile runs fastest.  With a panel of 4 the
     // tiles in flight at one time (one per CTA pair) cover 4 token tiles x about 18 row-tile pairs, and both the
     // token slabs and the packed weight rows are re-used out of L2; a panel of 1 (row tiles fastest) shares one
     // token slab among all tiles in flight but streams the whole weight matrix once per token tile, which is
     // right only while the matrix stays in L2 (the host picks).
-    const int m_tiles = (a.M + kPairTokens - 1) / kPairTokens;
+    const int m_tiles = (a.M + tokens - 1) / tokens;
     const int per_panel = a.panel * n_pairs;
     const int panel = pt / per_panel;
     const int q = pt - panel * per_panel;
@@ -634,7 +634,7 @@ __device__ __forceinline__ PairTile pair_tile(const TcArgs& a, int pt, int n_pai
         if (r.t == 1 && tile >= a.tiles[1]) { tile -= a.tiles[1]; r.t = 2; }
     }
     r.n0 = tile * kTileRows;
-    r.m0 = m_idx * kPairTokens;
+    r.m0 = m_idx * tokens;
     return r;
 }
 
@@ -645,12 +645,16 @@ __device__ __forceinline__ PairTile pair_tile(const TcArgs& a, int pt, int n_pai
 // its row per 256-element super-block straight from global memory, one super-block ahead.
 // Epilogue: fp32 accumulators -> fp16 -> a [token][row] staging tile in shared memory -> 16-byte row-contiguous
 // stores (a warp writes 256 consecutive bytes of two token rows), residual added from 16-byte loads.
-template <int MODE>
+// T: tokens of a pair's tile, 256 or 128 (the host takes 128 where there are fewer 256-token tiles than CTA pairs).
+template <int MODE, int T>
 __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(const __grid_constant__ TcArgs a) {
+    static_assert(T == 256 || T == 128, "token tile of the CTA-pair kernel");
     constexpr int NG = kPairGroups;
     constexpr int kDqWarps = kPairDqWarps;
     constexpr int kDqThreads = kDqWarps * 32;
-    constexpr int T = kPairTokens, Th = T / 2;
+    constexpr int Th = T / 2;
+    constexpr int kPartTokens = T / 4;       // tokens each of the four warp groups drains
+    constexpr int QN = kPartTokens / 16;     // 16-column tensor-memory loads per warp and tile
     constexpr int b_bytes = Th * 128;
     extern __shared__ uint8_t smem_raw_base[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw_base) + 1023) & ~uintptr_t(1023));
@@ -724,7 +728,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
         // ahead of the draining below by one super-block, so that the tensor core has work while a tile's outputs
         // are still on their way to global memory.
         int cur_it = 0, cur_sb = 0;
-        PairTile cur_pt = my_tiles > 0 ? pair_tile(a, pair_id, n_pairs, rank, MODE == kQkv) : PairTile{0, 0, 0};
+        PairTile cur_pt = my_tiles > 0 ? pair_tile(a, pair_id, n_pairs, rank, MODE == kQkv, T) : PairTile{0, 0, 0};
         uint32_t sc_next = my_tiles > 0 ? load_scales(cur_pt, 0) : 0u;
         auto advance = [&]() {      // dequantises the cursor's k-block; false when a bounded wait ran out
             const uint32_t sc_pair = sc_next;
@@ -733,7 +737,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
             if (++cur_sb == num_sb) {
                 cur_sb = 0;
                 ++cur_it;
-                if (cur_it < my_tiles) cur_pt = pair_tile(a, pair_id + cur_it * num_pairs, n_pairs, rank, MODE == kQkv);
+                if (cur_it < my_tiles) cur_pt = pair_tile(a, pair_id + cur_it * num_pairs, n_pairs, rank, MODE == kQkv, T);
             }
             if (cur_it < my_tiles) sc_next = load_scales(cur_pt, cur_sb);
             (void)sb;
@@ -777,7 +781,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
         // whose bounded wait ran out has raised the abort flag, and all warps leave together right after the
         // first barrier of the tile.
         for (int it = 0; it < my_tiles; ++it) {
-            const PairTile pt = pair_tile(a, pair_id + it * num_pairs, n_pairs, rank, MODE == kQkv);
+            const PairTile pt = pair_tile(a, pair_id + it * num_pairs, n_pairs, rank, MODE == kQkv, T);
             const int rows_t = a.rows[pt.t];
             while (ok && cur_it == it) ok = advance();          // the rest of this tile's k-blocks
             // Look-ahead: while the tensor core works off the tail of this tile, fill the ring with the first
@@ -785,7 +789,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
             // THIS tile, so the wait cannot depend on the draining below), so that the next tile starts the
             // moment its accumulators are free and keeps running while the outputs go to global memory.
             for (int la = 0; la < S / NG && ok && cur_it == it + 1 && cur_it < my_tiles; ++la) ok = advance();
-            // ---- drain this tile: 128 weight rows of this CTA x 256 tokens ----
+            // ---- drain this tile: 128 weight rows of this CTA x T tokens ----
             if (ok) ok = warp_wait(accum_full, acc_ph, s_abort, lane);
             acc_ph ^= 1;
             asm volatile("bar.sync 1, %0;" ::"n"(kDqThreads) : "memory");
@@ -801,11 +805,11 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
             if constexpr (MODE == kPlain) {
                 for (int p = 0; p < a.num_peers; ++p) vec_ok = vec_ok && reinterpret_cast<uintptr_t>(a.peer_out[p]) % 16 == 0;
             }
-            // (1) this warp's 32 rows x 64 tokens of the accumulators into registers; with that the tensor memory is
+            // (1) this warp's 32 rows x T / 4 tokens of the accumulators into registers; with that the tensor memory is
             // free, and the next tile's first MMA may overwrite it while the values are still being stored
-            uint32_t v[4][16];
+            uint32_t v[QN][16];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) tmem_ld16(lane_base + static_cast<uint32_t>(part * 64 + q * 16), v[q]);
+            for (int q = 0; q < QN; ++q) tmem_ld16(lane_base + static_cast<uint32_t>(part * kPartTokens + q * 16), v[q]);
             tmem_ld_wait();
             tc_fence_before();
             __syncwarp();
@@ -815,8 +819,8 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
             }
             // (2) fp32 -> fp16 -> staging tile [token][row]
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const int tok0 = part * 64 + q * 16;
+            for (int q = 0; q < QN; ++q) {
+                const int tok0 = part * kPartTokens + q * 16;
 #pragma unroll
                 for (int jj = 0; jj < 16; ++jj) {
                     const float acc = __uint_as_float(v[q][jj]);
@@ -919,7 +923,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
             uint32_t ph = 0;
             bool ok = true;
             for (int pt_i = pair_id; pt_i < total_pt && ok; pt_i += num_pairs) {
-                const PairTile pt = pair_tile(a, pt_i, n_pairs, rank, MODE == kQkv);
+                const PairTile pt = pair_tile(a, pt_i, n_pairs, rank, MODE == kQkv, T);
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!mbar_wait(ab_empty(s), ph ^ 1, s_abort)) { ok = false; break; }
                     if (leader) mbar_arrive_expect_tx(full(s), static_cast<uint32_t>(2 * b_bytes));
@@ -937,7 +941,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_w4a16_tc_pair_kernel(con
             uint32_t rph = 0;
             bool ok = true;
             for (int pt_i = pair_id; pt_i < total_pt && ok; pt_i += num_pairs) {
-                const PairTile pt = pair_tile(a, pt_i, n_pairs, rank, MODE == kQkv);
+                const PairTile pt = pair_tile(a, pt_i, n_pairs, rank, MODE == kQkv, T);
                 for (int sb = 0; sb < num_sb; ++sb) {
                     if (!mbar_wait(raw_empty(rs), rph ^ 1, s_abort)) { ok = false; break; }
                     mbar_arrive_expect_tx(raw_full(rs), kRawBytes);
@@ -1099,11 +1103,16 @@ int max_active_clusters(int mode, int groups, int ksplit, size_t smem) {
 }
 
 int gemm_tc_set_attributes() {
-    cudaError_t e = cudaFuncSetAttribute(gemm_w4a16_tc_pair_kernel<kPlain>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemm_w4a16_tc_pair_kernel<kQkv>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-    if (e == cudaSuccess)
-        e = cudaFuncSetAttribute(gemm_w4a16_tc_pair_kernel<kSwiglu>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    cudaError_t e = cudaSuccess;
+    auto raise_pair = [&e](auto* kernel) {
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+    };
+    raise_pair(gemm_w4a16_tc_pair_kernel<kPlain, 256>);
+    raise_pair(gemm_w4a16_tc_pair_kernel<kQkv, 256>);
+    raise_pair(gemm_w4a16_tc_pair_kernel<kSwiglu, 256>);
+    raise_pair(gemm_w4a16_tc_pair_kernel<kPlain, 128>);
+    raise_pair(gemm_w4a16_tc_pair_kernel<kQkv, 128>);
+    raise_pair(gemm_w4a16_tc_pair_kernel<kSwiglu, 128>);
     if (e == cudaSuccess) e = raise_tc_smem_modes<2>();
     if (e == cudaSuccess) e = raise_tc_smem_modes<4>();
     return static_cast<int>(e);
@@ -1200,6 +1209,14 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
         // 28672 x 8192 at 4096 tokens: 1.62 -> 1.56 ms, DRAM reads 1.77 -> under 1 GB); smaller ones: row tiles fastest
         const size_t weight_bytes = static_cast<size_t>(total_tiles) * kTileRows * (g.K / 2);
         a.panel = weight_bytes > (48u << 20) ? 4 : 1;
+        // Token tile: 256, or 128 where the 256-token tiles are fewer than the CTA pairs (QKV, O, down at 1024 tokens:
+        // 24-32 tiles on 74 pairs; half-size tiles keep twice as many pairs busy: 19.7 -> 18.1, 19.5 -> 17.7 us).  With
+        // more tiles than pairs the half-size tile loses: a tile's dequantisation costs the same for half the MMA
+        // work (O and down at 4096 tokens: 34 -> 43 and 148 -> 205 us).
+        const int pairs_avail = std::max(1, sm_count / 2);
+        const int tiles256 = (total_tiles / 2) * ((g.M + 255) / 256);
+        T = tiles256 < pairs_avail ? 128 : 256;
+        a.T = T;
         if (!encode_2d(&a.tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.x, static_cast<uint64_t>(g.K),
                        static_cast<uint64_t>(g.M), static_cast<uint64_t>(g.K) * 2, kBK, static_cast<uint32_t>(T / 2)))
             return W4A16_ERR_INVALID_ARG;
@@ -1210,11 +1227,14 @@ int gemm_tc_launch(const GemmArgs& g, int sm_count, cudaStream_t stream) {
         const size_t psmem = tc_pair_smem_bytes(SP);
         const bool pdl = pdl_enabled();
         cudaError_t pe;
+#define W4_PAIR_LAUNCH(M_) (T == 128 ? launch_kernel_cluster(gemm_w4a16_tc_pair_kernel<M_, 128>, pgrid, pblock, psmem, stream, pdl, pcluster, a) \
+                                      : launch_kernel_cluster(gemm_w4a16_tc_pair_kernel<M_, 256>, pgrid, pblock, psmem, stream, pdl, pcluster, a))
         switch (g.mode) {
-            case kPlain: pe = launch_kernel_cluster(gemm_w4a16_tc_pair_kernel<kPlain>, pgrid, pblock, psmem, stream, pdl, pcluster, a); break;
-            case kQkv: pe = launch_kernel_cluster(gemm_w4a16_tc_pair_kernel<kQkv>, pgrid, pblock, psmem, stream, pdl, pcluster, a); break;
-            default: pe = launch_kernel_cluster(gemm_w4a16_tc_pair_kernel<kSwiglu>, pgrid, pblock, psmem, stream, pdl, pcluster, a); break;
+            case kPlain: pe = W4_PAIR_LAUNCH(kPlain); break;
+            case kQkv: pe = W4_PAIR_LAUNCH(kQkv); break;
+            default: pe = W4_PAIR_LAUNCH(kSwiglu); break;
         }
+#undef W4_PAIR_LAUNCH
         return static_cast<int>(pe);
     }
     if (!encode_2d(&a.tmap_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, g.x, static_cast<uint64_t>(g.K),
