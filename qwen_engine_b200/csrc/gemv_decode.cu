@@ -946,15 +946,28 @@ int resident_warps_per_sm(GemvMode mode, int U) {
     return U == 8 ? 20 : 24;
 }
 
-// Picks the CTA shape.  units: output rows (or pairs).  Goals, in order: at least ~1.3 CTAs
-// per SM when the matrix allows it; all 32 sub-warps of a CTA busy; at most 8 loads per lane
-// per batch so one batch covers a lane's whole K slice for the model's shapes; and the whole grid
-// resident at once (a second wave of CTAs would start its weight loads only after the wait).
+// Picks the CTA shape.  units: output rows (or pairs).  Goals, in order: about 1.25 CTAs per SM when the matrix
+// allows it, and no more (see below); all 32 sub-warps of a CTA busy; at most 8 loads per lane per batch so one
+// batch covers a lane's whole K slice for the model's shapes; and the whole grid resident at once (a second wave
+// of CTAs would start its weight loads only after the wait).
 Plan make_plan(GemvMode mode, int units, int K, int sm_count) {
     const int steps = K / kStepElems;
-    const int target_ctas = (sm_count * 13 + 9) / 10;
-    int upc = 32;
-    while (upc > 4 && (units + upc - 1) / upc < target_ctas) upc /= 2;
+    // Fewest CTAs that still give every SM work (1.25 per SM; 1.3 where the K slices would otherwise not fit one batch
+    // of 8 loads per lane):
+    // what a grid leaves free on an SM is where the NEXT launch's CTAs become resident and fetch their weights
+    // while this one still runs (O projection 1536 x 1536: 192 CTAs instead of 384 let 53 % instead of 24 % of the
+    // following gate_up launch's CTAs start early, 5 % of the whole 28-layer pass).
+    auto depth_for = [&](int u) {
+        const int c = std::min(std::max(1, kMaxSubwarps / u), steps);
+        return (steps + c - 1) / c;
+    };
+    auto upc_for = [&](int target_ctas) {
+        int u = 32;
+        while (u > 4 && (units + u - 1) / u < target_ctas) u /= 2;
+        return u;
+    };
+    int upc = upc_for((sm_count * 5) / 4);
+    if (depth_for(upc) > 8) upc = upc_for((sm_count * 13 + 9) / 10);
     int cap = std::max(1, kMaxSubwarps / upc);   // most K slices the CTA can hold
     cap = std::min(cap, steps);
     int per = (steps + cap - 1) / cap;           // steps per slice if all slices were used
