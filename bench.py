@@ -142,7 +142,7 @@ class ClockSampler:
 
 # ---- CPU baseline (oracle port) ----------------------------------------------------------
 
-def time_cpu_sweep(layers_np, h0, budget_s: float = 12.0, max_reps: int = 20):
+def time_cpu_sweep(layers_np, h0, budget_s: float = 12.0, max_reps: int = 150):
     """Times the oracle's sweep on the host cores.  Returns (GB/s, cores, sample description, last h)."""
     import oracle
     from qwen_engine_b200 import synth
